@@ -1,0 +1,274 @@
+/*
+ * plast_b200.h — C ABI of libplast_b200.so: sm_100a kernels behind plast's kernel entry points.
+ *
+ * Every `<op>_cuda_forward/backward` symbol below has the signature the plast op table binds
+ * (ForwardKernel / BackwardKernel, include/core/op.h:5-6) and is called the same way:
+ * Tensor structs, their shape[] and strides[] arrays live in HOST memory; `data` (and
+ * `grad->data`) point to DEVICE memory of the current CUDA device. Strides are in elements.
+ * Forward overwrites output->data. Backward ACCUMULATES (+=) into inputs[i]->grad->data for
+ * every input with requires_grad set, reading output->grad->data.
+ *
+ * All launches go to the stream set with plast_b200_set_stream (default: the legacy default
+ * stream, which is what the reference uses). Entry points return void like the reference's;
+ * the outcome of the last call on this host thread is readable with plast_b200_last_error().
+ * A failed call prints one line on stderr (the reference's behaviour) and launches nothing.
+ *
+ * Struct layouts restate include/core/definitions.h:17-23 and include/core/tensor.h:8-30 of the
+ * reference; define PLAST_B200_USE_REFERENCE_TYPES and put the reference's include/ on the
+ * include path to compile against its own headers instead.
+ */
+#ifndef PLAST_B200_H
+#define PLAST_B200_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef PLAST_B200_USE_REFERENCE_TYPES
+#include "core/definitions.h"
+#include "core/tensor.h"
+#else
+
+#ifndef MAX_NDIM
+#define MAX_NDIM 8
+#endif
+
+typedef uint64_t u64;
+typedef int32_t i32;
+
+/* include/core/definitions.h:19-23 — 24 bytes: dim@0 keepdim@8 fval@16 */
+typedef struct {
+  u64 dim;     /* reduce axis; PLAST_FULL_REDUCE (= MAX_NDIM + 1) reduces every axis */
+  u64 keepdim; /* 0/1 */
+  float fval;  /* leaky-relu slope */
+} KernelParams;
+
+/* include/core/tensor.h:8 */
+typedef enum DTYPE { INT32, FLOAT32 } DTYPE;
+/* include/core/arena.h:17 */
+typedef enum DEVICE { CPU, CUDA } DEVICE;
+
+struct Node;
+
+/* include/core/tensor.h:20-30 — 176 bytes:
+ * grad@0 creator@8 data@16 shape@24 strides@88 ndim@152 dtype@160 device@164 requires_grad@168 */
+typedef struct Tensor {
+  struct Tensor *grad;
+  struct Node *creator;
+  void *data;
+  u64 shape[MAX_NDIM];
+  u64 strides[MAX_NDIM];
+  u64 ndim;
+  DTYPE dtype;
+  DEVICE device;
+  bool requires_grad;
+} Tensor;
+
+#endif /* PLAST_B200_USE_REFERENCE_TYPES */
+
+/* params.dim value that means "reduce all axes" (plast/tensor.py:601, reduce_ops.c:69). */
+#define PLAST_FULL_REDUCE ((u64)(MAX_NDIM + 1))
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------------
+ * Binary elementwise, NumPy broadcasting (right-aligned; size-1 dims read offset 0).
+ * Replaces include/kernels/ops/binary.h:19-29 (src/kernels/cuda/binary_ops.cu:94-141);
+ * semantics follow the CPU path include/kernels/kernel_macros.h:191-325.
+ * inputs = {a, b}. Backward of a broadcast operand is the broadcast-gradient reduce: the
+ * gradient is summed over the broadcast axes (deterministic tree order, no float atomics) and
+ * then added to the operand's grad buffer.
+ * ------------------------------------------------------------------------------------------ */
+void add_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void add_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+void sub_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void sub_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+void mul_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void mul_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+void div_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void div_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+
+/* ------------------------------------------------------------------------------------------
+ * Unary elementwise. Replaces include/kernels/ops/unary.h:23-33
+ * (src/kernels/cuda/unary_ops.cu); semantics follow src/kernels/cpu/unary_ops.c.
+ * Transcendentals are the accurate (not fast-math) versions. leaky_relu uses params.fval as
+ * the slope: x > 0 ? x : x * slope (so slope 0 gives -0.0 for negative x, as the CPU path).
+ * ------------------------------------------------------------------------------------------ */
+void abs_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void abs_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+void cos_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void cos_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+void sin_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void sin_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+void tan_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void tan_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+void exp_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void exp_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+void log_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void log_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+void neg_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void neg_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+void leaky_relu_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void leaky_relu_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+
+/* ------------------------------------------------------------------------------------------
+ * Reductions over one axis (params.dim, params.keepdim) or over everything
+ * (params.dim == PLAST_FULL_REDUCE, result shape [1]).
+ * Replaces include/kernels/ops/reduce.h:19-29 (src/kernels/cuda/reduce_ops.cu:338-514);
+ * semantics follow src/kernels/cpu/reduce_ops.c:24-278: the axis forward rewrites
+ * output->shape/ndim/strides like the CPU path (reduce_ops.c:80-81); mean divides the fp32
+ * sum by the count; max/min start from -/+FLT_MAX and compare with > / <; max/min backward
+ * splits the gradient evenly among tied elements (reduce_ops.c:166-177).
+ * ------------------------------------------------------------------------------------------ */
+void sum_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void sum_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+void mean_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void mean_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+void max_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void max_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+void min_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void min_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+
+/* argmax over one axis (or everything): output dtype INT32, lowest index on ties. The reference
+ * op table (include/core/ops.def:1-28) has no ARGMAX; this entry point keeps the ForwardKernel
+ * signature so it can be added to the table unchanged. The index counts along params.dim (for a
+ * full reduce: the row-major linear index of the view). */
+void argmax_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+
+/* ------------------------------------------------------------------------------------------
+ * Fused recipes. Each equals the op sequence the reference builds from primitives, with the
+ * same per-op fp32 rounding (no FMA contraction across ops), in one pass over the data.
+ * ------------------------------------------------------------------------------------------ */
+/* softmax / log_softmax along params.dim: plast/nn/functional.py:77-97
+ * (max -> sub -> exp -> sum -> div / log -> sub). inputs = {x}. */
+void softmax_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void softmax_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+void log_softmax_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void log_softmax_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+/* cross_entropy: plast/nn/functional.py:312-333 with reduction="mean". inputs = {logits [N,C]
+ * FLOAT32, labels [N] INT32 class indices}; output = [1] mean loss. The reference turns labels
+ * into a host-side one-hot matrix; here the label indexes the row directly. */
+void cross_entropy_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void cross_entropy_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+/* sigmoid: plast/nn/functional.py:42-47 (neg -> exp -> +1 -> 1/.). inputs = {x}. */
+void sigmoid_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void sigmoid_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+/* scale_bias_leaky_relu: leaky_relu(x * scale + bias) as mul -> add -> leaky_relu
+ * (include/kernels/kernel_macros.h:191-242, src/kernels/cpu/unary_ops.c:218-232).
+ * inputs = {x, scale, bias}; scale and bias broadcast against x. Backward computes
+ * g = dout * (y > 0 ? 1 : slope) once and accumulates dx += g * scale,
+ * dscale += sum_bcast(g * x), dbias += sum_bcast(g). */
+void scale_bias_leaky_relu_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void scale_bias_leaky_relu_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+/* add_leaky_relu: leaky_relu(a + b) as add -> leaky_relu. inputs = {a, b}. */
+void add_leaky_relu_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+void add_leaky_relu_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
+
+/* ------------------------------------------------------------------------------------------
+ * Fused elementwise chain: what the scheduler's chain fusion issues for a maximal subgraph of
+ * same-shape / broadcast elementwise nodes (the reference scheduler runs such a chain node by
+ * node, src/scheduler/scheduler.c:16-52, src/core/graph.c:57-60; its fusion pass only knows
+ * matmul/conv patterns, src/scheduler/fusion.c:28-90).
+ * The program is a list of steps over a small register file; register r < n_inputs is preloaded
+ * with inputs[r] (broadcast against the output shape); each step writes register
+ * n_inputs + step_index; the last step's register is stored to output. Every step rounds to
+ * fp32 exactly like the standalone op.
+ * ------------------------------------------------------------------------------------------ */
+typedef enum PlastChainOpcode {
+  PLAST_CHAIN_ADD = 0,
+  PLAST_CHAIN_SUB,
+  PLAST_CHAIN_MUL,
+  PLAST_CHAIN_DIV,
+  PLAST_CHAIN_NEG,
+  PLAST_CHAIN_ABS,
+  PLAST_CHAIN_EXP,
+  PLAST_CHAIN_LOG,
+  PLAST_CHAIN_SIN,
+  PLAST_CHAIN_COS,
+  PLAST_CHAIN_TAN,
+  PLAST_CHAIN_LEAKY_RELU, /* slope = fval */
+  PLAST_CHAIN_ADD_SCALAR, /* reg[a] + fval   (0-dim operand on the right) */
+  PLAST_CHAIN_RSUB_SCALAR, /* fval - reg[a] */
+  PLAST_CHAIN_MUL_SCALAR, /* reg[a] * fval */
+  PLAST_CHAIN_RDIV_SCALAR /* fval / reg[a]  (0-dim operand on the left) */
+} PlastChainOpcode;
+
+typedef struct PlastChainStep {
+  i32 opcode; /* PlastChainOpcode */
+  i32 a;      /* first operand register */
+  i32 b;      /* second operand register (binary opcodes) */
+  float fval; /* scalar operand / slope */
+} PlastChainStep;
+
+#define PLAST_CHAIN_MAX_INPUTS 4
+#define PLAST_CHAIN_MAX_STEPS 24
+
+void plast_b200_chain_forward(const Tensor **inputs, int n_inputs, Tensor *output,
+                              const PlastChainStep *steps, int n_steps);
+
+/* ------------------------------------------------------------------------------------------
+ * Symbols the reference's other translation units link against.
+ * ------------------------------------------------------------------------------------------ */
+/* include/kernels/cuda/cuda_tensor_init.h:9-11 (called from src/core/tensor.c:88,107,118,149) */
+void zeros_cuda(Tensor *t, u64 num_elements);
+void ones_cuda(Tensor *t, u64 num_elements);
+void set_ones_grad_cuda(Tensor *t);
+/* include/optimizers/zero_grad.h:11 */
+void zero_grad_cuda(Tensor *t);
+/* declared in src/kernels/cpu/shape_ops.c:8-11: da += dout for view-like ops, and the
+ * transposed accumulate (da[coords] += dout[coords with axis1/axis2 swapped]).
+ * shape/stride arrays are host pointers. */
+void reshape_backward_cuda(float *da, const float *dout, u64 num_elements);
+void transpose_backward_cuda(float *da, const float *dout, const u64 *a_shape,
+                             const u64 *da_strides, const u64 *dout_strides, u64 ndim, u64 axis1,
+                             u64 axis2, u64 num_elements);
+/* include/core/arena_cuda.h:9-14 (called from src/core/arena.c and src/python/bindings.cpp) */
+void *arena_alloc_cuda(u64 size);
+void arena_free_cuda(void *ptr);
+void arena_memset_cuda(void *ptr, int value, u64 size);
+void arena_memcpy_h2d_cuda(void *dest, const void *src, u64 size);
+void arena_memcpy_d2h_cuda(void *dest, const void *src, u64 size);
+void arena_memcpy_d2d_cuda(void *dest, const void *src, u64 size);
+/* Strided view -> contiguous copy: the gather behind include/kernels/pack.h:17-23
+ * (src/kernels/cuda/cuda_pack.cu:29-96). dst is caller-allocated, numel(t) elements. The
+ * C++-linkage cuda_tensor_pack_init/release wrappers are exported by the same library. */
+void plast_b200_pack(const Tensor *t, void *dst);
+
+/* ------------------------------------------------------------------------------------------
+ * Library control (no counterpart in the reference).
+ * ------------------------------------------------------------------------------------------ */
+typedef enum PlastB200Error {
+  PLAST_B200_OK = 0,
+  PLAST_B200_ERR_DTYPE = 1,     /* unsupported dtype (the reference prints and continues) */
+  PLAST_B200_ERR_SHAPE = 2,     /* shapes not broadcastable / bad axis / ndim > MAX_NDIM */
+  PLAST_B200_ERR_NULL = 3,      /* missing tensor, data or grad pointer */
+  PLAST_B200_ERR_CUDA = 4,      /* a CUDA runtime call failed */
+  PLAST_B200_ERR_UNSUPPORTED = 5, /* valid request this build has no kernel for */
+  PLAST_B200_ERR_LIMIT = 6      /* size beyond a stated maximum */
+} PlastB200Error;
+
+int plast_b200_last_error(void);
+const char *plast_b200_last_error_message(void);
+void plast_b200_clear_error(void);
+/* Stream for all following launches from any thread (a cudaStream_t; NULL = legacy default). */
+void plast_b200_set_stream(void *cuda_stream);
+void *plast_b200_get_stream(void);
+/* 1: cudaDeviceSynchronize after every entry point like the reference does
+ * (src/kernels/cuda/binary_ops.cu:113); 0 (default): asynchronous. */
+void plast_b200_set_sync(int on);
+/* Number of kernels this library has launched since load (all threads). */
+u64 plast_b200_launch_count(void);
+/* Name of the kernel family chosen by the last entry-point call on this thread
+ * (e.g. "ew_vec4", "reduce_row"); for tests and profiling. */
+const char *plast_b200_last_kernel(void);
+/* Frees the per-device scratch the reductions keep between calls. */
+void plast_b200_release_workspace(void);
+const char *plast_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* PLAST_B200_H */

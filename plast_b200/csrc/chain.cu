@@ -1,0 +1,333 @@
+// Fused elementwise recipes and the generic fused chain.
+//
+//   sigmoid                 neg -> exp -> +1 -> 1/.        (plast/nn/functional.py:42-47)
+//   add_leaky_relu          add -> leaky_relu
+//   scale_bias_leaky_relu   mul -> add -> leaky_relu
+//   plast_b200_chain_forward  any straight-line program of elementwise steps
+//
+// Every step is rounded to fp32 on its own (-fmad=false), so a fused result is bit-identical to
+// running the primitive ops one after another; the gain is that intermediates never touch HBM.
+#include "ew_engine.cuh"
+#include "functors.cuh"
+#include "grad_accum.cuh"
+
+namespace pb {
+
+// ---- fixed recipes ------------------------------------------------------------------------------------
+struct SigmoidF {
+  __device__ __forceinline__ float operator()(const float *x) const {
+    const float nx = -x[0];
+    const float e = expf(nx);
+    const float d = e + 1.0f;
+    return 1.0f / d;
+  }
+};
+struct SigmoidB { // x = {g, y, old}: dy/dx = y (1 - y)
+  __device__ __forceinline__ float operator()(const float *x) const {
+    return x[2] + x[0] * (x[1] * (1.0f - x[1]));
+  }
+};
+struct AddLeakyF { // x = {a, b}
+  float alpha;
+  __device__ __forceinline__ float operator()(const float *x) const {
+    const float u = x[0] + x[1];
+    return u > 0.0f ? u : u * alpha;
+  }
+};
+struct ScaleBiasLeakyF { // x = {v, scale, bias}
+  float alpha;
+  __device__ __forceinline__ float operator()(const float *x) const {
+    const float t = x[0] * x[1];
+    const float u = t + x[2];
+    return u > 0.0f ? u : u * alpha;
+  }
+};
+// Gradient terms. The pre-activation u is recomputed from the inputs (exact for any slope);
+// du = g * (u > 0 ? 1 : slope) is what leaky_relu's backward hands to the add / mul backward
+// (src/kernels/cpu/unary_ops.c:234-262, binary_ops.c:18-49).
+struct AddLeakyGrad { // x = {g, a, b}
+  float alpha;
+  __device__ __forceinline__ float operator()(const float *x) const {
+    const float u = x[1] + x[2];
+    return x[0] * (u > 0.0f ? 1.0f : alpha);
+  }
+};
+struct SblBiasGrad { // x = {g, v, scale, bias} -> du
+  float alpha;
+  __device__ __forceinline__ float operator()(const float *x) const {
+    const float t = x[1] * x[2];
+    const float u = t + x[3];
+    return x[0] * (u > 0.0f ? 1.0f : alpha);
+  }
+};
+struct SblScaleGrad { // du * v
+  float alpha;
+  __device__ __forceinline__ float operator()(const float *x) const {
+    const float t = x[1] * x[2];
+    const float u = t + x[3];
+    return (x[0] * (u > 0.0f ? 1.0f : alpha)) * x[1];
+  }
+};
+struct SblInputGrad { // du * scale
+  float alpha;
+  __device__ __forceinline__ float operator()(const float *x) const {
+    const float t = x[1] * x[2];
+    const float u = t + x[3];
+    return (x[0] * (u > 0.0f ? 1.0f : alpha)) * x[2];
+  }
+};
+
+// ---- generic chain -------------------------------------------------------------------------------------
+struct ChainProgram {
+  int n_inputs, n_steps;
+  unsigned char opcode[PLAST_CHAIN_MAX_STEPS], a[PLAST_CHAIN_MAX_STEPS], b[PLAST_CHAIN_MAX_STEPS];
+  float fval[PLAST_CHAIN_MAX_STEPS];
+};
+
+__device__ __forceinline__ float chain_step(int opcode, float p, float q, float f) {
+  switch (opcode) {
+  case PLAST_CHAIN_ADD: return p + q;
+  case PLAST_CHAIN_SUB: return p - q;
+  case PLAST_CHAIN_MUL: return p * q;
+  case PLAST_CHAIN_DIV: return p / q;
+  case PLAST_CHAIN_NEG: return -p;
+  case PLAST_CHAIN_ABS: return fabsf(p);
+  case PLAST_CHAIN_EXP: return expf(p);
+  case PLAST_CHAIN_LOG: return logf(p);
+  case PLAST_CHAIN_SIN: return sinf(p);
+  case PLAST_CHAIN_COS: return cosf(p);
+  case PLAST_CHAIN_TAN: return tanf(p);
+  case PLAST_CHAIN_LEAKY_RELU: return p > 0.0f ? p : p * f;
+  case PLAST_CHAIN_ADD_SCALAR: return p + f;
+  case PLAST_CHAIN_RSUB_SCALAR: return f - p;
+  case PLAST_CHAIN_MUL_SCALAR: return p * f;
+  default: return f / p; // PLAST_CHAIN_RDIV_SCALAR
+  }
+}
+
+// Interpreter: the program is uniform across threads, so the switch never diverges; the register
+// file is a small per-thread array.
+template <int NIN> struct ChainInterp {
+  ChainProgram prog;
+  __device__ __forceinline__ float operator()(const float *x) const {
+    float reg[PLAST_CHAIN_MAX_INPUTS + PLAST_CHAIN_MAX_STEPS];
+#pragma unroll
+    for (int i = 0; i < NIN; ++i) reg[i] = x[i];
+    for (int s = 0; s < prog.n_steps; ++s)
+      reg[NIN + s] = chain_step(prog.opcode[s], reg[prog.a[s]], reg[prog.b[s]], prog.fval[s]);
+    return reg[NIN + prog.n_steps - 1];
+  }
+};
+
+// z = sigmoid(x) * y + exp(-abs(x)) as the nine primitive steps, compiled ahead of time; chosen
+// when a submitted program is exactly this sequence.
+struct SigmoidMulAddExpNegAbs { // x = {x, y}
+  __device__ __forceinline__ float operator()(const float *x) const {
+    const float nx = -x[0];
+    const float e = expf(nx);
+    const float d = e + 1.0f;
+    const float sg = 1.0f / d;
+    const float t = sg * x[1];
+    const float ax = fabsf(x[0]);
+    const float nax = -ax;
+    const float e2 = expf(nax);
+    return t + e2;
+  }
+};
+static bool is_sigmoid_mul_add_exp_neg_abs(const ChainProgram &p) {
+  static const int ops[9] = {PLAST_CHAIN_NEG, PLAST_CHAIN_EXP, PLAST_CHAIN_ADD_SCALAR,
+                             PLAST_CHAIN_RDIV_SCALAR, PLAST_CHAIN_MUL, PLAST_CHAIN_ABS,
+                             PLAST_CHAIN_NEG, PLAST_CHAIN_EXP, PLAST_CHAIN_ADD};
+  static const int as[9] = {0, 2, 3, 4, 5, 0, 7, 8, 6};
+  static const int bs[9] = {0, 0, 0, 0, 1, 0, 0, 0, 9};
+  if (p.n_inputs != 2 || p.n_steps != 9) return false;
+  for (int s = 0; s < 9; ++s) {
+    if (p.opcode[s] != ops[s] || p.a[s] != as[s]) return false;
+    if ((ops[s] == PLAST_CHAIN_MUL || ops[s] == PLAST_CHAIN_ADD) && p.b[s] != bs[s]) return false;
+  }
+  return p.fval[2] == 1.0f && p.fval[3] == 1.0f;
+}
+
+static bool float_only(const Tensor *t, const char *op) {
+  if (t->dtype != FLOAT32) {
+    set_error(PLAST_B200_ERR_DTYPE, "%s: unsupported dtype %d", op, (int)t->dtype);
+    return false;
+  }
+  return true;
+}
+
+// out = f(inputs...) with every input broadcast against the output shape.
+template <class F, int NIN>
+static void fused_forward(const char *name, const Tensor **inputs, Tensor *output, const F &f) {
+  u64 st[NIN + 1][MAX_NDIM] = {};
+  const float *ins[NIN];
+  for (u64 d = 0; d < output->ndim; ++d) st[0][d] = output->strides[d];
+  for (int a = 0; a < NIN; ++a) {
+    if (!check_tensor(inputs[a], name) || !float_only(inputs[a], name)) return;
+    if (!broadcast_strides(inputs[a], output->shape, output->ndim, st[a + 1])) {
+      set_error(PLAST_B200_ERR_SHAPE, "%s: input %d does not broadcast to the output shape", name, a);
+      return;
+    }
+    ins[a] = (const float *)inputs[a]->data;
+  }
+  IterPlan plan;
+  make_plan(&plan, output->shape, output->ndim, NIN + 1, st, nullptr, 0);
+  launch_ew<F, NIN>(plan, (float *)output->data, ins, f);
+}
+
+// grad(inputs[which]) += term(g, inputs...), reduced over the dims inputs[which] broadcasts.
+template <class Term, int NOPS>
+static void fused_backward_one(const char *name, Tensor **inputs, const Tensor *output, int which,
+                               const Term &term) {
+  const Tensor *t = inputs[which];
+  if (!t->requires_grad) return;
+  if (!t->grad || !t->grad->data) {
+    set_error(PLAST_B200_ERR_NULL, "%s: input %d requires grad but has no grad tensor", name, which);
+    return;
+  }
+  const Tensor *dout = output->grad;
+  u64 in_st[NOPS + 1][MAX_NDIM] = {};
+  const float *ins[NOPS + 1];
+  for (u64 d = 0; d < dout->ndim; ++d) in_st[0][d] = dout->strides[d];
+  ins[0] = (const float *)dout->data;
+  for (int a = 0; a < NOPS; ++a) {
+    if (!broadcast_strides(inputs[a], dout->shape, dout->ndim, in_st[a + 1])) {
+      set_error(PLAST_B200_ERR_SHAPE, "%s: input %d does not broadcast to the gradient shape", name, a);
+      return;
+    }
+    ins[a + 1] = (const float *)inputs[a]->data;
+  }
+  accumulate_grad<Term, NOPS + 1>(dout->shape, dout->ndim, (float *)t->grad->data, in_st[which + 1],
+                                  in_st, ins, term);
+}
+
+static bool fused_backward_begin(const char *name, Tensor **inputs, int n, const Tensor *output) {
+  begin_call();
+  if (!inputs || !check_tensor(output, name, false)) return false;
+  bool any = false;
+  for (int a = 0; a < n; ++a) {
+    if (!check_tensor(inputs[a], name) || !float_only(inputs[a], name)) return false;
+    any = any || inputs[a]->requires_grad;
+  }
+  if (!any) return false;
+  if (!output->grad || !output->grad->data) {
+    set_error(PLAST_B200_ERR_NULL, "%s: output has no grad tensor", name);
+    return false;
+  }
+  return true;
+}
+
+} // namespace pb
+
+using namespace pb;
+
+extern "C" {
+
+void sigmoid_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams) {
+  begin_call();
+  if (!inputs || !check_tensor(output, "sigmoid")) return;
+  fused_forward<SigmoidF, 1>("sigmoid", inputs, output, SigmoidF{});
+  end_call();
+}
+void sigmoid_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams) {
+  begin_call();
+  if (!inputs || !check_tensor(inputs[0], "sigmoid") || !check_tensor(output, "sigmoid")) return;
+  const Tensor *a = inputs[0];
+  if (!a->requires_grad) return;
+  if (!a->grad || !a->grad->data || !output->grad || !output->grad->data) {
+    set_error(PLAST_B200_ERR_NULL, "sigmoid: missing grad tensor");
+    return;
+  }
+  u64 st[4][MAX_NDIM] = {};
+  for (u64 d = 0; d < a->ndim; ++d) {
+    st[0][d] = a->grad->strides[d];
+    st[1][d] = output->grad->strides[d];
+    st[2][d] = output->strides[d];
+    st[3][d] = a->grad->strides[d];
+  }
+  IterPlan plan;
+  make_plan(&plan, a->shape, a->ndim, 4, st, nullptr, 0);
+  const float *ins[3] = {(const float *)output->grad->data, (const float *)output->data,
+                         (const float *)a->grad->data};
+  launch_ew<SigmoidB, 3>(plan, (float *)a->grad->data, ins, SigmoidB{});
+  end_call();
+}
+
+void add_leaky_relu_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params) {
+  begin_call();
+  if (!inputs || !check_tensor(output, "add_leaky_relu")) return;
+  fused_forward<AddLeakyF, 2>("add_leaky_relu", inputs, output, AddLeakyF{params.fval});
+  end_call();
+}
+void add_leaky_relu_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params) {
+  if (!fused_backward_begin("add_leaky_relu", inputs, 2, output)) return;
+  const AddLeakyGrad term{params.fval};
+  fused_backward_one<AddLeakyGrad, 2>("add_leaky_relu", inputs, output, 0, term);
+  if (!failed()) fused_backward_one<AddLeakyGrad, 2>("add_leaky_relu", inputs, output, 1, term);
+  end_call();
+}
+
+void scale_bias_leaky_relu_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params) {
+  begin_call();
+  if (!inputs || !check_tensor(output, "scale_bias_leaky_relu")) return;
+  fused_forward<ScaleBiasLeakyF, 3>("scale_bias_leaky_relu", inputs, output,
+                                    ScaleBiasLeakyF{params.fval});
+  end_call();
+}
+void scale_bias_leaky_relu_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params) {
+  const char *name = "scale_bias_leaky_relu";
+  if (!fused_backward_begin(name, inputs, 3, output)) return;
+  fused_backward_one<SblInputGrad, 3>(name, inputs, output, 0, SblInputGrad{params.fval});
+  if (!failed()) fused_backward_one<SblScaleGrad, 3>(name, inputs, output, 1, SblScaleGrad{params.fval});
+  if (!failed()) fused_backward_one<SblBiasGrad, 3>(name, inputs, output, 2, SblBiasGrad{params.fval});
+  end_call();
+}
+
+void plast_b200_chain_forward(const Tensor **inputs, int n_inputs, Tensor *output,
+                              const PlastChainStep *steps, int n_steps) {
+  const char *name = "chain";
+  begin_call();
+  if (!inputs || !steps || !check_tensor(output, name)) {
+    if (!inputs || !steps) set_error(PLAST_B200_ERR_NULL, "chain: NULL inputs or steps");
+    return;
+  }
+  if (n_inputs < 1 || n_inputs > PLAST_CHAIN_MAX_INPUTS || n_steps < 1 ||
+      n_steps > PLAST_CHAIN_MAX_STEPS) {
+    set_error(PLAST_B200_ERR_LIMIT, "chain: %d inputs / %d steps (limits %d / %d)", n_inputs, n_steps,
+              PLAST_CHAIN_MAX_INPUTS, PLAST_CHAIN_MAX_STEPS);
+    return;
+  }
+  ChainProgram prog = {};
+  prog.n_inputs = n_inputs;
+  prog.n_steps = n_steps;
+  for (int s = 0; s < n_steps; ++s) {
+    const PlastChainStep &st = steps[s];
+    const bool binary = st.opcode <= PLAST_CHAIN_DIV;
+    if (st.opcode < 0 || st.opcode > PLAST_CHAIN_RDIV_SCALAR || st.a < 0 || st.a >= n_inputs + s ||
+        (binary && (st.b < 0 || st.b >= n_inputs + s))) {
+      set_error(PLAST_B200_ERR_SHAPE, "chain: step %d is malformed (opcode %d, a %d, b %d)", s,
+                st.opcode, st.a, st.b);
+      return;
+    }
+    prog.opcode[s] = (unsigned char)st.opcode;
+    prog.a[s] = (unsigned char)st.a;
+    prog.b[s] = (unsigned char)(binary ? st.b : st.a);
+    prog.fval[s] = st.fval;
+  }
+  if (is_sigmoid_mul_add_exp_neg_abs(prog)) {
+    fused_forward<SigmoidMulAddExpNegAbs, 2>(name, inputs, output, SigmoidMulAddExpNegAbs{});
+    if (!failed()) note_kernel("chain_precompiled");
+    end_call();
+    return;
+  }
+  switch (n_inputs) {
+  case 1: fused_forward<ChainInterp<1>, 1>(name, inputs, output, ChainInterp<1>{prog}); break;
+  case 2: fused_forward<ChainInterp<2>, 2>(name, inputs, output, ChainInterp<2>{prog}); break;
+  case 3: fused_forward<ChainInterp<3>, 3>(name, inputs, output, ChainInterp<3>{prog}); break;
+  default: fused_forward<ChainInterp<4>, 4>(name, inputs, output, ChainInterp<4>{prog}); break;
+  }
+  if (!failed()) note_kernel("chain_interpreter");
+  end_call();
+}
+
+} // extern "C"

@@ -1,0 +1,76 @@
+// Shared host-side plumbing of libplast_b200: error state, stream, launch accounting, the
+// per-device scratch workspace, and small device helpers used by every kernel file.
+#pragma once
+
+#include "plast_b200.h"
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+namespace pb {
+
+// ---- error state (thread local; entry points return void like the reference's) ---------------
+void set_error(int code, const char *fmt, ...);
+void begin_call();                 // clears the error of the previous call on this thread
+void note_kernel(const char *name); // remembers the kernel family for plast_b200_last_kernel()
+bool failed();
+
+cudaStream_t stream();
+void count_launch(int n = 1);
+void end_call(); // optional device sync (plast_b200_set_sync) + launch error check
+
+#define PB_CUDA(expr)                                                                              \
+  do {                                                                                             \
+    cudaError_t _e = (expr);                                                                       \
+    if (_e != cudaSuccess) {                                                                       \
+      pb::set_error(PLAST_B200_ERR_CUDA, "CUDA error at %s:%d: '%s': %s", __FILE__, __LINE__,      \
+                    #expr, cudaGetErrorString(_e));                                                \
+      return;                                                                                      \
+    }                                                                                              \
+  } while (0)
+
+#define PB_CUDA_RET(expr, ret)                                                                     \
+  do {                                                                                             \
+    cudaError_t _e = (expr);                                                                       \
+    if (_e != cudaSuccess) {                                                                       \
+      pb::set_error(PLAST_B200_ERR_CUDA, "CUDA error at %s:%d: '%s': %s", __FILE__, __LINE__,      \
+                    #expr, cudaGetErrorString(_e));                                                \
+      return ret;                                                                                  \
+    }                                                                                              \
+  } while (0)
+
+// ---- per-device scratch ------------------------------------------------------------------------
+// Reductions that split one output over several CTAs park their partials here and elect the
+// last-arriving CTA (a ticket counter) to combine them. One buffer per device, allocated on
+// first use and kept; counters live at the front, start at zero and are reset by the CTA that
+// consumes them, so no launch ever needs a memset.
+struct Workspace {
+  unsigned int *counters; // kCounters tickets
+  float *partials;        // kPartialFloats floats
+};
+constexpr size_t kCounters = 1 << 16;
+constexpr size_t kPartialFloats = (size_t)8 << 20; // 32 MiB
+bool get_workspace(Workspace *ws);
+
+int sm_count();
+
+// ---- tensor helpers ------------------------------------------------------------------------------
+inline u64 numel(const Tensor *t) {
+  u64 n = 1;
+  for (u64 i = 0; i < t->ndim; ++i) n *= t->shape[i];
+  return n;
+}
+// src/core/tensor.c:32-42: the stride of dim 0 is never examined.
+inline bool ref_is_contiguous(const Tensor *t) {
+  if (t->ndim == 0) return true;
+  u64 expect = 1;
+  for (u64 i = t->ndim - 1; i > 0; --i) {
+    if (t->strides[i] != expect) return false;
+    expect *= t->shape[i];
+  }
+  return true;
+}
+bool check_tensor(const Tensor *t, const char *what, bool need_data = true);
+
+} // namespace pb

@@ -1,0 +1,244 @@
+// Elementwise engine: one templated kernel family that evaluates out = f(in0 .. inN-1) over a
+// canonical iteration space (iter.h). Bound by HBM bandwidth, so everything here is about
+// bytes in flight and coalescing:
+//   * items are 16-byte (float4) or 8-byte (float2) vectors along the innermost dim whenever
+//     every operand is either contiguous or broadcast along it and the pointers allow it
+//     (arena allocations are only 8-byte aligned, src/core/tensor.c:66 -> float2 path);
+//   * every thread issues all loads of its kUnroll items before the first use, streaming
+//     (evict-first) for operands that are read once, default-cached for broadcast operands;
+//   * outer coordinates come from one multiply-shift division per dim (no 64-bit div/mod per
+//     element as in src/kernels/cuda/binary_ops.cu:41-54), or none at all for 1-D plans.
+#pragma once
+
+#include "common.cuh"
+#include "iter.h"
+
+namespace pb {
+
+constexpr int kEwThreads = 256;
+constexpr int kEwUnroll = 4;
+
+template <int VEC> struct VecOf;
+template <> struct VecOf<4> { using type = float4; };
+template <> struct VecOf<2> { using type = float2; };
+template <> struct VecOf<1> { using type = float; };
+
+template <int VEC> __device__ __forceinline__ void load_stream(const float *p, float *v);
+template <> __device__ __forceinline__ void load_stream<4>(const float *p, float *v) {
+  float4 t = __ldcs(reinterpret_cast<const float4 *>(p));
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <> __device__ __forceinline__ void load_stream<2>(const float *p, float *v) {
+  float2 t = __ldcs(reinterpret_cast<const float2 *>(p));
+  v[0] = t.x; v[1] = t.y;
+}
+template <> __device__ __forceinline__ void load_stream<1>(const float *p, float *v) { v[0] = *p; }
+
+template <int VEC> __device__ __forceinline__ void store_stream(float *p, const float *v);
+template <> __device__ __forceinline__ void store_stream<4>(float *p, const float *v) {
+  __stcs(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]));
+}
+template <> __device__ __forceinline__ void store_stream<2>(float *p, const float *v) {
+  __stcs(reinterpret_cast<float2 *>(p), make_float2(v[0], v[1]));
+}
+template <> __device__ __forceinline__ void store_stream<1>(float *p, const float *v) { *p = v[0]; }
+
+// Offsets of one item for NARGS operands. index_t = uint32_t when every count and offset fits
+// in 31 bits (multiply-shift division), uint64_t otherwise (hardware-emulated division).
+template <int NARGS, typename index_t> struct OffsetCalc {
+  int ndim;
+  index_t size[MAX_NDIM];   // size[0] counted in items
+  uint32_t magic[MAX_NDIM]; // uint32_t path: q = (umulhi(n, magic) + n) >> shift, n < 2^31
+  uint32_t shift[MAX_NDIM];
+  index_t stride[NARGS][MAX_NDIM]; // elements per step; stride[.][0] is per ITEM
+
+  __device__ __forceinline__ void get(index_t item, index_t *off) const {
+#pragma unroll
+    for (int a = 0; a < NARGS; ++a) off[a] = 0;
+#pragma unroll
+    for (int d = 0; d < MAX_NDIM; ++d) {
+      if (d >= ndim) break;
+      index_t q, r;
+      if (d == ndim - 1) { // outermost: no wrap
+        q = 0;
+        r = item;
+      } else if (sizeof(index_t) == 4) {
+        q = (index_t)((__umulhi((uint32_t)item, magic[d]) + (uint32_t)item) >> shift[d]);
+        r = item - q * size[d];
+      } else {
+        q = item / size[d];
+        r = item - q * size[d];
+      }
+#pragma unroll
+      for (int a = 0; a < NARGS; ++a) off[a] += r * stride[a][d];
+      item = q;
+    }
+  }
+};
+
+template <int NIN> struct InPtrs { const float *p[NIN]; };
+
+// vec_mask bit a set: input a is contiguous along dim 0 (vector load); clear: broadcast along
+// dim 0 (one scalar load, replicated). Only meaningful for VEC > 1.
+template <class F, int NIN, int VEC, typename index_t, bool ONE_D>
+__global__ void __launch_bounds__(kEwThreads)
+ew_kernel(F f, float *out, InPtrs<NIN> in, OffsetCalc<NIN + 1, index_t> oc, index_t n_items,
+          uint32_t vec_mask) {
+  const index_t tile = (index_t)blockIdx.x * (kEwThreads * kEwUnroll) + threadIdx.x;
+  float v[kEwUnroll][NIN][VEC];
+  index_t out_off[kEwUnroll];
+#pragma unroll
+  for (int u = 0; u < kEwUnroll; ++u) {
+    const index_t item = tile + (index_t)u * kEwThreads;
+    if (item < n_items) {
+      index_t off[NIN + 1];
+      if (ONE_D) {
+#pragma unroll
+        for (int a = 0; a <= NIN; ++a) off[a] = item * oc.stride[a][0];
+      } else {
+        oc.get(item, off);
+      }
+      out_off[u] = off[0];
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) {
+        const float *p = in.p[a] + off[a + 1];
+        if (VEC == 1) {
+          v[u][a][0] = *p;
+        } else if (vec_mask & (1u << a)) {
+          load_stream<VEC>(p, v[u][a]);
+        } else {
+          const float s = __ldg(p);
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) v[u][a][k] = s;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kEwUnroll; ++u) {
+    const index_t item = tile + (index_t)u * kEwThreads;
+    if (item < n_items) {
+      float r[VEC];
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        float x[NIN];
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) x[a] = v[u][a][k];
+        r[k] = f(x);
+      }
+      store_stream<VEC>(out + out_off[u], r);
+    }
+  }
+}
+
+struct FastDivU32 {
+  uint32_t magic, shift;
+};
+FastDivU32 make_fast_div(uint32_t d);
+
+// Chosen launch geometry, for tests and profiling.
+struct EwChoice {
+  int vec;
+  bool one_d;
+  bool idx64;
+};
+
+EwChoice choose_ew(const IterPlan &plan, const void *const *ptrs, int nargs, u64 *n_items,
+                   uint32_t *vec_mask);
+
+template <int NARGS, typename index_t>
+void fill_offset_calc(OffsetCalc<NARGS, index_t> *oc, const IterPlan &plan, int vec) {
+  oc->ndim = plan.ndim;
+  for (int d = 0; d < MAX_NDIM; ++d) {
+    u64 sz = d < plan.ndim ? plan.size[d] : 1;
+    if (d == 0) sz /= (u64)vec;
+    oc->size[d] = (index_t)sz;
+    FastDivU32 fd = make_fast_div((uint32_t)(sz > 0x7fffffffull ? 1 : (sz == 0 ? 1 : sz)));
+    oc->magic[d] = fd.magic;
+    oc->shift[d] = fd.shift;
+    for (int a = 0; a < NARGS; ++a) {
+      u64 s = d < plan.ndim ? plan.stride[a][d] : 0;
+      if (d == 0) s *= (u64)vec;
+      oc->stride[a][d] = (index_t)s;
+    }
+  }
+}
+
+// Launches f over the plan. ptrs[0] = output, ptrs[1..NIN] = inputs (device pointers).
+template <class F, int NIN>
+void launch_ew_one(const IterPlan &plan, float *out, const float *const *ins, const F &f) {
+  if (plan.numel == 0) return;
+  const void *ptrs[NIN + 1];
+  ptrs[0] = out;
+  for (int a = 0; a < NIN; ++a) ptrs[a + 1] = ins[a];
+  u64 n_items = 0;
+  uint32_t vec_mask = 0;
+  EwChoice c = choose_ew(plan, ptrs, NIN + 1, &n_items, &vec_mask);
+  InPtrs<NIN> ip;
+  for (int a = 0; a < NIN; ++a) ip.p[a] = ins[a];
+  const u64 per_block = (u64)kEwThreads * kEwUnroll;
+  const u64 blocks = (n_items + per_block - 1) / per_block;
+  if (blocks > 0x7fffffffull) {
+    set_error(PLAST_B200_ERR_LIMIT, "elementwise launch needs %llu blocks", (unsigned long long)blocks);
+    return;
+  }
+  dim3 grid((unsigned)blocks), block(kEwThreads);
+  cudaStream_t s = stream();
+#define PB_EW_LAUNCH(VEC, IDX, ONED)                                                               \
+  do {                                                                                             \
+    OffsetCalc<NIN + 1, IDX> oc;                                                                   \
+    fill_offset_calc(&oc, plan, VEC);                                                              \
+    ew_kernel<F, NIN, VEC, IDX, ONED><<<grid, block, 0, s>>>(f, out, ip, oc, (IDX)n_items,        \
+                                                              vec_mask);                           \
+  } while (0)
+#define PB_EW_BY_VEC(IDX, ONED)                                                                    \
+  do {                                                                                             \
+    if (c.vec == 4) PB_EW_LAUNCH(4, IDX, ONED);                                                    \
+    else if (c.vec == 2) PB_EW_LAUNCH(2, IDX, ONED);                                               \
+    else PB_EW_LAUNCH(1, IDX, ONED);                                                               \
+  } while (0)
+  if (c.idx64) {
+    if (c.one_d) PB_EW_BY_VEC(uint64_t, true);
+    else PB_EW_BY_VEC(uint64_t, false);
+  } else {
+    if (c.one_d) PB_EW_BY_VEC(uint32_t, true);
+    else PB_EW_BY_VEC(uint32_t, false);
+  }
+#undef PB_EW_BY_VEC
+#undef PB_EW_LAUNCH
+  count_launch();
+  static const char *names[3][2] = {{"ew_scalar_nd", "ew_scalar_1d"},
+                                    {"ew_vec2_nd", "ew_vec2_1d"},
+                                    {"ew_vec4_nd", "ew_vec4_1d"}};
+  note_kernel(names[c.vec == 4 ? 2 : (c.vec == 2 ? 1 : 0)][c.one_d ? 1 : 0]);
+}
+
+// Public entry: 1-D plans whose length is not a multiple of 4 run as a vector body plus a
+// <= 3 element tail, so an odd element count does not force the whole tensor onto scalar loads.
+template <class F, int NIN>
+void launch_ew(const IterPlan &plan, float *out, const float *const *ins, const F &f) {
+  if (plan.ndim == 1 && plan.size[0] >= 8 && (plan.size[0] & 3) != 0 && plan.stride[0][0] == 1) {
+    bool ok = true;
+    for (int a = 1; a <= NIN; ++a) ok = ok && plan.stride[a][0] <= 1;
+    if (ok) {
+      const u64 body_n = plan.size[0] & ~(u64)3;
+      IterPlan body = plan, tail = plan;
+      body.size[0] = body_n;
+      body.numel = body_n;
+      tail.size[0] = plan.size[0] - body_n;
+      tail.numel = tail.size[0];
+      const float *tins[NIN];
+      for (int a = 0; a <= NIN; ++a) {
+        body.max_offset[a] = (body_n - 1) * plan.stride[a][0];
+        tail.max_offset[a] = (tail.size[0] - 1) * plan.stride[a][0];
+        if (a > 0) tins[a - 1] = ins[a - 1] + body_n * plan.stride[a][0];
+      }
+      launch_ew_one<F, NIN>(body, out, ins, f);
+      launch_ew_one<F, NIN>(tail, out + body_n, tins, f);
+      return;
+    }
+  }
+  launch_ew_one<F, NIN>(plan, out, ins, f);
+}
+
+} // namespace pb

@@ -1,0 +1,221 @@
+// Symbols the reference's core, arena, shape ops and Python extension link against:
+// fills, arena memory calls, view-gradient accumulation and the strided -> contiguous pack.
+#include "ew_engine.cuh"
+#include "functors.cuh"
+
+#include <stdlib.h>
+
+namespace pb {
+
+struct CopyF { __device__ __forceinline__ float operator()(const float *x) const { return x[0]; } };
+struct AccF { __device__ __forceinline__ float operator()(const float *x) const { return x[1] + x[0]; } };
+
+// 16-byte stores; value is a 32-bit pattern so int32 and float32 share the kernel.
+__global__ void __launch_bounds__(256) fill_kernel(unsigned int *p, unsigned int value, u64 n) {
+  const u64 stride = (u64)gridDim.x * blockDim.x;
+  u64 i = (u64)blockIdx.x * blockDim.x + threadIdx.x;
+  // head until 16-byte aligned
+  const u64 head = (((uintptr_t)p) & 15) ? ((16 - (((uintptr_t)p) & 15)) >> 2) : 0;
+  const u64 h = head < n ? head : n;
+  if (i < h) p[i] = value;
+  uint4 *q = reinterpret_cast<uint4 *>(p + h);
+  const u64 nv = (n - h) >> 2;
+  const uint4 v = make_uint4(value, value, value, value);
+  for (u64 j = i; j < nv; j += stride) q[j] = v;
+  const u64 tail_begin = h + (nv << 2);
+  if (tail_begin + i < n && i < 4) p[tail_begin + i] = value;
+}
+
+static void fill32(void *data, unsigned int pattern, u64 n) {
+  if (n == 0) return;
+  u64 blocks = (n / 4 + 255) / 256;
+  const u64 cap = (u64)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks == 0) blocks = 1;
+  fill_kernel<<<(unsigned)blocks, 256, 0, stream()>>>((unsigned int *)data, pattern, n);
+  count_launch();
+  note_kernel("fill32");
+}
+
+static unsigned int one_pattern(DTYPE dt) {
+  if (dt == INT32) return 1u;
+  const float f = 1.0f;
+  unsigned int u;
+  memcpy(&u, &f, 4);
+  return u;
+}
+
+} // namespace pb
+
+using namespace pb;
+
+extern "C" {
+
+// src/kernels/cuda/cuda_tensor_init.cu:19-95
+void zeros_cuda(Tensor *t, u64 num_elements) {
+  begin_call();
+  if (!check_tensor(t, "zeros")) return;
+  fill32(t->data, 0u, num_elements);
+  end_call();
+}
+void ones_cuda(Tensor *t, u64 num_elements) {
+  begin_call();
+  if (!check_tensor(t, "ones")) return;
+  fill32(t->data, one_pattern(t->dtype), num_elements);
+  end_call();
+}
+void set_ones_grad_cuda(Tensor *t) {
+  begin_call();
+  if (!check_tensor(t, "set_ones_grad", false)) return;
+  if (!t->grad || !t->grad->data) {
+    set_error(PLAST_B200_ERR_NULL, "set_ones_grad: tensor has no grad");
+    return;
+  }
+  fill32(t->grad->data, one_pattern(t->dtype), numel(t));
+  end_call();
+}
+// src/optimizers/cuda/zero_grad.cu:11-25
+void zero_grad_cuda(Tensor *t) {
+  begin_call();
+  if (!t || !t->grad || !t->grad->data) return;
+  fill32(t->grad->data, 0u, numel(t->grad));
+  end_call();
+}
+
+// src/kernels/cuda/shape_ops_cuda.cu:38-43: da[i] += dout[i]
+void reshape_backward_cuda(float *da, const float *dout, u64 num_elements) {
+  begin_call();
+  if (!da || !dout) {
+    set_error(PLAST_B200_ERR_NULL, "reshape_backward: NULL pointer");
+    return;
+  }
+  const u64 shape[1] = {num_elements};
+  u64 st[3][MAX_NDIM] = {};
+  st[0][0] = st[1][0] = st[2][0] = 1;
+  IterPlan plan;
+  make_plan(&plan, shape, 1, 3, st, nullptr, 0);
+  const float *ins[2] = {dout, da};
+  launch_ew<AccF, 2>(plan, da, ins, AccF{});
+  end_call();
+}
+
+// src/kernels/cuda/shape_ops_cuda.cu:45-70 (src/kernels/cpu/shape_ops.c:82-120): for every
+// coordinate of a, da[coords . da_strides] += dout[swap(coords) . dout_strides]. Each da element
+// is written once, so no atomics are needed; shape/stride arrays are host memory.
+void transpose_backward_cuda(float *da, const float *dout, const u64 *a_shape,
+                             const u64 *da_strides, const u64 *dout_strides, u64 ndim, u64 axis1,
+                             u64 axis2, u64 num_elements) {
+  begin_call();
+  (void)num_elements;
+  if (!da || !dout || !a_shape || !da_strides || !dout_strides) {
+    set_error(PLAST_B200_ERR_NULL, "transpose_backward: NULL pointer");
+    return;
+  }
+  if (ndim > MAX_NDIM || axis1 >= ndim || axis2 >= ndim) {
+    set_error(PLAST_B200_ERR_SHAPE, "transpose_backward: bad ndim/axes");
+    return;
+  }
+  u64 st[3][MAX_NDIM] = {};
+  for (u64 d = 0; d < ndim; ++d) {
+    u64 od = d == axis1 ? axis2 : (d == axis2 ? axis1 : d);
+    st[0][d] = da_strides[d];
+    st[1][d] = dout_strides[od];
+    st[2][d] = da_strides[d];
+  }
+  IterPlan plan;
+  make_plan(&plan, a_shape, ndim, 3, st, nullptr, 0);
+  const float *ins[2] = {dout, da};
+  launch_ew<AccF, 2>(plan, da, ins, AccF{});
+  end_call();
+}
+
+// src/core/arena_cuda.cu:13-32. Allocation failures are fatal there (exit); here too, because the
+// arena has no way to report them.
+#define PB_FATAL(expr)                                                                             \
+  do {                                                                                             \
+    cudaError_t _e = (expr);                                                                       \
+    if (_e != cudaSuccess) {                                                                       \
+      fprintf(stderr, "CUDA Error: %s %s %d\n", cudaGetErrorString(_e), __FILE__, __LINE__);       \
+      exit(EXIT_FAILURE);                                                                          \
+    }                                                                                              \
+  } while (0)
+
+void *arena_alloc_cuda(u64 size) {
+  void *p = nullptr;
+  PB_FATAL(cudaMalloc(&p, size ? size : 1));
+  return p;
+}
+void arena_free_cuda(void *ptr) { PB_FATAL(cudaFree(ptr)); }
+// Stream-ordered on the library stream, so a fill never races the kernels around it.
+void arena_memset_cuda(void *ptr, int value, u64 size) {
+  PB_FATAL(cudaMemsetAsync(ptr, value, size, stream()));
+}
+void arena_memcpy_h2d_cuda(void *dest, const void *src, u64 size) {
+  PB_FATAL(cudaMemcpyAsync(dest, src, size, cudaMemcpyHostToDevice, stream()));
+  PB_FATAL(cudaStreamSynchronize(stream()));
+}
+void arena_memcpy_d2h_cuda(void *dest, const void *src, u64 size) {
+  PB_FATAL(cudaMemcpyAsync(dest, src, size, cudaMemcpyDeviceToHost, stream()));
+  PB_FATAL(cudaStreamSynchronize(stream()));
+}
+void arena_memcpy_d2d_cuda(void *dest, const void *src, u64 size) {
+  PB_FATAL(cudaMemcpyAsync(dest, src, size, cudaMemcpyDeviceToDevice, stream()));
+}
+
+// Strided gather into a contiguous buffer (src/kernels/cuda/cuda_pack.cu:5-27), through the
+// elementwise engine so contiguous inner runs move as 128-bit vectors.
+void plast_b200_pack(const Tensor *t, void *dst) {
+  begin_call();
+  if (!check_tensor(t, "pack") || !dst) {
+    if (!dst) set_error(PLAST_B200_ERR_NULL, "pack: dst is NULL");
+    return;
+  }
+  u64 st[2][MAX_NDIM] = {};
+  u64 s = 1;
+  for (u64 d = t->ndim; d-- > 0;) {
+    st[0][d] = s;
+    s *= t->shape[d];
+    st[1][d] = t->strides[d];
+  }
+  IterPlan plan;
+  make_plan(&plan, t->shape, t->ndim, 2, st, nullptr, 0);
+  const float *ins[1] = {(const float *)t->data};
+  launch_ew<CopyF, 1>(plan, (float *)dst, ins, CopyF{});
+  end_call();
+}
+
+} // extern "C"
+
+// include/kernels/pack.h:17-23 (C++ linkage in the reference). Contiguous tensors are passed
+// through; otherwise a buffer is allocated, filled by the gather and released by ..._release.
+struct CudaTensorPack {
+  void *data;
+  void *_d_buf;
+};
+void cuda_tensor_pack_init(CudaTensorPack *p, const Tensor *t) {
+  p->data = nullptr;
+  p->_d_buf = nullptr;
+  if (ref_is_contiguous(t)) {
+    p->data = t->data;
+    return;
+  }
+  const u64 bytes = numel(t) * sizeof(float);
+  if (cudaMalloc(&p->_d_buf, bytes ? bytes : 1) != cudaSuccess) {
+    p->_d_buf = nullptr;
+    return;
+  }
+  plast_b200_pack(t, p->_d_buf);
+  if (plast_b200_last_error() != PLAST_B200_OK) {
+    cudaFree(p->_d_buf);
+    p->_d_buf = nullptr;
+    return;
+  }
+  p->data = p->_d_buf;
+}
+void cuda_tensor_pack_release(CudaTensorPack *p) {
+  if (p->_d_buf) {
+    cudaFree(p->_d_buf);
+    p->_d_buf = nullptr;
+  }
+  p->data = nullptr;
+}

@@ -1,0 +1,384 @@
+// Reduction geometry + entry points of sum / mean / max / min (forward, backward) and argmax.
+#include "ew_engine.cuh"
+#include "functors.cuh"
+#include "reduce_engine.cuh"
+
+namespace pb {
+
+static u64 ceil_div(u64 a, u64 b) { return (a + b - 1) / b; }
+static int log2_ceil(u64 v) {
+  int l = 0;
+  while (((u64)1 << l) < v) ++l;
+  return l;
+}
+
+bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int nin,
+                          size_t elem_bytes, bool indexed, RedGeometry *g) {
+  // Vector width along dim 0 (same rule as the elementwise engine, inputs only).
+  g->vec = 1;
+  g->vec_mask = 0;
+  const int cand[2] = {4, 2};
+  for (int ci = 0; ci < 2; ++ci) {
+    const int vec = cand[ci];
+    bool ok = plan.size[0] % (u64)vec == 0;
+    unsigned mask = 0;
+    bool any_vec = false;
+    for (int a = 0; ok && a < nin; ++a) {
+      const u64 s0 = plan.stride[a + 1][0];
+      if (s0 == 0) continue;
+      if (s0 != 1) { ok = false; break; }
+      if (((uintptr_t)in_ptrs[a]) % (sizeof(float) * vec) != 0) { ok = false; break; }
+      for (int d = 1; d < plan.ndim; ++d)
+        if (plan.stride[a + 1][d] % (u64)vec != 0) { ok = false; break; }
+      mask |= 1u << a;
+      any_vec = true;
+    }
+    if (ok && any_vec) {
+      g->vec = vec;
+      g->vec_mask = mask;
+      break;
+    }
+  }
+  const u64 vec = (u64)g->vec;
+  g->len0_items = plan.size[0] / vec;
+  g->n_kept_dims = g->n_red_dims = 0;
+  g->n_kept = g->n_red = 1;
+  const bool dim0_reduced = plan.reduced[0];
+  int n_reduced_total = 0;
+  for (int d = 0; d < plan.ndim; ++d) n_reduced_total += plan.reduced[d] ? 1 : 0;
+  if (indexed && n_reduced_total > 1) {
+    set_error(PLAST_B200_ERR_UNSUPPORTED,
+              "argmax over more than one non-mergeable axis (a non-contiguous full reduce)");
+    return false;
+  }
+  for (int d = 1; d < plan.ndim; ++d) {
+    if (plan.reduced[d]) {
+      g->red_dims[g->n_red_dims++] = d;
+      g->n_red *= plan.size[d];
+    } else {
+      g->kept_dims[g->n_kept_dims++] = d;
+      g->n_kept *= plan.size[d];
+    }
+  }
+  const u64 sms = (u64)sm_count();
+  const u64 target_ctas = sms * 8;
+  g->splits = 1;
+  g->seg_len = g->nsplit0 = g->nseg = g->per_chunk = 0;
+  g->log_tx = 5;
+
+  if (dim0_reduced) {
+    if (indexed && plan.size[0] * (g->n_red) > 0xffffffffull) {
+      set_error(PLAST_B200_ERR_LIMIT, "argmax over more than 2^32 elements");
+      return false;
+    }
+    int log_tx = log2_ceil(g->len0_items);
+    if (log_tx > 5) log_tx = 5;
+    const u64 warps = g->n_kept * ((u64)1 << log_tx) / 32;
+    if (g->n_red == 1 && (warps >= sms * 16 || g->len0_items <= 256)) {
+      g->kind = kRedRows;
+      g->log_tx = log_tx;
+      const u64 rows_per_cta = (u64)kRedThreads >> log_tx;
+      u64 blocks = ceil_div(g->n_kept, rows_per_cta);
+      const u64 cap = sms * 64; // grid-stride beyond this
+      g->grid = blocks < cap ? blocks : cap;
+      return true;
+    }
+    g->kind = kRedSeg;
+    if (g->len0_items <= 1024) {
+      g->nsplit0 = 1;
+      g->seg_len = g->len0_items;
+      g->log_tx = log2_ceil(g->len0_items);
+      if (g->log_tx > 8) g->log_tx = 8;
+    } else {
+      g->seg_len = 1024;
+      g->nsplit0 = ceil_div(g->len0_items, 1024);
+      g->log_tx = 8;
+    }
+    g->nseg = g->nsplit0 * g->n_red;
+    const u64 ty_n = (u64)kRedThreads >> g->log_tx;
+    // a chunk should give every row-worker >= 2 segments and move >= ~64 KiB
+    u64 min_per = ty_n * 2;
+    const u64 seg_bytes = g->seg_len * vec * sizeof(float);
+    if (min_per * seg_bytes < (64u << 10)) min_per = ceil_div(64u << 10, seg_bytes);
+    u64 splits = ceil_div(target_ctas, g->n_kept);
+    const u64 max_splits = g->nseg / min_per > 0 ? g->nseg / min_per : 1;
+    if (splits > max_splits) splits = max_splits;
+    if (splits > 1 && (g->n_kept > kCounters ||
+                       g->n_kept * splits * elem_bytes > kPartialFloats / 2 * sizeof(float)))
+      splits = 1;
+    g->per_chunk = ceil_div(g->nseg, splits);
+    g->splits = (unsigned)ceil_div(g->nseg, g->per_chunk);
+    g->grid = g->n_kept * g->splits;
+  } else {
+    if (indexed && g->n_red > 0xffffffffull) {
+      set_error(PLAST_B200_ERR_LIMIT, "argmax over more than 2^32 elements");
+      return false;
+    }
+    g->kind = kRedCols;
+    const u64 strips = ceil_div(g->len0_items, 32);
+    const u64 tiles = g->n_kept * strips;
+    u64 splits = ceil_div(target_ctas, tiles);
+    const u64 max_splits = g->n_red / 64 > 0 ? g->n_red / 64 : 1;
+    if (splits > max_splits) splits = max_splits;
+    if (splits > 1 && (tiles > kCounters || tiles * splits * 32 * vec * elem_bytes >
+                                                kPartialFloats / 2 * sizeof(float)))
+      splits = 1;
+    g->per_chunk = ceil_div(g->n_red, splits);
+    g->splits = (unsigned)ceil_div(g->n_red, g->per_chunk);
+    g->grid = tiles * g->splits;
+  }
+  if (g->grid == 0 || g->grid > 0x7fffffffull) {
+    set_error(PLAST_B200_ERR_LIMIT, "reduction needs %llu blocks", (unsigned long long)g->grid);
+    return false;
+  }
+  return true;
+}
+
+// ---- forward ---------------------------------------------------------------------------------------
+// Shape the CPU path writes into the output of an axis reduce (src/kernels/cpu/cpu_utils.c:121-154).
+static void reduced_shape(const Tensor *a, u64 dim, bool keepdim, u64 *shape, u64 *ndim, u64 *strides) {
+  u64 nd = 0;
+  if (keepdim) {
+    for (u64 i = 0; i < a->ndim; ++i) shape[i] = (i == dim) ? 1 : a->shape[i];
+    nd = a->ndim;
+  } else {
+    for (u64 i = 0; i < a->ndim; ++i)
+      if (i != dim) shape[nd++] = a->shape[i];
+    if (nd == 0) {
+      shape[0] = 1;
+      nd = 1;
+    }
+  }
+  *ndim = nd;
+  u64 s = 1;
+  for (u64 i = nd; i-- > 0;) {
+    strides[i] = s;
+    s *= shape[i];
+  }
+}
+
+// Strides of the reduced tensor `c` seen from a's dims (0 on the reduced dim).
+static void out_strides_in_a_dims(const Tensor *a, u64 dim, bool keepdim, const u64 *c_strides,
+                                  u64 *st) {
+  for (u64 j = 0; j < a->ndim; ++j) {
+    if (j == dim) st[j] = 0;
+    else if (keepdim) st[j] = c_strides[j];
+    else st[j] = c_strides[j < dim ? j : j - 1];
+  }
+  // when every dim is reduced away the output is the single element at offset 0
+}
+
+static bool reduce_common_checks(const char *name, const Tensor *a, const Tensor *output, u64 dim) {
+  if (a->dtype != FLOAT32) {
+    set_error(PLAST_B200_ERR_DTYPE, "%s: unsupported dtype %d", name, (int)a->dtype);
+    return false;
+  }
+  if (dim != PLAST_FULL_REDUCE && dim >= a->ndim) {
+    set_error(PLAST_B200_ERR_SHAPE, "%s: axis %llu out of range for %llu dims", name,
+              (unsigned long long)dim, (unsigned long long)a->ndim);
+    return false;
+  }
+  (void)output;
+  return true;
+}
+
+// Builds the plan of reducing `a` over `dim` (or everything) into a target indexed by tst[].
+static void reduce_plan(IterPlan *plan, const Tensor *a, u64 dim, const u64 *target_strides) {
+  u64 st[2][MAX_NDIM] = {};
+  bool red[MAX_NDIM] = {};
+  for (u64 j = 0; j < a->ndim; ++j) {
+    st[0][j] = target_strides ? target_strides[j] : 0;
+    st[1][j] = a->strides[j];
+    red[j] = (dim == PLAST_FULL_REDUCE) || (j == dim);
+  }
+  make_plan(plan, a->shape, a->ndim, 2, st, red, 1);
+  if (a->ndim == 0 || plan->ndim == 1) {
+    // single element, or fully merged: make sure a lone dim of a full reduce is marked reduced
+    if (dim == PLAST_FULL_REDUCE) plan->reduced[0] = true;
+  }
+}
+
+template <class Op>
+static void reduce_forward(const char *name, const Tensor **inputs, Tensor *output,
+                           KernelParams params, bool mean) {
+  begin_call();
+  if (!inputs || !check_tensor(inputs[0], name) || !check_tensor(output, name)) return;
+  const Tensor *a = inputs[0];
+  const u64 dim = params.dim;
+  if (!reduce_common_checks(name, a, output, dim)) return;
+  u64 tst[MAX_NDIM] = {};
+  u64 count = 0;
+  if (dim == PLAST_FULL_REDUCE) {
+    count = numel(a);
+  } else {
+    const bool keepdim = params.keepdim != 0;
+    reduced_shape(a, dim, keepdim, output->shape, &output->ndim, output->strides);
+    out_strides_in_a_dims(a, dim, keepdim, output->strides, tst);
+    count = a->shape[dim];
+  }
+  IterPlan plan;
+  reduce_plan(&plan, a, dim, tst);
+  const float *ins[1] = {(const float *)a->data};
+  launch_reduce<Op, IdentityPro, 1>(plan, (typename Op::Out *)output->data, ins, IdentityPro{}, Op{},
+                                    false, mean ? (float)count : 0.0f);
+  end_call();
+}
+
+// ---- backward ----------------------------------------------------------------------------------------
+// sum / mean: da[coords] += g[out coords] (/ n): src/kernels/cpu/reduce_ops.c:90-154.
+struct AddGrad { // x = {g, old}
+  __device__ __forceinline__ float operator()(const float *x) const { return x[1] + x[0]; }
+};
+struct AddGradScaled { // mean: grad / n first, then accumulate
+  float n;
+  __device__ __forceinline__ float operator()(const float *x) const { return x[1] + x[0] / n; }
+};
+// max / min: da[i] += g / ties where a[i] equals the extreme (reduce_ops.c:157-262).
+struct EqualsPro { // x = {a, extreme}
+  __device__ __forceinline__ float operator()(const float *x) const { return x[0] == x[1] ? 1.0f : 0.0f; }
+};
+struct TieGrad { // x = {a, extreme, g, ties, old}
+  __device__ __forceinline__ float operator()(const float *x) const {
+    return x[0] == x[1] ? x[4] + x[2] / x[3] : x[4];
+  }
+};
+
+static bool backward_checks(const char *name, Tensor **inputs, const Tensor *output) {
+  if (!inputs || !check_tensor(inputs[0], name) || !check_tensor(output, name, false)) return false;
+  const Tensor *a = inputs[0];
+  if (a->dtype != FLOAT32) {
+    set_error(PLAST_B200_ERR_DTYPE, "%s: unsupported dtype %d", name, (int)a->dtype);
+    return false;
+  }
+  if (!a->requires_grad) return false; // nothing to do (reduce_ops.c:134)
+  if (!a->grad || !a->grad->data || !output->grad || !output->grad->data) {
+    set_error(PLAST_B200_ERR_NULL, "%s: missing grad tensor", name);
+    return false;
+  }
+  return true;
+}
+
+static void sum_mean_backward(const char *name, Tensor **inputs, const Tensor *output,
+                              KernelParams params, bool mean) {
+  begin_call();
+  if (!backward_checks(name, inputs, output)) return;
+  const Tensor *a = inputs[0];
+  const u64 dim = params.dim;
+  if (!reduce_common_checks(name, a, output, dim)) return;
+  u64 st[3][MAX_NDIM] = {};
+  u64 gst[MAX_NDIM] = {};
+  u64 count = numel(a);
+  if (dim != PLAST_FULL_REDUCE) {
+    out_strides_in_a_dims(a, dim, params.keepdim != 0, output->strides, gst);
+    count = a->shape[dim];
+  }
+  for (u64 j = 0; j < a->ndim; ++j) {
+    st[0][j] = a->grad->strides[j];
+    st[1][j] = gst[j];
+    st[2][j] = a->grad->strides[j];
+  }
+  IterPlan plan;
+  make_plan(&plan, a->shape, a->ndim, 3, st, nullptr, 0);
+  const float *ins[2] = {(const float *)output->grad->data, (const float *)a->grad->data};
+  if (mean) launch_ew<AddGradScaled, 2>(plan, (float *)a->grad->data, ins, AddGradScaled{(float)count});
+  else launch_ew<AddGrad, 2>(plan, (float *)a->grad->data, ins, AddGrad{});
+  end_call();
+}
+
+static void max_min_backward(const char *name, Tensor **inputs, const Tensor *output,
+                             KernelParams params) {
+  begin_call();
+  if (!backward_checks(name, inputs, output)) return;
+  const Tensor *a = inputs[0];
+  const u64 dim = params.dim;
+  if (!reduce_common_checks(name, a, output, dim)) return;
+  if (!output->data) {
+    set_error(PLAST_B200_ERR_NULL, "%s: output data is NULL", name);
+    return;
+  }
+  u64 cst[MAX_NDIM] = {};
+  u64 n_out = 1;
+  if (dim != PLAST_FULL_REDUCE) {
+    out_strides_in_a_dims(a, dim, params.keepdim != 0, output->strides, cst);
+    n_out = numel(a) / (a->shape[dim] ? a->shape[dim] : 1);
+  }
+  Workspace ws;
+  if (!get_workspace(&ws)) return;
+  if (n_out > kPartialFloats / 2) {
+    set_error(PLAST_B200_ERR_LIMIT, "%s backward: %llu outputs exceed the tie-count scratch (%llu)",
+              name, (unsigned long long)n_out, (unsigned long long)(kPartialFloats / 2));
+    return;
+  }
+  float *ties = ws.partials + kPartialFloats / 2; // second half: never used by split partials
+  // 1) ties[out] = number of elements equal to the extreme, laid out like the output
+  {
+    u64 st[3][MAX_NDIM] = {};
+    bool red[MAX_NDIM] = {};
+    for (u64 j = 0; j < a->ndim; ++j) {
+      st[0][j] = cst[j];
+      st[1][j] = a->strides[j];
+      st[2][j] = cst[j];
+      red[j] = (dim == PLAST_FULL_REDUCE) || (j == dim);
+    }
+    IterPlan plan;
+    make_plan(&plan, a->shape, a->ndim, 3, st, red, 1);
+    if (dim == PLAST_FULL_REDUCE) plan.reduced[0] = true;
+    const float *ins[2] = {(const float *)a->data, (const float *)output->data};
+    launch_reduce<SumOp, EqualsPro, 2>(plan, ties, ins, EqualsPro{}, SumOp{}, false, 0.0f);
+    if (failed()) return;
+  }
+  // 2) da += g / ties where equal
+  {
+    u64 st[6][MAX_NDIM] = {};
+    for (u64 j = 0; j < a->ndim; ++j) {
+      st[0][j] = a->grad->strides[j];
+      st[1][j] = a->strides[j];
+      st[2][j] = cst[j];
+      st[3][j] = cst[j];
+      st[4][j] = cst[j];
+      st[5][j] = a->grad->strides[j];
+    }
+    IterPlan plan;
+    make_plan(&plan, a->shape, a->ndim, 6, st, nullptr, 0);
+    const float *ins[5] = {(const float *)a->data, (const float *)output->data,
+                           (const float *)output->grad->data, ties, (const float *)a->grad->data};
+    launch_ew<TieGrad, 5>(plan, (float *)a->grad->data, ins, TieGrad{});
+  }
+  end_call();
+}
+
+} // namespace pb
+
+using namespace pb;
+
+extern "C" {
+
+void sum_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params) {
+  reduce_forward<SumOp>("sum", inputs, output, params, false);
+}
+void mean_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params) {
+  reduce_forward<SumOp>("mean", inputs, output, params, true);
+}
+void max_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params) {
+  reduce_forward<MaxOp>("max", inputs, output, params, false);
+}
+void min_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params) {
+  reduce_forward<MinOp>("min", inputs, output, params, false);
+}
+void argmax_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params) {
+  reduce_forward<ArgMaxOp>("argmax", inputs, output, params, false);
+}
+void sum_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params) {
+  sum_mean_backward("sum", inputs, output, params, false);
+}
+void mean_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params) {
+  sum_mean_backward("mean", inputs, output, params, true);
+}
+void max_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params) {
+  max_min_backward("max", inputs, output, params);
+}
+void min_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params) {
+  max_min_backward("min", inputs, output, params);
+}
+
+} // extern "C"

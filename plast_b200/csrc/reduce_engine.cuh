@@ -1,0 +1,534 @@
+// Reduction engine: out[kept coords] (+)= reduce over the reduced dims of pro(in0 .. inN-1).
+//
+// One engine serves the axis / full reductions (sum, mean, max, min, argmax) and the
+// broadcast-gradient reduce of the binary backward (a sum whose prologue computes the gradient
+// term on the fly). The canonical plan (iter.h) is ordered by the streamed input's strides, so
+// "dim 0" is the dim that is contiguous in memory; three kernel shapes cover every plan:
+//
+//   rows  dim 0 is reduced and is the only reduced dim: a (sub)warp per output walks its
+//         contiguous run with 128-bit loads and combines with shuffles.
+//   seg   dim 0 is reduced and either more reduced dims exist (N,H,W of an NCHW bias gradient)
+//         or there are too few outputs to fill 148 SMs (a full reduction is the extreme case):
+//         the reduction of one output is cut into segments; a CTA takes a chunk of segments;
+//         chunks are combined by the last-arriving CTA (ticket counter) in a fixed order.
+//   cols  dim 0 is kept: a CTA owns a 32*VEC-wide strip of outputs, its 8 warps stride over
+//         the reduced dims (every load is a full coalesced row), partial strips are combined
+//         in shared memory and, when the reduction is also split over CTAs, by ticket.
+//
+// No float atomics anywhere: results are bit-reproducible from run to run (the reference's
+// atomicAdd / omp-atomic order is not, src/kernels/cuda/binary_ops.cu:85-89).
+#pragma once
+
+#include "common.cuh"
+#include "iter.h"
+
+#include <float.h>
+
+namespace pb {
+
+constexpr int kRedThreads = 256;
+
+// ---- combine operators ----------------------------------------------------------------------------
+struct SumOp {
+  using T = float;
+  using Out = float;
+  static constexpr bool kIndexed = false;
+  __device__ __forceinline__ static T identity() { return 0.0f; }
+  __device__ __forceinline__ static T lift(float v, unsigned long long) { return v; }
+  __device__ __forceinline__ static T combine(T a, T b) { return a + b; }
+  __device__ __forceinline__ static T shfl_xor(T v, int m, int w) {
+    return __shfl_xor_sync(0xffffffffu, v, m, w);
+  }
+  __device__ __forceinline__ static T load_cg(const T *p) { return __ldcg(p); }
+  __device__ __forceinline__ static void store(Out *o, T v, bool acc, float div) {
+    if (div > 0.0f) v = v / div;
+    *o = acc ? *o + v : v;
+  }
+};
+// src/kernels/cpu/reduce_ops.c:9-10, 273-278: start at -/+FLT_MAX, keep acc unless strictly beaten.
+struct MaxOp {
+  using T = float;
+  using Out = float;
+  static constexpr bool kIndexed = false;
+  __device__ __forceinline__ static T identity() { return -FLT_MAX; }
+  __device__ __forceinline__ static T lift(float v, unsigned long long) { return v; }
+  __device__ __forceinline__ static T combine(T a, T b) { return a > b ? a : b; }
+  __device__ __forceinline__ static T shfl_xor(T v, int m, int w) {
+    return __shfl_xor_sync(0xffffffffu, v, m, w);
+  }
+  __device__ __forceinline__ static T load_cg(const T *p) { return __ldcg(p); }
+  __device__ __forceinline__ static void store(Out *o, T v, bool, float) { *o = v; }
+};
+struct MinOp {
+  using T = float;
+  using Out = float;
+  static constexpr bool kIndexed = false;
+  __device__ __forceinline__ static T identity() { return FLT_MAX; }
+  __device__ __forceinline__ static T lift(float v, unsigned long long) { return v; }
+  __device__ __forceinline__ static T combine(T a, T b) { return a < b ? a : b; }
+  __device__ __forceinline__ static T shfl_xor(T v, int m, int w) {
+    return __shfl_xor_sync(0xffffffffu, v, m, w);
+  }
+  __device__ __forceinline__ static T load_cg(const T *p) { return __ldcg(p); }
+  __device__ __forceinline__ static void store(Out *o, T v, bool, float) { *o = v; }
+};
+// Maximum with the position of its first occurrence (lowest index wins ties), any visiting order.
+struct ArgMaxOp {
+  struct T {
+    float v;
+    unsigned int i;
+  };
+  using Out = int;
+  static constexpr bool kIndexed = true;
+  __device__ __forceinline__ static T identity() { return T{-INFINITY, 0xffffffffu}; }
+  __device__ __forceinline__ static T lift(float v, unsigned long long i) {
+    return T{v, (unsigned int)i};
+  }
+  __device__ __forceinline__ static T combine(T a, T b) {
+    return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+  }
+  __device__ __forceinline__ static T shfl_xor(T v, int m, int w) {
+    T r;
+    r.v = __shfl_xor_sync(0xffffffffu, v.v, m, w);
+    r.i = __shfl_xor_sync(0xffffffffu, v.i, m, w);
+    return r;
+  }
+  __device__ __forceinline__ static T load_cg(const T *p) {
+    return T{__ldcg(&p->v), __ldcg(&p->i)};
+  }
+  __device__ __forceinline__ static void store(Out *o, T v, bool, float) { *o = (int)v.i; }
+};
+// Counts elements equal to a per-output target value (tie count of the max/min backward).
+struct IdentityPro {
+  __device__ __forceinline__ float operator()(const float *x) const { return x[0]; }
+};
+
+// ---- kernel parameters ------------------------------------------------------------------------------
+// A sub-space is a list of dims (innermost first) with, per dim, its size and the element
+// stride of the target and of every input.
+template <int NIN> struct SubSpace {
+  int n;
+  u64 size[MAX_NDIM];
+  u64 tstride[MAX_NDIM];
+  u64 istride[NIN][MAX_NDIM];
+
+  // Decodes a flat index into offsets (added to toff / ioff).
+  __device__ __forceinline__ void offsets(u64 flat, u64 *toff, u64 *ioff) const {
+#pragma unroll
+    for (int d = 0; d < MAX_NDIM; ++d) {
+      if (d >= n) break;
+      u64 q, r;
+      if (d == n - 1) {
+        q = 0;
+        r = flat;
+      } else {
+        q = flat / size[d];
+        r = flat - q * size[d];
+      }
+      *toff += r * tstride[d];
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) ioff[a] += r * istride[a][d];
+      flat = q;
+    }
+  }
+};
+
+template <int NIN> struct RedParams {
+  const float *in[NIN];
+  void *out;
+  SubSpace<NIN> kept;    // rows/seg: every kept dim; cols: kept dims other than dim 0
+  SubSpace<NIN> red;     // rows/seg: reduced dims other than dim 0; cols: every reduced dim
+  u64 n_kept;            // product of kept.size
+  u64 n_red;             // product of red.size
+  u64 len0;              // length of dim 0 in ITEMS (vectors of VEC elements)
+  u64 tstride0;          // target stride along dim 0 (cols only)
+  u64 istride0[NIN];     // per-ITEM input stride along dim 0 (0 = broadcast)
+  unsigned vec_mask;     // bit a: input a is vector-loaded along dim 0
+  int log_tx;            // threads per row-worker = 1 << log_tx
+  u64 seg_len;           // seg: items per segment of dim 0
+  u64 nsplit0;           // seg: segments per run of dim 0
+  u64 nseg;              // seg: segments per output = nsplit0 * n_red
+  u64 per_chunk;         // seg: segments per chunk; cols: reduced indices per chunk
+  unsigned splits;       // chunks per output (tile); 1 = direct store
+  bool accumulate;
+  float post_div;
+  unsigned int *counters;
+  void *partials;
+};
+
+template <int VEC>
+__device__ __forceinline__ void red_load(const float *p, bool vec, float *v) {
+  if (VEC == 4 && vec) {
+    const float4 t = __ldcs(reinterpret_cast<const float4 *>(p));
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else if (VEC == 2 && vec) {
+    const float2 t = __ldcs(reinterpret_cast<const float2 *>(p));
+    v[0] = t.x; v[1] = t.y;
+  } else {
+    const float s = __ldg(p);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) v[k] = s;
+  }
+}
+
+template <class Op> __device__ __forceinline__ typename Op::T warp_reduce(typename Op::T v, int width) {
+  for (int m = width >> 1; m > 0; m >>= 1) v = Op::combine(v, Op::shfl_xor(v, m, width));
+  return v;
+}
+
+// All kRedThreads threads -> one value, valid in thread 0.
+template <class Op> __device__ __forceinline__ typename Op::T block_reduce(typename Op::T v) {
+  using T = typename Op::T;
+  __shared__ T warp_vals[kRedThreads / 32];
+  v = warp_reduce<Op>(v, 32);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) warp_vals[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    v = lane < kRedThreads / 32 ? warp_vals[lane] : Op::identity();
+    v = warp_reduce<Op>(v, 8);
+  }
+  return v;
+}
+
+constexpr int kRedUnroll = 4;
+
+// Accumulates items [begin, end) of one contiguous run, thread tx of width tx_n.
+// idx_base: flat reduced index of element 0 of the run (argmax only).
+template <class Op, class Pro, int NIN, int VEC>
+__device__ __forceinline__ void accumulate_run(const RedParams<NIN> &p, const Pro &pro,
+                                               const u64 *ioff, u64 begin, u64 end, unsigned tx,
+                                               unsigned tx_n, u64 idx_base, typename Op::T *acc) {
+  u64 i = begin + tx;
+  for (; i + (u64)(kRedUnroll - 1) * tx_n < end; i += (u64)kRedUnroll * tx_n) {
+    float v[kRedUnroll][NIN][VEC];
+#pragma unroll
+    for (int u = 0; u < kRedUnroll; ++u)
+#pragma unroll
+      for (int a = 0; a < NIN; ++a)
+        red_load<VEC>(p.in[a] + ioff[a] + (i + (u64)u * tx_n) * p.istride0[a],
+                      (p.vec_mask >> a) & 1u, v[u][a]);
+#pragma unroll
+    for (int u = 0; u < kRedUnroll; ++u)
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        float x[NIN];
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) x[a] = v[u][a][k];
+        acc[k] = Op::combine(acc[k], Op::lift(pro(x), idx_base + (i + (u64)u * tx_n) * VEC + k));
+      }
+  }
+  for (; i < end; i += tx_n) {
+    float v[NIN][VEC];
+#pragma unroll
+    for (int a = 0; a < NIN; ++a)
+      red_load<VEC>(p.in[a] + ioff[a] + i * p.istride0[a], (p.vec_mask >> a) & 1u, v[a]);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      float x[NIN];
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) x[a] = v[a][k];
+      acc[k] = Op::combine(acc[k], Op::lift(pro(x), idx_base + i * VEC + k));
+    }
+  }
+}
+
+// ---- rows: one (sub)warp per output -----------------------------------------------------------------
+template <class Op, class Pro, int NIN, int VEC>
+__global__ void __launch_bounds__(kRedThreads) reduce_rows_kernel(RedParams<NIN> p, Pro pro) {
+  using T = typename Op::T;
+  const unsigned tx_n = 1u << p.log_tx;
+  const unsigned tx = threadIdx.x & (tx_n - 1), ty = threadIdx.x >> p.log_tx;
+  const unsigned ty_n = kRedThreads >> p.log_tx;
+  for (u64 row = (u64)blockIdx.x * ty_n + ty; row < p.n_kept; row += (u64)gridDim.x * ty_n) {
+    u64 toff = 0, ioff[NIN];
+#pragma unroll
+    for (int a = 0; a < NIN; ++a) ioff[a] = 0;
+    p.kept.offsets(row, &toff, ioff);
+    T acc[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[k] = Op::identity();
+    accumulate_run<Op, Pro, NIN, VEC>(p, pro, ioff, 0, p.len0, tx, tx_n, 0, acc);
+    T r = acc[0];
+#pragma unroll
+    for (int k = 1; k < VEC; ++k) r = Op::combine(r, acc[k]);
+    r = warp_reduce<Op>(r, (int)tx_n);
+    if (tx == 0) Op::store((typename Op::Out *)p.out + toff, r, p.accumulate, p.post_div);
+  }
+}
+
+// Last-arriving CTA of a tile: returns true in every thread of that CTA.
+__device__ __forceinline__ bool take_ticket(unsigned int *counter, unsigned splits) {
+  __shared__ bool is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned t = atomicAdd(counter, 1u);
+    is_last = (t == splits - 1);
+    if (is_last) *counter = 0; // ready for the next launch
+  }
+  __syncthreads();
+  if (is_last) __threadfence();
+  return is_last;
+}
+
+// ---- seg: CTA per (output, chunk of segments) ---------------------------------------------------------
+template <class Op, class Pro, int NIN, int VEC>
+__global__ void __launch_bounds__(kRedThreads) reduce_seg_kernel(RedParams<NIN> p, Pro pro) {
+  using T = typename Op::T;
+  const u64 out_idx = blockIdx.x / p.splits;
+  const unsigned chunk = blockIdx.x % p.splits;
+  const unsigned tx_n = 1u << p.log_tx;
+  const unsigned tx = threadIdx.x & (tx_n - 1), ty = threadIdx.x >> p.log_tx;
+  const unsigned ty_n = kRedThreads >> p.log_tx;
+
+  u64 toff = 0, base[NIN];
+#pragma unroll
+  for (int a = 0; a < NIN; ++a) base[a] = 0;
+  p.kept.offsets(out_idx, &toff, base);
+
+  T acc[VEC];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) acc[k] = Op::identity();
+
+  const u64 seg_begin = (u64)chunk * p.per_chunk;
+  u64 seg_end = seg_begin + p.per_chunk;
+  if (seg_end > p.nseg) seg_end = p.nseg;
+  for (u64 seg = seg_begin + ty; seg < seg_end; seg += ty_n) {
+    const u64 outer = seg / p.nsplit0;
+    const u64 piece = seg - outer * p.nsplit0;
+    u64 ioff[NIN], dummy = 0;
+#pragma unroll
+    for (int a = 0; a < NIN; ++a) ioff[a] = base[a];
+    p.red.offsets(outer, &dummy, ioff);
+    const u64 begin = piece * p.seg_len;
+    u64 end = begin + p.seg_len;
+    if (end > p.len0) end = p.len0;
+    accumulate_run<Op, Pro, NIN, VEC>(p, pro, ioff, begin, end, tx, tx_n, outer * p.len0 * VEC, acc);
+  }
+  T r = acc[0];
+#pragma unroll
+  for (int k = 1; k < VEC; ++k) r = Op::combine(r, acc[k]);
+  r = block_reduce<Op>(r);
+
+  if (p.splits == 1) {
+    if (threadIdx.x == 0) Op::store((typename Op::Out *)p.out + toff, r, p.accumulate, p.post_div);
+    return;
+  }
+  T *partials = (T *)p.partials + out_idx * p.splits;
+  if (threadIdx.x == 0) partials[chunk] = r;
+  if (!take_ticket(p.counters + out_idx, p.splits)) return;
+  // Fixed combine order: chunk 0, 1, 2, ... so the result does not depend on arrival order.
+  T v = Op::identity();
+  if (threadIdx.x < 32) {
+    for (unsigned c = threadIdx.x; c < p.splits; c += 32) v = Op::combine(v, Op::load_cg(partials + c));
+    v = warp_reduce<Op>(v, 32);
+    if (threadIdx.x == 0) Op::store((typename Op::Out *)p.out + toff, v, p.accumulate, p.post_div);
+  }
+}
+
+// ---- cols: CTA per (strip of 32*VEC outputs along dim 0, outer kept index, chunk of reduced) ---------
+template <class Op, class Pro, int NIN, int VEC>
+__global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN> p, Pro pro) {
+  using T = typename Op::T;
+  constexpr int kWarps = kRedThreads / 32;
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const u64 strips = (p.len0 + 31) / 32;
+  const u64 tile = blockIdx.x / p.splits; // (outer kept, strip)
+  const unsigned chunk = blockIdx.x % p.splits;
+  const u64 outer = tile / strips;
+  const u64 strip = tile - outer * strips;
+  const u64 item = strip * 32 + lane;
+  const bool live = item < p.len0;
+
+  u64 toff = 0, base[NIN];
+#pragma unroll
+  for (int a = 0; a < NIN; ++a) base[a] = 0;
+  p.kept.offsets(outer, &toff, base);
+  toff += item * VEC * p.tstride0;
+#pragma unroll
+  for (int a = 0; a < NIN; ++a) base[a] += item * p.istride0[a];
+
+  T acc[VEC];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) acc[k] = Op::identity();
+
+  const u64 r_begin = (u64)chunk * p.per_chunk;
+  u64 r_end = r_begin + p.per_chunk;
+  if (r_end > p.n_red) r_end = p.n_red;
+  if (live) {
+    u64 r = r_begin + warp;
+    for (; r + (u64)(kRedUnroll - 1) * kWarps < r_end; r += (u64)kRedUnroll * kWarps) {
+      float v[kRedUnroll][NIN][VEC];
+#pragma unroll
+      for (int u = 0; u < kRedUnroll; ++u) {
+        u64 ioff[NIN], dummy = 0;
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) ioff[a] = base[a];
+        p.red.offsets(r + (u64)u * kWarps, &dummy, ioff);
+#pragma unroll
+        for (int a = 0; a < NIN; ++a)
+          red_load<VEC>(p.in[a] + ioff[a], (p.vec_mask >> a) & 1u, v[u][a]);
+      }
+#pragma unroll
+      for (int u = 0; u < kRedUnroll; ++u)
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          float x[NIN];
+#pragma unroll
+          for (int a = 0; a < NIN; ++a) x[a] = v[u][a][k];
+          acc[k] = Op::combine(acc[k], Op::lift(pro(x), r + (u64)u * kWarps));
+        }
+    }
+    for (; r < r_end; r += kWarps) {
+      u64 ioff[NIN], dummy = 0;
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) ioff[a] = base[a];
+      p.red.offsets(r, &dummy, ioff);
+      float v[NIN][VEC];
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) red_load<VEC>(p.in[a] + ioff[a], (p.vec_mask >> a) & 1u, v[a]);
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        float x[NIN];
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) x[a] = v[a][k];
+        acc[k] = Op::combine(acc[k], Op::lift(pro(x), r));
+      }
+    }
+  }
+  // Combine the 8 warps' strips in shared memory: warp w holds reduced indices = w (mod 8).
+  __shared__ T strip_vals[kWarps][VEC][32];
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) strip_vals[warp][k][lane] = acc[k];
+  __syncthreads();
+  T r[VEC];
+  if (warp == 0) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      r[k] = strip_vals[0][k][lane];
+#pragma unroll
+      for (int w = 1; w < kWarps; ++w) r[k] = Op::combine(r[k], strip_vals[w][k][lane]);
+    }
+  }
+  typename Op::Out *out = (typename Op::Out *)p.out;
+  if (p.splits == 1) {
+    if (warp == 0 && live) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k)
+        Op::store(out + toff + (u64)k * p.tstride0, r[k], p.accumulate, p.post_div);
+    }
+    return;
+  }
+  T *partials = (T *)p.partials + tile * p.splits * (32 * VEC);
+  if (warp == 0) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) partials[((u64)chunk * VEC + k) * 32 + lane] = r[k];
+  }
+  if (!take_ticket(p.counters + tile, p.splits)) return;
+  if (warp == 0 && live) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      T v = Op::identity();
+      for (unsigned c = 0; c < p.splits; ++c)
+        v = Op::combine(v, Op::load_cg(partials + ((u64)c * VEC + k) * 32 + lane));
+      Op::store(out + toff + (u64)k * p.tstride0, v, p.accumulate, p.post_div);
+    }
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------------------------
+enum RedKind { kRedRows = 0, kRedSeg = 1, kRedCols = 2 };
+
+struct RedChoice {
+  RedKind kind;
+  int vec;
+  u64 grid;
+};
+
+// Fills every field of RedParams that does not depend on NIN-typed pointers; returns false (with
+// the error set) when the plan cannot run. Implemented in reduce.cu.
+struct RedGeometry {
+  RedKind kind;
+  int vec;
+  unsigned vec_mask;
+  int log_tx;
+  u64 len0_items, seg_len, nsplit0, nseg, per_chunk, n_kept, n_red, grid;
+  unsigned splits;
+  int kept_dims[MAX_NDIM], n_kept_dims; // plan dim indices in each sub-space
+  int red_dims[MAX_NDIM], n_red_dims;
+};
+bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int nin,
+                          size_t elem_bytes, bool indexed, RedGeometry *g);
+
+template <class Op, class Pro, int NIN>
+void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *const *ins,
+                   const Pro &pro, const Op &, bool accumulate, float post_div) {
+  if (plan.numel == 0) return;
+  RedGeometry g;
+  const void *ptrs[NIN];
+  for (int a = 0; a < NIN; ++a) ptrs[a] = ins[a];
+  if (!plan_reduce_geometry(plan, ptrs, NIN, sizeof(typename Op::T), Op::kIndexed, &g)) return;
+
+  RedParams<NIN> p;
+  for (int a = 0; a < NIN; ++a) p.in[a] = ins[a];
+  p.out = out;
+  p.kept.n = g.n_kept_dims;
+  p.red.n = g.n_red_dims;
+  for (int d = 0; d < MAX_NDIM; ++d) {
+    const int kd = d < g.n_kept_dims ? g.kept_dims[d] : -1;
+    const int rd = d < g.n_red_dims ? g.red_dims[d] : -1;
+    p.kept.size[d] = kd >= 0 ? plan.size[kd] : 1;
+    p.kept.tstride[d] = kd >= 0 ? plan.stride[0][kd] : 0;
+    p.red.size[d] = rd >= 0 ? plan.size[rd] : 1;
+    p.red.tstride[d] = 0;
+    for (int a = 0; a < NIN; ++a) {
+      p.kept.istride[a][d] = kd >= 0 ? plan.stride[a + 1][kd] : 0;
+      p.red.istride[a][d] = rd >= 0 ? plan.stride[a + 1][rd] : 0;
+    }
+  }
+  p.n_kept = g.n_kept;
+  p.n_red = g.n_red;
+  p.len0 = g.len0_items;
+  p.tstride0 = plan.stride[0][0];
+  for (int a = 0; a < NIN; ++a) p.istride0[a] = plan.stride[a + 1][0] * (u64)g.vec;
+  p.vec_mask = g.vec_mask;
+  p.log_tx = g.log_tx;
+  p.seg_len = g.seg_len;
+  p.nsplit0 = g.nsplit0;
+  p.nseg = g.nseg;
+  p.per_chunk = g.per_chunk;
+  p.splits = g.splits;
+  p.accumulate = accumulate;
+  p.post_div = post_div;
+  p.counters = nullptr;
+  p.partials = nullptr;
+  if (g.splits > 1) {
+    Workspace ws;
+    if (!get_workspace(&ws)) return;
+    p.counters = ws.counters;
+    p.partials = ws.partials;
+  }
+  cudaStream_t s = stream();
+  dim3 grid((unsigned)g.grid), block(kRedThreads);
+#define PB_RED_LAUNCH(KERNEL)                                                                      \
+  do {                                                                                             \
+    if (g.vec == 4) KERNEL<Op, Pro, NIN, 4><<<grid, block, 0, s>>>(p, pro);                        \
+    else if (g.vec == 2) KERNEL<Op, Pro, NIN, 2><<<grid, block, 0, s>>>(p, pro);                   \
+    else KERNEL<Op, Pro, NIN, 1><<<grid, block, 0, s>>>(p, pro);                                   \
+  } while (0)
+  if (g.kind == kRedRows) {
+    PB_RED_LAUNCH(reduce_rows_kernel);
+    note_kernel(g.vec == 4 ? "reduce_rows_vec4" : (g.vec == 2 ? "reduce_rows_vec2" : "reduce_rows_scalar"));
+  } else if (g.kind == kRedSeg) {
+    PB_RED_LAUNCH(reduce_seg_kernel);
+    note_kernel(g.vec == 4 ? "reduce_seg_vec4" : (g.vec == 2 ? "reduce_seg_vec2" : "reduce_seg_scalar"));
+  } else {
+    PB_RED_LAUNCH(reduce_cols_kernel);
+    note_kernel(g.vec == 4 ? "reduce_cols_vec4" : (g.vec == 2 ? "reduce_cols_vec2" : "reduce_cols_scalar"));
+  }
+#undef PB_RED_LAUNCH
+  count_launch();
+}
+
+} // namespace pb

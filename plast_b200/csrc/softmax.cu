@@ -1,0 +1,456 @@
+// Fused softmax / log_softmax / cross_entropy (forward and backward) along one axis.
+//
+// The reference builds these from primitives (plast/nn/functional.py:77-97, 312-333):
+//   softmax      max -> sub -> exp -> sum -> div          5 kernels, ~7 passes over the data
+//   log_softmax  max -> sub -> exp -> sum -> log -> sub   6 kernels
+//   cross_entropy  log_softmax -> one-hot mul -> sum(dim=1) -> neg -> mean
+// Here a row is read from HBM once, kept in registers, and written once. Each intermediate is
+// rounded to fp32 exactly where the primitive chain rounds it (the library is built with
+// -fmad=false), so only the order of the row sum differs from the reference.
+//
+// Two kernels per op:
+//   fast     rows are contiguous along the axis, 16-byte aligned, cols % 4 == 0 and
+//            cols <= 8192: TX threads per row (32..256), up to 8 float4 per thread.
+//   generic  anything else (long rows, strided axis, odd sizes): one CTA per row, an online
+//            running (max, sum) pair in a single read pass, then one more pass to write.
+#include "common.cuh"
+#include "iter.h"
+#include "reduce_engine.cuh"
+
+#include <float.h>
+
+namespace pb {
+
+enum SmMode { kSoftmax = 0, kLogSoftmax = 1, kCrossEntropy = 2 };
+
+constexpr int kSmThreads = 256;
+constexpr int kSmMaxVpt = 8;
+
+struct SmRows {
+  SubSpace<2> outer;  // dims other than the axis: tstride = out, istride[0] = x, istride[1] = 2nd input
+  u64 rows, cols;
+  u64 x_axis_stride, y_axis_stride, z_axis_stride; // element strides along the axis
+};
+
+// Reduction over the TX threads of a row-worker (TX = 1 << log_tx, 32 <= TX <= 256).
+// Every thread of the CTA must call it (it synchronises when TX > 32).
+template <class Op>
+__device__ __forceinline__ float row_reduce(float v, int log_tx, float *smem /* [8] */) {
+  v = warp_reduce<Op>(v, 32);
+  if (log_tx > 5) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wpr = 1 << (log_tx - 5); // warps per row-worker
+    __syncthreads();                   // previous use of smem is over
+    if (lane == 0) smem[warp] = v;
+    __syncthreads();
+    const int first = (warp / wpr) * wpr;
+    v = smem[first];
+    for (int w = 1; w < wpr; ++w) v = Op::combine(v, smem[first + w]);
+  }
+  return v;
+}
+
+// ---- forward, fast path ---------------------------------------------------------------------------
+// CE: `labels` int32 per row, per-CTA partial loss sums go through the ticket scheme.
+template <int MODE, int VPT>
+__global__ void __launch_bounds__(kSmThreads)
+softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const int *__restrict__ labels,
+                    SmRows g, int log_tx, unsigned int *counter, float *partials) {
+  __shared__ float red_smem[kSmThreads / 32];
+  const int tx_n = 1 << log_tx;
+  const int tx = threadIdx.x & (tx_n - 1), ty = threadIdx.x >> log_tx;
+  const int rows_per_cta = kSmThreads >> log_tx;
+  const u64 row = (u64)blockIdx.x * rows_per_cta + ty;
+  const bool live = row < g.rows;
+  const u64 nvec = g.cols >> 2;
+  u64 yoff = 0, ioff[2] = {0, 0};
+  if (live) g.outer.offsets(row, &yoff, ioff);
+  const float4 *xr = reinterpret_cast<const float4 *>(x + ioff[0]);
+
+  float4 v[VPT];
+  float m = -FLT_MAX; // src/kernels/cpu/reduce_ops.c:273
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const u64 j = (u64)tx + (u64)i * tx_n;
+    if (live && j < nvec) {
+      v[i] = __ldcs(xr + j);
+      m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+    }
+  }
+  m = row_reduce<MaxOp>(m, log_tx, red_smem);
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const u64 j = (u64)tx + (u64)i * tx_n;
+    if (live && j < nvec) {
+      // sub, then exp: two separately rounded ops
+      v[i].x = v[i].x - m; v[i].y = v[i].y - m; v[i].z = v[i].z - m; v[i].w = v[i].w - m;
+      if (MODE == kSoftmax) {
+        v[i].x = expf(v[i].x); v[i].y = expf(v[i].y); v[i].z = expf(v[i].z); v[i].w = expf(v[i].w);
+        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+      } else {
+        s += (expf(v[i].x) + expf(v[i].y)) + (expf(v[i].z) + expf(v[i].w));
+      }
+    }
+  }
+  s = row_reduce<SumOp>(s, log_tx, red_smem);
+
+  if (MODE == kCrossEntropy) {
+    // loss_row = -( (x[label] - m) - log(s) ); mean over rows by ticket.
+    float loss = 0.0f;
+    if (live && tx == 0) {
+      const int label = labels[row];
+      if (label >= 0 && (u64)label < g.cols) {
+        const float sh = (x + ioff[0])[label] - m;
+        const float lp = sh - logf(s);
+        loss = -lp;
+      }
+    }
+    float part = block_reduce<SumOp>(loss);
+    if (threadIdx.x == 0) partials[blockIdx.x] = part;
+    if (!take_ticket(counter, gridDim.x)) return;
+    float acc = 0.0f;
+    for (unsigned c = threadIdx.x; c < gridDim.x; c += kSmThreads) acc += __ldcg(partials + c);
+    acc = block_reduce<SumOp>(acc);
+    if (threadIdx.x == 0) y[0] = acc / (float)g.rows; // src/kernels/cpu/reduce_ops.c:13
+    return;
+  }
+
+  float4 *yr = reinterpret_cast<float4 *>(y + yoff);
+  const float lse = (MODE == kLogSoftmax) ? logf(s) : 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const u64 j = (u64)tx + (u64)i * tx_n;
+    if (live && j < nvec) {
+      float4 r;
+      if (MODE == kSoftmax) {
+        r.x = v[i].x / s; r.y = v[i].y / s; r.z = v[i].z / s; r.w = v[i].w / s;
+      } else {
+        r.x = v[i].x - lse; r.y = v[i].y - lse; r.z = v[i].z - lse; r.w = v[i].w - lse;
+      }
+      __stcs(yr + j, r);
+    }
+  }
+}
+
+// ---- forward, generic path: online (max, sum) ---------------------------------------------------------
+struct MaxSum {
+  float m, s;
+};
+__device__ __forceinline__ MaxSum ms_combine(MaxSum a, MaxSum b) {
+  // sum of exp(x - m) re-based onto the larger maximum
+  if (a.m >= b.m) return MaxSum{a.m, a.s + b.s * expf(b.m - a.m)};
+  return MaxSum{b.m, b.s + a.s * expf(a.m - b.m)};
+}
+__device__ __forceinline__ MaxSum ms_block_reduce(MaxSum v) {
+  __shared__ MaxSum sm[kSmThreads / 32];
+  for (int o = 16; o > 0; o >>= 1) {
+    MaxSum t;
+    t.m = __shfl_xor_sync(0xffffffffu, v.m, o);
+    t.s = __shfl_xor_sync(0xffffffffu, v.s, o);
+    v = ms_combine(v, t);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) sm[warp] = v;
+  __syncthreads();
+  v = sm[0];
+  for (int w = 1; w < kSmThreads / 32; ++w) v = ms_combine(v, sm[w]);
+  return v; // valid in every thread
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kSmThreads)
+softmax_generic_kernel(const float *x, float *y, const int *labels, SmRows g, unsigned int *counter,
+                       float *partials) {
+  float cta_loss = 0.0f;
+  for (u64 row = blockIdx.x; row < g.rows; row += gridDim.x) {
+    u64 yoff = 0, ioff[2] = {0, 0};
+    g.outer.offsets(row, &yoff, ioff);
+    const float *xr = x + ioff[0];
+    MaxSum acc{-FLT_MAX, 0.0f};
+    for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
+      const float xv = xr[j * g.x_axis_stride];
+      if (xv > acc.m) {
+        acc.s = acc.s * expf(acc.m - xv) + 1.0f;
+        acc.m = xv;
+      } else {
+        acc.s += expf(xv - acc.m);
+      }
+    }
+    acc = ms_block_reduce(acc);
+    if (MODE == kCrossEntropy) {
+      if (threadIdx.x == 0) {
+        const int label = labels[row];
+        if (label >= 0 && (u64)label < g.cols) {
+          const float sh = xr[(u64)label * g.x_axis_stride] - acc.m;
+          cta_loss += -(sh - logf(acc.s));
+        }
+      }
+      continue;
+    }
+    float *yr = y + yoff;
+    const float lse = (MODE == kLogSoftmax) ? logf(acc.s) : 0.0f;
+    for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
+      const float sh = xr[j * g.x_axis_stride] - acc.m;
+      yr[j * g.y_axis_stride] = (MODE == kSoftmax) ? expf(sh) / acc.s : sh - lse;
+    }
+  }
+  if (MODE == kCrossEntropy) {
+    if (threadIdx.x == 0) partials[blockIdx.x] = cta_loss;
+    if (!take_ticket(counter, gridDim.x)) return;
+    float acc = 0.0f;
+    for (unsigned c = threadIdx.x; c < gridDim.x; c += kSmThreads) acc += __ldcg(partials + c);
+    acc = block_reduce<SumOp>(acc);
+    if (threadIdx.x == 0) y[0] = acc / (float)g.rows;
+  }
+}
+
+// ---- backward ---------------------------------------------------------------------------------------
+// One CTA per row, strided scalar access (rows are re-read from L2 for the second pass).
+//   softmax      dx += y * (dy - sum(dy * y))
+//   log_softmax  dx += dy - exp(y) * sum(dy)
+//   cross_entropy (mean)  dlogits += (softmax(x) - onehot(label)) * dout / rows
+template <int MODE>
+__global__ void __launch_bounds__(kSmThreads)
+softmax_backward_kernel(const float *y_or_x, const float *dy, float *dx, const int *labels, SmRows g) {
+  for (u64 row = blockIdx.x; row < g.rows; row += gridDim.x) {
+    u64 doff = 0, ioff[2] = {0, 0};
+    g.outer.offsets(row, &doff, ioff);
+    const float *a = y_or_x + ioff[0]; // y (softmax / log_softmax) or logits x (cross entropy)
+    float *dxr = dx + doff;
+    if (MODE == kCrossEntropy) {
+      MaxSum acc{-FLT_MAX, 0.0f};
+      for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
+        const float xv = a[j * g.x_axis_stride];
+        if (xv > acc.m) {
+          acc.s = acc.s * expf(acc.m - xv) + 1.0f;
+          acc.m = xv;
+        } else {
+          acc.s += expf(xv - acc.m);
+        }
+      }
+      acc = ms_block_reduce(acc);
+      const float gscale = dy[0] / (float)g.rows;
+      const int label = labels[row];
+      for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
+        const float p = expf(a[j * g.x_axis_stride] - acc.m) / acc.s;
+        const float t = ((u64)label == j) ? 1.0f : 0.0f;
+        dxr[j * g.y_axis_stride] += (p - t) * gscale;
+      }
+      continue;
+    }
+    const float *dyr = dy + ioff[1];
+    float part = 0.0f;
+    for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
+      const float d = dyr[j * g.z_axis_stride];
+      part += (MODE == kSoftmax) ? d * a[j * g.x_axis_stride] : d;
+    }
+    __syncthreads();
+    float tot = block_reduce<SumOp>(part);
+    __shared__ float bcast;
+    if (threadIdx.x == 0) bcast = tot;
+    __syncthreads();
+    tot = bcast;
+    for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
+      const float d = dyr[j * g.z_axis_stride];
+      const float yv = a[j * g.x_axis_stride];
+      const float gr = (MODE == kSoftmax) ? yv * (d - tot) : d - expf(yv) * tot;
+      dxr[j * g.y_axis_stride] += gr;
+    }
+  }
+}
+
+// ---- host ---------------------------------------------------------------------------------------------
+// Describes "rows along `axis`" of tensors that share x's shape. t = tensor written / indexed
+// by tstride (output or dx), x = first input, z = optional second input (dy).
+static bool make_rows(const char *name, const Tensor *x, const Tensor *t, const Tensor *z, u64 axis,
+                      SmRows *g) {
+  if (x->ndim == 0 || axis >= x->ndim) {
+    set_error(PLAST_B200_ERR_SHAPE, "%s: axis %llu out of range for %llu dims", name,
+              (unsigned long long)axis, (unsigned long long)x->ndim);
+    return false;
+  }
+  g->cols = x->shape[axis];
+  g->rows = 1;
+  g->x_axis_stride = x->strides[axis];
+  g->y_axis_stride = t ? t->strides[axis] : 0;
+  g->z_axis_stride = z ? z->strides[axis] : 0;
+  int n = 0;
+  for (u64 d = x->ndim; d-- > 0;) { // innermost first
+    if (d == axis || x->shape[d] == 1) continue;
+    g->outer.size[n] = x->shape[d];
+    g->outer.tstride[n] = t ? t->strides[d] : 0;
+    g->outer.istride[0][n] = x->strides[d];
+    g->outer.istride[1][n] = z ? z->strides[d] : 0;
+    g->rows *= x->shape[d];
+    ++n;
+  }
+  g->outer.n = n;
+  for (int d = n; d < MAX_NDIM; ++d) {
+    g->outer.size[d] = 1;
+    g->outer.tstride[d] = g->outer.istride[0][d] = g->outer.istride[1][d] = 0;
+  }
+  return true;
+}
+
+static bool fast_ok(const SmRows &g, const void *x, const void *y, bool writes_rows) {
+  if (g.cols == 0 || (g.cols & 3) || g.cols > (u64)kSmThreads * 4 * kSmMaxVpt) return false;
+  if (g.x_axis_stride != 1 || ((uintptr_t)x & 15)) return false;
+  if (writes_rows && (g.y_axis_stride != 1 || ((uintptr_t)y & 15))) return false;
+  for (int d = 0; d < g.outer.n; ++d) {
+    if (g.outer.istride[0][d] & 3) return false;
+    if (writes_rows && (g.outer.tstride[d] & 3)) return false;
+  }
+  return true;
+}
+
+template <int MODE>
+static void softmax_family_forward(const char *name, const Tensor **inputs, Tensor *output,
+                                   KernelParams params) {
+  begin_call();
+  if (!inputs || !check_tensor(inputs[0], name) || !check_tensor(output, name)) return;
+  const Tensor *x = inputs[0];
+  if (x->dtype != FLOAT32) {
+    set_error(PLAST_B200_ERR_DTYPE, "%s: unsupported dtype %d", name, (int)x->dtype);
+    return;
+  }
+  const int *labels = nullptr;
+  u64 axis = params.dim;
+  if (MODE == kCrossEntropy) {
+    if (!check_tensor(inputs[1], name)) return;
+    if (inputs[1]->dtype != INT32) {
+      set_error(PLAST_B200_ERR_DTYPE, "%s: labels must be INT32 class indices", name);
+      return;
+    }
+    if (x->ndim != 2 || inputs[1]->ndim != 1 || inputs[1]->shape[0] != x->shape[0] ||
+        inputs[1]->strides[0] != 1) {
+      set_error(PLAST_B200_ERR_SHAPE, "%s: expects logits [N,C] and contiguous labels [N]", name);
+      return;
+    }
+    labels = (const int *)inputs[1]->data;
+    axis = 1; // plast/nn/functional.py:322
+  }
+  SmRows g;
+  if (!make_rows(name, x, MODE == kCrossEntropy ? nullptr : output, nullptr, axis, &g)) return;
+  if (g.rows == 0 || g.cols == 0) return;
+  cudaStream_t s = stream();
+  const bool fast = fast_ok(g, x->data, output->data, MODE != kCrossEntropy);
+  unsigned int *counter = nullptr;
+  float *partials = nullptr;
+  u64 grid;
+  int log_tx = 5, vpt = 1;
+  if (fast) {
+    const u64 nvec = g.cols >> 2;
+    while (((u64)kSmMaxVpt << log_tx) < nvec) ++log_tx; // smallest TX with <= 8 vectors per thread
+    vpt = (int)((nvec + ((u64)1 << log_tx) - 1) >> log_tx);
+    const u64 rows_per_cta = (u64)kSmThreads >> log_tx;
+    grid = (g.rows + rows_per_cta - 1) / rows_per_cta;
+  } else {
+    grid = g.rows;
+    const u64 cap = (u64)sm_count() * 16;
+    if (grid > cap) grid = cap;
+  }
+  if (MODE == kCrossEntropy) {
+    Workspace ws;
+    if (!get_workspace(&ws)) return;
+    if (grid > kPartialFloats / 2) {
+      set_error(PLAST_B200_ERR_LIMIT, "%s: %llu rows exceed the partial-sum scratch", name,
+                (unsigned long long)g.rows);
+      return;
+    }
+    counter = ws.counters;
+    partials = ws.partials;
+  }
+  if (grid > 0x7fffffffull) {
+    set_error(PLAST_B200_ERR_LIMIT, "%s: too many rows", name);
+    return;
+  }
+  float *y = (float *)output->data;
+  const float *xd = (const float *)x->data;
+  if (fast) {
+    int v = 1;
+    while (v < vpt) v <<= 1;
+    switch (v) {
+    case 1: softmax_fast_kernel<MODE, 1><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, counter, partials); break;
+    case 2: softmax_fast_kernel<MODE, 2><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, counter, partials); break;
+    case 4: softmax_fast_kernel<MODE, 4><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, counter, partials); break;
+    default: softmax_fast_kernel<MODE, 8><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, counter, partials); break;
+    }
+    note_kernel(MODE == kSoftmax ? "softmax_fast" : (MODE == kLogSoftmax ? "log_softmax_fast" : "cross_entropy_fast"));
+  } else {
+    softmax_generic_kernel<MODE><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, counter, partials);
+    note_kernel(MODE == kSoftmax ? "softmax_online" : (MODE == kLogSoftmax ? "log_softmax_online" : "cross_entropy_online"));
+  }
+  count_launch();
+  end_call();
+}
+
+template <int MODE>
+static void softmax_family_backward(const char *name, Tensor **inputs, const Tensor *output,
+                                    KernelParams params) {
+  begin_call();
+  if (!inputs || !check_tensor(inputs[0], name) || !check_tensor(output, name)) return;
+  const Tensor *x = inputs[0];
+  if (x->dtype != FLOAT32) {
+    set_error(PLAST_B200_ERR_DTYPE, "%s: unsupported dtype %d", name, (int)x->dtype);
+    return;
+  }
+  if (!x->requires_grad) return;
+  if (!x->grad || !x->grad->data || !output->grad || !output->grad->data) {
+    set_error(PLAST_B200_ERR_NULL, "%s: missing grad tensor", name);
+    return;
+  }
+  SmRows g;
+  const int *labels = nullptr;
+  const float *a = nullptr;
+  if (MODE == kCrossEntropy) {
+    if (!check_tensor(inputs[1], name)) return;
+    if (inputs[1]->dtype != INT32 || x->ndim != 2 || inputs[1]->ndim != 1 ||
+        inputs[1]->shape[0] != x->shape[0] || inputs[1]->strides[0] != 1) {
+      set_error(PLAST_B200_ERR_SHAPE, "%s: expects logits [N,C] and contiguous INT32 labels [N]", name);
+      return;
+    }
+    labels = (const int *)inputs[1]->data;
+    if (!make_rows(name, x, x->grad, nullptr, 1, &g)) return;
+    a = (const float *)x->data;
+  } else {
+    // rows of y (the forward result), dy and dx, all shaped like x
+    if (!make_rows(name, output, x->grad, output->grad, params.dim, &g)) return;
+    a = (const float *)output->data;
+  }
+  if (g.rows == 0 || g.cols == 0) return;
+  u64 grid = g.rows;
+  const u64 cap = (u64)sm_count() * 16;
+  if (grid > cap) grid = cap;
+  softmax_backward_kernel<MODE><<<(unsigned)grid, kSmThreads, 0, stream()>>>(
+      a, (const float *)output->grad->data, (float *)x->grad->data, labels, g);
+  count_launch();
+  note_kernel("softmax_backward");
+  end_call();
+}
+
+} // namespace pb
+
+using namespace pb;
+
+extern "C" {
+void softmax_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params) {
+  softmax_family_forward<kSoftmax>("softmax", inputs, output, params);
+}
+void log_softmax_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params) {
+  softmax_family_forward<kLogSoftmax>("log_softmax", inputs, output, params);
+}
+void cross_entropy_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params) {
+  softmax_family_forward<kCrossEntropy>("cross_entropy", inputs, output, params);
+}
+void softmax_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params) {
+  softmax_family_backward<kSoftmax>("softmax", inputs, output, params);
+}
+void log_softmax_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params) {
+  softmax_family_backward<kLogSoftmax>("log_softmax", inputs, output, params);
+}
+void cross_entropy_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params) {
+  softmax_family_backward<kCrossEntropy>("cross_entropy", inputs, output, params);
+}
+}

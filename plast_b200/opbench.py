@@ -1,0 +1,162 @@
+"""Per-op throughput table for the five benchmark configurations (used by bench.py).
+
+Every row is one entry-point call through the C ABI on device-resident data, timed with CUDA
+events on the launch stream (median of `reps`), reported as effective GB/s = algorithmic bytes
+(each operand read once, each result written once) / time, and as a fraction of the measured
+copy bandwidth and of the 8 TB/s nominal figure. Working sets under 256 MiB have L2 flushed
+(a 512 MiB buffer is overwritten) before every timed launch; larger ones need no flush.
+
+Inputs are synthetic with the shapes and value distributions of the configs, generated on the
+device (the per-op numbers do not depend on the exact values).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+NOMINAL = 8000.0
+
+
+def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2, 3, 4, 5)):
+    gen = torch.Generator(device=dev)
+    flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    rows = []
+
+    def wrap(t, shape=None, strides=None, dtype=pb.FLOAT32):
+        shape = list(t.shape) if shape is None else shape
+        return pb.Tensor.wrap_pointer(t.data_ptr(), shape, strides=strides, dtype=dtype, owner=t)
+
+    def randn(shape, seed, std=1.0):
+        gen.manual_seed(seed)
+        return torch.randn(shape, generator=gen, device=dev, dtype=torch.float32) * std
+
+    def uniform(shape, seed, lo, hi):
+        gen.manual_seed(seed)
+        return torch.rand(shape, generator=gen, device=dev, dtype=torch.float32) * (hi - lo) + lo
+
+    def timeit(cfg, name, fn, nbytes, elems, working_set):
+        flush = working_set < (256 << 20)
+        fn(); pb.check_error()
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        kernel = pb.last_kernel()
+        times = []
+        for _ in range(reps):
+            if flush:
+                flush_buf.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        ms = float(np.median(times))
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        rows.append({"config": cfg, "op": name, "kernel": kernel, "ms": round(ms, 5),
+                     "bytes": int(nbytes), "GBps": round(gbs, 1), "elements_per_s": elems / (ms * 1e-3),
+                     "frac_of_measured": round(gbs / peak_gbs, 4), "frac_of_nominal": round(gbs / NOMINAL, 4),
+                     "l2_flushed": flush})
+
+    F = 4
+    if 1 in configs:
+        M = N = 1024
+        A, b, G = uniform((M, N), 0, -1, 1), uniform((1, N), 1, -1, 1), randn((M, N), 2)
+        AB, Cc, s = torch.empty_like(A), torch.empty_like(A), torch.empty(M, device=dev)
+        gb = torch.zeros((1, N), device=dev)
+        tA, tb, tAB, tC, ts = wrap(A), wrap(b), wrap(AB), wrap(Cc), wrap(s)
+        ws = 3 * M * N * F
+        timeit(1, "add_broadcast", lambda: pb.forward("add", [tA, tb], tAB, check=False), (2 * M * N + N) * F, M * N, ws)
+        timeit(1, "relu", lambda: pb.forward("leaky_relu", [tAB], tC, fval=0.0, check=False), 2 * M * N * F, M * N, ws)
+        timeit(1, "row_sum", lambda: pb.forward("sum", [tC], ts, dim=1, check=False), (M * N + M) * F, M * N, ws)
+        timeit(1, "fused_add_relu", lambda: pb.forward("add_leaky_relu", [tA, tb], tC, fval=0.0, check=False),
+               (2 * M * N + N) * F, M * N, ws)
+        tbg = wrap(b); tbg.c.requires_grad = True
+        gtb = wrap(gb); tbg.grad = gtb; tbg.c.grad = C.pointer(gtb.c)
+        tCg = wrap(Cc); gC = wrap(G); tCg.grad = gC; tCg.c.grad = C.pointer(gC.c)
+        timeit(1, "fused_bwd_grad_b", lambda: pb.backward("add_leaky_relu", [tA, tbg], tCg, fval=0.0, check=False),
+               (2 * M * N + 2 * N) * F, M * N, ws)
+        del A, b, G, AB, Cc, s
+    if 2 in configs:
+        n = 1 << 28
+        x, y, z = randn((n,), 0), randn((n,), 1), torch.empty(n, device=dev)
+        one = torch.ones((), device=dev)
+        tx, ty, tz = wrap(x), wrap(y), wrap(z)
+        tone = wrap(one, shape=[])
+        ws = 3 * n * F
+        for op in ("neg", "exp", "abs"):
+            timeit(2, op, lambda op=op: pb.forward(op, [tx], tz, check=False), 2 * n * F, n, ws)
+        timeit(2, "add_scalar", lambda: pb.forward("add", [tx, tone], tz, check=False), 2 * n * F, n, ws)
+        timeit(2, "rdiv_scalar", lambda: pb.forward("div", [tone, tx], tz, check=False), 2 * n * F, n, ws)
+        timeit(2, "mul", lambda: pb.forward("mul", [tx, ty], tz, check=False), 3 * n * F, n, ws)
+        timeit(2, "add", lambda: pb.forward("add", [tx, ty], tz, check=False), 3 * n * F, n, ws)
+        timeit(2, "sigmoid_fused", lambda: pb.forward("sigmoid", [tx], tz, check=False), 2 * n * F, n, ws)
+        steps = [("neg", 0, 0, 0.0), ("exp", 2, 0, 0.0), ("add_scalar", 3, 0, 1.0), ("rdiv_scalar", 4, 0, 1.0),
+                 ("mul", 5, 1, 0.0), ("abs", 0, 0, 0.0), ("neg", 7, 0, 0.0), ("exp", 8, 0, 0.0), ("add", 6, 9, 0.0)]
+        timeit(2, "fused_chain", lambda: pb.chain_forward([tx, ty], tz, steps, check=False), 3 * n * F, n, ws)
+        # the same chain as nine separate launches (what the reference scheduler issues)
+        t = [torch.empty(n, device=dev) for _ in range(4)]
+        w = [wrap(v) for v in t]
+
+        def unfused():
+            pb.forward("neg", [tx], w[0], check=False); pb.forward("exp", [w[0]], w[0], check=False)
+            pb.forward("add", [w[0], tone], w[0], check=False); pb.forward("div", [tone, w[0]], w[0], check=False)
+            pb.forward("mul", [w[0], ty], w[1], check=False); pb.forward("abs", [tx], w[2], check=False)
+            pb.forward("neg", [w[2]], w[2], check=False); pb.forward("exp", [w[2]], w[2], check=False)
+            pb.forward("add", [w[1], w[2]], tz, check=False)
+        timeit(2, "chain_as_9_launches", unfused, 3 * n * F, n, ws)
+        del x, y, z, t, w
+    if 3 in configs:
+        R, Cn = 65536, 4096
+        X = randn((R, Cn), 0, std=2.0)
+        Y = torch.empty_like(X)
+        out = torch.empty(R, device=dev)
+        outi = torch.empty(R, device=dev, dtype=torch.int32)
+        gen.manual_seed(1)
+        labels = torch.randint(0, Cn, (R,), generator=gen, device=dev, dtype=torch.int32)
+        loss = torch.empty(1, device=dev)
+        tX, tY, tout = wrap(X), wrap(Y), wrap(out)
+        touti, tl, tloss = wrap(outi, dtype=pb.INT32), wrap(labels, dtype=pb.INT32), wrap(loss)
+        ws = 2 * R * Cn * F
+        for op in ("sum", "mean", "max"):
+            timeit(3, f"row_{op}", lambda op=op: pb.forward(op, [tX], tout, dim=1, check=False),
+                   (R * Cn + R) * F, R * Cn, ws)
+        timeit(3, "row_argmax", lambda: pb.forward("argmax", [tX], touti, dim=1, check=False), (R * Cn + R) * F, R * Cn, ws)
+        timeit(3, "softmax", lambda: pb.forward("softmax", [tX], tY, dim=1, check=False), 2 * R * Cn * F, R * Cn, ws)
+        timeit(3, "log_softmax", lambda: pb.forward("log_softmax", [tX], tY, dim=1, check=False), 2 * R * Cn * F, R * Cn, ws)
+        timeit(3, "cross_entropy_mean", lambda: pb.forward("cross_entropy", [tX, tl], tloss, check=False),
+               (R * Cn + R) * F + 4, R * Cn, ws)
+        del X, Y
+    if 4 in configs:
+        M = 8192
+        X = uniform((M, M), 0, -1, 1)
+        out, one = torch.empty(M, device=dev), torch.empty(1, device=dev)
+        tX, tout, tone = wrap(X), wrap(out), wrap(one)
+        tXT = wrap(X, shape=[M, M], strides=[1, M])
+        ws = M * M * F
+        for name, tin in (("", tX), ("_transposed_view", tXT)):
+            timeit(4, "sum_axis0" + name, lambda tin=tin: pb.forward("sum", [tin], tout, dim=0, check=False),
+                   (M * M + M) * F, M * M, ws)
+            timeit(4, "full_sum" + name, lambda tin=tin: pb.forward("sum", [tin], tone, dim=pb.FULL_REDUCE, check=False),
+                   M * M * F + 4, M * M, ws)
+            timeit(4, "full_max" + name, lambda tin=tin: pb.forward("max", [tin], tone, dim=pb.FULL_REDUCE, check=False),
+                   M * M * F + 4, M * M, ws)
+        del X
+    if 5 in configs:
+        shape, pshape = (256, 256, 56, 56), (1, 256, 1, 1)
+        n = int(np.prod(shape))
+        X, G = randn(shape, 0), randn(shape, 3)
+        S, B = uniform(pshape, 1, -.5, .5), uniform(pshape, 2, -.5, .5)
+        Y = torch.empty_like(X)
+        gS, gB = torch.zeros(pshape, device=dev), torch.zeros(pshape, device=dev)
+        tX, tS, tB, tY = wrap(X), wrap(S), wrap(B), wrap(Y)
+        ws = 2 * n * F
+        timeit(5, "scale_bias_relu_fwd", lambda: pb.forward("scale_bias_leaky_relu", [tX, tS, tB], tY, fval=0.0, check=False),
+               2 * n * F + 2048, n, ws)
+        tBg = wrap(B); tBg.c.requires_grad = True
+        g = wrap(gB); tBg.grad = g; tBg.c.grad = C.pointer(g.c)
+        tYg = wrap(Y); gy = wrap(G); tYg.grad = gy; tYg.c.grad = C.pointer(gy.c)
+        timeit(5, "bias_grad_masked_reduce", lambda: pb.backward("scale_bias_leaky_relu", [tX, tS, tBg], tYg, fval=0.0, check=False),
+               2 * n * F + 1024, n, ws)
+        del X, G, Y
+    torch.cuda.synchronize()
+    return rows
