@@ -96,7 +96,7 @@ __device__ __forceinline__ float chain_step(int opcode, float p, float q, float 
   case PLAST_CHAIN_LOG: return logf(p);
   case PLAST_CHAIN_SIN: return sinf(p);
   case PLAST_CHAIN_COS: return cosf(p);
-  case PLAST_CHAIN_TAN: return tanf(p);
+  case PLAST_CHAIN_TAN: return tan_accurate(p);
   case PLAST_CHAIN_LEAKY_RELU: return p > 0.0f ? p : p * f;
   case PLAST_CHAIN_ADD_SCALAR: return p + f;
   case PLAST_CHAIN_RSUB_SCALAR: return f - p;

@@ -35,7 +35,10 @@ struct ExpF { __device__ __forceinline__ float operator()(const float *x) const 
 struct LogF { __device__ __forceinline__ float operator()(const float *x) const { return logf(x[0]); } };
 struct SinF { __device__ __forceinline__ float operator()(const float *x) const { return sinf(x[0]); } };
 struct CosF { __device__ __forceinline__ float operator()(const float *x) const { return cosf(x[0]); } };
-struct TanF { __device__ __forceinline__ float operator()(const float *x) const { return tanf(x[0]); } };
+// CUDA's tanf may be 4 ulp off; the contract is <= 2 ulp of glibc's tanf, so tan is evaluated in
+// double and rounded once (<= 1 ulp of the correctly rounded value).
+__device__ __forceinline__ float tan_accurate(float x) { return (float)tan((double)x); }
+struct TanF { __device__ __forceinline__ float operator()(const float *x) const { return tan_accurate(x[0]); } };
 struct LeakyReluF {
   float alpha;
   __device__ __forceinline__ float operator()(const float *x) const {
@@ -57,7 +60,7 @@ struct SinB { __device__ __forceinline__ float operator()(const float *x) const 
 struct CosB { __device__ __forceinline__ float operator()(const float *x) const { return x[2] + x[0] * (-sinf(x[1])); } };
 struct TanB {
   __device__ __forceinline__ float operator()(const float *x) const {
-    const float t = tanf(x[1]);
+    const float t = tan_accurate(x[1]);
     return x[2] + x[0] * (1.0f + t * t);
   }
 };

@@ -13,7 +13,7 @@ static int log2_ceil(u64 v) {
 }
 
 bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int nin,
-                          size_t elem_bytes, bool indexed, RedGeometry *g) {
+                          size_t elem_bytes, bool indexed, const RedOccupancy &occ, RedGeometry *g) {
   // Vector width along dim 0 (same rule as the elementwise engine, inputs only).
   g->vec = 1;
   g->vec_mask = 0;
@@ -61,7 +61,10 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
     }
   }
   const u64 sms = (u64)sm_count();
-  const u64 target_ctas = sms * 8;
+  // One resident wave: every CTA of a split reduction gets the same share of the work, so more
+  // CTAs than fit at once would only add a second, partly empty wave.
+  const int vi = g->vec == 4 ? 2 : (g->vec == 2 ? 1 : 0);
+  const u64 target_ctas = sms * (u64)occ.ctas_per_sm[dim0_reduced ? kRedSeg : kRedCols][vi];
   g->splits = 1;
   g->seg_len = g->nsplit0 = g->nseg = g->per_chunk = 0;
   g->log_tx = 5;
@@ -84,14 +87,15 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
       return true;
     }
     g->kind = kRedSeg;
-    if (g->len0_items <= 1024) {
+    if (g->len0_items <= (u64)kRedThreads * (nin == 1 ? 8 : 4)) {
       g->nsplit0 = 1;
       g->seg_len = g->len0_items;
       g->log_tx = log2_ceil(g->len0_items);
       if (g->log_tx > 8) g->log_tx = 8;
     } else {
-      g->seg_len = 1024;
-      g->nsplit0 = ceil_div(g->len0_items, 1024);
+      // one trip of the load batch per segment: threads * loads in flight
+      g->seg_len = (u64)kRedThreads * (nin == 1 ? 8 : 4);
+      g->nsplit0 = ceil_div(g->len0_items, g->seg_len);
       g->log_tx = 8;
     }
     g->nseg = g->nsplit0 * g->n_red;

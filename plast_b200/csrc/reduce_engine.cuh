@@ -34,7 +34,7 @@ struct SumOp {
   using Out = float;
   static constexpr bool kIndexed = false;
   __device__ __forceinline__ static T identity() { return 0.0f; }
-  __device__ __forceinline__ static T lift(float v, unsigned long long) { return v; }
+  __device__ __forceinline__ static T step(T acc, float v, unsigned) { return acc + v; }
   __device__ __forceinline__ static T combine(T a, T b) { return a + b; }
   __device__ __forceinline__ static T shfl_xor(T v, int m, int w) {
     return __shfl_xor_sync(0xffffffffu, v, m, w);
@@ -51,7 +51,7 @@ struct MaxOp {
   using Out = float;
   static constexpr bool kIndexed = false;
   __device__ __forceinline__ static T identity() { return -FLT_MAX; }
-  __device__ __forceinline__ static T lift(float v, unsigned long long) { return v; }
+  __device__ __forceinline__ static T step(T acc, float v, unsigned) { return acc > v ? acc : v; }
   __device__ __forceinline__ static T combine(T a, T b) { return a > b ? a : b; }
   __device__ __forceinline__ static T shfl_xor(T v, int m, int w) {
     return __shfl_xor_sync(0xffffffffu, v, m, w);
@@ -64,7 +64,7 @@ struct MinOp {
   using Out = float;
   static constexpr bool kIndexed = false;
   __device__ __forceinline__ static T identity() { return FLT_MAX; }
-  __device__ __forceinline__ static T lift(float v, unsigned long long) { return v; }
+  __device__ __forceinline__ static T step(T acc, float v, unsigned) { return acc < v ? acc : v; }
   __device__ __forceinline__ static T combine(T a, T b) { return a < b ? a : b; }
   __device__ __forceinline__ static T shfl_xor(T v, int m, int w) {
     return __shfl_xor_sync(0xffffffffu, v, m, w);
@@ -81,8 +81,10 @@ struct ArgMaxOp {
   using Out = int;
   static constexpr bool kIndexed = true;
   __device__ __forceinline__ static T identity() { return T{-INFINITY, 0xffffffffu}; }
-  __device__ __forceinline__ static T lift(float v, unsigned long long i) {
-    return T{v, (unsigned int)i};
+  // a thread visits its elements in increasing index order, so only a strictly greater value
+  // replaces the running best
+  __device__ __forceinline__ static T step(T acc, float v, unsigned i) {
+    return (v > acc.v || acc.i == 0xffffffffu) ? T{v, i} : acc;
   }
   __device__ __forceinline__ static T combine(T a, T b) {
     return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
@@ -191,44 +193,45 @@ template <class Op> __device__ __forceinline__ typename Op::T block_reduce(typen
   return v;
 }
 
-constexpr int kRedUnroll = 4;
+// Loads in flight per thread and input: 8 when one tensor is streamed, 4 with a prologue that
+// reads several (registers).
+template <int NIN> struct RedUnroll { static constexpr int value = NIN == 1 ? 8 : 4; };
 
-// Accumulates items [begin, end) of one contiguous run, thread tx of width tx_n.
+// Accumulates items [begin, end) of one contiguous run, thread tx of width tx_n. Each trip issues
+// up to kRedUnroll loads per input before the first use (predicated at the ragged end, so every
+// thread of the row-worker makes the same number of trips).
 // idx_base: flat reduced index of element 0 of the run (argmax only).
 template <class Op, class Pro, int NIN, int VEC>
 __device__ __forceinline__ void accumulate_run(const RedParams<NIN> &p, const Pro &pro,
                                                const u64 *ioff, u64 begin, u64 end, unsigned tx,
-                                               unsigned tx_n, u64 idx_base, typename Op::T *acc) {
-  u64 i = begin + tx;
-  for (; i + (u64)(kRedUnroll - 1) * tx_n < end; i += (u64)kRedUnroll * tx_n) {
+                                               unsigned tx_n, unsigned idx_base, typename Op::T *acc) {
+  const float *base[NIN];
+#pragma unroll
+  for (int a = 0; a < NIN; ++a) base[a] = p.in[a] + ioff[a];
+  constexpr int kRedUnroll = RedUnroll<NIN>::value;
+  for (u64 b = begin + tx; b < end + tx; b += (u64)kRedUnroll * tx_n) {
     float v[kRedUnroll][NIN][VEC];
 #pragma unroll
-    for (int u = 0; u < kRedUnroll; ++u)
+    for (int u = 0; u < kRedUnroll; ++u) {
+      const u64 i = b + (u64)u * tx_n;
+      if (i < end) {
 #pragma unroll
-      for (int a = 0; a < NIN; ++a)
-        red_load<VEC>(p.in[a] + ioff[a] + (i + (u64)u * tx_n) * p.istride0[a],
-                      (p.vec_mask >> a) & 1u, v[u][a]);
-#pragma unroll
-    for (int u = 0; u < kRedUnroll; ++u)
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        float x[NIN];
-#pragma unroll
-        for (int a = 0; a < NIN; ++a) x[a] = v[u][a][k];
-        acc[k] = Op::combine(acc[k], Op::lift(pro(x), idx_base + (i + (u64)u * tx_n) * VEC + k));
+        for (int a = 0; a < NIN; ++a)
+          red_load<VEC>(base[a] + i * p.istride0[a], (p.vec_mask >> a) & 1u, v[u][a]);
       }
-  }
-  for (; i < end; i += tx_n) {
-    float v[NIN][VEC];
+    }
 #pragma unroll
-    for (int a = 0; a < NIN; ++a)
-      red_load<VEC>(p.in[a] + ioff[a] + i * p.istride0[a], (p.vec_mask >> a) & 1u, v[a]);
+    for (int u = 0; u < kRedUnroll; ++u) {
+      const u64 i = b + (u64)u * tx_n;
+      if (i < end) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-      float x[NIN];
+        for (int k = 0; k < VEC; ++k) {
+          float x[NIN];
 #pragma unroll
-      for (int a = 0; a < NIN; ++a) x[a] = v[a][k];
-      acc[k] = Op::combine(acc[k], Op::lift(pro(x), idx_base + i * VEC + k));
+          for (int a = 0; a < NIN; ++a) x[a] = v[u][a][k];
+          acc[k] = Op::step(acc[k], pro(x), idx_base + (unsigned)i * VEC + k);
+        }
+      }
     }
   }
 }
@@ -304,7 +307,8 @@ __global__ void __launch_bounds__(kRedThreads) reduce_seg_kernel(RedParams<NIN> 
     const u64 begin = piece * p.seg_len;
     u64 end = begin + p.seg_len;
     if (end > p.len0) end = p.len0;
-    accumulate_run<Op, Pro, NIN, VEC>(p, pro, ioff, begin, end, tx, tx_n, outer * p.len0 * VEC, acc);
+    accumulate_run<Op, Pro, NIN, VEC>(p, pro, ioff, begin, end, tx, tx_n,
+                                      (unsigned)(outer * p.len0 * VEC), acc);
   }
   T r = acc[0];
 #pragma unroll
@@ -356,6 +360,7 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
   const u64 r_begin = (u64)chunk * p.per_chunk;
   u64 r_end = r_begin + p.per_chunk;
   if (r_end > p.n_red) r_end = p.n_red;
+  constexpr int kRedUnroll = RedUnroll<NIN>::value;
   if (live) {
     u64 r = r_begin + warp;
     for (; r + (u64)(kRedUnroll - 1) * kWarps < r_end; r += (u64)kRedUnroll * kWarps) {
@@ -377,7 +382,7 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
           float x[NIN];
 #pragma unroll
           for (int a = 0; a < NIN; ++a) x[a] = v[u][a][k];
-          acc[k] = Op::combine(acc[k], Op::lift(pro(x), r + (u64)u * kWarps));
+          acc[k] = Op::step(acc[k], pro(x), (unsigned)(r + (u64)u * kWarps));
         }
     }
     for (; r < r_end; r += kWarps) {
@@ -393,7 +398,7 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
         float x[NIN];
 #pragma unroll
         for (int a = 0; a < NIN; ++a) x[a] = v[a][k];
-        acc[k] = Op::combine(acc[k], Op::lift(pro(x), r));
+        acc[k] = Op::step(acc[k], pro(x), (unsigned)r);
       }
     }
   }
@@ -458,8 +463,37 @@ struct RedGeometry {
   int kept_dims[MAX_NDIM], n_kept_dims; // plan dim indices in each sub-space
   int red_dims[MAX_NDIM], n_red_dims;
 };
+// Resident CTAs per SM of each kernel shape ([kind][vec 1,2,4]), from the occupancy calculator.
+struct RedOccupancy {
+  int ctas_per_sm[3][3];
+};
 bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int nin,
-                          size_t elem_bytes, bool indexed, RedGeometry *g);
+                          size_t elem_bytes, bool indexed, const RedOccupancy &occ, RedGeometry *g);
+
+template <class Op, class Pro, int NIN> const RedOccupancy &reduce_occupancy() {
+  static RedOccupancy occ = [] {
+    RedOccupancy o;
+    auto q = [](auto kernel) {
+      int n = 0;
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, kRedThreads, 0) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = 4;
+      }
+      return n;
+    };
+    o.ctas_per_sm[kRedRows][0] = q(reduce_rows_kernel<Op, Pro, NIN, 1>);
+    o.ctas_per_sm[kRedRows][1] = q(reduce_rows_kernel<Op, Pro, NIN, 2>);
+    o.ctas_per_sm[kRedRows][2] = q(reduce_rows_kernel<Op, Pro, NIN, 4>);
+    o.ctas_per_sm[kRedSeg][0] = q(reduce_seg_kernel<Op, Pro, NIN, 1>);
+    o.ctas_per_sm[kRedSeg][1] = q(reduce_seg_kernel<Op, Pro, NIN, 2>);
+    o.ctas_per_sm[kRedSeg][2] = q(reduce_seg_kernel<Op, Pro, NIN, 4>);
+    o.ctas_per_sm[kRedCols][0] = q(reduce_cols_kernel<Op, Pro, NIN, 1>);
+    o.ctas_per_sm[kRedCols][1] = q(reduce_cols_kernel<Op, Pro, NIN, 2>);
+    o.ctas_per_sm[kRedCols][2] = q(reduce_cols_kernel<Op, Pro, NIN, 4>);
+    return o;
+  }();
+  return occ;
+}
 
 template <class Op, class Pro, int NIN>
 void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *const *ins,
@@ -468,7 +502,9 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   RedGeometry g;
   const void *ptrs[NIN];
   for (int a = 0; a < NIN; ++a) ptrs[a] = ins[a];
-  if (!plan_reduce_geometry(plan, ptrs, NIN, sizeof(typename Op::T), Op::kIndexed, &g)) return;
+  if (!plan_reduce_geometry(plan, ptrs, NIN, sizeof(typename Op::T), Op::kIndexed,
+                            reduce_occupancy<Op, Pro, NIN>(), &g))
+    return;
 
   RedParams<NIN> p;
   for (int a = 0; a < NIN; ++a) p.in[a] = ins[a];

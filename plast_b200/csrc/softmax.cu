@@ -55,80 +55,86 @@ __device__ __forceinline__ float row_reduce(float v, int log_tx, float *smem /* 
 template <int MODE, int VPT>
 __global__ void __launch_bounds__(kSmThreads)
 softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const int *__restrict__ labels,
-                    SmRows g, int log_tx, unsigned int *counter, float *partials) {
+                    SmRows g, int log_tx, float *row_loss) {
   __shared__ float red_smem[kSmThreads / 32];
   const int tx_n = 1 << log_tx;
   const int tx = threadIdx.x & (tx_n - 1), ty = threadIdx.x >> log_tx;
   const int rows_per_cta = kSmThreads >> log_tx;
-  const u64 row = (u64)blockIdx.x * rows_per_cta + ty;
-  const bool live = row < g.rows;
   const u64 nvec = g.cols >> 2;
-  u64 yoff = 0, ioff[2] = {0, 0};
-  if (live) g.outer.offsets(row, &yoff, ioff);
-  const float4 *xr = reinterpret_cast<const float4 *>(x + ioff[0]);
+  // Uniform trip count for every thread of the CTA (row_reduce synchronises).
+  for (u64 row0 = (u64)blockIdx.x * rows_per_cta; row0 < g.rows; row0 += (u64)gridDim.x * rows_per_cta) {
+    const u64 row = row0 + ty;
+    const bool live = row < g.rows;
+    u64 yoff = 0, ioff[2] = {0, 0};
+    if (live) g.outer.offsets(row, &yoff, ioff);
+    const float4 *xr = reinterpret_cast<const float4 *>(x + ioff[0]);
 
-  float4 v[VPT];
-  float m = -FLT_MAX; // src/kernels/cpu/reduce_ops.c:273
+    float4 v[VPT];
+    float m = -FLT_MAX; // src/kernels/cpu/reduce_ops.c:273
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const u64 j = (u64)tx + (u64)i * tx_n;
-    if (live && j < nvec) {
-      v[i] = __ldcs(xr + j);
-      m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+    for (int i = 0; i < VPT; ++i) {
+      const u64 j = (u64)tx + (u64)i * tx_n;
+      if (live && j < nvec) v[i] = __ldcs(xr + j);
     }
-  }
-  m = row_reduce<MaxOp>(m, log_tx, red_smem);
-  float s = 0.0f;
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const u64 j = (u64)tx + (u64)i * tx_n;
-    if (live && j < nvec) {
-      // sub, then exp: two separately rounded ops
-      v[i].x = v[i].x - m; v[i].y = v[i].y - m; v[i].z = v[i].z - m; v[i].w = v[i].w - m;
-      if (MODE == kSoftmax) {
-        v[i].x = expf(v[i].x); v[i].y = expf(v[i].y); v[i].z = expf(v[i].z); v[i].w = expf(v[i].w);
-        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-      } else {
-        s += (expf(v[i].x) + expf(v[i].y)) + (expf(v[i].z) + expf(v[i].w));
+    for (int i = 0; i < VPT; ++i) {
+      const u64 j = (u64)tx + (u64)i * tx_n;
+      if (live && j < nvec) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+    }
+    m = row_reduce<MaxOp>(m, log_tx, red_smem);
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const u64 j = (u64)tx + (u64)i * tx_n;
+      if (live && j < nvec) {
+        // sub, then exp: two separately rounded ops
+        v[i].x = v[i].x - m; v[i].y = v[i].y - m; v[i].z = v[i].z - m; v[i].w = v[i].w - m;
+        if (MODE == kSoftmax) {
+          v[i].x = expf(v[i].x); v[i].y = expf(v[i].y); v[i].z = expf(v[i].z); v[i].w = expf(v[i].w);
+          s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        } else {
+          s += (expf(v[i].x) + expf(v[i].y)) + (expf(v[i].z) + expf(v[i].w));
+        }
       }
     }
-  }
-  s = row_reduce<SumOp>(s, log_tx, red_smem);
+    s = row_reduce<SumOp>(s, log_tx, red_smem);
 
-  if (MODE == kCrossEntropy) {
-    // loss_row = -( (x[label] - m) - log(s) ); mean over rows by ticket.
-    float loss = 0.0f;
-    if (live && tx == 0) {
-      const int label = labels[row];
-      if (label >= 0 && (u64)label < g.cols) {
-        const float sh = (x + ioff[0])[label] - m;
-        const float lp = sh - logf(s);
-        loss = -lp;
-      }
-    }
-    float part = block_reduce<SumOp>(loss);
-    if (threadIdx.x == 0) partials[blockIdx.x] = part;
-    if (!take_ticket(counter, gridDim.x)) return;
-    float acc = 0.0f;
-    for (unsigned c = threadIdx.x; c < gridDim.x; c += kSmThreads) acc += __ldcg(partials + c);
-    acc = block_reduce<SumOp>(acc);
-    if (threadIdx.x == 0) y[0] = acc / (float)g.rows; // src/kernels/cpu/reduce_ops.c:13
-    return;
-  }
-
-  float4 *yr = reinterpret_cast<float4 *>(y + yoff);
-  const float lse = (MODE == kLogSoftmax) ? logf(s) : 0.0f;
+    if (MODE == kCrossEntropy) {
+      // loss_row = -((x[label] - m) - log(s)); v[] still holds x - m, so the thread that loaded
+      // the label's vector picks it from its registers (no second trip to memory).
+      if (live) {
+        const int label = labels[row];
+        if (label >= 0 && (u64)label < g.cols) {
+          const u64 jv = (u64)label >> 2;
+          if ((int)(jv & (u64)(tx_n - 1)) == tx) {
+            const int slot = (int)(jv >> log_tx), comp = label & 3;
+            float sh = 0.0f;
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const u64 j = (u64)tx + (u64)i * tx_n;
-    if (live && j < nvec) {
-      float4 r;
-      if (MODE == kSoftmax) {
-        r.x = v[i].x / s; r.y = v[i].y / s; r.z = v[i].z / s; r.w = v[i].w / s;
-      } else {
-        r.x = v[i].x - lse; r.y = v[i].y - lse; r.z = v[i].z - lse; r.w = v[i].w - lse;
+            for (int i = 0; i < VPT; ++i)
+              if (i == slot) sh = comp == 0 ? v[i].x : (comp == 1 ? v[i].y : (comp == 2 ? v[i].z : v[i].w));
+            row_loss[row] = -(sh - logf(s));
+          }
+        } else if (tx == 0) {
+          row_loss[row] = 0.0f; // label outside [0, cols): contributes nothing
+        }
       }
-      __stcs(yr + j, r);
+      continue;
+    }
+
+    float4 *yr = reinterpret_cast<float4 *>(y + yoff);
+    const float lse = (MODE == kLogSoftmax) ? logf(s) : 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const u64 j = (u64)tx + (u64)i * tx_n;
+      if (live && j < nvec) {
+        float4 r;
+        if (MODE == kSoftmax) {
+          r.x = v[i].x / s; r.y = v[i].y / s; r.z = v[i].z / s; r.w = v[i].w / s;
+        } else {
+          r.x = v[i].x - lse; r.y = v[i].y - lse; r.z = v[i].z - lse; r.w = v[i].w - lse;
+        }
+        __stcs(yr + j, r);
+      }
     }
   }
 }
@@ -161,9 +167,7 @@ __device__ __forceinline__ MaxSum ms_block_reduce(MaxSum v) {
 
 template <int MODE>
 __global__ void __launch_bounds__(kSmThreads)
-softmax_generic_kernel(const float *x, float *y, const int *labels, SmRows g, unsigned int *counter,
-                       float *partials) {
-  float cta_loss = 0.0f;
+softmax_generic_kernel(const float *x, float *y, const int *labels, SmRows g, float *row_loss) {
   for (u64 row = blockIdx.x; row < g.rows; row += gridDim.x) {
     u64 yoff = 0, ioff[2] = {0, 0};
     g.outer.offsets(row, &yoff, ioff);
@@ -182,10 +186,12 @@ softmax_generic_kernel(const float *x, float *y, const int *labels, SmRows g, un
     if (MODE == kCrossEntropy) {
       if (threadIdx.x == 0) {
         const int label = labels[row];
+        float loss = 0.0f;
         if (label >= 0 && (u64)label < g.cols) {
           const float sh = xr[(u64)label * g.x_axis_stride] - acc.m;
-          cta_loss += -(sh - logf(acc.s));
+          loss = -(sh - logf(acc.s));
         }
+        row_loss[row] = loss;
       }
       continue;
     }
@@ -195,14 +201,6 @@ softmax_generic_kernel(const float *x, float *y, const int *labels, SmRows g, un
       const float sh = xr[j * g.x_axis_stride] - acc.m;
       yr[j * g.y_axis_stride] = (MODE == kSoftmax) ? expf(sh) / acc.s : sh - lse;
     }
-  }
-  if (MODE == kCrossEntropy) {
-    if (threadIdx.x == 0) partials[blockIdx.x] = cta_loss;
-    if (!take_ticket(counter, gridDim.x)) return;
-    float acc = 0.0f;
-    for (unsigned c = threadIdx.x; c < gridDim.x; c += kSmThreads) acc += __ldcg(partials + c);
-    acc = block_reduce<SumOp>(acc);
-    if (threadIdx.x == 0) y[0] = acc / (float)g.rows;
   }
 }
 
@@ -336,8 +334,6 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
   if (g.rows == 0 || g.cols == 0) return;
   cudaStream_t s = stream();
   const bool fast = fast_ok(g, x->data, output->data, MODE != kCrossEntropy);
-  unsigned int *counter = nullptr;
-  float *partials = nullptr;
   u64 grid;
   int log_tx = 5, vpt = 1;
   if (fast) {
@@ -345,22 +341,23 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
     while (((u64)kSmMaxVpt << log_tx) < nvec) ++log_tx; // smallest TX with <= 8 vectors per thread
     vpt = (int)((nvec + ((u64)1 << log_tx) - 1) >> log_tx);
     const u64 rows_per_cta = (u64)kSmThreads >> log_tx;
-    grid = (g.rows + rows_per_cta - 1) / rows_per_cta;
+    grid = (g.rows + rows_per_cta - 1) / rows_per_cta; // one trip per CTA: many small CTAs balance best
   } else {
     grid = g.rows;
     const u64 cap = (u64)sm_count() * 16;
     if (grid > cap) grid = cap;
   }
+  // cross entropy: per-row losses go to scratch, then one full reduce takes their mean
+  float *row_loss = nullptr;
   if (MODE == kCrossEntropy) {
     Workspace ws;
     if (!get_workspace(&ws)) return;
-    if (grid > kPartialFloats / 2) {
-      set_error(PLAST_B200_ERR_LIMIT, "%s: %llu rows exceed the partial-sum scratch", name,
-                (unsigned long long)g.rows);
+    if (g.rows > kPartialFloats / 2) {
+      set_error(PLAST_B200_ERR_LIMIT, "%s: %llu rows exceed the per-row loss scratch (%llu)", name,
+                (unsigned long long)g.rows, (unsigned long long)(kPartialFloats / 2));
       return;
     }
-    counter = ws.counters;
-    partials = ws.partials;
+    row_loss = ws.partials + kPartialFloats / 2; // second half: never used by split partials
   }
   if (grid > 0x7fffffffull) {
     set_error(PLAST_B200_ERR_LIMIT, "%s: too many rows", name);
@@ -372,17 +369,30 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
     int v = 1;
     while (v < vpt) v <<= 1;
     switch (v) {
-    case 1: softmax_fast_kernel<MODE, 1><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, counter, partials); break;
-    case 2: softmax_fast_kernel<MODE, 2><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, counter, partials); break;
-    case 4: softmax_fast_kernel<MODE, 4><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, counter, partials); break;
-    default: softmax_fast_kernel<MODE, 8><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, counter, partials); break;
+    case 1: softmax_fast_kernel<MODE, 1><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, row_loss); break;
+    case 2: softmax_fast_kernel<MODE, 2><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, row_loss); break;
+    case 4: softmax_fast_kernel<MODE, 4><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, row_loss); break;
+    default: softmax_fast_kernel<MODE, 8><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, row_loss); break;
     }
-    note_kernel(MODE == kSoftmax ? "softmax_fast" : (MODE == kLogSoftmax ? "log_softmax_fast" : "cross_entropy_fast"));
   } else {
-    softmax_generic_kernel<MODE><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, counter, partials);
-    note_kernel(MODE == kSoftmax ? "softmax_online" : (MODE == kLogSoftmax ? "log_softmax_online" : "cross_entropy_online"));
+    softmax_generic_kernel<MODE><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, row_loss);
   }
   count_launch();
+  if (MODE == kCrossEntropy) {
+    // mean = sum(loss) / rows (plast/nn/functional.py:391-396, src/kernels/cpu/reduce_ops.c:13)
+    const u64 shape[1] = {g.rows};
+    u64 st[2][MAX_NDIM] = {};
+    st[1][0] = 1;
+    const bool red[1] = {true};
+    IterPlan plan;
+    make_plan(&plan, shape, 1, 2, st, red, 1);
+    plan.reduced[0] = true;
+    const float *ins[1] = {row_loss};
+    launch_reduce<SumOp, IdentityPro, 1>(plan, y, ins, IdentityPro{}, SumOp{}, false, (float)g.rows);
+  }
+  if (!failed())
+    note_kernel(fast ? (MODE == kSoftmax ? "softmax_fast" : (MODE == kLogSoftmax ? "log_softmax_fast" : "cross_entropy_fast"))
+                     : (MODE == kSoftmax ? "softmax_online" : (MODE == kLogSoftmax ? "log_softmax_online" : "cross_entropy_online")));
   end_call();
 }
 

@@ -42,14 +42,21 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
             fn()
         torch.cuda.synchronize()
         kernel = pb.last_kernel()
+        # Working sets beyond L2 are timed as `inner` back-to-back launches per event pair, so the
+        # few microseconds between an event and a launch are not billed to a 40 us kernel; small
+        # working sets need the flush before every launch and are timed one launch at a time.
+        inner = 1 if flush else 5
         times = []
         for _ in range(reps):
             if flush:
                 flush_buf.zero_()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(); fn(); e1.record()
+            e0.record()
+            for _ in range(inner):
+                fn()
+            e1.record()
             torch.cuda.synchronize()
-            times.append(e0.elapsed_time(e1))
+            times.append(e0.elapsed_time(e1) / inner)
         ms = float(np.median(times))
         gbs = nbytes / (ms * 1e-3) / 1e9
         rows.append({"config": cfg, "op": name, "kernel": kernel, "ms": round(ms, 5),

@@ -156,6 +156,8 @@ def assert_bit_equal(got, want, what=""):
     got, want = np.asarray(got), np.asarray(want)
     assert got.shape == want.shape, f"{what}: shape {got.shape} vs {want.shape}"
     bad = bits(got) != bits(want)
+    if got.dtype.kind == "f":
+        bad &= ~(np.isnan(got) & np.isnan(want))  # NaN payload / sign is not part of the contract
     if bad.any():
         i = np.argwhere(bad)[0]
         raise AssertionError(f"{what}: {bad.sum()} of {bad.size} elements differ bitwise; first at "

@@ -252,7 +252,8 @@ def test_sigmoid_and_chain(cuda, recipes):
     X, Y = rand_normal(0, (n,)), rand_normal(1, (n,))
     out = cuda.empty((n,))
     cuda.forward("sigmoid", [cuda.tensor(X)], out)
-    assert_ulp(out.numpy(), recipes.sigmoid(X), 2, "sigmoid")
+    # exp is <= 2 ulp off glibc's; the +1 and the reciprocal each round once more
+    assert_ulp(out.numpy(), recipes.sigmoid(X), 4, "sigmoid")
     import plast_b200 as pb
     steps = [("neg", 0, 0, 0), ("exp", 2, 0, 0), ("add_scalar", 3, 0, 1.0), ("rdiv_scalar", 4, 0, 1.0),
              ("mul", 5, 1, 0), ("abs", 0, 0, 0), ("neg", 7, 0, 0), ("exp", 8, 0, 0), ("add", 6, 9, 0)]
@@ -260,7 +261,11 @@ def test_sigmoid_and_chain(cuda, recipes):
     pb.chain_forward([cuda.tensor(X), cuda.tensor(Y)], z, steps)
     assert pb.last_kernel() == "chain_precompiled"
     want = recipes.chain(X, Y)
-    assert_ulp(z.numpy(), want, 4, "fused chain")       # two exps, each <= 2 ulp, then an add
+    # z = t + e2 can cancel, so the bound is in ulps of the terms: each exp is <= 2 ulp off the
+    # oracle's, which moves t and e2 by <= ~3 ulp each
+    x64, y64 = X.astype(np.float64), Y.astype(np.float64)
+    terms = np.abs(y64) / (1 + np.exp(-x64)) + np.exp(-np.abs(x64))
+    assert (np.abs(z.numpy().astype(np.float64) - want) <= 4 * 2.0 ** -23 * terms).all(), "fused chain"
     # the same program with one step changed takes the interpreter and must agree with it
     steps2 = steps[:-1] + [("sub", 6, 9, 0)]
     z2 = cuda.empty((n,))
