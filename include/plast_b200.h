@@ -266,6 +266,14 @@ const char *plast_b200_last_kernel(void);
 /* Frees the per-device scratch the reductions keep between calls. */
 void plast_b200_release_workspace(void);
 const char *plast_b200_version(void);
+/* Test hook: runs the host-side iteration planner (drop size-1 dims, order by the strides of
+ * argument `sort_arg`, merge dims every argument walks as one run) on caller-supplied metadata.
+ * strides / out_strides are [nargs][MAX_NDIM] row-major, outermost dim first on input; the
+ * result lists the innermost dim first. Returns the planned ndim, or -1 on bad arguments.
+ * Needs no GPU. */
+int plast_b200_plan_debug(const u64 *shape, u64 ndim, int nargs, const u64 *strides,
+                          const unsigned char *reduced, int sort_arg, u64 *out_size,
+                          u64 *out_strides, unsigned char *out_reduced);
 
 #ifdef __cplusplus
 }

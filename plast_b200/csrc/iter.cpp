@@ -120,3 +120,26 @@ bool is_dense(const IterPlan *plan, int a) {
 }
 
 } // namespace pb
+
+// Test hook (declared in include/plast_b200.h): runs the planner on caller-supplied metadata.
+extern "C" int plast_b200_plan_debug(const u64 *shape, u64 ndim, int nargs, const u64 *strides,
+                                     const unsigned char *reduced, int sort_arg, u64 *out_size,
+                                     u64 *out_strides, unsigned char *out_reduced) {
+  if (!shape || !strides || !out_size || !out_strides || ndim > MAX_NDIM || nargs < 1 ||
+      nargs > pb::kMaxArgs || sort_arg < 0 || sort_arg >= nargs)
+    return -1;
+  u64 st[pb::kMaxArgs][MAX_NDIM] = {};
+  bool red[MAX_NDIM] = {};
+  for (int a = 0; a < nargs; ++a)
+    for (u64 d = 0; d < ndim; ++d) st[a][d] = strides[(u64)a * MAX_NDIM + d];
+  if (reduced)
+    for (u64 d = 0; d < ndim; ++d) red[d] = reduced[d] != 0;
+  pb::IterPlan plan;
+  pb::make_plan(&plan, shape, ndim, nargs, st, reduced ? red : nullptr, sort_arg);
+  for (int d = 0; d < MAX_NDIM; ++d) {
+    out_size[d] = plan.size[d];
+    if (out_reduced) out_reduced[d] = plan.reduced[d] ? 1 : 0;
+    for (int a = 0; a < nargs; ++a) out_strides[(u64)a * MAX_NDIM + d] = plan.stride[a][d];
+  }
+  return plan.ndim;
+}

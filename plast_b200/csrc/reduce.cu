@@ -119,12 +119,19 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
       return false;
     }
     g->kind = kRedCols;
-    const u64 strips = ceil_div(g->len0_items, 32);
+    // strip width: as many lanes across dim 0 as it has items (32 .. 256)
+    g->log_tx = log2_ceil(g->len0_items);
+    if (g->log_tx < 5) g->log_tx = 5;
+    if (g->log_tx > 8) g->log_tx = 8;
+    const u64 tx_n = (u64)1 << g->log_tx, ty_n = (u64)kRedThreads >> g->log_tx;
+    const u64 strips = ceil_div(g->len0_items, tx_n);
     const u64 tiles = g->n_kept * strips;
     u64 splits = ceil_div(target_ctas, tiles);
-    const u64 max_splits = g->n_red / 64 > 0 ? g->n_red / 64 : 1;
+    // every row-worker of a chunk should get at least two full load batches
+    const u64 min_per = ty_n * (nin == 1 ? 8 : 4) * 2;
+    const u64 max_splits = g->n_red / min_per > 0 ? g->n_red / min_per : 1;
     if (splits > max_splits) splits = max_splits;
-    if (splits > 1 && (tiles > kCounters || tiles * splits * 32 * vec * elem_bytes >
+    if (splits > 1 && (tiles > kCounters || tiles * splits * tx_n * vec * elem_bytes >
                                                 kPartialFloats / 2 * sizeof(float)))
       splits = 1;
     g->per_chunk = ceil_div(g->n_red, splits);

@@ -206,8 +206,12 @@ __device__ __forceinline__ void accumulate_run(const RedParams<NIN> &p, const Pr
                                                const u64 *ioff, u64 begin, u64 end, unsigned tx,
                                                unsigned tx_n, unsigned idx_base, typename Op::T *acc) {
   const float *base[NIN];
+  float fixed[NIN]; // inputs that broadcast along the run (per-channel scale / bias): read once
 #pragma unroll
-  for (int a = 0; a < NIN; ++a) base[a] = p.in[a] + ioff[a];
+  for (int a = 0; a < NIN; ++a) {
+    base[a] = p.in[a] + ioff[a];
+    fixed[a] = p.istride0[a] == 0 ? __ldg(base[a]) : 0.0f;
+  }
   constexpr int kRedUnroll = RedUnroll<NIN>::value;
   for (u64 b = begin + tx; b < end + tx; b += (u64)kRedUnroll * tx_n) {
     float v[kRedUnroll][NIN][VEC];
@@ -217,7 +221,8 @@ __device__ __forceinline__ void accumulate_run(const RedParams<NIN> &p, const Pr
       if (i < end) {
 #pragma unroll
         for (int a = 0; a < NIN; ++a)
-          red_load<VEC>(base[a] + i * p.istride0[a], (p.vec_mask >> a) & 1u, v[u][a]);
+          if (p.istride0[a] != 0)
+            red_load<VEC>(base[a] + i * p.istride0[a], (p.vec_mask >> a) & 1u, v[u][a]);
       }
     }
 #pragma unroll
@@ -228,7 +233,7 @@ __device__ __forceinline__ void accumulate_run(const RedParams<NIN> &p, const Pr
         for (int k = 0; k < VEC; ++k) {
           float x[NIN];
 #pragma unroll
-          for (int a = 0; a < NIN; ++a) x[a] = v[u][a][k];
+          for (int a = 0; a < NIN; ++a) x[a] = p.istride0[a] != 0 ? v[u][a][k] : fixed[a];
           acc[k] = Op::step(acc[k], pro(x), idx_base + (unsigned)i * VEC + k);
         }
       }
@@ -298,8 +303,19 @@ __global__ void __launch_bounds__(kRedThreads) reduce_seg_kernel(RedParams<NIN> 
   u64 seg_end = seg_begin + p.per_chunk;
   if (seg_end > p.nseg) seg_end = p.nseg;
   for (u64 seg = seg_begin + ty; seg < seg_end; seg += ty_n) {
-    const u64 outer = seg / p.nsplit0;
-    const u64 piece = seg - outer * p.nsplit0;
+    // The two common shapes need no 64-bit division: one run cut into pieces (a full reduce),
+    // or whole runs as segments (N,H,W of a channel gradient).
+    u64 outer, piece;
+    if (p.n_red == 1) {
+      outer = 0;
+      piece = seg;
+    } else if (p.nsplit0 == 1) {
+      outer = seg;
+      piece = 0;
+    } else {
+      outer = seg / p.nsplit0;
+      piece = seg - outer * p.nsplit0;
+    }
     u64 ioff[NIN], dummy = 0;
 #pragma unroll
     for (int a = 0; a < NIN; ++a) ioff[a] = base[a];
@@ -335,14 +351,18 @@ __global__ void __launch_bounds__(kRedThreads) reduce_seg_kernel(RedParams<NIN> 
 template <class Op, class Pro, int NIN, int VEC>
 __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN> p, Pro pro) {
   using T = typename Op::T;
-  constexpr int kWarps = kRedThreads / 32;
-  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const u64 strips = (p.len0 + 31) / 32;
+  // tx_n lanes across dim 0 (a strip of tx_n * VEC outputs, one coalesced run per reduced index),
+  // ty_n row-workers striding over the reduced indices. Wide strips (up to 256 lanes = 4 KiB per
+  // row) keep every DRAM page access long; narrow ones serve small dim 0.
+  const unsigned tx_n = 1u << p.log_tx;
+  const unsigned lane = threadIdx.x & (tx_n - 1), ty = threadIdx.x >> p.log_tx;
+  const unsigned ty_n = kRedThreads >> p.log_tx;
+  const u64 strips = (p.len0 + tx_n - 1) >> p.log_tx;
   const u64 tile = blockIdx.x / p.splits; // (outer kept, strip)
   const unsigned chunk = blockIdx.x % p.splits;
   const u64 outer = tile / strips;
   const u64 strip = tile - outer * strips;
-  const u64 item = strip * 32 + lane;
+  const u64 item = (strip << p.log_tx) + lane;
   const bool live = item < p.len0;
 
   u64 toff = 0, base[NIN];
@@ -362,81 +382,76 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
   if (r_end > p.n_red) r_end = p.n_red;
   constexpr int kRedUnroll = RedUnroll<NIN>::value;
   if (live) {
-    u64 r = r_begin + warp;
-    for (; r + (u64)(kRedUnroll - 1) * kWarps < r_end; r += (u64)kRedUnroll * kWarps) {
+    for (u64 rb = r_begin + ty; rb < r_end; rb += (u64)kRedUnroll * ty_n) {
       float v[kRedUnroll][NIN][VEC];
 #pragma unroll
       for (int u = 0; u < kRedUnroll; ++u) {
-        u64 ioff[NIN], dummy = 0;
+        const u64 r = rb + (u64)u * ty_n;
+        if (r < r_end) {
+          u64 ioff[NIN], dummy = 0;
 #pragma unroll
-        for (int a = 0; a < NIN; ++a) ioff[a] = base[a];
-        p.red.offsets(r + (u64)u * kWarps, &dummy, ioff);
+          for (int a = 0; a < NIN; ++a) ioff[a] = base[a];
+          p.red.offsets(r, &dummy, ioff);
 #pragma unroll
-        for (int a = 0; a < NIN; ++a)
-          red_load<VEC>(p.in[a] + ioff[a], (p.vec_mask >> a) & 1u, v[u][a]);
+          for (int a = 0; a < NIN; ++a)
+            red_load<VEC>(p.in[a] + ioff[a], (p.vec_mask >> a) & 1u, v[u][a]);
+        }
       }
 #pragma unroll
-      for (int u = 0; u < kRedUnroll; ++u)
+      for (int u = 0; u < kRedUnroll; ++u) {
+        const u64 r = rb + (u64)u * ty_n;
+        if (r < r_end) {
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) {
-          float x[NIN];
+          for (int k = 0; k < VEC; ++k) {
+            float x[NIN];
 #pragma unroll
-          for (int a = 0; a < NIN; ++a) x[a] = v[u][a][k];
-          acc[k] = Op::step(acc[k], pro(x), (unsigned)(r + (u64)u * kWarps));
+            for (int a = 0; a < NIN; ++a) x[a] = v[u][a][k];
+            acc[k] = Op::step(acc[k], pro(x), (unsigned)r);
+          }
         }
-    }
-    for (; r < r_end; r += kWarps) {
-      u64 ioff[NIN], dummy = 0;
-#pragma unroll
-      for (int a = 0; a < NIN; ++a) ioff[a] = base[a];
-      p.red.offsets(r, &dummy, ioff);
-      float v[NIN][VEC];
-#pragma unroll
-      for (int a = 0; a < NIN; ++a) red_load<VEC>(p.in[a] + ioff[a], (p.vec_mask >> a) & 1u, v[a]);
-#pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        float x[NIN];
-#pragma unroll
-        for (int a = 0; a < NIN; ++a) x[a] = v[a][k];
-        acc[k] = Op::step(acc[k], pro(x), (unsigned)r);
       }
     }
   }
-  // Combine the 8 warps' strips in shared memory: warp w holds reduced indices = w (mod 8).
-  __shared__ T strip_vals[kWarps][VEC][32];
-#pragma unroll
-  for (int k = 0; k < VEC; ++k) strip_vals[warp][k][lane] = acc[k];
-  __syncthreads();
+  // Combine the row-workers in shared memory: worker t holds reduced indices = t (mod ty_n).
+  __shared__ T strip_vals[kRedThreads * VEC];
   T r[VEC];
-  if (warp == 0) {
+  if (ty_n > 1) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-      r[k] = strip_vals[0][k][lane];
+    for (int k = 0; k < VEC; ++k) strip_vals[((ty * VEC + k) << p.log_tx) + lane] = acc[k];
+    __syncthreads();
+    if (ty == 0) {
 #pragma unroll
-      for (int w = 1; w < kWarps; ++w) r[k] = Op::combine(r[k], strip_vals[w][k][lane]);
+      for (int k = 0; k < VEC; ++k) {
+        r[k] = strip_vals[(k << p.log_tx) + lane];
+        for (unsigned t = 1; t < ty_n; ++t)
+          r[k] = Op::combine(r[k], strip_vals[((t * VEC + k) << p.log_tx) + lane]);
+      }
     }
+  } else {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) r[k] = acc[k];
   }
   typename Op::Out *out = (typename Op::Out *)p.out;
   if (p.splits == 1) {
-    if (warp == 0 && live) {
+    if (ty == 0 && live) {
 #pragma unroll
       for (int k = 0; k < VEC; ++k)
         Op::store(out + toff + (u64)k * p.tstride0, r[k], p.accumulate, p.post_div);
     }
     return;
   }
-  T *partials = (T *)p.partials + tile * p.splits * (32 * VEC);
-  if (warp == 0) {
+  T *partials = (T *)p.partials + tile * p.splits * ((u64)VEC << p.log_tx);
+  if (ty == 0) {
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) partials[((u64)chunk * VEC + k) * 32 + lane] = r[k];
+    for (int k = 0; k < VEC; ++k) partials[(((u64)chunk * VEC + k) << p.log_tx) + lane] = r[k];
   }
   if (!take_ticket(p.counters + tile, p.splits)) return;
-  if (warp == 0 && live) {
+  if (ty == 0 && live) {
 #pragma unroll
     for (int k = 0; k < VEC; ++k) {
       T v = Op::identity();
       for (unsigned c = 0; c < p.splits; ++c)
-        v = Op::combine(v, Op::load_cg(partials + ((u64)c * VEC + k) * 32 + lane));
+        v = Op::combine(v, Op::load_cg(partials + (((u64)c * VEC + k) << p.log_tx) + lane));
       Op::store(out + toff + (u64)k * p.tstride0, v, p.accumulate, p.post_div);
     }
   }

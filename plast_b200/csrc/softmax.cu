@@ -53,7 +53,7 @@ __device__ __forceinline__ float row_reduce(float v, int log_tx, float *smem /* 
 // ---- forward, fast path ---------------------------------------------------------------------------
 // CE: `labels` int32 per row, per-CTA partial loss sums go through the ticket scheme.
 template <int MODE, int VPT>
-__global__ void __launch_bounds__(kSmThreads)
+__global__ void __launch_bounds__(kSmThreads, 4)
 softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const int *__restrict__ labels,
                     SmRows g, int log_tx, float *row_loss) {
   __shared__ float red_smem[kSmThreads / 32];
@@ -61,9 +61,9 @@ softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const in
   const int tx = threadIdx.x & (tx_n - 1), ty = threadIdx.x >> log_tx;
   const int rows_per_cta = kSmThreads >> log_tx;
   const u64 nvec = g.cols >> 2;
-  // Uniform trip count for every thread of the CTA (row_reduce synchronises).
-  for (u64 row0 = (u64)blockIdx.x * rows_per_cta; row0 < g.rows; row0 += (u64)gridDim.x * rows_per_cta) {
-    const u64 row = row0 + ty;
+  // Every thread of the CTA reaches both row_reduce calls (they synchronise when TX > 32).
+  { // one group of rows per CTA (the grid covers every row)
+    const u64 row = (u64)blockIdx.x * rows_per_cta + ty;
     const bool live = row < g.rows;
     u64 yoff = 0, ioff[2] = {0, 0};
     if (live) g.outer.offsets(row, &yoff, ioff);
@@ -118,7 +118,7 @@ softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const in
           row_loss[row] = 0.0f; // label outside [0, cols): contributes nothing
         }
       }
-      continue;
+      return;
     }
 
     float4 *yr = reinterpret_cast<float4 *>(y + yoff);
