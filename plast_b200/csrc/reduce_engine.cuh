@@ -205,36 +205,50 @@ template <class Op, class Pro, int NIN, int VEC>
 __device__ __forceinline__ void accumulate_run(const RedParams<NIN> &p, const Pro &pro,
                                                const u64 *ioff, u64 begin, u64 end, unsigned tx,
                                                unsigned tx_n, unsigned idx_base, typename Op::T *acc) {
+  // Pointers to item `begin` of the run; inside the run a 32-bit item index suffices (the host
+  // never plans runs of 2^31 items or more). With VEC > 1 an input is either vector-loaded
+  // (consecutive items are consecutive vectors) or constant along the run.
   const float *base[NIN];
   float fixed[NIN]; // inputs that broadcast along the run (per-channel scale / bias): read once
 #pragma unroll
   for (int a = 0; a < NIN; ++a) {
-    base[a] = p.in[a] + ioff[a];
+    base[a] = p.in[a] + ioff[a] + begin * p.istride0[a];
     fixed[a] = p.istride0[a] == 0 ? __ldg(base[a]) : 0.0f;
   }
+  const unsigned n = (unsigned)(end - begin);
+  idx_base += (unsigned)begin * VEC;
   constexpr int kRedUnroll = RedUnroll<NIN>::value;
-  for (u64 b = begin + tx; b < end + tx; b += (u64)kRedUnroll * tx_n) {
+  for (unsigned b = tx; b < n + tx; b += kRedUnroll * tx_n) {
     float v[kRedUnroll][NIN][VEC];
 #pragma unroll
     for (int u = 0; u < kRedUnroll; ++u) {
-      const u64 i = b + (u64)u * tx_n;
-      if (i < end) {
+      const unsigned i = b + u * tx_n;
+      if (i < n) {
 #pragma unroll
-        for (int a = 0; a < NIN; ++a)
-          if (p.istride0[a] != 0)
-            red_load<VEC>(base[a] + i * p.istride0[a], (p.vec_mask >> a) & 1u, v[u][a]);
+        for (int a = 0; a < NIN; ++a) {
+          if (p.istride0[a] == 0) continue;
+          if (VEC == 4) {
+            const float4 t = __ldcs(reinterpret_cast<const float4 *>(base[a]) + i);
+            v[u][a][0] = t.x; v[u][a][1] = t.y; v[u][a][2] = t.z; v[u][a][3] = t.w;
+          } else if (VEC == 2) {
+            const float2 t = __ldcs(reinterpret_cast<const float2 *>(base[a]) + i);
+            v[u][a][0] = t.x; v[u][a][1] = t.y;
+          } else {
+            v[u][a][0] = __ldg(base[a] + (u64)i * p.istride0[a]);
+          }
+        }
       }
     }
 #pragma unroll
     for (int u = 0; u < kRedUnroll; ++u) {
-      const u64 i = b + (u64)u * tx_n;
-      if (i < end) {
+      const unsigned i = b + u * tx_n;
+      if (i < n) {
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
           float x[NIN];
 #pragma unroll
           for (int a = 0; a < NIN; ++a) x[a] = p.istride0[a] != 0 ? v[u][a][k] : fixed[a];
-          acc[k] = Op::step(acc[k], pro(x), idx_base + (unsigned)i * VEC + k);
+          acc[k] = Op::step(acc[k], pro(x), idx_base + i * VEC + k);
         }
       }
     }
@@ -381,17 +395,54 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
   u64 r_end = r_begin + p.per_chunk;
   if (r_end > p.n_red) r_end = p.n_red;
   constexpr int kRedUnroll = RedUnroll<NIN>::value;
-  if (live) {
-    for (u64 rb = r_begin + ty; rb < r_end; rb += (u64)kRedUnroll * ty_n) {
+  const unsigned n = (unsigned)(r_end - r_begin); // the host keeps a chunk below 2^31 indices
+  if (live && p.red.n <= 1) {
+    // One reduced dim (the usual case): walk it with pointer increments, no index decoding.
+    const float *ptr[NIN];
+    u64 step[NIN];
+#pragma unroll
+    for (int a = 0; a < NIN; ++a) {
+      const u64 rs = p.red.n == 1 ? p.red.istride[a][0] : 0;
+      ptr[a] = p.in[a] + base[a] + (r_begin + ty) * rs;
+      step[a] = (u64)ty_n * rs;
+    }
+    for (unsigned rb = ty; rb < n + ty; rb += kRedUnroll * ty_n) {
       float v[kRedUnroll][NIN][VEC];
 #pragma unroll
       for (int u = 0; u < kRedUnroll; ++u) {
-        const u64 r = rb + (u64)u * ty_n;
-        if (r < r_end) {
+        if (rb + u * ty_n < n) {
+#pragma unroll
+          for (int a = 0; a < NIN; ++a)
+            red_load<VEC>(ptr[a] + (u64)u * step[a], (p.vec_mask >> a) & 1u, v[u][a]);
+        }
+      }
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) ptr[a] += (u64)kRedUnroll * step[a];
+#pragma unroll
+      for (int u = 0; u < kRedUnroll; ++u) {
+        const unsigned r = rb + u * ty_n;
+        if (r < n) {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) {
+            float x[NIN];
+#pragma unroll
+            for (int a = 0; a < NIN; ++a) x[a] = v[u][a][k];
+            acc[k] = Op::step(acc[k], pro(x), (unsigned)r_begin + r);
+          }
+        }
+      }
+    }
+  } else if (live) {
+    for (unsigned rb = ty; rb < n + ty; rb += kRedUnroll * ty_n) {
+      float v[kRedUnroll][NIN][VEC];
+#pragma unroll
+      for (int u = 0; u < kRedUnroll; ++u) {
+        const unsigned r = rb + u * ty_n;
+        if (r < n) {
           u64 ioff[NIN], dummy = 0;
 #pragma unroll
           for (int a = 0; a < NIN; ++a) ioff[a] = base[a];
-          p.red.offsets(r, &dummy, ioff);
+          p.red.offsets(r_begin + r, &dummy, ioff);
 #pragma unroll
           for (int a = 0; a < NIN; ++a)
             red_load<VEC>(p.in[a] + ioff[a], (p.vec_mask >> a) & 1u, v[u][a]);
@@ -399,14 +450,14 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
       }
 #pragma unroll
       for (int u = 0; u < kRedUnroll; ++u) {
-        const u64 r = rb + (u64)u * ty_n;
-        if (r < r_end) {
+        const unsigned r = rb + u * ty_n;
+        if (r < n) {
 #pragma unroll
           for (int k = 0; k < VEC; ++k) {
             float x[NIN];
 #pragma unroll
             for (int a = 0; a < NIN; ++a) x[a] = v[u][a][k];
-            acc[k] = Op::step(acc[k], pro(x), (unsigned)r);
+            acc[k] = Op::step(acc[k], pro(x), (unsigned)r_begin + r);
           }
         }
       }

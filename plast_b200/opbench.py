@@ -57,7 +57,7 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
             e1.record()
             torch.cuda.synchronize()
             times.append(e0.elapsed_time(e1) / inner)
-        ms = float(np.median(times))
+        ms = float(np.median(times)) if times else float('nan')
         gbs = nbytes / (ms * 1e-3) / 1e9
         rows.append({"config": cfg, "op": name, "kernel": kernel, "ms": round(ms, 5),
                      "bytes": int(nbytes), "GBps": round(gbs, 1), "elements_per_s": elems / (ms * 1e-3),
