@@ -173,6 +173,13 @@ __device__ __forceinline__ void red_load(const float *p, bool vec, float *v) {
   }
 }
 
+// Asks the memory system to bring [p, p + bytes) into L2 (p 16-byte aligned, bytes a multiple of
+// 16); returns at once, nothing waits on it.
+constexpr int kPrefetchAhead = 3;
+__device__ __forceinline__ void prefetch_l2(const void *p, unsigned bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 template <class Op> __device__ __forceinline__ typename Op::T warp_reduce(typename Op::T v, int width) {
   for (int m = width >> 1; m > 0; m >>= 1) v = Op::combine(v, Op::shfl_xor(v, m, width));
   return v;
@@ -316,9 +323,10 @@ __global__ void __launch_bounds__(kRedThreads) reduce_seg_kernel(RedParams<NIN> 
   const u64 seg_begin = (u64)chunk * p.per_chunk;
   u64 seg_end = seg_begin + p.per_chunk;
   if (seg_end > p.nseg) seg_end = p.nseg;
-  for (u64 seg = seg_begin + ty; seg < seg_end; seg += ty_n) {
-    // The two common shapes need no 64-bit division: one run cut into pieces (a full reduce),
-    // or whole runs as segments (N,H,W of a channel gradient).
+  // Locates segment `seg`: input offsets of its run and the item range inside the run. The two
+  // common shapes need no 64-bit division: one run cut into pieces (a full reduce), or whole
+  // runs as segments (N,H,W of a channel gradient).
+  auto locate = [&](u64 seg, u64 *ioff, u64 *begin, u64 *end, u64 *outer_out) {
     u64 outer, piece;
     if (p.n_red == 1) {
       outer = 0;
@@ -330,13 +338,31 @@ __global__ void __launch_bounds__(kRedThreads) reduce_seg_kernel(RedParams<NIN> 
       outer = seg / p.nsplit0;
       piece = seg - outer * p.nsplit0;
     }
-    u64 ioff[NIN], dummy = 0;
+    u64 dummy = 0;
 #pragma unroll
     for (int a = 0; a < NIN; ++a) ioff[a] = base[a];
     p.red.offsets(outer, &dummy, ioff);
-    const u64 begin = piece * p.seg_len;
-    u64 end = begin + p.seg_len;
-    if (end > p.len0) end = p.len0;
+    *begin = piece * p.seg_len;
+    *end = *begin + p.seg_len;
+    if (*end > p.len0) *end = p.len0;
+    *outer_out = outer;
+  };
+  for (u64 seg = seg_begin + ty; seg < seg_end; seg += ty_n) {
+    // Pull a segment this row-worker reads kPrefetchAhead trips from now into L2 with one bulk
+    // prefetch per input, so DRAM stays busy beyond what the registers can keep in flight.
+    if (VEC == 4 && tx == 0) {
+      const u64 ahead = seg + (u64)kPrefetchAhead * ty_n;
+      if (ahead < seg_end) {
+        u64 poff[NIN], pb, pe, po;
+        locate(ahead, poff, &pb, &pe, &po);
+#pragma unroll
+        for (int a = 0; a < NIN; ++a)
+          if ((p.vec_mask >> a) & 1u)
+            prefetch_l2(p.in[a] + poff[a] + pb * VEC, (unsigned)((pe - pb) * VEC * sizeof(float)));
+      }
+    }
+    u64 ioff[NIN], begin, end, outer;
+    locate(seg, ioff, &begin, &end, &outer);
     accumulate_run<Op, Pro, NIN, VEC>(p, pro, ioff, begin, end, tx, tx_n,
                                       (unsigned)(outer * p.len0 * VEC), acc);
   }
