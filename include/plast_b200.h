@@ -137,6 +137,20 @@ void min_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams param
  * full reduce: the row-major linear index of the view). */
 void argmax_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
 
+/* Column sum for callers that must not allocate device memory. No counterpart in the reference:
+ * this is an addition of this library. It computes what sum_cuda_forward computes for
+ * params.dim == 0 on a contiguous 2-D FLOAT32 tensor [rows, cols] (the shape of a bias /
+ * broadcast gradient), but keeps its split partials in a fixed ~1 MiB array inside the library
+ * image instead of the cudaMalloc'ed workspace, and calls no allocating routine at all. Use it
+ * from code that has given all device memory to its own arena, or that must never trigger the
+ * allocator's device-wide synchronisation.
+ * Limits: cols <= 16384 and rows < 2^31, else PLAST_B200_ERR_LIMIT and nothing is launched;
+ * any other layout / axis gives PLAST_B200_ERR_UNSUPPORTED. All calls on a device share the array
+ * (it keeps the previous call's contents; what must start at zero is cleared per call): calls
+ * whose kernels overlap on the GPU race, so issue them on one stream. The first call on each
+ * device looks up the array's device address; make that call before any stream capture. */
+void sum_axis0_noalloc_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
+
 /* ------------------------------------------------------------------------------------------
  * Fused recipes. Each equals the op sequence the reference builds from primitives, with the
  * same per-op fp32 rounding (no FMA contraction across ops), in one pass over the data.

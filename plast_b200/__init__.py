@@ -88,6 +88,7 @@ def declared_symbols() -> list[str]:
         "plast_b200_clear_error", "plast_b200_set_stream", "plast_b200_get_stream",
         "plast_b200_set_sync", "plast_b200_launch_count", "plast_b200_last_kernel",
         "plast_b200_release_workspace", "plast_b200_version", "plast_b200_plan_debug",
+        "sum_axis0_noalloc_cuda_forward",
     ]
     return syms
 
@@ -106,6 +107,8 @@ def _load() -> C.CDLL:
         fn = getattr(lib, f"{op}_cuda_backward")
         fn.argtypes = [C.POINTER(C.POINTER(CTensor)), C.POINTER(CTensor), KernelParams]
         fn.restype = None
+    lib.sum_axis0_noalloc_cuda_forward.argtypes = [C.POINTER(C.POINTER(CTensor)), C.POINTER(CTensor), KernelParams]
+    lib.sum_axis0_noalloc_cuda_forward.restype = None
     lib.plast_b200_chain_forward.argtypes = [C.POINTER(C.POINTER(CTensor)), C.c_int, C.POINTER(CTensor),
                                              C.POINTER(ChainStep), C.c_int]
     lib.plast_b200_chain_forward.restype = None
