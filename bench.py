@@ -283,6 +283,14 @@ def run_ours(args):
         del x_h, y_h, z_h
         per_op = per_op_table(torch, pb, dev, peak, reps=args.op_reps)
 
+    sharded = None
+    if world > 1 and not args.no_per_op:
+        # reductions that cross the sharded dim: local kernel + one NCCL all-reduce (strong scaling
+        # of the fixed config 3 / 4 tensors); every rank takes part
+        from plast_b200.dist import sharded_reduction_table
+        del x_h, y_h, z_h
+        sharded = sharded_reduction_table(torch, dist, pb, dev, peak, reps=args.op_reps)
+
     cpu_info = None
     if rank == 0 and world == 1:
         _, cpu_info, _ = cpu_chain_baseline(1 << 25, 3)
@@ -303,6 +311,8 @@ def run_ours(args):
         }
         if per_op is not None:
             line["per_op"] = per_op
+        if sharded is not None:
+            line["sharded_reductions"] = sharded
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -1,0 +1,172 @@
+"""Multi-GPU layer of the hot path: one process per GPU, `torch.distributed` for the plumbing.
+
+plast itself has no distributed code (its README lists "MPI + NCCL" as a roadmap item), so this is
+new. The path shards naturally:
+
+* elementwise ops, axis reductions over a non-sharded axis, softmax / argmax rows: contiguous
+  blocks of the OUTERMOST non-reduced dim per rank, broadcast operands replicated, no
+  communication at all;
+* reductions that cross the sharded dim (full sum / max / mean, column sums of a row-sharded
+  matrix, a bias gradient of a batch-sharded activation, the cross-entropy mean): every rank
+  reduces its shard with the single-GPU kernel, then ONE all-reduce of the tiny partial
+  (4 bytes .. 32 KiB) over NCCL / NVLink combines them. A mean is the all-reduced SUM divided by
+  the GLOBAL count (never a mean of means); an argmax is an all-reduce MAX of the values followed
+  by an all-reduce MIN of the indices that attain it.
+
+Everything here works on any backend: the tests run it with `gloo` on CPU tensors (the local
+reduce is supplied by the caller), the benchmark with `nccl` on CUDA tensors.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+
+@dataclass(frozen=True)
+class Shard:
+    """Contiguous block [start, start + count) of a dim of length `total` owned by `rank`."""
+
+    start: int
+    count: int
+    total: int
+    rank: int
+    world: int
+
+
+def shard_dim(total: int, rank: int, world: int) -> Shard:
+    """Blocks differ by at most one element; the first `total % world` ranks get the extra one.
+    Ranks beyond `total` own an empty block (count 0) and contribute the identity."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad rank {rank} / world {world}")
+    base, extra = divmod(total, world)
+    count = base + (1 if rank < extra else 0)
+    start = rank * base + min(rank, extra)
+    return Shard(start, count, total, rank, world)
+
+
+def all_reduce_sum(dist, t):
+    """In place; `t` holds this rank's partial sums (any shape, identical on every rank)."""
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return t
+
+
+def all_reduce_max(dist, t):
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t
+
+
+def all_reduce_min(dist, t):
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return t
+
+
+def global_mean(dist, local_sum, global_count: int):
+    """Mean over all shards = all-reduced sum / global count (src/kernels/cpu/reduce_ops.c:13
+    divides the fp32 sum by the count once; so does this)."""
+    all_reduce_sum(dist, local_sum)
+    local_sum /= float(global_count)
+    return local_sum
+
+
+def global_argmax(dist, torch, local_value, local_index, index_offset: int):
+    """Full-tensor argmax across shards, lowest global index on ties.
+
+    local_value / local_index: this rank's maximum and its index inside the shard (tensors of the
+    same shape, index dtype int64); index_offset: global index of the shard's first element.
+    An empty shard passes value -inf."""
+    gmax = local_value.clone()
+    all_reduce_max(dist, gmax)
+    sentinel = torch.iinfo(torch.int64).max
+    cand = torch.where(local_value == gmax, local_index + index_offset,
+                       torch.full_like(local_index, sentinel))
+    all_reduce_min(dist, cand)
+    return gmax, cand
+
+
+# ---- benchmark of the sharded reductions (rank-parallel, CUDA) -------------------------------------
+def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 10):
+    """Strong-scaling rows for the reductions that need the all-reduce: the FIXED tensors of
+    configs 3, 4 and 5 are split across ranks along their outermost dim; every step is the local
+    kernel followed by the all-reduce, timed with CUDA events, max over ranks."""
+    import numpy as np
+
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    gen = torch.Generator(device=dev)
+    rows = []
+
+    def wrap(t, shape=None, dtype=pb.FLOAT32):
+        return pb.Tensor.wrap_pointer(t.data_ptr(), list(t.shape) if shape is None else shape,
+                                      dtype=dtype, owner=t)
+
+    def timeit(name, fn, total_bytes):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        times = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(5):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) / 5)
+        t = torch.tensor([float(np.median(times))], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        gbs = total_bytes / (ms * 1e-3) / 1e9
+        rows.append({"op": name, "n_gpus": world, "ms": round(ms, 5), "GBps": round(gbs, 1),
+                     "frac_of_measured_aggregate": round(gbs / (peak_gbs * world), 4)})
+
+    # config 4: X[8192, 8192], rows sharded; full sum / full max -> 4-byte all-reduce,
+    # sum over axis 0 -> 32 KiB all-reduce
+    M = 8192
+    sh = shard_dim(M, rank, world)
+    gen.manual_seed(100 + rank)
+    X = torch.rand((max(sh.count, 1), M), generator=gen, device=dev) * 2 - 1
+    tX = wrap(X, shape=[sh.count, M])
+    one, col = torch.zeros(1, device=dev), torch.zeros(M, device=dev)
+    tone, tcol = wrap(one), wrap(col)
+
+    def full_sum():
+        pb.forward("sum", [tX], tone, dim=pb.FULL_REDUCE, check=False)
+        all_reduce_sum(dist, one)
+
+    def full_max():
+        pb.forward("max", [tX], tone, dim=pb.FULL_REDUCE, check=False)
+        all_reduce_max(dist, one)
+
+    def sum_axis0():
+        pb.forward("sum", [tX], tcol, dim=0, check=False)
+        all_reduce_sum(dist, col)
+
+    timeit("config4_full_sum+allreduce", full_sum, M * M * 4 + 4)
+    timeit("config4_full_max+allreduce", full_max, M * M * 4 + 4)
+    timeit("config4_sum_axis0+allreduce", sum_axis0, (M * M + M) * 4)
+    del X
+
+    # config 3: cross-entropy mean over row-sharded logits -> 4-byte all-reduce of the loss SUM
+    R, Cn = 65536, 4096
+    sh = shard_dim(R, rank, world)
+    gen.manual_seed(200 + rank)
+    L = torch.randn((sh.count, Cn), generator=gen, device=dev) * 2.0
+    labels = torch.randint(0, Cn, (sh.count,), generator=gen, device=dev, dtype=torch.int32)
+    tL, tl = wrap(L), wrap(labels, dtype=pb.INT32)
+    loss = torch.zeros(1, device=dev)
+    tloss = wrap(loss)
+
+    def ce_mean():
+        pb.forward("cross_entropy", [tL, tl], tloss, check=False)  # local mean
+        loss.mul_(float(sh.count))                                   # back to the local sum
+        global_mean(dist, loss, R)
+
+    timeit("config3_cross_entropy_mean+allreduce", ce_mean, (R * Cn + R) * 4 + 4)
+    del L
+    torch.cuda.synchronize()
+    return rows
