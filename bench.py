@@ -129,44 +129,47 @@ class ClockSampler:
         self._th = None
         self.max_mhz = None
 
-    def _run_nvml(self) -> bool:
-        """Fast path: NVML queries (sub-millisecond), so even a short timed region is sampled."""
+    def _init_nvml(self) -> bool:
+        """NVML handle for the sampled GPU, set up BEFORE the timed region starts."""
         try:
             import pynvml as nv
             nv.nvmlInit()
-            uuid = None
+            h = None
             try:
                 import torch
-                uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(self.index).uuid)
+                h = nv.nvmlDeviceGetHandleByUUID(uuid.encode())
             except Exception:
-                pass
-            h = None
-            if uuid:
-                for cand in (f"GPU-{uuid}", uuid):
-                    try:
-                        h = nv.nvmlDeviceGetHandleByUUID(cand.encode() if isinstance(cand, str) else cand)
-                        break
-                    except Exception:
-                        h = None
+                h = None
             if h is None:
                 h = nv.nvmlDeviceGetHandleByIndex(self.index)
             self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
-            bits = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
-                    "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
-                    "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
-                    "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+            self._nv, self._h = nv, h
+            self._bits = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
+                          "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                          "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
+                          "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+            return True
         except Exception:
+            self._nv = None
             return False
-        while not self._stop.is_set():
+
+    def _run_nvml(self) -> bool:
+        """NVML queries take well under a millisecond, so even a short timed region is sampled."""
+        nv = getattr(self, "_nv", None)
+        if nv is None:
+            return False
+        while True:
             try:
-                self.samples.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
-                r = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
-                for n, b in bits.items():
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for n, b in self._bits.items():
                     if r & b:
                         self.reasons.add(n)
             except Exception:
                 pass
-            self._stop.wait(0.002)
+            if self._stop.wait(0.002):
+                break
         return True
 
     def _run(self):
@@ -191,6 +194,7 @@ class ClockSampler:
             self._stop.wait(0.1)
 
     def start(self):
+        self._init_nvml()
         self._th = threading.Thread(target=self._run, daemon=True)
         self._th.start()
 
