@@ -317,12 +317,14 @@ def run_ours(args):
                 "achieved": achieved, "peak": peak, "peak_source": f"of {peak_kind}", "unit": UNIT,
                 "frac": achieved / peak, "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
                 "traffic": None, "algorithmic_bytes_per_launch": BYTES_PER_ELEM * n}
-    prof = ROOT / "profiles" / "chain_2p28_traffic.json"
-    if prof.exists():
-        try:
-            roofline["traffic"] = json.loads(prof.read_text())["dram_bytes_per_launch"]
-        except Exception:
-            pass
+    # per-launch DRAM traffic from the committed ncu summary (measured at 2^26 elements, scaled)
+    prof = ROOT / "profiles" / "ew_kernel_chain_config2.md"
+    if prof.exists() and n == N_ELEMS:
+        import re
+        m = re.search(r"^dram_bytes_per_launch\s*=\s*(\d+)", prof.read_text(), flags=re.M)
+        if m:
+            roofline["traffic"] = int(m.group(1))
+            roofline["traffic_source"] = "ncu dram__bytes_read+write on 2^26 elements x4, profiles/ew_kernel_chain_config2.md"
 
     per_op = None
     if rank == 0 and world == 1 and not args.no_per_op:

@@ -378,13 +378,14 @@ __global__ void __launch_bounds__(kRedThreads) reduce_seg_kernel(RedParams<NIN> 
   T *partials = (T *)p.partials + out_idx * p.splits;
   if (threadIdx.x == 0) partials[chunk] = r;
   if (!take_ticket(p.counters + out_idx, p.splits)) return;
-  // Fixed combine order: chunk 0, 1, 2, ... so the result does not depend on arrival order.
+  // Fixed assignment of chunks to threads, then the block tree: the result does not depend on
+  // which CTA arrived last. All 256 threads share the partials so nobody walks a long chain of
+  // dependent L2 loads at the very end of the kernel.
   T v = Op::identity();
-  if (threadIdx.x < 32) {
-    for (unsigned c = threadIdx.x; c < p.splits; c += 32) v = Op::combine(v, Op::load_cg(partials + c));
-    v = warp_reduce<Op>(v, 32);
-    if (threadIdx.x == 0) Op::store((typename Op::Out *)p.out + toff, v, p.accumulate, p.post_div);
-  }
+  for (unsigned c = threadIdx.x; c < p.splits; c += kRedThreads) v = Op::combine(v, Op::load_cg(partials + c));
+  __syncthreads(); // block_reduce's scratch was used above
+  v = block_reduce<Op>(v);
+  if (threadIdx.x == 0) Op::store((typename Op::Out *)p.out + toff, v, p.accumulate, p.post_div);
 }
 
 // ---- cols: CTA per (strip of 32*VEC outputs along dim 0, outer kept index, chunk of reduced) ---------
@@ -420,7 +421,7 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
   const u64 r_begin = (u64)chunk * p.per_chunk;
   u64 r_end = r_begin + p.per_chunk;
   if (r_end > p.n_red) r_end = p.n_red;
-  constexpr int kRedUnroll = RedUnroll<NIN>::value;
+  constexpr int kRedUnroll = 4;
   const unsigned n = (unsigned)(r_end - r_begin); // the host keeps a chunk below 2^31 indices
   if (live && p.red.n <= 1) {
     // One reduced dim (the usual case): walk it with pointer increments, no index decoding.
@@ -432,30 +433,57 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
       ptr[a] = p.in[a] + base[a] + (r_begin + ty) * rs;
       step[a] = (u64)ty_n * rs;
     }
-    for (unsigned rb = ty; rb < n + ty; rb += kRedUnroll * ty_n) {
+    // Full batches first (every load of the batch issued back to back, nothing predicated),
+    // then the ragged rest one row at a time.
+    auto load_row = [&](const float *q, int a, float *v) {
+      if ((p.vec_mask >> a) & 1u) {
+        if (VEC == 4) {
+          const float4 t = __ldcs(reinterpret_cast<const float4 *>(q));
+          v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        } else if (VEC == 2) {
+          const float2 t = __ldcs(reinterpret_cast<const float2 *>(q));
+          v[0] = t.x; v[1] = t.y;
+        } else {
+          v[0] = __ldg(q);
+        }
+      } else {
+        const float sc = __ldg(q);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v[k] = sc;
+      }
+    };
+    unsigned rb = ty;
+    for (; rb + (kRedUnroll - 1) * ty_n < n; rb += kRedUnroll * ty_n) {
       float v[kRedUnroll][NIN][VEC];
 #pragma unroll
-      for (int u = 0; u < kRedUnroll; ++u) {
-        if (rb + u * ty_n < n) {
+      for (int u = 0; u < kRedUnroll; ++u)
 #pragma unroll
-          for (int a = 0; a < NIN; ++a)
-            red_load<VEC>(ptr[a] + (u64)u * step[a], (p.vec_mask >> a) & 1u, v[u][a]);
-        }
-      }
+        for (int a = 0; a < NIN; ++a) load_row(ptr[a] + (u64)u * step[a], a, v[u][a]);
 #pragma unroll
       for (int a = 0; a < NIN; ++a) ptr[a] += (u64)kRedUnroll * step[a];
 #pragma unroll
-      for (int u = 0; u < kRedUnroll; ++u) {
-        const unsigned r = rb + u * ty_n;
-        if (r < n) {
+      for (int u = 0; u < kRedUnroll; ++u)
 #pragma unroll
-          for (int k = 0; k < VEC; ++k) {
-            float x[NIN];
+        for (int k = 0; k < VEC; ++k) {
+          float x[NIN];
 #pragma unroll
-            for (int a = 0; a < NIN; ++a) x[a] = v[u][a][k];
-            acc[k] = Op::step(acc[k], pro(x), (unsigned)r_begin + r);
-          }
+          for (int a = 0; a < NIN; ++a) x[a] = v[u][a][k];
+          acc[k] = Op::step(acc[k], pro(x), (unsigned)r_begin + rb + u * ty_n);
         }
+    }
+    for (; rb < n; rb += ty_n) {
+      float v[NIN][VEC];
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) {
+        load_row(ptr[a], a, v[a]);
+        ptr[a] += step[a];
+      }
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        float x[NIN];
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) x[a] = v[a][k];
+        acc[k] = Op::step(acc[k], pro(x), (unsigned)r_begin + rb);
       }
     }
   } else if (live) {
@@ -523,16 +551,39 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
     for (int k = 0; k < VEC; ++k) partials[(((u64)chunk * VEC + k) << p.log_tx) + lane] = r[k];
   }
   if (!take_ticket(p.counters + tile, p.splits)) return;
-  if (ty == 0 && live) {
+  // Last CTA of the tile: row-worker t adds chunks t, t + ty_n, ... (independent loads), then the
+  // workers are combined in shared memory as above. Fixed assignment -> reproducible result.
+  T fin[VEC];
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-      T v = Op::identity();
-      for (unsigned c = 0; c < p.splits; ++c)
-        v = Op::combine(v, Op::load_cg(partials + (((u64)c * VEC + k) << p.log_tx) + lane));
-      Op::store(out + toff + (u64)k * p.tstride0, v, p.accumulate, p.post_div);
+  for (int k = 0; k < VEC; ++k) {
+    fin[k] = Op::identity();
+    if (live)
+      for (unsigned c = ty; c < p.splits; c += ty_n)
+        fin[k] = Op::combine(fin[k], Op::load_cg(partials + (((u64)c * VEC + k) << p.log_tx) + lane));
+  }
+  if (ty_n > 1) {
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) strip_vals[((ty * VEC + k) << p.log_tx) + lane] = fin[k];
+    __syncthreads();
+    if (ty == 0) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k)
+        for (unsigned t = 1; t < ty_n; ++t)
+          fin[k] = Op::combine(fin[k], strip_vals[((t * VEC + k) << p.log_tx) + lane]);
     }
   }
+  if (ty == 0 && live) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) Op::store(out + toff + (u64)k * p.tstride0, fin[k], p.accumulate, p.post_div);
+  }
 }
+
+} // namespace pb
+
+#include "reduce_stream.cuh" // streamed (bulk-copy) variants of the seg and cols kernels
+
+namespace pb {
 
 // ---- host side ----------------------------------------------------------------------------------------
 enum RedKind { kRedRows = 0, kRedSeg = 1, kRedCols = 2 };
@@ -554,13 +605,23 @@ struct RedGeometry {
   unsigned splits;
   int kept_dims[MAX_NDIM], n_kept_dims; // plan dim indices in each sub-space
   int red_dims[MAX_NDIM], n_red_dims;
+  // streamed (bulk-copy) variant, see reduce_stream.cuh
+  bool stream;
+  int n_streamed;
+  unsigned tile_items, rows_per_tile;
 };
 // Resident CTAs per SM of each kernel shape ([kind][vec 1,2,4]), from the occupancy calculator.
 struct RedOccupancy {
   int ctas_per_sm[3][3];
 };
 bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int nin,
-                          size_t elem_bytes, bool indexed, const RedOccupancy &occ, RedGeometry *g);
+                          size_t elem_bytes, bool indexed, const RedOccupancy &occ, bool allow_stream,
+                          RedGeometry *g);
+
+// PLAST_B200_STREAM=1 in the environment routes eligible reductions through the bulk-copy kernels
+// of reduce_stream.cuh (an A/B switch; the register-staged kernels measured faster on B200 and
+// are the default).
+bool stream_reductions_enabled();
 
 template <class Op, class Pro, int NIN> const RedOccupancy &reduce_occupancy() {
   static RedOccupancy occ = [] {
@@ -595,7 +656,7 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   const void *ptrs[NIN];
   for (int a = 0; a < NIN; ++a) ptrs[a] = ins[a];
   if (!plan_reduce_geometry(plan, ptrs, NIN, sizeof(typename Op::T), Op::kIndexed,
-                            reduce_occupancy<Op, Pro, NIN>(), &g))
+                            reduce_occupancy<Op, Pro, NIN>(), stream_reductions_enabled(), &g))
     return;
 
   RedParams<NIN> p;
@@ -631,14 +692,44 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   p.post_div = post_div;
   p.counters = nullptr;
   p.partials = nullptr;
-  if (g.splits > 1) {
-    Workspace ws;
+  Workspace ws = {};
+  if (g.splits > 1 || g.stream) {
     if (!get_workspace(&ws)) return;
     p.counters = ws.counters;
     p.partials = ws.partials;
   }
   cudaStream_t s = stream();
   dim3 grid((unsigned)g.grid), block(kRedThreads);
+  if (g.stream) {
+    StreamParams<NIN> sp;
+    int next = 0;
+    for (int a = 0; a < NIN; ++a) sp.slot[a] = ((g.vec_mask >> a) & 1u) ? next++ : -1;
+    sp.n_streamed = g.n_streamed;
+    sp.tile_items = g.tile_items;
+    sp.rows_per_tile = g.rows_per_tile;
+    sp.gave_up = ws.gave_up;
+    // dynamic shared memory beyond 48 KiB has to be opted into once per kernel
+    static bool seg_ready = false, cols_ready = false;
+    if (g.kind == kRedSeg) {
+      if (!seg_ready) {
+        PB_CUDA(cudaFuncSetAttribute(reduce_seg_stream_kernel<Op, Pro, NIN>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStreamSmemBytes));
+        seg_ready = true;
+      }
+      reduce_seg_stream_kernel<Op, Pro, NIN><<<grid, block, kStreamSmemBytes, s>>>(p, sp, pro);
+      note_kernel("reduce_seg_stream");
+    } else {
+      if (!cols_ready) {
+        PB_CUDA(cudaFuncSetAttribute(reduce_cols_stream_kernel<Op, Pro, NIN>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStreamSmemBytes));
+        cols_ready = true;
+      }
+      reduce_cols_stream_kernel<Op, Pro, NIN><<<grid, block, kStreamSmemBytes, s>>>(p, sp, pro);
+      note_kernel("reduce_cols_stream");
+    }
+    count_launch();
+    return;
+  }
 #define PB_RED_LAUNCH(KERNEL)                                                                      \
   do {                                                                                             \
     if (g.vec == 4) KERNEL<Op, Pro, NIN, 4><<<grid, block, 0, s>>>(p, pro);                        \
