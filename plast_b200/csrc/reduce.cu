@@ -113,9 +113,12 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
     g->stream = can_stream && g->len0_items >= 64;
     const u64 seg_cap = g->stream ? (u64)g->tile_items : (u64)kRedThreads * (nin == 1 ? 8 : 4);
     if (g->len0_items <= seg_cap) {
+      // whole runs as segments: a row-worker of ~1/16 of the run's items walks it in several
+      // full load batches; the other row-workers of the CTA take the next runs
       g->nsplit0 = 1;
       g->seg_len = g->len0_items;
-      g->log_tx = log2_ceil(g->len0_items);
+      g->log_tx = log2_ceil(ceil_div(g->len0_items, 16));
+      if (g->log_tx < 5 && g->len0_items >= 32) g->log_tx = 5;
       if (g->log_tx > 8) g->log_tx = 8;
     } else {
       // one trip of the load batch (or one stage of the ring) per segment

@@ -208,62 +208,76 @@ template <int NIN> struct RedUnroll { static constexpr int value = NIN == 1 ? 8 
 // up to kRedUnroll loads per input before the first use (predicated at the ragged end, so every
 // thread of the row-worker makes the same number of trips).
 // idx_base: flat reduced index of element 0 of the run (argmax only).
-template <class Op, class Pro, int NIN, int VEC>
+// NS: number of LEADING inputs that vary along the run. NS == NIN decides per input at run time
+// (any mix); NS < NIN states at compile time that inputs [NS, NIN) are constant along the run
+// (per-channel scale / bias of a gradient prologue), so they take one register each instead of a
+// whole load batch.
+template <class Op, class Pro, int NIN, int VEC, int NS>
 __device__ __forceinline__ void accumulate_run(const RedParams<NIN> &p, const Pro &pro,
                                                const u64 *ioff, u64 begin, u64 end, unsigned tx,
                                                unsigned tx_n, unsigned idx_base, typename Op::T *acc) {
   // Pointers to item `begin` of the run; inside the run a 32-bit item index suffices (the host
   // never plans runs of 2^31 items or more). With VEC > 1 an input is either vector-loaded
   // (consecutive items are consecutive vectors) or constant along the run.
+  constexpr bool kStatic = NS < NIN;
+  constexpr int NV = kStatic ? NS : NIN; // inputs that get load slots
   const float *base[NIN];
-  float fixed[NIN]; // inputs that broadcast along the run (per-channel scale / bias): read once
+  float fixed[NIN];
 #pragma unroll
   for (int a = 0; a < NIN; ++a) {
     base[a] = p.in[a] + ioff[a] + begin * p.istride0[a];
-    fixed[a] = p.istride0[a] == 0 ? __ldg(base[a]) : 0.0f;
+    const bool is_fixed = kStatic ? a >= NS : p.istride0[a] == 0;
+    fixed[a] = is_fixed ? __ldg(base[a]) : 0.0f;
   }
   const unsigned n = (unsigned)(end - begin);
   idx_base += (unsigned)begin * VEC;
-  constexpr int kRedUnroll = RedUnroll<NIN>::value;
+  constexpr int kRedUnroll = RedUnroll<NV>::value;
+  auto load_item = [&](int a, unsigned i, float *v) {
+    if (!kStatic && p.istride0[a] == 0) return;
+    if (VEC == 4) {
+      const float4 t = __ldcs(reinterpret_cast<const float4 *>(base[a]) + i);
+      v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else if (VEC == 2) {
+      const float2 t = __ldcs(reinterpret_cast<const float2 *>(base[a]) + i);
+      v[0] = t.x; v[1] = t.y;
+    } else {
+      v[0] = __ldg(base[a] + (u64)i * p.istride0[a]);
+    }
+  };
+  auto consume = [&](const float (*v)[VEC], unsigned i) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+      float x[NIN];
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) {
+        const bool is_fixed = kStatic ? a >= NS : p.istride0[a] == 0;
+        x[a] = is_fixed ? fixed[a] : v[a < NV ? a : 0][k];
+      }
+      acc[k] = Op::step(acc[k], pro(x), idx_base + i * VEC + k);
+    }
+  };
+  // Every trip issues up to kRedUnroll loads per input before the first use; the ragged last trip
+  // is predicated, so it is still one batch (not a chain of single dependent loads).
   for (unsigned b = tx; b < n + tx; b += kRedUnroll * tx_n) {
-    float v[kRedUnroll][NIN][VEC];
+    float v[kRedUnroll][NV][VEC];
 #pragma unroll
     for (int u = 0; u < kRedUnroll; ++u) {
       const unsigned i = b + u * tx_n;
       if (i < n) {
 #pragma unroll
-        for (int a = 0; a < NIN; ++a) {
-          if (p.istride0[a] == 0) continue;
-          if (VEC == 4) {
-            const float4 t = __ldcs(reinterpret_cast<const float4 *>(base[a]) + i);
-            v[u][a][0] = t.x; v[u][a][1] = t.y; v[u][a][2] = t.z; v[u][a][3] = t.w;
-          } else if (VEC == 2) {
-            const float2 t = __ldcs(reinterpret_cast<const float2 *>(base[a]) + i);
-            v[u][a][0] = t.x; v[u][a][1] = t.y;
-          } else {
-            v[u][a][0] = __ldg(base[a] + (u64)i * p.istride0[a]);
-          }
-        }
+        for (int a = 0; a < NV; ++a) load_item(a, i, v[u][a]);
       }
     }
 #pragma unroll
     for (int u = 0; u < kRedUnroll; ++u) {
       const unsigned i = b + u * tx_n;
-      if (i < n) {
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) {
-          float x[NIN];
-#pragma unroll
-          for (int a = 0; a < NIN; ++a) x[a] = p.istride0[a] != 0 ? v[u][a][k] : fixed[a];
-          acc[k] = Op::step(acc[k], pro(x), idx_base + i * VEC + k);
-        }
-      }
+      if (i < n) consume(v[u], i);
     }
   }
 }
 
 // ---- rows: one (sub)warp per output -----------------------------------------------------------------
-template <class Op, class Pro, int NIN, int VEC>
+template <class Op, class Pro, int NIN, int VEC, int NS = NIN>
 __global__ void __launch_bounds__(kRedThreads) reduce_rows_kernel(RedParams<NIN> p, Pro pro) {
   using T = typename Op::T;
   const unsigned tx_n = 1u << p.log_tx;
@@ -277,7 +291,7 @@ __global__ void __launch_bounds__(kRedThreads) reduce_rows_kernel(RedParams<NIN>
     T acc[VEC];
 #pragma unroll
     for (int k = 0; k < VEC; ++k) acc[k] = Op::identity();
-    accumulate_run<Op, Pro, NIN, VEC>(p, pro, ioff, 0, p.len0, tx, tx_n, 0, acc);
+    accumulate_run<Op, Pro, NIN, VEC, NS>(p, pro, ioff, 0, p.len0, tx, tx_n, 0, acc);
     T r = acc[0];
 #pragma unroll
     for (int k = 1; k < VEC; ++k) r = Op::combine(r, acc[k]);
@@ -302,7 +316,7 @@ __device__ __forceinline__ bool take_ticket(unsigned int *counter, unsigned spli
 }
 
 // ---- seg: CTA per (output, chunk of segments) ---------------------------------------------------------
-template <class Op, class Pro, int NIN, int VEC>
+template <class Op, class Pro, int NIN, int VEC, int NS = NIN>
 __global__ void __launch_bounds__(kRedThreads) reduce_seg_kernel(RedParams<NIN> p, Pro pro) {
   using T = typename Op::T;
   const u64 out_idx = blockIdx.x / p.splits;
@@ -363,7 +377,7 @@ __global__ void __launch_bounds__(kRedThreads) reduce_seg_kernel(RedParams<NIN> 
     }
     u64 ioff[NIN], begin, end, outer;
     locate(seg, ioff, &begin, &end, &outer);
-    accumulate_run<Op, Pro, NIN, VEC>(p, pro, ioff, begin, end, tx, tx_n,
+    accumulate_run<Op, Pro, NIN, VEC, NS>(p, pro, ioff, begin, end, tx, tx_n,
                                       (unsigned)(outer * p.len0 * VEC), acc);
   }
   T r = acc[0];
@@ -659,6 +673,42 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
                             reduce_occupancy<Op, Pro, NIN>(), stream_reductions_enabled(), &g))
     return;
 
+  // Several reduced dims around long contiguous runs (N, H, W of an NCHW channel gradient) with
+  // plenty of (kept x outer-reduced) combinations: reduce every run on its own with the rows
+  // kernel (the fastest shape: a warp per run, no cross-CTA traffic) into a small scratch matrix
+  // [outer reduced][kept], then reduce that matrix over the outer dims. Two launches, but the
+  // second one touches kilobytes.
+  if (g.kind == kRedSeg && g.n_red > 1 && !Op::kIndexed && g.len0_items * (u64)g.vec >= 256 &&
+      g.n_kept * g.n_red >= 4096 && g.n_kept * g.n_red <= kPartialFloats / 4) {
+    Workspace ws2;
+    if (!get_workspace(&ws2)) return;
+    float *scratch = ws2.partials + (kPartialFloats / 4) * 3; // last quarter: two-stage partials
+    IterPlan first = plan;
+    u64 sh2[MAX_NDIM], st2[2][MAX_NDIM];
+    bool red2[MAX_NDIM];
+    u64 kflat = 1, rflat = g.n_kept;
+    for (int d = 1; d < plan.ndim; ++d) {
+      const u64 sst = plan.reduced[d] ? rflat : kflat;
+      (plan.reduced[d] ? rflat : kflat) *= plan.size[d];
+      first.reduced[d] = false;
+      first.stride[0][d] = sst;
+      const int o = plan.ndim - 1 - d; // outermost first for make_plan
+      sh2[o] = plan.size[d];
+      st2[0][o] = plan.stride[0][d];
+      st2[1][o] = sst;
+      red2[o] = plan.reduced[d];
+    }
+    first.stride[0][0] = 0;
+    first.max_offset[0] = g.n_kept * g.n_red - 1;
+    launch_reduce<Op, Pro, NIN>(first, (typename Op::Out *)scratch, ins, pro, Op{}, false, 0.0f);
+    if (failed()) return;
+    IterPlan second;
+    make_plan(&second, sh2, (u64)(plan.ndim - 1), 2, st2, red2, 1);
+    const float *ins2[1] = {scratch};
+    launch_reduce<Op, IdentityPro, 1>(second, out, ins2, IdentityPro{}, Op{}, accumulate, post_div);
+    return;
+  }
+
   RedParams<NIN> p;
   for (int a = 0; a < NIN; ++a) p.in[a] = ins[a];
   p.out = out;
@@ -736,16 +786,28 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
     else if (g.vec == 2) KERNEL<Op, Pro, NIN, 2><<<grid, block, 0, s>>>(p, pro);                   \
     else KERNEL<Op, Pro, NIN, 1><<<grid, block, 0, s>>>(p, pro);                                   \
   } while (0)
+  // float4 plans whose inputs are "the first m vary along the run, the rest are constant"
+  // (m = 1 or 2 < NIN) get the kernel that knows this at compile time (fewer registers).
+  int lead = 0;
+  while (lead < NIN && ((g.vec_mask >> lead) & 1u)) ++lead;
+  const bool prefix = g.vec == 4 && lead < NIN && g.vec_mask == ((1u << lead) - 1u) && (lead == 1 || lead == 2);
+#define PB_RED_LAUNCH_NS(KERNEL)                                                                   \
+  do {                                                                                             \
+    if (prefix && lead == 1) KERNEL<Op, Pro, NIN, 4, (NIN > 1 ? 1 : NIN)><<<grid, block, 0, s>>>(p, pro); \
+    else if (prefix && lead == 2) KERNEL<Op, Pro, NIN, 4, (NIN > 2 ? 2 : NIN)><<<grid, block, 0, s>>>(p, pro); \
+    else PB_RED_LAUNCH(KERNEL);                                                                    \
+  } while (0)
   if (g.kind == kRedRows) {
-    PB_RED_LAUNCH(reduce_rows_kernel);
+    PB_RED_LAUNCH_NS(reduce_rows_kernel);
     note_kernel(g.vec == 4 ? "reduce_rows_vec4" : (g.vec == 2 ? "reduce_rows_vec2" : "reduce_rows_scalar"));
   } else if (g.kind == kRedSeg) {
-    PB_RED_LAUNCH(reduce_seg_kernel);
+    PB_RED_LAUNCH_NS(reduce_seg_kernel);
     note_kernel(g.vec == 4 ? "reduce_seg_vec4" : (g.vec == 2 ? "reduce_seg_vec2" : "reduce_seg_scalar"));
   } else {
     PB_RED_LAUNCH(reduce_cols_kernel);
     note_kernel(g.vec == 4 ? "reduce_cols_vec4" : (g.vec == 2 ? "reduce_cols_vec2" : "reduce_cols_scalar"));
   }
+#undef PB_RED_LAUNCH_NS
 #undef PB_RED_LAUNCH
   count_launch();
 }

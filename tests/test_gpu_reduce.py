@@ -133,7 +133,9 @@ def test_max_backward_tie_split(cuda):
 
 
 BCAST_GRAD = [((64, 48), (1, 48)), ((64, 48), (64, 1)), ((64, 48), ()), ((6, 8, 5, 5), (1, 8, 1, 1)),
-              ((3, 1, 4), (1, 2, 1)), ((33, 7), (7,)), ((1024, 256), (1, 256)), ((5, 4, 3), (4, 1))]
+              ((3, 1, 4), (1, 2, 1)), ((33, 7), (7,)), ((1024, 256), (1, 256)), ((5, 4, 3), (4, 1)),
+              # enough (channel x batch) runs for the two-stage path: run sums, then a column sum
+              ((64, 64, 16, 16), (1, 64, 1, 1)), ((70, 60, 8, 8), (60, 1, 1))]
 
 
 @pytest.mark.parametrize("op", ["add", "sub", "mul", "div"])
