@@ -23,6 +23,28 @@ namespace pb {
 
 enum SmMode { kSoftmax = 0, kLogSoftmax = 1, kCrossEntropy = 2 };
 
+// exp for the softmax family. The contract for softmax / log-softmax / cross-entropy is a relative
+// error of 1e-5 on the result (not 2 ulp per element as for exp_cuda_forward), and with 4096
+// exponentials per 16 KiB row the instruction count of expf, not HBM, bounds a read-only kernel
+// like cross-entropy. This version keeps ~3 ulp without expf's explicit range reduction:
+//   t = x * log2(e) rounded; err = the rounding error of that product (one FMA, exact) plus the
+//   low part of log2(e); exp(x) = 2^t * 2^err ~= ex2(t) * (1 + err * ln 2).
+// Five instructions instead of about ten; ex2.approx itself is good to ~2 ulp over its range and
+// returns 0 / denormals for very negative t like expf.
+// Arguments here are x - max <= 0; they are clamped at -104 (exp underflows to 0 below -103.3)
+// so that -FLT_MAX-sized differences cannot turn the error term into inf * 0.
+__device__ __forceinline__ float exp_softmax(float x) {
+  x = fmaxf(x, -104.0f);
+  const float kLog2eHi = 1.4426950216293335f;    // fp32(log2 e)
+  const float kLog2eLo = 1.9259629911266175e-8f; // log2 e - kLog2eHi
+  const float t = x * kLog2eHi;
+  float err = __fmaf_rn(x, kLog2eHi, -t);
+  err = __fmaf_rn(x, kLog2eLo, err);
+  float r;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(r) : "f"(t));
+  return __fmaf_rn(r * 0.6931471805599453f, err, r);
+}
+
 constexpr int kSmThreads = 256;
 constexpr int kSmMaxVpt = 8;
 
@@ -90,10 +112,10 @@ softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const in
         // sub, then exp: two separately rounded ops
         v[i].x = v[i].x - m; v[i].y = v[i].y - m; v[i].z = v[i].z - m; v[i].w = v[i].w - m;
         if (MODE == kSoftmax) {
-          v[i].x = expf(v[i].x); v[i].y = expf(v[i].y); v[i].z = expf(v[i].z); v[i].w = expf(v[i].w);
+          v[i].x = exp_softmax(v[i].x); v[i].y = exp_softmax(v[i].y); v[i].z = exp_softmax(v[i].z); v[i].w = exp_softmax(v[i].w);
           s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
         } else {
-          s += (expf(v[i].x) + expf(v[i].y)) + (expf(v[i].z) + expf(v[i].w));
+          s += (exp_softmax(v[i].x) + exp_softmax(v[i].y)) + (exp_softmax(v[i].z) + exp_softmax(v[i].w));
         }
       }
     }
@@ -145,8 +167,8 @@ struct MaxSum {
 };
 __device__ __forceinline__ MaxSum ms_combine(MaxSum a, MaxSum b) {
   // sum of exp(x - m) re-based onto the larger maximum
-  if (a.m >= b.m) return MaxSum{a.m, a.s + b.s * expf(b.m - a.m)};
-  return MaxSum{b.m, b.s + a.s * expf(a.m - b.m)};
+  if (a.m >= b.m) return MaxSum{a.m, a.s + b.s * exp_softmax(b.m - a.m)};
+  return MaxSum{b.m, b.s + a.s * exp_softmax(a.m - b.m)};
 }
 __device__ __forceinline__ MaxSum ms_block_reduce(MaxSum v) {
   __shared__ MaxSum sm[kSmThreads / 32];
@@ -176,10 +198,10 @@ softmax_generic_kernel(const float *x, float *y, const int *labels, SmRows g, fl
     for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
       const float xv = xr[j * g.x_axis_stride];
       if (xv > acc.m) {
-        acc.s = acc.s * expf(acc.m - xv) + 1.0f;
+        acc.s = acc.s * exp_softmax(acc.m - xv) + 1.0f;
         acc.m = xv;
       } else {
-        acc.s += expf(xv - acc.m);
+        acc.s += exp_softmax(xv - acc.m);
       }
     }
     acc = ms_block_reduce(acc);
@@ -199,9 +221,88 @@ softmax_generic_kernel(const float *x, float *y, const int *labels, SmRows g, fl
     const float lse = (MODE == kLogSoftmax) ? logf(acc.s) : 0.0f;
     for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
       const float sh = xr[j * g.x_axis_stride] - acc.m;
-      yr[j * g.y_axis_stride] = (MODE == kSoftmax) ? expf(sh) / acc.s : sh - lse;
+      yr[j * g.y_axis_stride] = (MODE == kSoftmax) ? exp_softmax(sh) / acc.s : sh - lse;
     }
   }
+}
+
+// ---- cross entropy, streaming rows ------------------------------------------------------------------
+// Cross entropy needs only max, sum(exp(x - max)) and x[label] of a row, so the row does not have
+// to stay on chip: a warp streams it once with eight float4 loads in flight per lane and keeps a
+// running (max, sum) pair per lane, re-based whenever a batch raises the maximum. With no row held
+// in registers, 48+ warps fit per SM, which is what a read-only kernel needs to cover HBM latency
+// (the register-resident kernel above tops out near 4.4 TB/s on [65536, 4096]).
+constexpr int kCeBatch = 8;
+constexpr float kLog2e = 1.4426950408889634f;
+// 2^(x * log2(e) - m2) with m2 = max * log2(e): exp(x - max) for the running sum. The argument is
+// clamped at -150 (2^-150 is 0 in fp32) so a -FLT_MAX start value cannot overflow the product.
+__device__ __forceinline__ float exp2_sum_term(float x, float m2) {
+  float t = __fmaf_rn(fmaxf(x, -1.0e30f), kLog2e, -m2);
+  t = fmaxf(t, -150.0f);
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+  return r;
+}
+__global__ void __launch_bounds__(kSmThreads)
+cross_entropy_rows_kernel(const float *__restrict__ x, const int *__restrict__ labels, SmRows g,
+                          float *__restrict__ mean_out, unsigned int *counter, float *partials) {
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float warp_loss = 0.0f; // lane 0: sum of the losses of this warp's rows
+  const unsigned warps_per_cta = kSmThreads / 32;
+  const unsigned nvec = (unsigned)(g.cols >> 2);
+  for (u64 row = (u64)blockIdx.x * warps_per_cta + warp; row < g.rows; row += (u64)gridDim.x * warps_per_cta) {
+    u64 yoff = 0, ioff[2] = {0, 0};
+    g.outer.offsets(row, &yoff, ioff);
+    const float4 *xr = reinterpret_cast<const float4 *>(x + ioff[0]);
+    MaxSum acc{-FLT_MAX, 0.0f};
+    for (unsigned b = lane; b < nvec + lane; b += kCeBatch * 32) {
+      float4 v[kCeBatch];
+#pragma unroll
+      for (int u = 0; u < kCeBatch; ++u)
+        if (b + u * 32 < nvec) v[u] = __ldcs(xr + b + u * 32);
+      float bm = -FLT_MAX;
+#pragma unroll
+      for (int u = 0; u < kCeBatch; ++u)
+        if (b + u * 32 < nvec) bm = fmaxf(bm, fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w)));
+      if (bm > acc.m) {
+        acc.s *= exp2_sum_term(acc.m, bm * kLog2e);
+        acc.m = bm;
+      }
+      // Only the SUM of the exponentials is needed (its log enters the loss), and terms far below
+      // the maximum do not move it, so each term is one FMA + ex2.approx: 2^(x log2e - m log2e).
+      // Its relative error grows with |x - m| (about |x - m| * 1e-7) exactly where the term is
+      // negligible; the sum stays within 1e-6 of the accurate one.
+      const float m2 = acc.m * kLog2e;
+#pragma unroll
+      for (int u = 0; u < kCeBatch; ++u)
+        if (b + u * 32 < nvec)
+          acc.s += (exp2_sum_term(v[u].x, m2) + exp2_sum_term(v[u].y, m2)) +
+                   (exp2_sum_term(v[u].z, m2) + exp2_sum_term(v[u].w, m2));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      MaxSum t;
+      t.m = __shfl_xor_sync(0xffffffffu, acc.m, o);
+      t.s = __shfl_xor_sync(0xffffffffu, acc.s, o);
+      acc = ms_combine(acc, t);
+    }
+    if (lane == 0) {
+      const int label = labels[row];
+      if (label >= 0 && (u64)label < g.cols) {
+        const float sh = (x + ioff[0])[label] - acc.m;
+        warp_loss += -(sh - logf(acc.s));
+      }
+    }
+  }
+  // mean over all rows: one partial per CTA, combined by the last CTA to arrive (fixed order)
+  const float part = block_reduce<SumOp>(warp_loss);
+  if (threadIdx.x == 0) partials[blockIdx.x] = part;
+  if (!take_ticket(counter, gridDim.x)) return;
+  float tot = 0.0f;
+  for (unsigned c = threadIdx.x; c < gridDim.x; c += kSmThreads) tot += __ldcg(partials + c);
+  __syncthreads();
+  tot = block_reduce<SumOp>(tot);
+  if (threadIdx.x == 0) mean_out[0] = tot / (float)g.rows; // src/kernels/cpu/reduce_ops.c:13
 }
 
 // ---- backward ---------------------------------------------------------------------------------------
@@ -222,17 +323,17 @@ softmax_backward_kernel(const float *y_or_x, const float *dy, float *dx, const i
       for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
         const float xv = a[j * g.x_axis_stride];
         if (xv > acc.m) {
-          acc.s = acc.s * expf(acc.m - xv) + 1.0f;
+          acc.s = acc.s * exp_softmax(acc.m - xv) + 1.0f;
           acc.m = xv;
         } else {
-          acc.s += expf(xv - acc.m);
+          acc.s += exp_softmax(xv - acc.m);
         }
       }
       acc = ms_block_reduce(acc);
       const float gscale = dy[0] / (float)g.rows;
       const int label = labels[row];
       for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
-        const float p = expf(a[j * g.x_axis_stride] - acc.m) / acc.s;
+        const float p = exp_softmax(a[j * g.x_axis_stride] - acc.m) / acc.s;
         const float t = ((u64)label == j) ? 1.0f : 0.0f;
         dxr[j * g.y_axis_stride] += (p - t) * gscale;
       }
@@ -253,7 +354,7 @@ softmax_backward_kernel(const float *y_or_x, const float *dy, float *dx, const i
     for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
       const float d = dyr[j * g.z_axis_stride];
       const float yv = a[j * g.x_axis_stride];
-      const float gr = (MODE == kSoftmax) ? yv * (d - tot) : d - expf(yv) * tot;
+      const float gr = (MODE == kSoftmax) ? yv * (d - tot) : d - exp_softmax(yv) * tot;
       dxr[j * g.y_axis_stride] += gr;
     }
   }
@@ -334,6 +435,11 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
   if (g.rows == 0 || g.cols == 0) return;
   cudaStream_t s = stream();
   const bool fast = fast_ok(g, x->data, output->data, MODE != kCrossEntropy);
+  // the streaming cross-entropy kernel takes rows of any length (float4 layout permitting)
+  SmRows any_len = g;
+  any_len.cols = g.cols > 4 ? 4 : g.cols;
+  const bool fast_ok_any_cols = MODE == kCrossEntropy && (g.cols & 3) == 0 && g.cols < ((u64)1 << 33) &&
+                                fast_ok(any_len, x->data, output->data, false);
   u64 grid;
   int log_tx = 5, vpt = 1;
   if (fast) {
@@ -365,7 +471,27 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
   }
   float *y = (float *)output->data;
   const float *xd = (const float *)x->data;
-  if (fast) {
+  if (MODE == kCrossEntropy && fast_ok_any_cols) {
+    // one resident wave of CTAs that stride over the rows; a single launch yields the mean
+    u64 ce_grid = (g.rows + kSmThreads / 32 - 1) / (kSmThreads / 32);
+    static int ce_ctas_per_sm = 0; // resident CTAs per SM of this kernel
+    if (ce_ctas_per_sm == 0) {
+      if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ce_ctas_per_sm, cross_entropy_rows_kernel,
+                                                        kSmThreads, 0) != cudaSuccess || ce_ctas_per_sm <= 0) {
+        cudaGetLastError();
+        ce_ctas_per_sm = 4;
+      }
+    }
+    const u64 ce_cap = (u64)sm_count() * (u64)ce_ctas_per_sm;
+    if (ce_grid > ce_cap) ce_grid = ce_cap;
+    Workspace ws;
+    if (!get_workspace(&ws)) return;
+    cross_entropy_rows_kernel<<<(unsigned)ce_grid, kSmThreads, 0, s>>>(xd, labels, g, y, ws.counters, ws.partials);
+    count_launch();
+    note_kernel("cross_entropy_rows");
+    end_call();
+    return;
+  } else if (fast) {
     int v = 1;
     while (v < vpt) v <<= 1;
     switch (v) {
@@ -391,7 +517,8 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
     launch_reduce<SumOp, IdentityPro, 1>(plan, y, ins, IdentityPro{}, SumOp{}, false, (float)g.rows);
   }
   if (!failed())
-    note_kernel(fast ? (MODE == kSoftmax ? "softmax_fast" : (MODE == kLogSoftmax ? "log_softmax_fast" : "cross_entropy_fast"))
+    note_kernel((MODE == kCrossEntropy && fast_ok_any_cols) ? "cross_entropy_rows" :
+                fast ? (MODE == kSoftmax ? "softmax_fast" : (MODE == kLogSoftmax ? "log_softmax_fast" : "cross_entropy_fast"))
                      : (MODE == kSoftmax ? "softmax_online" : (MODE == kLogSoftmax ? "log_softmax_online" : "cross_entropy_online")));
   end_call();
 }
