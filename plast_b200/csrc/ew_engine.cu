@@ -49,4 +49,25 @@ EwChoice choose_ew(const IterPlan &plan, const void *const *ptrs, int nargs, u64
   return c;
 }
 
+int choose_tiled_dim(const IterPlan &plan, int nargs, unsigned *tmask) {
+  *tmask = 0;
+  if (plan.ndim < 2 || plan.stride[0][0] != 1) return -1; // output must run along dim 0
+  int dT = -1;
+  unsigned mask = 0;
+  for (int a = 1; a < nargs; ++a) {
+    const u64 s0 = plan.stride[a][0];
+    if (s0 <= 1) continue; // contiguous or broadcast along dim 0: read directly
+    int mine = -1;
+    for (int d = 1; d < plan.ndim; ++d)
+      if (plan.stride[a][d] == 1 && plan.size[d] > 1) mine = d;
+    if (mine < 0 || (dT >= 0 && mine != dT)) return -1; // strided with no unit-stride dim, or two different ones
+    dT = mine;
+    mask |= 1u << (a - 1);
+  }
+  if (dT < 0) return -1;
+  if (plan.size[0] < 8 || plan.size[dT] < 8) return -1; // tiny extents: the generic kernel is fine
+  *tmask = mask;
+  return dT;
+}
+
 } // namespace pb

@@ -213,6 +213,113 @@ void launch_ew_one(const IterPlan &plan, float *out, const float *const *ins, co
   note_kernel(names[c.vec == 4 ? 2 : (c.vec == 2 ? 1 : 0)][c.one_d ? 1 : 0]);
 }
 
+// ---- transposed operands: shared-memory tile transpose ------------------------------------------------
+// When the output is contiguous along dim 0 but some input is contiguous along another dim dT
+// (a transposed view: x.T + y, pack(x.T), the transpose gradient), reading that input along dim 0
+// would touch one 32-byte sector per element. Instead a CTA owns a 32 x 32 tile of (dim 0, dT):
+// transposed inputs are loaded with threads running along dT (coalesced), parked in shared memory
+// [32][33] (the pad avoids bank conflicts) and read back with threads running along dim 0, where
+// the other inputs and the output are coalesced.
+constexpr int kTileDim = 32;
+constexpr int kTileRows = 8; // threads per tile column; each thread handles 32 / 8 = 4 rows
+
+template <int NIN> struct TiledParams {
+  const float *in[NIN];
+  float *out;
+  u64 n0, nT;             // extents of dim 0 and dT
+  u64 s0[NIN + 1], sT[NIN + 1]; // element strides of out (index 0) and inputs along dim 0 / dT
+  int n_outer;            // remaining dims, flattened into blockIdx.z
+  u64 outer_size[MAX_NDIM];
+  u64 outer_stride[NIN + 1][MAX_NDIM];
+  unsigned tmask;         // bit a: input a is contiguous along dT (goes through shared memory)
+  u64 tiles0;             // tiles along dim 0 (blockIdx.x = tile0 + tiles0 * tileT)
+};
+
+template <class F, int NIN>
+__global__ void __launch_bounds__(kTileDim * kTileRows) ew_tiled_kernel(F f, TiledParams<NIN> p) {
+  __shared__ float tile[NIN][kTileDim][kTileDim + 1];
+  const u64 t0 = blockIdx.x % p.tiles0, tT = blockIdx.x / p.tiles0;
+  u64 off[NIN + 1];
+#pragma unroll
+  for (int a = 0; a <= NIN; ++a) off[a] = 0;
+  u64 rest = blockIdx.y;
+  for (int d = 0; d < p.n_outer; ++d) {
+    const u64 q = rest / p.outer_size[d], r = rest - q * p.outer_size[d];
+#pragma unroll
+    for (int a = 0; a <= NIN; ++a) off[a] += r * p.outer_stride[a][d];
+    rest = q;
+  }
+  const unsigned tx = threadIdx.x, ty = threadIdx.y;
+  // phase 1: transposed inputs, threads along dT
+#pragma unroll
+  for (int a = 0; a < NIN; ++a) {
+    if (!((p.tmask >> a) & 1u)) continue;
+    const u64 cT = tT * kTileDim + tx;
+#pragma unroll
+    for (int j = 0; j < kTileDim; j += kTileRows) {
+      const u64 c0 = t0 * kTileDim + ty + j;
+      if (cT < p.nT && c0 < p.n0)
+        tile[a][ty + j][tx] = p.in[a][off[a + 1] + c0 * p.s0[a + 1] + cT * p.sT[a + 1]];
+    }
+  }
+  __syncthreads();
+  // phase 2: threads along dim 0
+  const u64 c0 = t0 * kTileDim + tx;
+#pragma unroll
+  for (int j = 0; j < kTileDim; j += kTileRows) {
+    const u64 cT = tT * kTileDim + ty + j;
+    if (c0 < p.n0 && cT < p.nT) {
+      float x[NIN];
+#pragma unroll
+      for (int a = 0; a < NIN; ++a)
+        x[a] = ((p.tmask >> a) & 1u) ? tile[a][tx][ty + j]
+                                     : p.in[a][off[a + 1] + c0 * p.s0[a + 1] + cT * p.sT[a + 1]];
+      p.out[off[0] + c0 * p.s0[0] + cT * p.sT[0]] = f(x);
+    }
+  }
+}
+
+// Picks dT (>= 1) when the plan fits the tiled kernel; returns -1 otherwise.
+int choose_tiled_dim(const IterPlan &plan, int nargs, unsigned *tmask);
+
+template <class F, int NIN>
+bool launch_ew_tiled(const IterPlan &plan, float *out, const float *const *ins, const F &f) {
+  unsigned tmask = 0;
+  const int dT = choose_tiled_dim(plan, NIN + 1, &tmask);
+  if (dT < 0) return false;
+  TiledParams<NIN> p;
+  for (int a = 0; a < NIN; ++a) p.in[a] = ins[a];
+  p.out = out;
+  p.n0 = plan.size[0];
+  p.nT = plan.size[dT];
+  p.tmask = tmask;
+  p.n_outer = 0;
+  u64 outer = 1;
+  for (int d = 1; d < plan.ndim; ++d) {
+    if (d == dT) continue;
+    p.outer_size[p.n_outer] = plan.size[d];
+    for (int a = 0; a <= NIN; ++a) p.outer_stride[a][p.n_outer] = plan.stride[a][d];
+    outer *= plan.size[d];
+    ++p.n_outer;
+  }
+  for (int d = p.n_outer; d < MAX_NDIM; ++d) {
+    p.outer_size[d] = 1;
+    for (int a = 0; a <= NIN; ++a) p.outer_stride[a][d] = 0;
+  }
+  for (int a = 0; a <= NIN; ++a) {
+    p.s0[a] = plan.stride[a][0];
+    p.sT[a] = plan.stride[a][dT];
+  }
+  p.tiles0 = (p.n0 + kTileDim - 1) / kTileDim;
+  const u64 tilesT = (p.nT + kTileDim - 1) / kTileDim;
+  if (p.tiles0 * tilesT > 0x7fffffffull || outer > 65535) return false; // grid limits: generic path
+  dim3 grid((unsigned)(p.tiles0 * tilesT), (unsigned)outer), block(kTileDim, kTileRows);
+  ew_tiled_kernel<F, NIN><<<grid, block, 0, stream()>>>(f, p);
+  count_launch();
+  note_kernel("ew_tiled_transpose");
+  return true;
+}
+
 // Public entry: 1-D plans whose length is not a multiple of 4 run as a vector body plus a
 // <= 3 element tail, so an odd element count does not force the whole tensor onto scalar loads.
 template <class F, int NIN>
@@ -238,6 +345,7 @@ void launch_ew(const IterPlan &plan, float *out, const float *const *ins, const 
       return;
     }
   }
+  if (plan.numel != 0 && launch_ew_tiled<F, NIN>(plan, out, ins, f)) return;
   launch_ew_one<F, NIN>(plan, out, ins, f);
 }
 

@@ -147,7 +147,14 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
                    M * M * F + 4, M * M, ws)
             timeit(4, "full_max" + name, lambda tin=tin: pb.forward("max", [tin], tone, dim=pb.FULL_REDUCE, check=False),
                    M * M * F + 4, M * M, ws)
-        del X
+        # elementwise ops on the transposed view: the view is staged through shared-memory tiles
+        Y2, Z2 = uniform((M, M), 1, -1, 1), torch.empty((M, M), device=dev)
+        tY2, tZ2 = wrap(Y2), wrap(Z2)
+        timeit(4, "add_transposed_view_plus_contiguous", lambda: pb.forward("add", [tXT, tY2], tZ2, check=False),
+               3 * M * M * F, M * M, 3 * ws)
+        timeit(4, "pack_transposed_view", lambda: pb.lib.plast_b200_pack(C.byref(tXT.c), C.c_void_p(Z2.data_ptr())),
+               2 * M * M * F, M * M, 2 * ws)
+        del X, Y2, Z2
     if 5 in configs:
         shape, pshape = (256, 256, 56, 56), (1, 256, 1, 1)
         n = int(np.prod(shape))

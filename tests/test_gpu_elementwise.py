@@ -82,6 +82,26 @@ def test_binary_transposed_and_expanded_views(cuda, oracle):
             outs.append((out.numpy(), out2.numpy()))
         assert_bit_equal(outs[0][0], outs[1][0], f"{op} transposed")
         assert_bit_equal(outs[0][1], outs[1][1], f"{op} expanded")
+    # a transposed operand goes through the shared-memory tile kernel, whatever the extents
+    import plast_b200 as pb
+    for m, n in [(8, 8), (33, 65), (100, 7), (7, 100), (256, 513)]:
+        a, b = rand_normal(3, (m, n)), rand_normal(4, (n, m))
+        outs = []
+        for be in (cuda, oracle):
+            out = be.empty((n, m))
+            be.forward("mul", [be.tensor(a).transpose(0, 1), be.tensor(b)], out)
+            outs.append(out.numpy())
+        if m >= 8 and n >= 8:
+            assert pb.last_kernel() == "ew_tiled_transpose"
+        assert_bit_equal(outs[0], outs[1], f"tiled {m}x{n}")
+    # 3-D: [B, M, N] with the last two axes swapped, plus a broadcast operand
+    a, b = rand_normal(5, (5, 40, 24)), rand_normal(6, (1, 24, 1))
+    outs = []
+    for be in (cuda, oracle):
+        out = be.empty((5, 24, 40))
+        be.forward("add", [be.tensor(a).transpose(1, 2), be.tensor(b)], out)
+        outs.append(out.numpy())
+    assert_bit_equal(outs[0], outs[1], "tiled 3-D")
 
 
 def test_relu_negative_zero_and_config1_forward(cuda, oracle):
