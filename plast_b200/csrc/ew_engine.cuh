@@ -282,6 +282,88 @@ __global__ void __launch_bounds__(kTileDim * kTileRows) ew_tiled_kernel(F f, Til
 // Picks dT (>= 1) when the plan fits the tiled kernel; returns -1 otherwise.
 int choose_tiled_dim(const IterPlan &plan, int nargs, unsigned *tmask);
 
+// 64 x 64 tiles moved as float4 in both directions (extents, strides and pointers permitting):
+// four 16-byte loads in flight per thread and input instead of four 4-byte ones.
+constexpr int kTile4 = 64;
+template <class F, int NIN>
+__global__ void __launch_bounds__(256) ew_tiled4_kernel(F f, TiledParams<NIN> p) {
+  extern __shared__ float tile4_smem[]; // [NIN][64][65]
+  const u64 t0 = blockIdx.x % p.tiles0, tT = blockIdx.x / p.tiles0;
+  u64 off[NIN + 1];
+#pragma unroll
+  for (int a = 0; a <= NIN; ++a) off[a] = 0;
+  u64 rest = blockIdx.y;
+  for (int d = 0; d < p.n_outer; ++d) {
+    const u64 q = rest / p.outer_size[d], r = rest - q * p.outer_size[d];
+#pragma unroll
+    for (int a = 0; a <= NIN; ++a) off[a] += r * p.outer_stride[a][d];
+    rest = q;
+  }
+  const unsigned q4 = threadIdx.x & 15, row = threadIdx.x >> 4; // 16 float4 across, 16 rows per pass
+  // phase 1: transposed inputs, float4 along dT, rows along dim 0
+#pragma unroll
+  for (int a = 0; a < NIN; ++a) {
+    if (!((p.tmask >> a) & 1u)) continue;
+    float *tl = tile4_smem + (size_t)a * kTile4 * (kTile4 + 1);
+    const u64 cT = tT * kTile4 + q4 * 4;
+    float4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const u64 c0 = t0 * kTile4 + row + j * 16;
+      if (cT < p.nT && c0 < p.n0)
+        v[j] = __ldcs(reinterpret_cast<const float4 *>(p.in[a] + off[a + 1] + c0 * p.s0[a + 1] + cT));
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float *dst = tl + (row + j * 16) * (kTile4 + 1) + q4 * 4;
+      dst[0] = v[j].x; dst[1] = v[j].y; dst[2] = v[j].z; dst[3] = v[j].w;
+    }
+  }
+  __syncthreads();
+  // phase 2: float4 along dim 0, rows along dT
+  const u64 c0 = t0 * kTile4 + q4 * 4;
+  float4 direct[4][NIN];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const u64 cT = tT * kTile4 + row + j * 16;
+    if (c0 < p.n0 && cT < p.nT) {
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) {
+        if ((p.tmask >> a) & 1u) continue;
+        const float *q = p.in[a] + off[a + 1] + c0 * p.s0[a + 1] + cT * p.sT[a + 1];
+        if (p.s0[a + 1] == 1) {
+          direct[j][a] = __ldcs(reinterpret_cast<const float4 *>(q));
+        } else { // broadcast along dim 0
+          const float sc = __ldg(q);
+          direct[j][a] = make_float4(sc, sc, sc, sc);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const u64 cT = tT * kTile4 + row + j * 16;
+    if (c0 < p.n0 && cT < p.nT) {
+      float r[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float x[NIN];
+#pragma unroll
+        for (int a = 0; a < NIN; ++a) {
+          if ((p.tmask >> a) & 1u) {
+            x[a] = tile4_smem[(size_t)a * kTile4 * (kTile4 + 1) + (q4 * 4 + k) * (kTile4 + 1) + row + j * 16];
+          } else {
+            const float4 d = direct[j][a];
+            x[a] = k == 0 ? d.x : (k == 1 ? d.y : (k == 2 ? d.z : d.w));
+          }
+        }
+        r[k] = f(x);
+      }
+      __stcs(reinterpret_cast<float4 *>(p.out + off[0] + c0 + cT * p.sT[0]), make_float4(r[0], r[1], r[2], r[3]));
+    }
+  }
+}
+
 template <class F, int NIN>
 bool launch_ew_tiled(const IterPlan &plan, float *out, const float *const *ins, const F &f) {
   unsigned tmask = 0;
@@ -310,9 +392,37 @@ bool launch_ew_tiled(const IterPlan &plan, float *out, const float *const *ins, 
     p.s0[a] = plan.stride[a][0];
     p.sT[a] = plan.stride[a][dT];
   }
+  if (outer > 65535) return false; // grid limit: the generic path takes it
+  // float4 both ways needs 4-divisible extents, 16-byte aligned bases and 4-divisible strides
+  bool vec4 = (p.n0 % 4 == 0) && (p.nT % 4 == 0) && (((uintptr_t)out) % 16 == 0);
+  for (int a = 0; vec4 && a < NIN; ++a) vec4 = ((uintptr_t)ins[a]) % 16 == 0;
+  for (int a = 0; vec4 && a <= NIN; ++a) {
+    const bool t = a > 0 && ((tmask >> (a - 1)) & 1u);
+    // along the arg's own contiguous dim the stride is 1; every other stride must keep alignment
+    if ((t ? p.s0[a] : p.sT[a]) % 4 != 0) vec4 = false;
+    for (int d = 0; d < p.n_outer; ++d)
+      if (p.outer_stride[a][d] % 4 != 0) vec4 = false;
+  }
+  const size_t smem4 = (size_t)NIN * kTile4 * (kTile4 + 1) * sizeof(float);
+  if (vec4 && smem4 <= 99 * 1024) {
+    p.tiles0 = (p.n0 + kTile4 - 1) / kTile4;
+    const u64 tilesT = (p.nT + kTile4 - 1) / kTile4;
+    if (p.tiles0 * tilesT <= 0x7fffffffull) {
+      static bool ready = false;
+      if (!ready) {
+        cudaFuncSetAttribute(ew_tiled4_kernel<F, NIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4);
+        ready = true;
+      }
+      dim3 grid((unsigned)(p.tiles0 * tilesT), (unsigned)outer);
+      ew_tiled4_kernel<F, NIN><<<grid, 256, smem4, stream()>>>(f, p);
+      count_launch();
+      note_kernel("ew_tiled_transpose");
+      return true;
+    }
+  }
   p.tiles0 = (p.n0 + kTileDim - 1) / kTileDim;
   const u64 tilesT = (p.nT + kTileDim - 1) / kTileDim;
-  if (p.tiles0 * tilesT > 0x7fffffffull || outer > 65535) return false; // grid limits: generic path
+  if (p.tiles0 * tilesT > 0x7fffffffull) return false;
   dim3 grid((unsigned)(p.tiles0 * tilesT), (unsigned)outer), block(kTileDim, kTileRows);
   ew_tiled_kernel<F, NIN><<<grid, block, 0, stream()>>>(f, p);
   count_launch();
