@@ -330,7 +330,8 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_per_op:
         from plast_b200.opbench import per_op_table
         del x_h, y_h, z_h
-        per_op = per_op_table(torch, pb, dev, peak, reps=args.op_reps)
+        per_op = per_op_table(torch, pb, dev, peak, reps=args.op_reps,
+                              configs=tuple(int(c) for c in args.configs.split(",")))
 
     sharded = None
     if world > 1 and not args.no_per_op:
@@ -368,6 +369,21 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_per_op_only(args):
+    import torch
+    import plast_b200 as pb
+    from plast_b200.opbench import per_op_table
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    pb.lib.plast_b200_set_stream(C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    peak, kind = measured_peak()
+    cfgs = tuple(int(c) for c in args.configs.split(","))
+    rows = per_op_table(torch, pb, dev, peak, reps=args.op_reps, configs=cfgs)
+    print(json.dumps({"per_op": rows, "peak_gbs": peak, "peak_source": f"of {kind}"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -378,9 +394,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-per-op", action="store_true", help="skip the per-op table of configs 1-5")
     ap.add_argument("--op-reps", type=int, default=10)
+    ap.add_argument("--per-op-only", action="store_true",
+                    help="only the per-op table (1 GPU); with --op-reps 0 every op is launched 3 times and "
+                         "not timed, which is the command the profiler captures use")
+    ap.add_argument("--configs", default="1,2,3,4,5", help="configs of the per-op table")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.per_op_only:
+        run_per_op_only(args)
     else:
         run_ours(args)
 

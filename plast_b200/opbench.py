@@ -59,10 +59,39 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
             times.append(e0.elapsed_time(e1) / inner)
         ms = float(np.median(times)) if times else float('nan')
         gbs = nbytes / (ms * 1e-3) / 1e9
-        rows.append({"config": cfg, "op": name, "kernel": kernel, "ms": round(ms, 5),
-                     "bytes": int(nbytes), "GBps": round(gbs, 1), "elements_per_s": elems / (ms * 1e-3),
-                     "frac_of_measured": round(gbs / peak_gbs, 4), "frac_of_nominal": round(gbs / NOMINAL, 4),
-                     "l2_flushed": flush})
+        row = {"config": cfg, "op": name, "kernel": kernel, "ms": round(ms, 5),
+               "bytes": int(nbytes), "GBps": round(gbs, 1), "elements_per_s": elems / (ms * 1e-3),
+               "frac_of_measured": round(gbs / peak_gbs, 4), "frac_of_nominal": round(gbs / NOMINAL, 4),
+               "l2_flushed": flush}
+        if flush and reps > 0:
+            # Launch-bound sizes: also time 50 launches replayed from one CUDA graph (no host launch
+            # cost, data stays in L2) - the per-launch cost a graph-capturing scheduler would see.
+            try:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.stream(side):
+                    pb.lib.plast_b200_set_stream(C.c_void_p(side.cuda_stream))
+                    fn()
+                    with torch.cuda.graph(graph, stream=side):
+                        for _ in range(50):
+                            fn()
+                pb.lib.plast_b200_set_stream(C.c_void_p(torch.cuda.current_stream().cuda_stream))
+                torch.cuda.synchronize()
+                graph.replay()
+                gt = []
+                for _ in range(5):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(); graph.replay(); e1.record()
+                    torch.cuda.synchronize()
+                    gt.append(e0.elapsed_time(e1) / 50)
+                gms = float(np.median(gt))
+                row["graph_replay_ms_per_launch_l2_resident"] = round(gms, 5)
+                row["graph_replay_GBps_l2_resident"] = round(nbytes / (gms * 1e-3) / 1e9, 1)
+            except Exception as exc:  # capture is an extra; never fail the table for it
+                pb.lib.plast_b200_set_stream(C.c_void_p(torch.cuda.current_stream().cuda_stream))
+                row["graph_replay_error"] = str(exc)[:120]
+        rows.append(row)
 
     F = 4
     if 1 in configs:
