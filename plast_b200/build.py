@@ -30,6 +30,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC,-O2,-fvisibility=default",
     "-I", str(ROOT / "include"),
     "-I", str(CSRC),
+    "-I", str(OBJ),
 ]
 
 
@@ -60,6 +61,12 @@ def _stale(src: Path, obj: Path, headers_mtime: float) -> bool:
 def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
     nvcc = _nvcc()
     OBJ.mkdir(parents=True, exist_ok=True)
+    # the device side of the elementwise engine as a string literal, for the NVRTC chain compiler
+    dev_src = (CSRC / "ew_kernel_device.cuh").read_text()
+    inc = OBJ / "ew_kernel_device_src.inc"
+    text = 'R"PBSRC(' + dev_src + ')PBSRC"\n'
+    if not inc.exists() or inc.read_text() != text:
+        inc.write_text(text)
     headers = list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list((ROOT / "include").glob("*.h"))
     headers_mtime = max(h.stat().st_mtime for h in headers)
     jobs = []

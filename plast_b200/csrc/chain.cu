@@ -148,6 +148,14 @@ static bool is_sigmoid_mul_add_exp_neg_abs(const ChainProgram &p) {
   return p.fval[2] == 1.0f && p.fval[3] == 1.0f;
 }
 
+// chain_jit.cu
+struct ChainProgramView {
+  int n_inputs, n_steps;
+  const unsigned char *opcode, *a, *b;
+  const float *fval;
+};
+bool launch_chain_jit(const ChainProgramView &p, const IterPlan &plan, float *out, const float *const *ins);
+
 static bool float_only(const Tensor *t, const char *op) {
   if (t->dtype != FLOAT32) {
     set_error(PLAST_B200_ERR_DTYPE, "%s: unsupported dtype %d", op, (int)t->dtype);
@@ -319,6 +327,30 @@ void plast_b200_chain_forward(const Tensor **inputs, int n_inputs, Tensor *outpu
     if (!failed()) note_kernel("chain_precompiled");
     end_call();
     return;
+  }
+  // Run-time compiled functor (NVRTC), same rounding as the interpreter; falls through to the
+  // interpreter when the compiler is unavailable.
+  {
+    u64 st[PLAST_CHAIN_MAX_INPUTS + 1][MAX_NDIM] = {};
+    const float *ins[PLAST_CHAIN_MAX_INPUTS] = {};
+    for (u64 d = 0; d < output->ndim; ++d) st[0][d] = output->strides[d];
+    bool ok = true;
+    for (int a = 0; ok && a < n_inputs; ++a) {
+      if (!check_tensor(inputs[a], name) || !float_only(inputs[a], name)) return;
+      if (!broadcast_strides(inputs[a], output->shape, output->ndim, st[a + 1])) {
+        set_error(PLAST_B200_ERR_SHAPE, "%s: input %d does not broadcast to the output shape", name, a);
+        return;
+      }
+      ins[a] = (const float *)inputs[a]->data;
+    }
+    IterPlan plan;
+    make_plan(&plan, output->shape, output->ndim, n_inputs + 1, st, nullptr, 0);
+    const ChainProgramView view{n_inputs, n_steps, prog.opcode, prog.a, prog.b, prog.fval};
+    if (launch_chain_jit(view, plan, (float *)output->data, ins)) {
+      note_kernel("chain_jit");
+      end_call();
+      return;
+    }
   }
   switch (n_inputs) {
   case 1: fused_forward<ChainInterp<1>, 1>(name, inputs, output, ChainInterp<1>{prog}); break;

@@ -1,0 +1,278 @@
+// Run-time compilation of fused elementwise chains.
+//
+// plast_b200_chain_forward receives a straight-line program of elementwise steps. Interpreting it
+// inside a kernel keeps the result exact but indexes a per-thread register file dynamically, which
+// lands in local memory and costs a multiple of the HBM time. Here the program is turned into a
+// functor in CUDA C++ (one `const float rK = ...;` per step, every step still rounded on its own:
+// NVRTC gets --fmad=false), compiled by NVRTC for sm_100a together with the very same ew_kernel
+// template the ahead-of-time build uses (ew_kernel_device.cuh is embedded as text), and launched
+// through the driver API. Compiled kernels are cached per (program structure, inputs, vector
+// width, index width, 1-D); scalar constants travel as kernel arguments, so a chain that differs
+// only in its constants reuses the binary. This is the role the reference's README assigns to its
+// NVRTC JIT ("in development", README.md:90,188).
+//
+// libnvrtc and libcuda are opened with dlopen on first use; when either is missing, or a compile
+// fails, the caller falls back to the in-kernel interpreter (still a GPU kernel of this library).
+#include "ew_engine.cuh"
+
+#include <dlfcn.h>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+
+namespace pb {
+
+static const char *kDeviceSource =
+#include "ew_kernel_device_src.inc"
+    ;
+
+struct ChainProgramView { // mirrors ChainProgram of chain.cu (kept POD so both files agree)
+  int n_inputs, n_steps;
+  const unsigned char *opcode, *a, *b;
+  const float *fval;
+};
+
+namespace {
+
+// ---- minimal NVRTC / driver API surface, resolved at run time -------------------------------------
+typedef int nvrtcResult;
+typedef struct _nvrtcProgram *nvrtcProgram;
+typedef int CUresult;
+typedef struct CUmod_st *CUmodule;
+typedef struct CUfunc_st *CUfunction;
+typedef struct CUstream_st *CUstream;
+
+struct Api {
+  bool ok = false;
+  nvrtcResult (*CreateProgram)(nvrtcProgram *, const char *, const char *, int, const char *const *,
+                               const char *const *) = nullptr;
+  nvrtcResult (*DestroyProgram)(nvrtcProgram *) = nullptr;
+  nvrtcResult (*CompileProgram)(nvrtcProgram, int, const char *const *) = nullptr;
+  nvrtcResult (*AddNameExpression)(nvrtcProgram, const char *) = nullptr;
+  nvrtcResult (*GetLoweredName)(nvrtcProgram, const char *, const char **) = nullptr;
+  nvrtcResult (*GetCUBINSize)(nvrtcProgram, size_t *) = nullptr;
+  nvrtcResult (*GetCUBIN)(nvrtcProgram, char *) = nullptr;
+  nvrtcResult (*GetProgramLogSize)(nvrtcProgram, size_t *) = nullptr;
+  nvrtcResult (*GetProgramLog)(nvrtcProgram, char *) = nullptr;
+  CUresult (*ModuleLoadData)(CUmodule *, const void *) = nullptr;
+  CUresult (*ModuleGetFunction)(CUfunction *, CUmodule, const char *) = nullptr;
+  CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
+                           unsigned, CUstream, void **, void **) = nullptr;
+};
+
+template <class Fn> bool resolve(void *lib, const char *name, Fn *out) {
+  *out = reinterpret_cast<Fn>(dlsym(lib, name));
+  return *out != nullptr;
+}
+
+Api &api() {
+  static Api a = [] {
+    Api r;
+    void *rtc = nullptr;
+    for (const char *n : {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12"}) {
+      rtc = dlopen(n, RTLD_NOW | RTLD_LOCAL);
+      if (rtc) break;
+    }
+    void *drv = dlopen("libcuda.so.1", RTLD_NOW | RTLD_LOCAL);
+    if (!rtc || !drv) return r;
+    bool ok = resolve(rtc, "nvrtcCreateProgram", &r.CreateProgram) &&
+              resolve(rtc, "nvrtcDestroyProgram", &r.DestroyProgram) &&
+              resolve(rtc, "nvrtcCompileProgram", &r.CompileProgram) &&
+              resolve(rtc, "nvrtcAddNameExpression", &r.AddNameExpression) &&
+              resolve(rtc, "nvrtcGetLoweredName", &r.GetLoweredName) &&
+              resolve(rtc, "nvrtcGetCUBINSize", &r.GetCUBINSize) &&
+              resolve(rtc, "nvrtcGetCUBIN", &r.GetCUBIN) &&
+              resolve(rtc, "nvrtcGetProgramLogSize", &r.GetProgramLogSize) &&
+              resolve(rtc, "nvrtcGetProgramLog", &r.GetProgramLog) &&
+              resolve(drv, "cuModuleLoadData", &r.ModuleLoadData) &&
+              resolve(drv, "cuModuleGetFunction", &r.ModuleGetFunction) &&
+              resolve(drv, "cuLaunchKernel", &r.LaunchKernel);
+    r.ok = ok;
+    return r;
+  }();
+  return a;
+}
+
+// ---- source generation --------------------------------------------------------------------------------
+const char *step_expr(int opcode) {
+  switch (opcode) {
+  case PLAST_CHAIN_ADD: return "A + B";
+  case PLAST_CHAIN_SUB: return "A - B";
+  case PLAST_CHAIN_MUL: return "A * B";
+  case PLAST_CHAIN_DIV: return "A / B";
+  case PLAST_CHAIN_NEG: return "-A";
+  case PLAST_CHAIN_ABS: return "fabsf(A)";
+  case PLAST_CHAIN_EXP: return "expf(A)";
+  case PLAST_CHAIN_LOG: return "logf(A)";
+  case PLAST_CHAIN_SIN: return "sinf(A)";
+  case PLAST_CHAIN_COS: return "cosf(A)";
+  case PLAST_CHAIN_TAN: return "(float)tan((double)A)";
+  case PLAST_CHAIN_LEAKY_RELU: return "(A > 0.0f ? A : A * C)";
+  case PLAST_CHAIN_ADD_SCALAR: return "A + C";
+  case PLAST_CHAIN_RSUB_SCALAR: return "C - A";
+  case PLAST_CHAIN_MUL_SCALAR: return "A * C";
+  default: return "C / A"; // PLAST_CHAIN_RDIV_SCALAR
+  }
+}
+
+std::string functor_source(const ChainProgramView &p) {
+  std::string s = "namespace pb {\nstruct JitF {\n  float c[" + std::to_string(PLAST_CHAIN_MAX_STEPS) +
+                  "];\n  __device__ __forceinline__ float operator()(const float *x) const {\n";
+  for (int i = 0; i < p.n_inputs; ++i)
+    s += "    const float r" + std::to_string(i) + " = x[" + std::to_string(i) + "];\n";
+  for (int k = 0; k < p.n_steps; ++k) {
+    std::string e = step_expr(p.opcode[k]);
+    auto sub = [&](const std::string &from, const std::string &to) {
+      for (size_t pos = 0; (pos = e.find(from, pos)) != std::string::npos; pos += to.size())
+        e.replace(pos, from.size(), to);
+    };
+    // single capital letters never occur in the function names above except as placeholders
+    sub("A", "r" + std::to_string(p.a[k]));
+    sub("B", "r" + std::to_string(p.b[k]));
+    sub("C", "c[" + std::to_string(k) + "]");
+    s += "    const float r" + std::to_string(p.n_inputs + k) + " = " + e + ";\n";
+  }
+  s += "    return r" + std::to_string(p.n_inputs + p.n_steps - 1) + ";\n  }\n};\n} // namespace pb\n";
+  return s;
+}
+
+std::string structure_key(const ChainProgramView &p) {
+  std::string k = std::to_string(p.n_inputs) + ":";
+  for (int i = 0; i < p.n_steps; ++i)
+    k += std::to_string(p.opcode[i]) + "," + std::to_string(p.a[i]) + "," + std::to_string(p.b[i]) + ";";
+  return k;
+}
+
+std::mutex g_mutex;
+std::unordered_map<std::string, CUfunction> g_cache; // nullptr = compile failed, do not retry
+
+CUfunction get_kernel(const ChainProgramView &p, int vec, bool idx64, bool one_d) {
+  Api &a = api();
+  if (!a.ok) return nullptr;
+  const std::string inst = "pb::ew_kernel<pb::JitF, " + std::to_string(p.n_inputs) + ", " +
+                           std::to_string(vec) + ", " + (idx64 ? "unsigned long long" : "unsigned int") +
+                           ", " + (one_d ? "true" : "false") + ">";
+  const std::string key = structure_key(p) + inst;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  auto it = g_cache.find(key);
+  if (it != g_cache.end()) return it->second;
+  CUfunction fn = nullptr;
+  const std::string src = std::string(kDeviceSource) + "\n" + functor_source(p) +
+                          "\ntemplate __global__ void " + inst +
+                          "(pb::JitF, float *, pb::InPtrs<" + std::to_string(p.n_inputs) + ">, pb::OffsetCalc<" +
+                          std::to_string(p.n_inputs + 1) + ", " + (idx64 ? "unsigned long long" : "unsigned int") +
+                          ">, " + (idx64 ? "unsigned long long" : "unsigned int") + ", unsigned int);\n";
+  nvrtcProgram prog = nullptr;
+  if (a.CreateProgram(&prog, src.c_str(), "plast_chain.cu", 0, nullptr, nullptr) == 0) {
+    a.AddNameExpression(prog, inst.c_str());
+    const char *opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "--std=c++17"};
+    const nvrtcResult rc = a.CompileProgram(prog, 3, opts);
+    if (rc == 0) {
+      const char *lowered = nullptr;
+      size_t size = 0;
+      if (a.GetLoweredName(prog, inst.c_str(), &lowered) == 0 && lowered &&
+          a.GetCUBINSize(prog, &size) == 0 && size > 0) {
+        std::string cubin(size, '\0');
+        CUmodule mod = nullptr;
+        if (a.GetCUBIN(prog, &cubin[0]) == 0 && a.ModuleLoadData(&mod, cubin.data()) == 0)
+          if (a.ModuleGetFunction(&fn, mod, lowered) != 0) fn = nullptr;
+      }
+    } else {
+      size_t n = 0;
+      a.GetProgramLogSize(prog, &n);
+      std::string log(n + 1, '\0');
+      if (n) a.GetProgramLog(prog, &log[0]);
+      fprintf(stderr, "plast: chain JIT compile failed (%d), using the interpreter:\n%s\n", rc, log.c_str());
+    }
+    a.DestroyProgram(&prog);
+  }
+  g_cache[key] = fn;
+  return fn;
+}
+
+struct JitFHost {
+  float c[PLAST_CHAIN_MAX_STEPS];
+};
+
+template <int NIN, typename index_t>
+bool launch_variant(CUfunction fn, const IterPlan &plan, float *out, const float *const *ins,
+                    const JitFHost &f, int vec, u64 n_items, uint32_t vec_mask, unsigned blocks) {
+  InPtrs<NIN> ip;
+  for (int a = 0; a < NIN; ++a) ip.p[a] = ins[a];
+  OffsetCalc<NIN + 1, index_t> oc;
+  fill_offset_calc(&oc, plan, vec);
+  index_t n = (index_t)n_items;
+  JitFHost fcopy = f;
+  void *args[] = {&fcopy, &out, &ip, &oc, &n, &vec_mask};
+  return api().LaunchKernel(fn, blocks, 1, 1, kEwThreads, 1, 1, 0, (CUstream)stream(), args, nullptr) == 0;
+}
+
+template <int NIN>
+bool launch_one(const ChainProgramView &p, const IterPlan &plan, float *out, const float *const *ins,
+                const JitFHost &f) {
+  if (plan.numel == 0) return true;
+  const void *ptrs[NIN + 1];
+  ptrs[0] = out;
+  for (int a = 0; a < NIN; ++a) ptrs[a + 1] = ins[a];
+  u64 n_items = 0;
+  uint32_t vec_mask = 0;
+  const EwChoice c = choose_ew(plan, ptrs, NIN + 1, &n_items, &vec_mask);
+  const u64 per_block = (u64)kEwThreads * kEwUnroll;
+  const u64 blocks = (n_items + per_block - 1) / per_block;
+  if (blocks > 0x7fffffffull) return false;
+  CUfunction fn = get_kernel(p, c.vec, c.idx64, c.one_d);
+  if (!fn) return false;
+  const bool ok = c.idx64 ? launch_variant<NIN, uint64_t>(fn, plan, out, ins, f, c.vec, n_items, vec_mask, (unsigned)blocks)
+                          : launch_variant<NIN, uint32_t>(fn, plan, out, ins, f, c.vec, n_items, vec_mask, (unsigned)blocks);
+  if (ok) count_launch();
+  return ok;
+}
+
+template <int NIN>
+bool launch_plan(const ChainProgramView &p, const IterPlan &plan, float *out, const float *const *ins,
+                 const JitFHost &f) {
+  // same body + tail split as launch_ew for 1-D plans of odd length
+  if (plan.ndim == 1 && plan.size[0] >= 8 && (plan.size[0] & 3) != 0 && plan.stride[0][0] == 1) {
+    bool ok = true;
+    for (int a = 1; a <= NIN; ++a) ok = ok && plan.stride[a][0] <= 1;
+    if (ok) {
+      const u64 body_n = plan.size[0] & ~(u64)3;
+      IterPlan body = plan, tail = plan;
+      body.size[0] = body_n;
+      body.numel = body_n;
+      tail.size[0] = plan.size[0] - body_n;
+      tail.numel = tail.size[0];
+      const float *tins[NIN];
+      for (int a = 0; a <= NIN; ++a) {
+        body.max_offset[a] = (body_n - 1) * plan.stride[a][0];
+        tail.max_offset[a] = (tail.size[0] - 1) * plan.stride[a][0];
+        if (a > 0) tins[a - 1] = ins[a - 1] + body_n * plan.stride[a][0];
+      }
+      return launch_one<NIN>(p, body, out, ins, f) && launch_one<NIN>(p, tail, out + body_n, tins, f);
+    }
+  }
+  return launch_one<NIN>(p, plan, out, ins, f);
+}
+
+} // namespace
+
+// Returns false when the chain could not be compiled or launched this way; nothing has been
+// launched in that case (a failed tail after a launched body is reported as an error instead).
+bool launch_chain_jit(const ChainProgramView &p, const IterPlan &plan, float *out, const float *const *ins) {
+  static const bool disabled = [] {
+    const char *e = getenv("PLAST_B200_CHAIN_JIT");
+    return e && e[0] == '0';
+  }();
+  if (disabled || !api().ok) return false;
+  JitFHost f = {};
+  for (int k = 0; k < p.n_steps; ++k) f.c[k] = p.fval[k];
+  switch (p.n_inputs) {
+  case 1: return launch_plan<1>(p, plan, out, ins, f);
+  case 2: return launch_plan<2>(p, plan, out, ins, f);
+  case 3: return launch_plan<3>(p, plan, out, ins, f);
+  case 4: return launch_plan<4>(p, plan, out, ins, f);
+  default: return false;
+  }
+}
+
+} // namespace pb
