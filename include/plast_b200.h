@@ -188,7 +188,10 @@ void add_leaky_relu_cuda_backward(Tensor **inputs, const Tensor *output, KernelP
  * The program is a list of steps over a small register file; register r < n_inputs is preloaded
  * with inputs[r] (broadcast against the output shape); each step writes register
  * n_inputs + step_index; the last step's register is stored to output. Every step rounds to
- * fp32 exactly like the standalone op.
+ * fp32 exactly like the standalone op. A program is compiled at run time on first use (NVRTC,
+ * cached per program structure; the scalar constants are arguments) and runs at the speed of a
+ * hand-written fused kernel; without libnvrtc / libcuda an in-kernel interpreter is used
+ * (PLAST_B200_CHAIN_JIT=0 forces it).
  * ------------------------------------------------------------------------------------------ */
 typedef enum PlastChainOpcode {
   PLAST_CHAIN_ADD = 0,
