@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-per-op]
 
-Headline workload (BASELINE config 2): the fused chain z = sigmoid(x) * y + exp(-abs(x)) over
+Headline workload (benchmark configuration 2): the fused chain z = sigmoid(x) * y + exp(-abs(x)) over
 2^28 fp32 elements per GPU (x ~ N(0,1) seed 0, y ~ N(0,1) seed 1), one step = one pass = one
 launch of plast_b200_chain_forward. Algorithmic bytes per element: 12 (read x, y; write z).
 The 3 GiB working set is far larger than L2, so no flush is needed between steps.
@@ -234,7 +234,7 @@ def run_ours(args):
     pb.lib.plast_b200_set_stream(C.c_void_p(torch.cuda.current_stream().cuda_stream))
 
     n = args.elems
-    # BASELINE config 2 inputs; rank r draws seeds (2r, 2r+1) so shards differ
+    # configuration 2 inputs; rank r draws seeds (2r, 2r+1) so shards differ
     x_h = torch.from_numpy(np.random.RandomState(2 * rank).randn(n).astype(np.float32)).pin_memory()
     y_h = torch.from_numpy(np.random.RandomState(2 * rank + 1).randn(n).astype(np.float32)).pin_memory()
     z_h = torch.empty(n, dtype=torch.float32).pin_memory()
@@ -389,7 +389,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--elems", type=int, default=N_ELEMS,
-                    help="elements per GPU (default 2^28, the BASELINE size; smaller only for profiler captures)")
+                    help="elements per GPU (default 2^28, the benchmark size; smaller only for profiler captures)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-per-op", action="store_true", help="skip the per-op table of configs 1-5")

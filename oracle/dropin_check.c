@@ -13,7 +13,7 @@
  * reference's op table dispatching into this library). It compares the two and exits non-zero on
  * a mismatch.
  *
- * Graphs: (1) BASELINE config 1 in small: C = relu(A + b), s = sum(C, axis 1), backward from an
+ * Graphs: (1) benchmark configuration 1 in small: C = relu(A + b), s = sum(C, axis 1), backward from an
  * upstream gradient on C into b.grad (leaky_relu backward, then the broadcast-gradient reduce of
  * add backward); (2) the softmax recipe of plast/nn/functional.py:77-86 as five nodes;
  * (3) reductions over a transposed view made by the reference's transpose node.

@@ -1,5 +1,6 @@
 """The drop-in boundary, checked without a GPU: struct layouts, exported symbols, planner."""
 import ctypes as C
+import os
 import re
 import subprocess
 from pathlib import Path
@@ -11,7 +12,7 @@ import plast_b200 as pb
 
 ROOT = Path(__file__).resolve().parent.parent
 HEADER = ROOT / "include" / "plast_b200.h"
-REF_INCLUDE = Path("/root/reference/include")
+REF_INCLUDE = Path(os.environ.get("PLAST_REFERENCE", "/root/reference")) / "include"
 
 PROBE = r"""
 #include <stdio.h>

@@ -1,4 +1,4 @@
-"""The BASELINE configurations at FULL size, checked through properties that need no CPU pass over
+"""The five benchmark configurations at FULL size, checked through properties that need no CPU pass over
 the data: idempotence, involution, planted extrema, exact sums of exactly-representable values,
 rows of a softmax summing to one, a checksum of checksums. The seeded small-size parity tests
 (test_gpu_elementwise / test_gpu_reduce) pin the arithmetic; these pin the indexing, the vector
