@@ -78,7 +78,8 @@ typedef struct {
 
 static float frand(unsigned *st) {
   *st = *st * 1664525u + 1013904223u;
-  return (float)((*st >> 8) & 0xffff) / 32768.0f - 1.0f;
+  /* scaled by a value with a full mantissa so that sums really depend on the order of addition */
+  return ((float)((*st >> 8) & 0xffff) / 32768.0f - 1.0f) * 0.7317519f;
 }
 
 static void run(DEVICE dev, Results *res) {

@@ -88,7 +88,7 @@ def declared_symbols() -> list[str]:
         "plast_b200_clear_error", "plast_b200_set_stream", "plast_b200_get_stream",
         "plast_b200_set_sync", "plast_b200_launch_count", "plast_b200_last_kernel",
         "plast_b200_release_workspace", "plast_b200_version", "plast_b200_plan_debug",
-        "sum_axis0_noalloc_cuda_forward",
+        "sum_axis0_noalloc_cuda_forward", "plast_b200_chain_source", "plast_b200_chain_try_compile",
     ]
     return syms
 

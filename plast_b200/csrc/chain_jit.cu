@@ -16,6 +16,7 @@
 #include "ew_engine.cuh"
 
 #include <dlfcn.h>
+#include <string.h>
 #include <mutex>
 #include <string>
 #include <unordered_map>
@@ -32,8 +33,6 @@ struct ChainProgramView { // mirrors ChainProgram of chain.cu (kept POD so both 
   const float *fval;
 };
 
-namespace {
-
 // ---- minimal NVRTC / driver API surface, resolved at run time -------------------------------------
 typedef int nvrtcResult;
 typedef struct _nvrtcProgram *nvrtcProgram;
@@ -43,7 +42,8 @@ typedef struct CUfunc_st *CUfunction;
 typedef struct CUstream_st *CUstream;
 
 struct Api {
-  bool ok = false;
+  bool ok = false;      // compiler and driver both available
+  bool rtc_ok = false;  // compiler available (enough to check that a program compiles)
   nvrtcResult (*CreateProgram)(nvrtcProgram *, const char *, const char *, int, const char *const *,
                                const char *const *) = nullptr;
   nvrtcResult (*DestroyProgram)(nvrtcProgram *) = nullptr;
@@ -74,7 +74,7 @@ Api &api() {
       if (rtc) break;
     }
     void *drv = dlopen("libcuda.so.1", RTLD_NOW | RTLD_LOCAL);
-    if (!rtc || !drv) return r;
+    if (!rtc) return r;
     bool ok = resolve(rtc, "nvrtcCreateProgram", &r.CreateProgram) &&
               resolve(rtc, "nvrtcDestroyProgram", &r.DestroyProgram) &&
               resolve(rtc, "nvrtcCompileProgram", &r.CompileProgram) &&
@@ -83,11 +83,11 @@ Api &api() {
               resolve(rtc, "nvrtcGetCUBINSize", &r.GetCUBINSize) &&
               resolve(rtc, "nvrtcGetCUBIN", &r.GetCUBIN) &&
               resolve(rtc, "nvrtcGetProgramLogSize", &r.GetProgramLogSize) &&
-              resolve(rtc, "nvrtcGetProgramLog", &r.GetProgramLog) &&
-              resolve(drv, "cuModuleLoadData", &r.ModuleLoadData) &&
-              resolve(drv, "cuModuleGetFunction", &r.ModuleGetFunction) &&
-              resolve(drv, "cuLaunchKernel", &r.LaunchKernel);
-    r.ok = ok;
+              resolve(rtc, "nvrtcGetProgramLog", &r.GetProgramLog);
+    r.rtc_ok = ok;
+    r.ok = ok && drv && resolve(drv, "cuModuleLoadData", &r.ModuleLoadData) &&
+           resolve(drv, "cuModuleGetFunction", &r.ModuleGetFunction) &&
+           resolve(drv, "cuLaunchKernel", &r.LaunchKernel);
     return r;
   }();
   return a;
@@ -143,25 +143,30 @@ std::string structure_key(const ChainProgramView &p) {
   return k;
 }
 
+std::string instance_name(const ChainProgramView &p, int vec, bool idx64, bool one_d) {
+  return "pb::ew_kernel<pb::JitF, " + std::to_string(p.n_inputs) + ", " + std::to_string(vec) + ", " +
+         (idx64 ? "unsigned long long" : "unsigned int") + ", " + (one_d ? "true" : "false") + ">";
+}
+std::string program_source(const ChainProgramView &p, const std::string &inst, bool idx64) {
+  const char *idx = idx64 ? "unsigned long long" : "unsigned int";
+  return std::string(kDeviceSource) + "\n" + functor_source(p) + "\ntemplate __global__ void " + inst +
+         "(pb::JitF, float *, pb::InPtrs<" + std::to_string(p.n_inputs) + ">, pb::OffsetCalc<" +
+         std::to_string(p.n_inputs + 1) + ", " + idx + ">, " + idx + ", unsigned int);\n";
+}
+
 std::mutex g_mutex;
 std::unordered_map<std::string, CUfunction> g_cache; // nullptr = compile failed, do not retry
 
 CUfunction get_kernel(const ChainProgramView &p, int vec, bool idx64, bool one_d) {
   Api &a = api();
   if (!a.ok) return nullptr;
-  const std::string inst = "pb::ew_kernel<pb::JitF, " + std::to_string(p.n_inputs) + ", " +
-                           std::to_string(vec) + ", " + (idx64 ? "unsigned long long" : "unsigned int") +
-                           ", " + (one_d ? "true" : "false") + ">";
+  const std::string inst = instance_name(p, vec, idx64, one_d);
   const std::string key = structure_key(p) + inst;
   std::lock_guard<std::mutex> lock(g_mutex);
   auto it = g_cache.find(key);
   if (it != g_cache.end()) return it->second;
   CUfunction fn = nullptr;
-  const std::string src = std::string(kDeviceSource) + "\n" + functor_source(p) +
-                          "\ntemplate __global__ void " + inst +
-                          "(pb::JitF, float *, pb::InPtrs<" + std::to_string(p.n_inputs) + ">, pb::OffsetCalc<" +
-                          std::to_string(p.n_inputs + 1) + ", " + (idx64 ? "unsigned long long" : "unsigned int") +
-                          ">, " + (idx64 ? "unsigned long long" : "unsigned int") + ", unsigned int);\n";
+  const std::string src = program_source(p, inst, idx64);
   nvrtcProgram prog = nullptr;
   if (a.CreateProgram(&prog, src.c_str(), "plast_chain.cu", 0, nullptr, nullptr) == 0) {
     a.AddNameExpression(prog, inst.c_str());
@@ -254,8 +259,6 @@ bool launch_plan(const ChainProgramView &p, const IterPlan &plan, float *out, co
   return launch_one<NIN>(p, plan, out, ins, f);
 }
 
-} // namespace
-
 // Returns false when the chain could not be compiled or launched this way; nothing has been
 // launched in that case (a failed tail after a launched body is reported as an error instead).
 bool launch_chain_jit(const ChainProgramView &p, const IterPlan &plan, float *out, const float *const *ins) {
@@ -276,3 +279,62 @@ bool launch_chain_jit(const ChainProgramView &p, const IterPlan &plan, float *ou
 }
 
 } // namespace pb
+
+// ---- test hooks (declared in include/plast_b200.h; need no GPU) ------------------------------------------
+static bool view_of(const PlastChainStep *steps, int n_steps, int n_inputs, unsigned char *op,
+                    unsigned char *a, unsigned char *b, float *f, pb::ChainProgramView *v) {
+  if (!steps || n_inputs < 1 || n_inputs > PLAST_CHAIN_MAX_INPUTS || n_steps < 1 || n_steps > PLAST_CHAIN_MAX_STEPS)
+    return false;
+  for (int s = 0; s < n_steps; ++s) {
+    const bool binary = steps[s].opcode <= PLAST_CHAIN_DIV;
+    if (steps[s].opcode < 0 || steps[s].opcode > PLAST_CHAIN_RDIV_SCALAR || steps[s].a < 0 ||
+        steps[s].a >= n_inputs + s || (binary && (steps[s].b < 0 || steps[s].b >= n_inputs + s)))
+      return false;
+    op[s] = (unsigned char)steps[s].opcode;
+    a[s] = (unsigned char)steps[s].a;
+    b[s] = (unsigned char)(binary ? steps[s].b : steps[s].a);
+    f[s] = steps[s].fval;
+  }
+  *v = pb::ChainProgramView{n_inputs, n_steps, op, a, b, f};
+  return true;
+}
+
+extern "C" int plast_b200_chain_source(const PlastChainStep *steps, int n_steps, int n_inputs, char *buf,
+                                       size_t capacity) {
+  unsigned char op[PLAST_CHAIN_MAX_STEPS], a[PLAST_CHAIN_MAX_STEPS], b[PLAST_CHAIN_MAX_STEPS];
+  float f[PLAST_CHAIN_MAX_STEPS];
+  pb::ChainProgramView v;
+  if (!view_of(steps, n_steps, n_inputs, op, a, b, f, &v)) return -1;
+  const std::string src = pb::functor_source(v);
+  if (buf && capacity > 0) {
+    const size_t n = src.size() < capacity - 1 ? src.size() : capacity - 1;
+    memcpy(buf, src.data(), n);
+    buf[n] = 0;
+  }
+  return (int)src.size();
+}
+
+extern "C" int plast_b200_chain_try_compile(const PlastChainStep *steps, int n_steps, int n_inputs) {
+  unsigned char op[PLAST_CHAIN_MAX_STEPS], a[PLAST_CHAIN_MAX_STEPS], b[PLAST_CHAIN_MAX_STEPS];
+  float f[PLAST_CHAIN_MAX_STEPS];
+  pb::ChainProgramView v;
+  if (!view_of(steps, n_steps, n_inputs, op, a, b, f, &v)) return -1;
+  pb::Api &api = pb::api();
+  if (!api.rtc_ok) return -2;
+  const std::string inst = pb::instance_name(v, 4, false, true);
+  const std::string src = pb::program_source(v, inst, false);
+  pb::nvrtcProgram prog = nullptr;
+  if (api.CreateProgram(&prog, src.c_str(), "plast_chain.cu", 0, nullptr, nullptr) != 0) return -3;
+  api.AddNameExpression(prog, inst.c_str());
+  const char *opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "--std=c++17"};
+  const int rc = api.CompileProgram(prog, 3, opts);
+  if (rc != 0) {
+    size_t n = 0;
+    api.GetProgramLogSize(prog, &n);
+    std::string log(n + 1, '\0');
+    if (n) api.GetProgramLog(prog, &log[0]);
+    fprintf(stderr, "%s\n", log.c_str());
+  }
+  api.DestroyProgram(&prog);
+  return rc;
+}

@@ -56,6 +56,9 @@ bool get_workspace(Workspace *ws);
 
 int sm_count();
 
+// Fills n 32-bit words with a bit pattern on the library stream (helpers.cu).
+void fill32(void *data, unsigned int pattern, u64 n);
+
 // ---- tensor helpers ------------------------------------------------------------------------------
 inline u64 numel(const Tensor *t) {
   u64 n = 1;

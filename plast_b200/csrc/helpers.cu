@@ -26,7 +26,7 @@ __global__ void __launch_bounds__(256) fill_kernel(unsigned int *p, unsigned int
   if (tail_begin + i < n && i < 4) p[tail_begin + i] = value;
 }
 
-static void fill32(void *data, unsigned int pattern, u64 n) {
+void fill32(void *data, unsigned int pattern, u64 n) {
   if (n == 0) return;
   u64 blocks = (n / 4 + 255) / 256;
   const u64 cap = (u64)sm_count() * 16;

@@ -4,6 +4,8 @@
 #include "reduce_engine.cuh"
 
 #include <stdlib.h>
+#include <string.h>
+#include <type_traits>
 
 namespace pb {
 
@@ -260,6 +262,25 @@ static void reduce_forward(const char *name, const Tensor **inputs, Tensor *outp
     reduced_shape(a, dim, keepdim, output->shape, &output->ndim, output->strides);
     out_strides_in_a_dims(a, dim, keepdim, output->strides, tst);
     count = a->shape[dim];
+  }
+  if (numel(a) == 0) {
+    // Nothing to reduce: every output holds the start value of the CPU loop
+    // (src/kernels/cpu/reduce_ops.c:26,53: 0 for sum, -/+FLT_MAX for max / min; mean is 0 / 0).
+    u64 n_out = 1;
+    if (dim != PLAST_FULL_REDUCE) {
+      n_out = 1;
+      for (u64 j = 0; j < output->ndim; ++j) n_out *= output->shape[j];
+    }
+    float start = 0.0f;
+    if (std::is_same<Op, MaxOp>::value) start = -FLT_MAX;
+    if (std::is_same<Op, MinOp>::value) start = FLT_MAX;
+    if (mean) start = nanf("");
+    unsigned int bits;
+    memcpy(&bits, &start, 4);
+    if (std::is_same<Op, ArgMaxOp>::value) bits = 0;
+    fill32(output->data, bits, n_out);
+    end_call();
+    return;
   }
   IterPlan plan;
   reduce_plan(&plan, a, dim, tst);

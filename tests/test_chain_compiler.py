@@ -1,0 +1,60 @@
+"""The run-time chain compiler, checked without a GPU: the functor generated for a program, and a
+trial NVRTC compile of the complete kernel for sm_100a (skipped where libnvrtc is absent)."""
+import ctypes as C
+
+import pytest
+
+import plast_b200 as pb
+
+CHAIN = [("neg", 0, 0, 0.0), ("exp", 2, 0, 0.0), ("add_scalar", 3, 0, 1.0), ("rdiv_scalar", 4, 0, 1.0),
+         ("mul", 5, 1, 0.0), ("abs", 0, 0, 0.0), ("neg", 7, 0, 0.0), ("exp", 8, 0, 0.0), ("sub", 6, 9, 0.0)]
+
+
+def steps_array(steps):
+    arr = (pb.ChainStep * len(steps))()
+    for i, (name, a, b, f) in enumerate(steps):
+        arr[i] = pb.ChainStep(pb.CHAIN_OPCODES[name], a, b, f)
+    return arr
+
+
+def lib():
+    handle = C.CDLL(str(pb.LIB_PATH))
+    handle.plast_b200_chain_source.argtypes = [C.POINTER(pb.ChainStep), C.c_int, C.c_int, C.c_char_p, C.c_size_t]
+    handle.plast_b200_chain_source.restype = C.c_int
+    handle.plast_b200_chain_try_compile.argtypes = [C.POINTER(pb.ChainStep), C.c_int, C.c_int]
+    handle.plast_b200_chain_try_compile.restype = C.c_int
+    return handle
+
+
+def test_generated_functor_has_one_rounded_statement_per_step():
+    buf = C.create_string_buffer(8192)
+    n = lib().plast_b200_chain_source(steps_array(CHAIN), len(CHAIN), 2, buf, len(buf))
+    src = buf.value.decode()
+    assert n == len(src)
+    lines = [l.strip() for l in src.splitlines()]
+    assert "const float r0 = x[0];" in lines and "const float r1 = x[1];" in lines
+    assert "const float r2 = -r0;" in lines
+    assert "const float r3 = expf(r2);" in lines
+    assert "const float r4 = r3 + c[2];" in lines            # constants are kernel arguments
+    assert "const float r5 = c[3] / r4;" in lines
+    assert "const float r6 = r5 * r1;" in lines
+    assert "const float r7 = fabsf(r0);" in lines
+    assert "const float r10 = r6 - r9;" in lines and "return r10;" in lines
+    assert sum(l.startswith("const float r") for l in lines) == 2 + len(CHAIN)
+
+
+def test_malformed_programs_are_rejected():
+    h = lib()
+    assert h.plast_b200_chain_source(steps_array([("add", 0, 5, 0.0)]), 1, 2, None, 0) == -1   # register not yet written
+    assert h.plast_b200_chain_source(steps_array(CHAIN), len(CHAIN), 9, None, 0) == -1         # too many inputs
+
+
+def test_every_opcode_compiles_for_sm_100a():
+    prog = [("add", 0, 1, 0), ("sub", 2, 0, 0), ("mul", 3, 1, 0), ("div", 4, 1, 0), ("neg", 5, 0, 0), ("abs", 6, 0, 0),
+            ("exp", 7, 0, 0), ("log", 8, 0, 0), ("sin", 9, 0, 0), ("cos", 10, 0, 0), ("tan", 11, 0, 0),
+            ("leaky_relu", 12, 0, 0.1), ("add_scalar", 13, 0, 1.0), ("rsub_scalar", 14, 0, 2.0),
+            ("mul_scalar", 15, 0, 0.5), ("rdiv_scalar", 16, 0, 3.0)]
+    rc = lib().plast_b200_chain_try_compile(steps_array(prog), len(prog), 2)
+    if rc == -2:
+        pytest.skip("libnvrtc not available on this machine")
+    assert rc == 0

@@ -60,6 +60,21 @@ def test_reduce_all_axes(cuda, oracle, op, shape):
                 assert_sum_close(got.reshape(-1), want.reshape(-1), np.asarray(scale).reshape(-1), what=what)
 
 
+def test_empty_and_single_element_reductions(cuda, oracle):
+    # nothing to reduce: the outputs hold the start value of the CPU loop
+    for op, want in (("sum", 0.0), ("max", -np.finfo(np.float32).max), ("min", np.finfo(np.float32).max)):
+        got, ref = reduce_both(cuda, oracle, op, np.zeros((4, 0), np.float32), 1, False)
+        assert got.shape == (4,) and np.all(got == np.float32(want)) and np.array_equal(got, ref)
+    got, _ = reduce_both(cuda, oracle, "mean", np.zeros((4, 0), np.float32), 1, False)
+    assert np.all(np.isnan(got))
+    # 0-dim and single-element tensors
+    for shape in ((), (1,), (1, 1, 1)):
+        A = np.float32(3.5).reshape(shape)
+        for op in ("sum", "mean", "max", "min"):
+            got, ref = reduce_both(cuda, oracle, op, A, FULL_REDUCE, False)
+            assert got[0] == 3.5 == ref[0]
+
+
 def test_argmax_ties_pick_lowest_index(cuda, oracle):
     A = np.zeros((64, 4096), np.float32)
     A[:, 100] = 5.0; A[:, 3000] = 5.0; A[:, 4095] = 5.0
