@@ -219,7 +219,7 @@ typedef struct PlastChainStep {
   float fval; /* scalar operand / slope */
 } PlastChainStep;
 
-#define PLAST_CHAIN_MAX_INPUTS 4
+#define PLAST_CHAIN_MAX_INPUTS 8
 #define PLAST_CHAIN_MAX_STEPS 24
 
 void plast_b200_chain_forward(const Tensor **inputs, int n_inputs, Tensor *output,

@@ -16,7 +16,13 @@
  * Graphs: (1) benchmark configuration 1 in small: C = relu(A + b), s = sum(C, axis 1), backward from an
  * upstream gradient on C into b.grad (leaky_relu backward, then the broadcast-gradient reduce of
  * add backward); (2) the softmax recipe of plast/nn/functional.py:77-86 as five nodes;
- * (3) reductions over a transposed view made by the reference's transpose node.
+ * (3) reductions over a transposed view made by the reference's transpose node;
+ * (4) z = sigmoid(x) * y + exp(-abs(x)) as the nine nodes plast/tensor.py builds (the two 1.0
+ * constants are 0-dim tensors).
+ * On CUDA, (1), (2) and (4) run a second time on fresh graphs that go through build_dag, this
+ * library's plast_b200_fuse_graph (the call a maintainer adds after fusion_optimize in
+ * src/scheduler/scheduler.c:33) and the reference's dag_forward / dag_backward: the fused DAGs
+ * must have 2, 1 and 1 nodes and give the results of the node-by-node runs.
  */
 #include "core/arena.h"
 #include "core/graph.h"
@@ -25,6 +31,9 @@
 #include "core/tensor.h"
 #include "scheduler/jit.h"
 #include "scheduler/scheduler.h"
+
+#define PLAST_B200_USE_REFERENCE_TYPES
+#include "plast_b200_graph.h"
 
 #include <math.h>
 #include <stdio.h>
@@ -69,12 +78,63 @@ static Tensor *node2(Ctx *c, OP_TYPE op, Tensor *a, Tensor *b, const u64 *shape,
   return out;
 }
 
-enum { M = 64, N = 48, R = 33, K = 130 };
+enum { M = 64, N = 48, R = 33, K = 130, CH = 4099 };
 typedef struct {
   float ab[M * N], c[M * N], s[M], grad_b[N];
   float softmax[R * K];
   float tsum0[R], tmax_full[1], tsum1[K];
+  float chain[CH];
+  /* the same graphs after plast_b200_fuse_graph (CUDA only) */
+  float f_c[M * N], f_s[M], f_grad_b[N], f_softmax[R * K], f_chain[CH];
+  unsigned f_nodes[3], f_launches[3];
 } Results;
+
+static Tensor *config1_graph(Ctx *c, const float *A, const float *b, Tensor **tb_out, Tensor **cc_out) {
+  Tensor *tA = mk(c, (u64[]){M, N}, 2, false);
+  Tensor *tb = mk(c, (u64[]){1, N}, 2, true);
+  upload(c, tA->data, A, M * N);
+  upload(c, tb->data, b, N);
+  Tensor *ab = node2(c, ADD, tA, tb, (u64[]){M, N}, 2, true);
+  Tensor *cc = node1(c, LEAKY_RELU, ab, (u64[]){M, N}, 2, true, (KernelParams){0, 0, 0.0f});
+  *tb_out = tb;
+  *cc_out = cc;
+  return node1(c, SUM, cc, (u64[]){M}, 1, true, (KernelParams){1, 0, 0.0f});
+}
+static Tensor *softmax_graph(Ctx *c, Tensor *tX) {
+  Tensor *mx = node1(c, MAX, tX, (u64[]){R, 1}, 2, false, (KernelParams){1, 1, 0.0f});
+  Tensor *sh = node2(c, SUB, tX, mx, (u64[]){R, K}, 2, false);
+  Tensor *ex = node1(c, EXP, sh, (u64[]){R, K}, 2, false, (KernelParams){0, 0, 0.0f});
+  Tensor *se = node1(c, SUM, ex, (u64[]){R, 1}, 2, false, (KernelParams){1, 1, 0.0f});
+  return node2(c, DIV, ex, se, (u64[]){R, K}, 2, false);
+}
+static Tensor *chain_graph(Ctx *c, const float *x, const float *y) {
+  const KernelParams none = {0, 0, 0.0f};
+  const float one = 1.0f;
+  Tensor *tx = mk(c, (u64[]){CH}, 1, false), *ty = mk(c, (u64[]){CH}, 1, false);
+  Tensor *one_a = mk(c, NULL, 0, false), *one_b = mk(c, NULL, 0, false);
+  upload(c, tx->data, x, CH);
+  upload(c, ty->data, y, CH);
+  upload(c, one_a->data, &one, 1);
+  upload(c, one_b->data, &one, 1);
+  Tensor *nx = node1(c, NEG, tx, (u64[]){CH}, 1, false, none);
+  Tensor *e = node1(c, EXP, nx, (u64[]){CH}, 1, false, none);
+  Tensor *d = node2(c, ADD, one_a, e, (u64[]){CH}, 1, false);
+  Tensor *sg = node2(c, DIV, one_b, d, (u64[]){CH}, 1, false);
+  Tensor *t = node2(c, MUL, sg, ty, (u64[]){CH}, 1, false);
+  Tensor *ax = node1(c, ABS, tx, (u64[]){CH}, 1, false, none);
+  Tensor *nax = node1(c, NEG, ax, (u64[]){CH}, 1, false, none);
+  Tensor *e2 = node1(c, EXP, nax, (u64[]){CH}, 1, false, none);
+  return node2(c, ADD, t, e2, (u64[]){CH}, 1, false);
+}
+/* What schedule() does in JIT mode (scheduler.c:29-33) with this library's pass added. */
+static DAG *fused_dag(Ctx *c, Tensor *root, unsigned *n_nodes) {
+  DAG *dag = alloc_dag(MIN_DAG_CAPACITY);
+  dag->arena = &c->meta;
+  build_dag(dag, root->creator);
+  plast_b200_fuse_graph(dag);
+  *n_nodes = dag->count;
+  return dag;
+}
 
 static float frand(unsigned *st) {
   *st = *st * 1664525u + 1013904223u;
@@ -89,20 +149,18 @@ static void run(DEVICE dev, Results *res) {
   c.data = arena_create(Mib(16), dev);
   c.sched = init_scheduler(jit_create(16));
   unsigned st = 12345;
-  static float A[M * N], b[N], G[M * N], X[R * K];
+  static float A[M * N], b[N], G[M * N], X[R * K], CX[CH], CY[CH];
   for (int i = 0; i < M * N; ++i) A[i] = frand(&st);
   for (int i = 0; i < N; ++i) b[i] = frand(&st);
   for (int i = 0; i < M * N; ++i) G[i] = frand(&st) * 3.0f;
   for (int i = 0; i < R * K; ++i) X[i] = frand(&st) * 4.0f;
+  for (int i = 0; i < CH; ++i) CX[i] = frand(&st) * 6.0f;
+  for (int i = 0; i < CH; ++i) CY[i] = frand(&st);
 
   /* (1) config 1 */
-  Tensor *tA = mk(&c, (u64[]){M, N}, 2, false);
-  Tensor *tb = mk(&c, (u64[]){1, N}, 2, true);
-  upload(&c, tA->data, A, M * N);
-  upload(&c, tb->data, b, N);
-  Tensor *ab = node2(&c, ADD, tA, tb, (u64[]){M, N}, 2, true);
-  Tensor *cc = node1(&c, LEAKY_RELU, ab, (u64[]){M, N}, 2, true, (KernelParams){0, 0, 0.0f});
-  Tensor *s = node1(&c, SUM, cc, (u64[]){M}, 1, true, (KernelParams){1, 0, 0.0f});
+  Tensor *tb, *cc;
+  Tensor *s = config1_graph(&c, A, b, &tb, &cc);
+  Tensor *ab = cc->creator->inputs[0];
   schedule(c.sched, s->creator, FORWARD, &c.meta);
   download(&c, res->ab, ab->data, M * N);
   download(&c, res->c, cc->data, M * N);
@@ -114,13 +172,45 @@ static void run(DEVICE dev, Results *res) {
   /* (2) softmax = max(keepdim) -> sub -> exp -> sum(keepdim) -> div */
   Tensor *tX = mk(&c, (u64[]){R, K}, 2, false);
   upload(&c, tX->data, X, R * K);
-  Tensor *mx = node1(&c, MAX, tX, (u64[]){R, 1}, 2, false, (KernelParams){1, 1, 0.0f});
-  Tensor *sh = node2(&c, SUB, tX, mx, (u64[]){R, K}, 2, false);
-  Tensor *ex = node1(&c, EXP, sh, (u64[]){R, K}, 2, false, (KernelParams){0, 0, 0.0f});
-  Tensor *se = node1(&c, SUM, ex, (u64[]){R, 1}, 2, false, (KernelParams){1, 1, 0.0f});
-  Tensor *sm = node2(&c, DIV, ex, se, (u64[]){R, K}, 2, false);
+  Tensor *sm = softmax_graph(&c, tX);
   schedule(c.sched, sm->creator, FORWARD, &c.meta);
   download(&c, res->softmax, sm->data, R * K);
+
+  /* (4) the nine-node chain */
+  Tensor *z = chain_graph(&c, CX, CY);
+  schedule(c.sched, z->creator, FORWARD, &c.meta);
+  download(&c, res->chain, z->data, CH);
+
+  if (dev == CUDA) {
+    Tensor *ftb, *fcc;
+    Tensor *fs = config1_graph(&c, A, b, &ftb, &fcc);
+    DAG *d1 = fused_dag(&c, fs, &res->f_nodes[0]);
+    u64 before = plast_b200_launch_count();
+    dag_forward(d1);
+    res->f_launches[0] = (unsigned)(plast_b200_launch_count() - before);
+    download(&c, res->f_c, fcc->data, M * N);
+    download(&c, res->f_s, fs->data, M);
+    upload(&c, fcc->grad->data, G, M * N);
+    execute_backward(fcc->creator); /* the fused add + leaky_relu node */
+    download(&c, res->f_grad_b, ftb->grad->data, N);
+    dag_release(d1);
+
+    Tensor *fsm = softmax_graph(&c, tX);
+    DAG *d2 = fused_dag(&c, fsm, &res->f_nodes[1]);
+    before = plast_b200_launch_count();
+    dag_forward(d2);
+    res->f_launches[1] = (unsigned)(plast_b200_launch_count() - before);
+    download(&c, res->f_softmax, fsm->data, R * K);
+    dag_release(d2);
+
+    Tensor *fz = chain_graph(&c, CX, CY);
+    DAG *d3 = fused_dag(&c, fz, &res->f_nodes[2]);
+    before = plast_b200_launch_count();
+    dag_forward(d3);
+    res->f_launches[2] = (unsigned)(plast_b200_launch_count() - before);
+    download(&c, res->f_chain, fz->data, CH);
+    dag_release(d3);
+  }
 
   /* (3) reductions over the transposed view [K, R] of X (strides [1, K], no copy) */
   Tensor *xt = node1(&c, TRANSPOSE, tX, (u64[]){K, R}, 2, false, (KernelParams){0, 1, 0.0f});
@@ -165,6 +255,19 @@ int main(void) {
   bad += close_to("sum(X.T, axis 0)", cpu.tsum0, gpu.tsum0, R, 4.0f * K);
   bad += close_to("sum(X.T, axis 1)", cpu.tsum1, gpu.tsum1, K, 4.0f * R);
   bad += same_bits("max(X.T)", cpu.tmax_full, gpu.tmax_full, 1);
+  bad += close_to("chain (9 nodes)", cpu.chain, gpu.chain, CH, 2.0f);
+  printf("fused DAGs: config 1 %u nodes / %u launches, softmax %u / %u, chain %u / %u\n", gpu.f_nodes[0],
+         gpu.f_launches[0], gpu.f_nodes[1], gpu.f_launches[1], gpu.f_nodes[2], gpu.f_launches[2]);
+  if (gpu.f_nodes[0] != 2 || gpu.f_nodes[1] != 1 || gpu.f_nodes[2] != 1 || gpu.f_launches[0] != 2 ||
+      gpu.f_launches[1] != 1 || gpu.f_launches[2] > 2) {
+    printf("fused DAG sizes                MISMATCH\n");
+    ++bad;
+  }
+  bad += same_bits("fused: relu(A + b)", gpu.c, gpu.f_c, M * N);
+  bad += same_bits("fused: sum(C, axis 1)", gpu.s, gpu.f_s, M);
+  bad += close_to("fused: grad_b", cpu.grad_b, gpu.f_grad_b, N, 3.0f * M);
+  bad += close_to("fused: softmax", cpu.softmax, gpu.f_softmax, R * K, 1.0f);
+  bad += same_bits("fused: chain vs 9 nodes", gpu.chain, gpu.f_chain, CH);
   printf(bad ? "DROPIN FAILED\n" : "DROPIN OK\n");
   return bad ? 1 : 0;
 }

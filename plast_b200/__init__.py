@@ -78,7 +78,7 @@ _FWD = C.CFUNCTYPE(None, C.POINTER(C.POINTER(CTensor)), C.POINTER(CTensor), Kern
 
 
 def declared_symbols() -> list[str]:
-    """Every extern "C" symbol include/plast_b200.h declares."""
+    """Every extern "C" symbol include/plast_b200.h and include/plast_b200_graph.h declare."""
     syms = [f"{op}_cuda_forward" for op in FORWARD_OPS] + [f"{op}_cuda_backward" for op in BACKWARD_OPS]
     syms += [
         "plast_b200_chain_forward", "zeros_cuda", "ones_cuda", "set_ones_grad_cuda", "zero_grad_cuda",
@@ -89,6 +89,8 @@ def declared_symbols() -> list[str]:
         "plast_b200_set_sync", "plast_b200_launch_count", "plast_b200_last_kernel",
         "plast_b200_release_workspace", "plast_b200_version", "plast_b200_plan_debug",
         "sum_axis0_noalloc_cuda_forward", "plast_b200_chain_source", "plast_b200_chain_try_compile",
+        "plast_b200_fuse_graph", "plast_b200_fusion_release", "plast_b200_fusion_program",
+        "chain_cuda_forward", "chain_cuda_backward",
     ]
     return syms
 

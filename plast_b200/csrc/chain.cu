@@ -353,10 +353,10 @@ void plast_b200_chain_forward(const Tensor **inputs, int n_inputs, Tensor *outpu
     }
   }
   switch (n_inputs) {
-  case 1: fused_forward<ChainInterp<1>, 1>(name, inputs, output, ChainInterp<1>{prog}); break;
-  case 2: fused_forward<ChainInterp<2>, 2>(name, inputs, output, ChainInterp<2>{prog}); break;
-  case 3: fused_forward<ChainInterp<3>, 3>(name, inputs, output, ChainInterp<3>{prog}); break;
-  default: fused_forward<ChainInterp<4>, 4>(name, inputs, output, ChainInterp<4>{prog}); break;
+#define PB_INTERP(N) case N: fused_forward<ChainInterp<N>, N>(name, inputs, output, ChainInterp<N>{prog}); break;
+    PB_INTERP(1) PB_INTERP(2) PB_INTERP(3) PB_INTERP(4) PB_INTERP(5) PB_INTERP(6) PB_INTERP(7)
+  default: fused_forward<ChainInterp<8>, 8>(name, inputs, output, ChainInterp<8>{prog}); break;
+#undef PB_INTERP
   }
   if (!failed()) note_kernel("chain_interpreter");
   end_call();

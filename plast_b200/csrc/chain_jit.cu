@@ -274,6 +274,10 @@ bool launch_chain_jit(const ChainProgramView &p, const IterPlan &plan, float *ou
   case 2: return launch_plan<2>(p, plan, out, ins, f);
   case 3: return launch_plan<3>(p, plan, out, ins, f);
   case 4: return launch_plan<4>(p, plan, out, ins, f);
+  case 5: return launch_plan<5>(p, plan, out, ins, f);
+  case 6: return launch_plan<6>(p, plan, out, ins, f);
+  case 7: return launch_plan<7>(p, plan, out, ins, f);
+  case 8: return launch_plan<8>(p, plan, out, ins, f);
   default: return false;
   }
 }

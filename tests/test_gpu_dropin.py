@@ -18,4 +18,5 @@ def test_reference_runtime_drives_the_library():
     print(p.stdout, p.stderr)
     assert p.returncode == 0, p.stdout + p.stderr
     assert "DROPIN OK" in p.stdout
-    assert p.stdout.count("bit-exact") == 3          # A + b, relu(A + b), max(X.T)
+    # A + b, relu(A + b), max(X.T); fused relu(A + b), row sums and chain against the node-by-node runs
+    assert p.stdout.count("bit-exact") == 6
