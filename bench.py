@@ -392,12 +392,12 @@ def main():
                     help="elements per GPU (default 2^28, the benchmark size; smaller only for profiler captures)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-per-op", action="store_true", help="skip the per-op table of configs 1-5")
+    ap.add_argument("--no-per-op", action="store_true", help="skip the per-op table (configs 1-5 and the optimiser steps)")
     ap.add_argument("--op-reps", type=int, default=10)
     ap.add_argument("--per-op-only", action="store_true",
                     help="only the per-op table (1 GPU); with --op-reps 0 every op is launched 3 times and "
                          "not timed, which is the command the profiler captures use")
-    ap.add_argument("--configs", default="1,2,3,4,5", help="configs of the per-op table")
+    ap.add_argument("--configs", default="1,2,3,4,5,6", help="configs of the per-op table (6 = optimiser steps)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -497,4 +497,37 @@ void oracle_sigmoid_mul_add_exp_neg_abs(const float *x, const float *y, float *z
   }
 }
 
+/* ---- optimiser steps (flat float arrays, one parameter per call) ---------------------------------
+ * src/optimizers/cpu/sgd.c:23-30 */
+void oracle_sgd_step(float *data, const float *grad, u64 n, float lr) {
+  for (u64 j = 0; j < n; ++j) data[j] -= lr * grad[j];
+}
+/* src/optimizers/cpu/adam.c:48-49: the bias-corrected step size of step t (t >= 1). sqrt is the
+ * double function there, so the expression is evaluated in double and rounded to float once. */
+float oracle_adam_lr_t(float lr, float beta1, float beta2, int t) {
+  float lr_t = lr * sqrt(1.0f - powf(beta2, t)) / (1.0f - powf(beta1, t));
+  return lr_t;
+}
+/* src/optimizers/cpu/adam.c:62-66; t is the step count AFTER the increment of adam.c:28. */
+void oracle_adam_step(float *data, const float *grad, float *m_data, float *v_data, u64 n, float lr,
+                      float beta1, float beta2, float epsilon, int t) {
+  const float lr_t = oracle_adam_lr_t(lr, beta1, beta2, t);
+  for (u64 j = 0; j < n; ++j) {
+    m_data[j] = beta1 * m_data[j] + (1.0f - beta1) * grad[j];
+    v_data[j] = beta2 * v_data[j] + (1.0f - beta2) * grad[j] * grad[j];
+    data[j] -= lr_t * m_data[j] / (sqrtf(v_data[j]) + epsilon);
+  }
+}
+/* src/optimizers/cpu/adamw.c:64-71: decoupled weight decay, then the Adam update. */
+void oracle_adamw_step(float *data, const float *grad, float *m_data, float *v_data, u64 n, float lr,
+                       float beta1, float beta2, float epsilon, float weight_decay, int t) {
+  const float lr_t = oracle_adam_lr_t(lr, beta1, beta2, t);
+  for (u64 j = 0; j < n; ++j) {
+    data[j] -= lr * weight_decay * data[j];
+    m_data[j] = beta1 * m_data[j] + (1.0f - beta1) * grad[j];
+    v_data[j] = beta2 * v_data[j] + (1.0f - beta2) * grad[j] * grad[j];
+    data[j] -= lr_t * m_data[j] / (sqrtf(v_data[j]) + epsilon);
+  }
+}
+
 const char *oracle_version(void) { return "plast-oracle 1"; }

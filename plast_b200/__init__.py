@@ -78,7 +78,7 @@ _FWD = C.CFUNCTYPE(None, C.POINTER(C.POINTER(CTensor)), C.POINTER(CTensor), Kern
 
 
 def declared_symbols() -> list[str]:
-    """Every extern "C" symbol include/plast_b200.h and include/plast_b200_graph.h declare."""
+    """Every extern "C" symbol the headers under include/ declare."""
     syms = [f"{op}_cuda_forward" for op in FORWARD_OPS] + [f"{op}_cuda_backward" for op in BACKWARD_OPS]
     syms += [
         "plast_b200_chain_forward", "zeros_cuda", "ones_cuda", "set_ones_grad_cuda", "zero_grad_cuda",
@@ -91,6 +91,7 @@ def declared_symbols() -> list[str]:
         "sum_axis0_noalloc_cuda_forward", "plast_b200_chain_source", "plast_b200_chain_try_compile",
         "plast_b200_fuse_graph", "plast_b200_fusion_release", "plast_b200_fusion_program",
         "chain_cuda_forward", "chain_cuda_backward",
+        "sgd_step_cuda", "adam_step_cuda", "adamw_step_cuda", "plast_b200_adam_state_release",
     ]
     return syms
 

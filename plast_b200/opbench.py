@@ -18,7 +18,7 @@ import numpy as np
 NOMINAL = 8000.0
 
 
-def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2, 3, 4, 5)):
+def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2, 3, 4, 5, 6)):
     gen = torch.Generator(device=dev)
     flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
     rows = []
@@ -140,6 +140,22 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
             pb.forward("neg", [w[2]], w[2], check=False); pb.forward("exp", [w[2]], w[2], check=False)
             pb.forward("add", [w[1], w[2]], tz, check=False)
         timeit(2, "chain_as_9_launches", unfused, 3 * n * F, n, ws)
+        # the chain as the nine nodes the scheduler holds (the two 1.0 constants are 0-dim tensors),
+        # collapsed by the graph fusion pass into one run-time compiled node
+        from . import graph as G
+        one_b = torch.ones((), device=dev)
+        tone_b = wrap(one_b, shape=[])
+        t2 = [torch.empty(n, device=dev) for _ in range(8)]              # one buffer per intermediate node
+        w2 = [wrap(v) for v in t2]
+        gr = G.Graph()
+        gr.node("NEG", [tx], w2[0]); gr.node("EXP", [w2[0]], w2[1]); gr.node("ADD", [tone, w2[1]], w2[2])
+        gr.node("DIV", [tone_b, w2[2]], w2[3]); gr.node("MUL", [w2[3], ty], w2[4])
+        gr.node("ABS", [tx], w2[5]); gr.node("NEG", [w2[5]], w2[6]); gr.node("EXP", [w2[6]], w2[7])
+        gr.node("ADD", [w2[4], w2[7]], tz)
+        dag = gr.dag()
+        if G.fuse(dag) == 1 and dag.count == 1:
+            timeit(2, "chain_fused_by_graph_pass", lambda: G.dag_forward(dag), 3 * n * F + 8, n, ws)
+        del t2, w2
         del x, y, z, t, w
     if 3 in configs:
         R, Cn = 65536, 4096
@@ -201,5 +217,30 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
         timeit(5, "bias_grad_masked_reduce", lambda: pb.backward("scale_bias_leaky_relu", [tX, tS, tBg], tYg, fval=0.0, check=False),
                2 * n * F + 1024, n, ws)
         del X, G, Y
+    if 6 in configs:
+        # Optimiser steps (not one of the reference's benchmark configurations): a parameter set of
+        # 12 weight matrices [4096, 2048] and 12 biases [4096], one multi-tensor launch per step.
+        from . import optim as O
+        shapes = [(4096, 2048), (4096,)] * 12
+        ps = [randn(sh, 10 + i, 0.1) for i, sh in enumerate(shapes)]
+        gs = [randn(sh, 50 + i, 0.01) for i, sh in enumerate(shapes)]
+        params = []
+        for p_, g_ in zip(ps, gs):
+            tp, tg = wrap(p_), wrap(g_)
+            tp.grad = tg; tp.c.grad = C.pointer(tg.c); tp.c.requires_grad = True
+            params.append(tp)
+        arr = O.param_array(params)
+        n = sum(int(np.prod(sh)) for sh in shapes)
+        sgd = O.SGD(1e-3)
+        timeit(6, "sgd_step_24_params", lambda: pb.lib.sgd_step_cuda(C.byref(sgd), arr, len(params)), 3 * n * F, n, 2 * n * F)
+        adam = O.Adam()
+        adam.lr, adam.beta1, adam.beta2, adam.epsilon, adam.t = 1e-3, 0.9, 0.999, 1e-8, 0
+        timeit(6, "adam_step_24_params", lambda: pb.lib.adam_step_cuda(C.byref(adam), arr, len(params)), 7 * n * F, n, 4 * n * F)
+        O.release_state(adam)
+        adamw = O.AdamW()
+        adamw.lr, adamw.beta1, adamw.beta2, adamw.epsilon, adamw.weight_decay, adamw.t = 1e-3, 0.9, 0.999, 1e-8, 0.01, 0
+        timeit(6, "adamw_step_24_params", lambda: pb.lib.adamw_step_cuda(C.byref(adamw), arr, len(params)), 7 * n * F, n, 4 * n * F)
+        O.release_state(adamw)
+        del ps, gs
     torch.cuda.synchronize()
     return rows
