@@ -286,10 +286,13 @@ const char *plast_b200_version(void);
 /* Test hooks of the chain compiler (no GPU needed): the CUDA C++ functor generated for a program
  * (returns its length, copies at most capacity - 1 characters; -1 = malformed program), and a trial
  * compile of the whole kernel with NVRTC for sm_100a (0 = compiled, -2 = libnvrtc not available,
- * other = the NVRTC error, log on stderr). */
-int plast_b200_chain_source(const PlastChainStep *steps, int n_steps, int n_inputs, char *buf,
-                            size_t capacity);
-int plast_b200_chain_try_compile(const PlastChainStep *steps, int n_steps, int n_inputs);
+ * other = the NVRTC error, log on stderr). Bit i of scalar_mask marks input i as a one-element
+ * constant, which the compiler reads once per thread through a pointer (at run time it finds
+ * these itself: inputs that broadcast along every dim of the output). */
+int plast_b200_chain_source(const PlastChainStep *steps, int n_steps, int n_inputs, unsigned scalar_mask,
+                            char *buf, size_t capacity);
+int plast_b200_chain_try_compile(const PlastChainStep *steps, int n_steps, int n_inputs,
+                                 unsigned scalar_mask);
 /* Test hook: runs the host-side iteration planner (drop size-1 dims, order by the strides of
  * argument `sort_arg`, merge dims every argument walks as one run) on caller-supplied metadata.
  * strides / out_strides are [nargs][MAX_NDIM] row-major, outermost dim first on input; the

@@ -153,6 +153,7 @@ struct ChainProgramView {
   int n_inputs, n_steps;
   const unsigned char *opcode, *a, *b;
   const float *fval;
+  unsigned scalar_mask; // filled by the compiler from the plan
 };
 bool launch_chain_jit(const ChainProgramView &p, const IterPlan &plan, float *out, const float *const *ins);
 
@@ -345,7 +346,7 @@ void plast_b200_chain_forward(const Tensor **inputs, int n_inputs, Tensor *outpu
     }
     IterPlan plan;
     make_plan(&plan, output->shape, output->ndim, n_inputs + 1, st, nullptr, 0);
-    const ChainProgramView view{n_inputs, n_steps, prog.opcode, prog.a, prog.b, prog.fval};
+    const ChainProgramView view{n_inputs, n_steps, prog.opcode, prog.a, prog.b, prog.fval, 0u};
     if (launch_chain_jit(view, plan, (float *)output->data, ins)) {
       note_kernel("chain_jit");
       end_call();

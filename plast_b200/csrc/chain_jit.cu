@@ -31,7 +31,16 @@ struct ChainProgramView { // mirrors ChainProgram of chain.cu (kept POD so both 
   int n_inputs, n_steps;
   const unsigned char *opcode, *a, *b;
   const float *fval;
+  // bit i set: input i is one element whatever the output index (a 0-dim constant such as the 1.0
+  // of `1.0 + x`). Such inputs are read once per thread through a pointer in the functor instead
+  // of occupying an operand slot of the kernel (registers and a load per element).
+  unsigned scalar_mask;
 };
+static int tensor_inputs(const ChainProgramView &p) {
+  int n = 0;
+  for (int i = 0; i < p.n_inputs; ++i) n += !((p.scalar_mask >> i) & 1u);
+  return n;
+}
 
 // ---- minimal NVRTC / driver API surface, resolved at run time -------------------------------------
 typedef int nvrtcResult;
@@ -117,9 +126,14 @@ const char *step_expr(int opcode) {
 
 std::string functor_source(const ChainProgramView &p) {
   std::string s = "namespace pb {\nstruct JitF {\n  float c[" + std::to_string(PLAST_CHAIN_MAX_STEPS) +
+                  "];\n  const float *sp[" + std::to_string(PLAST_CHAIN_MAX_INPUTS) +
                   "];\n  __device__ __forceinline__ float operator()(const float *x) const {\n";
-  for (int i = 0; i < p.n_inputs; ++i)
-    s += "    const float r" + std::to_string(i) + " = x[" + std::to_string(i) + "];\n";
+  for (int i = 0, slot = 0, sc = 0; i < p.n_inputs; ++i) {
+    if ((p.scalar_mask >> i) & 1u)
+      s += "    const float r" + std::to_string(i) + " = __ldg(sp[" + std::to_string(sc++) + "]);\n";
+    else
+      s += "    const float r" + std::to_string(i) + " = x[" + std::to_string(slot++) + "];\n";
+  }
   for (int k = 0; k < p.n_steps; ++k) {
     std::string e = step_expr(p.opcode[k]);
     auto sub = [&](const std::string &from, const std::string &to) {
@@ -137,21 +151,21 @@ std::string functor_source(const ChainProgramView &p) {
 }
 
 std::string structure_key(const ChainProgramView &p) {
-  std::string k = std::to_string(p.n_inputs) + ":";
+  std::string k = std::to_string(p.n_inputs) + "/" + std::to_string(p.scalar_mask) + ":";
   for (int i = 0; i < p.n_steps; ++i)
     k += std::to_string(p.opcode[i]) + "," + std::to_string(p.a[i]) + "," + std::to_string(p.b[i]) + ";";
   return k;
 }
 
 std::string instance_name(const ChainProgramView &p, int vec, bool idx64, bool one_d) {
-  return "pb::ew_kernel<pb::JitF, " + std::to_string(p.n_inputs) + ", " + std::to_string(vec) + ", " +
+  return "pb::ew_kernel<pb::JitF, " + std::to_string(tensor_inputs(p)) + ", " + std::to_string(vec) + ", " +
          (idx64 ? "unsigned long long" : "unsigned int") + ", " + (one_d ? "true" : "false") + ">";
 }
 std::string program_source(const ChainProgramView &p, const std::string &inst, bool idx64) {
   const char *idx = idx64 ? "unsigned long long" : "unsigned int";
   return std::string(kDeviceSource) + "\n" + functor_source(p) + "\ntemplate __global__ void " + inst +
-         "(pb::JitF, float *, pb::InPtrs<" + std::to_string(p.n_inputs) + ">, pb::OffsetCalc<" +
-         std::to_string(p.n_inputs + 1) + ", " + idx + ">, " + idx + ", unsigned int);\n";
+         "(pb::JitF, float *, pb::InPtrs<" + std::to_string(tensor_inputs(p)) + ">, pb::OffsetCalc<" +
+         std::to_string(tensor_inputs(p) + 1) + ", " + idx + ">, " + idx + ", unsigned int);\n";
 }
 
 std::mutex g_mutex;
@@ -197,6 +211,7 @@ CUfunction get_kernel(const ChainProgramView &p, int vec, bool idx64, bool one_d
 
 struct JitFHost {
   float c[PLAST_CHAIN_MAX_STEPS];
+  const float *sp[PLAST_CHAIN_MAX_INPUTS];
 };
 
 template <int NIN, typename index_t>
@@ -269,15 +284,35 @@ bool launch_chain_jit(const ChainProgramView &p, const IterPlan &plan, float *ou
   if (disabled || !api().ok) return false;
   JitFHost f = {};
   for (int k = 0; k < p.n_steps; ++k) f.c[k] = p.fval[k];
-  switch (p.n_inputs) {
-  case 1: return launch_plan<1>(p, plan, out, ins, f);
-  case 2: return launch_plan<2>(p, plan, out, ins, f);
-  case 3: return launch_plan<3>(p, plan, out, ins, f);
-  case 4: return launch_plan<4>(p, plan, out, ins, f);
-  case 5: return launch_plan<5>(p, plan, out, ins, f);
-  case 6: return launch_plan<6>(p, plan, out, ins, f);
-  case 7: return launch_plan<7>(p, plan, out, ins, f);
-  case 8: return launch_plan<8>(p, plan, out, ins, f);
+  // Inputs the plan never advances are constants: hand them to the functor as pointers and plan
+  // the launch over the remaining operands only (at least one stays, so the kernel has an operand).
+  ChainProgramView q = p;
+  q.scalar_mask = 0;
+  IterPlan lean = plan;
+  const float *tensor_ins[PLAST_CHAIN_MAX_INPUTS] = {};
+  int n_tensor = 0, n_scalar = 0;
+  for (int a = 0; a < p.n_inputs; ++a) {
+    bool moves = false;
+    for (int d = 0; d < plan.ndim; ++d) moves = moves || plan.stride[a + 1][d] != 0;
+    if (!moves && !(n_tensor == 0 && a == p.n_inputs - 1)) {
+      q.scalar_mask |= 1u << a;
+      f.sp[n_scalar++] = ins[a];
+      continue;
+    }
+    for (int d = 0; d < MAX_NDIM; ++d) lean.stride[n_tensor + 1][d] = plan.stride[a + 1][d];
+    lean.max_offset[n_tensor + 1] = plan.max_offset[a + 1];
+    tensor_ins[n_tensor++] = ins[a];
+  }
+  lean.nargs = n_tensor + 1;
+  switch (n_tensor) {
+  case 1: return launch_plan<1>(q, lean, out, tensor_ins, f);
+  case 2: return launch_plan<2>(q, lean, out, tensor_ins, f);
+  case 3: return launch_plan<3>(q, lean, out, tensor_ins, f);
+  case 4: return launch_plan<4>(q, lean, out, tensor_ins, f);
+  case 5: return launch_plan<5>(q, lean, out, tensor_ins, f);
+  case 6: return launch_plan<6>(q, lean, out, tensor_ins, f);
+  case 7: return launch_plan<7>(q, lean, out, tensor_ins, f);
+  case 8: return launch_plan<8>(q, lean, out, tensor_ins, f);
   default: return false;
   }
 }
@@ -285,10 +320,11 @@ bool launch_chain_jit(const ChainProgramView &p, const IterPlan &plan, float *ou
 } // namespace pb
 
 // ---- test hooks (declared in include/plast_b200.h; need no GPU) ------------------------------------------
-static bool view_of(const PlastChainStep *steps, int n_steps, int n_inputs, unsigned char *op,
-                    unsigned char *a, unsigned char *b, float *f, pb::ChainProgramView *v) {
+static bool view_of(const PlastChainStep *steps, int n_steps, int n_inputs, unsigned scalar_mask,
+                    unsigned char *op, unsigned char *a, unsigned char *b, float *f, pb::ChainProgramView *v) {
   if (!steps || n_inputs < 1 || n_inputs > PLAST_CHAIN_MAX_INPUTS || n_steps < 1 || n_steps > PLAST_CHAIN_MAX_STEPS)
     return false;
+  if (scalar_mask >> n_inputs || scalar_mask == (1u << n_inputs) - 1u) return false; // one operand must stay
   for (int s = 0; s < n_steps; ++s) {
     const bool binary = steps[s].opcode <= PLAST_CHAIN_DIV;
     if (steps[s].opcode < 0 || steps[s].opcode > PLAST_CHAIN_RDIV_SCALAR || steps[s].a < 0 ||
@@ -299,16 +335,16 @@ static bool view_of(const PlastChainStep *steps, int n_steps, int n_inputs, unsi
     b[s] = (unsigned char)(binary ? steps[s].b : steps[s].a);
     f[s] = steps[s].fval;
   }
-  *v = pb::ChainProgramView{n_inputs, n_steps, op, a, b, f};
+  *v = pb::ChainProgramView{n_inputs, n_steps, op, a, b, f, scalar_mask};
   return true;
 }
 
-extern "C" int plast_b200_chain_source(const PlastChainStep *steps, int n_steps, int n_inputs, char *buf,
-                                       size_t capacity) {
+extern "C" int plast_b200_chain_source(const PlastChainStep *steps, int n_steps, int n_inputs,
+                                       unsigned scalar_mask, char *buf, size_t capacity) {
   unsigned char op[PLAST_CHAIN_MAX_STEPS], a[PLAST_CHAIN_MAX_STEPS], b[PLAST_CHAIN_MAX_STEPS];
   float f[PLAST_CHAIN_MAX_STEPS];
   pb::ChainProgramView v;
-  if (!view_of(steps, n_steps, n_inputs, op, a, b, f, &v)) return -1;
+  if (!view_of(steps, n_steps, n_inputs, scalar_mask, op, a, b, f, &v)) return -1;
   const std::string src = pb::functor_source(v);
   if (buf && capacity > 0) {
     const size_t n = src.size() < capacity - 1 ? src.size() : capacity - 1;
@@ -318,11 +354,12 @@ extern "C" int plast_b200_chain_source(const PlastChainStep *steps, int n_steps,
   return (int)src.size();
 }
 
-extern "C" int plast_b200_chain_try_compile(const PlastChainStep *steps, int n_steps, int n_inputs) {
+extern "C" int plast_b200_chain_try_compile(const PlastChainStep *steps, int n_steps, int n_inputs,
+                                            unsigned scalar_mask) {
   unsigned char op[PLAST_CHAIN_MAX_STEPS], a[PLAST_CHAIN_MAX_STEPS], b[PLAST_CHAIN_MAX_STEPS];
   float f[PLAST_CHAIN_MAX_STEPS];
   pb::ChainProgramView v;
-  if (!view_of(steps, n_steps, n_inputs, op, a, b, f, &v)) return -1;
+  if (!view_of(steps, n_steps, n_inputs, scalar_mask, op, a, b, f, &v)) return -1;
   pb::Api &api = pb::api();
   if (!api.rtc_ok) return -2;
   const std::string inst = pb::instance_name(v, 4, false, true);

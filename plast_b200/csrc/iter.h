@@ -15,7 +15,8 @@
 
 namespace pb {
 
-constexpr int kMaxArgs = 6; // output + up to 5 operands
+constexpr int kMaxArgs = 9; // output + up to 8 operands (the widest fused chain)
+static_assert(PLAST_CHAIN_MAX_INPUTS + 1 <= kMaxArgs, "a chain's operands must fit the planner");
 
 struct IterPlan {
   int ndim = 0;  // >= 1 after planning (a single element plans as one dim of size 1)

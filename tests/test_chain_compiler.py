@@ -19,16 +19,16 @@ def steps_array(steps):
 
 def lib():
     handle = C.CDLL(str(pb.LIB_PATH))
-    handle.plast_b200_chain_source.argtypes = [C.POINTER(pb.ChainStep), C.c_int, C.c_int, C.c_char_p, C.c_size_t]
+    handle.plast_b200_chain_source.argtypes = [C.POINTER(pb.ChainStep), C.c_int, C.c_int, C.c_uint, C.c_char_p, C.c_size_t]
     handle.plast_b200_chain_source.restype = C.c_int
-    handle.plast_b200_chain_try_compile.argtypes = [C.POINTER(pb.ChainStep), C.c_int, C.c_int]
+    handle.plast_b200_chain_try_compile.argtypes = [C.POINTER(pb.ChainStep), C.c_int, C.c_int, C.c_uint]
     handle.plast_b200_chain_try_compile.restype = C.c_int
     return handle
 
 
 def test_generated_functor_has_one_rounded_statement_per_step():
     buf = C.create_string_buffer(8192)
-    n = lib().plast_b200_chain_source(steps_array(CHAIN), len(CHAIN), 2, buf, len(buf))
+    n = lib().plast_b200_chain_source(steps_array(CHAIN), len(CHAIN), 2, 0, buf, len(buf))
     src = buf.value.decode()
     assert n == len(src)
     lines = [l.strip() for l in src.splitlines()]
@@ -45,8 +45,8 @@ def test_generated_functor_has_one_rounded_statement_per_step():
 
 def test_malformed_programs_are_rejected():
     h = lib()
-    assert h.plast_b200_chain_source(steps_array([("add", 0, 5, 0.0)]), 1, 2, None, 0) == -1   # register not yet written
-    assert h.plast_b200_chain_source(steps_array(CHAIN), len(CHAIN), 9, None, 0) == -1         # too many inputs
+    assert h.plast_b200_chain_source(steps_array([("add", 0, 5, 0.0)]), 1, 2, 0, None, 0) == -1   # register not yet written
+    assert h.plast_b200_chain_source(steps_array(CHAIN), len(CHAIN), 9, 0, None, 0) == -1         # too many inputs
 
 
 def test_every_opcode_compiles_for_sm_100a():
@@ -54,7 +54,24 @@ def test_every_opcode_compiles_for_sm_100a():
             ("exp", 7, 0, 0), ("log", 8, 0, 0), ("sin", 9, 0, 0), ("cos", 10, 0, 0), ("tan", 11, 0, 0),
             ("leaky_relu", 12, 0, 0.1), ("add_scalar", 13, 0, 1.0), ("rsub_scalar", 14, 0, 2.0),
             ("mul_scalar", 15, 0, 0.5), ("rdiv_scalar", 16, 0, 3.0)]
-    rc = lib().plast_b200_chain_try_compile(steps_array(prog), len(prog), 2)
+    rc = lib().plast_b200_chain_try_compile(steps_array(prog), len(prog), 2, 0)
+    if rc == -2:
+        pytest.skip("libnvrtc not available on this machine")
+    assert rc == 0
+
+
+def test_one_element_constants_are_read_through_pointers_and_compile():
+    # the nine nodes of z = sigmoid(x) * y + exp(-abs(x)) as the graph holds them: inputs x, 1.0, 1.0, y
+    prog = [("neg", 0, 0, 0), ("exp", 4, 0, 0), ("add", 1, 5, 0), ("div", 2, 6, 0), ("mul", 7, 3, 0),
+            ("abs", 0, 0, 0), ("neg", 9, 0, 0), ("exp", 10, 0, 0), ("add", 8, 11, 0)]
+    buf = C.create_string_buffer(8192)
+    h = lib()
+    assert h.plast_b200_chain_source(steps_array(prog), len(prog), 4, 0b0110, buf, len(buf)) > 0
+    lines = [l.strip() for l in buf.value.decode().splitlines()]
+    assert "const float r0 = x[0];" in lines and "const float r3 = x[1];" in lines
+    assert "const float r1 = __ldg(sp[0]);" in lines and "const float r2 = __ldg(sp[1]);" in lines
+    assert h.plast_b200_chain_source(steps_array(prog), len(prog), 4, 0b1111, None, 0) == -1   # no operand left
+    rc = h.plast_b200_chain_try_compile(steps_array(prog), len(prog), 4, 0b0110)
     if rc == -2:
         pytest.skip("libnvrtc not available on this machine")
     assert rc == 0

@@ -142,3 +142,26 @@ def test_config5_epilogue_graph_fuses_to_scale_bias_relu(cuda):
     gscale = np.abs(Gup).sum(axis=(0, 2, 3), keepdims=True)
     assert_sum_close(res[1][2], res[0][2], gscale, what="bias grad")
     assert_sum_close(res[1][1], res[0][1], np.abs(Gup * X).sum(axis=(0, 2, 3), keepdims=True), what="scale grad")
+
+
+def test_chain_with_eight_operands_and_constants_in_every_position(cuda):
+    shape = (33, 1025)
+    xs = [rand_normal(10 + i, shape) for i in range(5)]
+    consts = [np.float32(v).reshape(()) for v in (0.5, -1.25, 3.0)]
+    res = []
+    for fused in (False, True):
+        tx = [cuda.tensor(x) for x in xs]
+        tc = [cuda.tensor(c) for c in consts]
+        t = [cuda.empty(shape) for _ in range(7)]
+        g = G.Graph()
+        g.node("MUL", [tc[0], tx[0]], t[0]); g.node("ADD", [t[0], tx[1]], t[1]); g.node("SUB", [t[1], tc[1]], t[2])
+        g.node("MUL", [t[2], tx[2]], t[3]); g.node("DIV", [t[3], tc[2]], t[4]); g.node("ADD", [t[4], tx[3]], t[5])
+        g.node("SUB", [tx[4], t[5]], t[6])
+        dag = g.dag()
+        if fused:
+            assert G.fuse(dag) == 1 and dag.count == 1 and dag.nodes[0].contents.num_inputs == 8
+        G.dag_forward(dag); pb.check_error()
+        res.append(t[6].numpy().copy())
+    assert_bit_equal(res[1], res[0], "eight-operand chain")
+    want = xs[4] - (((np.float32(0.5) * xs[0] + xs[1]) - np.float32(-1.25)) * xs[2] / np.float32(3.0) + xs[3])
+    assert_bit_equal(res[1], want.astype(np.float32), "eight-operand chain vs numpy")
