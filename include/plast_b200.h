@@ -253,6 +253,21 @@ void arena_memcpy_d2d_cuda(void *dest, const void *src, u64 size);
  * C++-linkage cuda_tensor_pack_init/release wrappers are exported by the same library. */
 void plast_b200_pack(const Tensor *t, void *dst);
 
+/* Backward pieces of the reference's fused GEMM / conv epilogues (matmul_relu, matmul_bias_relu,
+ * conv_relu), which stay the reference's own kernels but spend their backward in these two
+ * bandwidth-bound steps. plast_b200_relu_grad_modulate replaces launch_relu_grad_modulate_cuda
+ * (src/kernels/cuda/matmul_relu.cu:137-150) without the launch dims:
+ * dc[i] = dout[i] * (out_data[i] > 0 ? 1 : alpha). plast_b200_bias_grad_reduce replaces the
+ * cudaMemset + bias_grad_reduce_kernel pair (matmul_bias_relu.cu:143-151, 219-223): dbias[c] =
+ * sum over rows of the contiguous [num_elements / cols, cols] matrix dc_mod (overwrites dbias;
+ * deterministic, no float atomics). plast_b200_bias_grad_masked does both in one pass over dout
+ * and out_data, so the dc_mod buffer is not needed for the bias gradient. */
+void plast_b200_relu_grad_modulate(const float *dout, const float *out_data, float *dc, u64 num_elements,
+                                   float alpha);
+void plast_b200_bias_grad_reduce(const float *dc_mod, float *dbias, u64 num_elements, u64 cols);
+void plast_b200_bias_grad_masked(const float *dout, const float *out_data, float *dbias, u64 num_elements,
+                                 u64 cols, float alpha);
+
 /* ------------------------------------------------------------------------------------------
  * Library control (no counterpart in the reference).
  * ------------------------------------------------------------------------------------------ */

@@ -92,6 +92,7 @@ def declared_symbols() -> list[str]:
         "plast_b200_fuse_graph", "plast_b200_fusion_release", "plast_b200_fusion_program",
         "chain_cuda_forward", "chain_cuda_backward",
         "sgd_step_cuda", "adam_step_cuda", "adamw_step_cuda", "plast_b200_adam_state_release",
+        "plast_b200_relu_grad_modulate", "plast_b200_bias_grad_reduce", "plast_b200_bias_grad_masked",
     ]
     return syms
 
@@ -115,6 +116,11 @@ def _load() -> C.CDLL:
     lib.plast_b200_chain_forward.argtypes = [C.POINTER(C.POINTER(CTensor)), C.c_int, C.POINTER(CTensor),
                                              C.POINTER(ChainStep), C.c_int]
     lib.plast_b200_chain_forward.restype = None
+    lib.plast_b200_relu_grad_modulate.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_float]
+    lib.plast_b200_bias_grad_reduce.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64]
+    lib.plast_b200_bias_grad_masked.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_float]
+    for name in ("plast_b200_relu_grad_modulate", "plast_b200_bias_grad_reduce", "plast_b200_bias_grad_masked"):
+        getattr(lib, name).restype = None
     for name in ("zeros_cuda", "ones_cuda"):
         getattr(lib, name).argtypes = [C.POINTER(CTensor), C.c_uint64]
         getattr(lib, name).restype = None

@@ -2,6 +2,7 @@
 // fills, arena memory calls, view-gradient accumulation and the strided -> contiguous pack.
 #include "ew_engine.cuh"
 #include "functors.cuh"
+#include "grad_accum.cuh"
 
 #include <stdlib.h>
 
@@ -35,6 +36,40 @@ void fill32(void *data, unsigned int pattern, u64 n) {
   fill_kernel<<<(unsigned)blocks, 256, 0, stream()>>>((unsigned int *)data, pattern, n);
   count_launch();
   note_kernel("fill32");
+}
+
+// dout * (y > 0 ? 1 : slope): the gradient a leaky_relu epilogue hands to what it is fused onto.
+struct ReluGradModulate { // x = {dout, y}
+  float alpha;
+  __device__ __forceinline__ float operator()(const float *x) const {
+    return x[0] * (x[1] > 0.0f ? 1.0f : alpha);
+  }
+};
+
+// Column sums of a contiguous [num_elements / cols, cols] matrix of Term values, written to dbias.
+template <class Term, int NIN>
+static void column_sums(const char *name, const float *const *ins, float *dbias, u64 num_elements, u64 cols,
+                        const Term &term) {
+  if (cols == 0 || num_elements % cols != 0) {
+    set_error(PLAST_B200_ERR_SHAPE, "%s: %llu elements are not rows of %llu columns", name,
+              (unsigned long long)num_elements, (unsigned long long)cols);
+    return;
+  }
+  if (num_elements == 0) {
+    fill32(dbias, 0u, cols);
+    return;
+  }
+  const u64 shape[2] = {num_elements / cols, cols};
+  const bool reduced[2] = {true, false};
+  u64 st[NIN + 1][MAX_NDIM] = {};
+  st[0][1] = 1; // target: one value per column
+  for (int a = 0; a < NIN; ++a) {
+    st[a + 1][0] = cols;
+    st[a + 1][1] = 1;
+  }
+  IterPlan plan;
+  make_plan(&plan, shape, 2, NIN + 1, st, reduced, 1);
+  launch_reduce<SumOp, Term, NIN>(plan, dbias, ins, term, SumOp{}, /*accumulate=*/false, 0.0f);
 }
 
 static unsigned int one_pattern(DTYPE dt) {
@@ -160,6 +195,52 @@ void arena_memcpy_d2h_cuda(void *dest, const void *src, u64 size) {
 }
 void arena_memcpy_d2d_cuda(void *dest, const void *src, u64 size) {
   PB_FATAL(cudaMemcpyAsync(dest, src, size, cudaMemcpyDeviceToDevice, stream()));
+}
+
+// ---- backward pieces of the reference's fused GEMM / conv epilogues ---------------------------------
+// src/kernels/cuda/matmul_relu.cu:137-150 (launch_relu_grad_modulate_cuda):
+// dc[i] = dout[i] * (out[i] > 0 ? 1 : alpha), 128-bit accesses.
+void plast_b200_relu_grad_modulate(const float *dout, const float *out_data, float *dc, u64 num_elements,
+                                   float alpha) {
+  begin_call();
+  if (!dout || !out_data || !dc) {
+    set_error(PLAST_B200_ERR_NULL, "relu_grad_modulate: NULL pointer");
+    return;
+  }
+  const u64 shape[1] = {num_elements};
+  u64 st[3][MAX_NDIM] = {};
+  st[0][0] = st[1][0] = st[2][0] = 1;
+  IterPlan plan;
+  make_plan(&plan, shape, 1, 3, st, nullptr, 0);
+  const float *ins[2] = {dout, out_data};
+  launch_ew<ReluGradModulate, 2>(plan, dc, ins, ReluGradModulate{alpha});
+  end_call();
+}
+// src/kernels/cuda/matmul_bias_relu.cu:143-151, 219-223: dbias[c] = sum over rows of dc_mod[r, c]
+// (the reference zeroes dbias and then issues one float atomic per element; here a deterministic
+// tree sum overwrites dbias).
+void plast_b200_bias_grad_reduce(const float *dc_mod, float *dbias, u64 num_elements, u64 cols) {
+  begin_call();
+  if (!dc_mod || !dbias) {
+    set_error(PLAST_B200_ERR_NULL, "bias_grad_reduce: NULL pointer");
+    return;
+  }
+  const float *ins[1] = {dc_mod};
+  column_sums<CopyF, 1>("bias_grad_reduce", ins, dbias, num_elements, cols, CopyF{});
+  end_call();
+}
+// Both steps in one pass, without the dc_mod buffer (and the cudaMalloc / cudaFree around it,
+// matmul_bias_relu.cu:177-179, 226): dbias[c] = sum_r dout[r, c] * (out[r, c] > 0 ? 1 : alpha).
+void plast_b200_bias_grad_masked(const float *dout, const float *out_data, float *dbias, u64 num_elements,
+                                 u64 cols, float alpha) {
+  begin_call();
+  if (!dout || !out_data || !dbias) {
+    set_error(PLAST_B200_ERR_NULL, "bias_grad_masked: NULL pointer");
+    return;
+  }
+  const float *ins[2] = {dout, out_data};
+  column_sums<ReluGradModulate, 2>("bias_grad_masked", ins, dbias, num_elements, cols, ReluGradModulate{alpha});
+  end_call();
 }
 
 // Strided gather into a contiguous buffer (src/kernels/cuda/cuda_pack.cu:5-27), through the
