@@ -225,6 +225,17 @@ typedef struct PlastChainStep {
 void plast_b200_chain_forward(const Tensor **inputs, int n_inputs, Tensor *output,
                               const PlastChainStep *steps, int n_steps);
 
+/* The same chain on HOST buffers (what a caller pays when its data starts and ends on the host,
+ * the reference's numpy -> tensor -> op -> numpy() round trip, src/python/bindings.cpp:93,144):
+ * host_inputs[i] holds input_elems[i] floats, either n or 1 (a constant); host_output receives n
+ * floats. The work is cut into 32 MiB chunks that are copied in, computed and copied out on three
+ * streams at once (three staging slots on the device, kept until plast_b200_release_workspace),
+ * so both directions of the link stay busy; pass pinned memory, pageable memory serialises the
+ * copies. Everything is queued behind the work already on the library stream and is complete
+ * when that stream is: synchronise it before reading host_output. */
+void plast_b200_chain_forward_host(const float *const *host_inputs, const u64 *input_elems, int n_inputs,
+                                   float *host_output, u64 n, const PlastChainStep *steps, int n_steps);
+
 /* ------------------------------------------------------------------------------------------
  * Symbols the reference's other translation units link against.
  * ------------------------------------------------------------------------------------------ */

@@ -81,7 +81,7 @@ def declared_symbols() -> list[str]:
     """Every extern "C" symbol the headers under include/ declare."""
     syms = [f"{op}_cuda_forward" for op in FORWARD_OPS] + [f"{op}_cuda_backward" for op in BACKWARD_OPS]
     syms += [
-        "plast_b200_chain_forward", "zeros_cuda", "ones_cuda", "set_ones_grad_cuda", "zero_grad_cuda",
+        "plast_b200_chain_forward", "plast_b200_chain_forward_host", "zeros_cuda", "ones_cuda", "set_ones_grad_cuda", "zero_grad_cuda",
         "reshape_backward_cuda", "transpose_backward_cuda", "arena_alloc_cuda", "arena_free_cuda",
         "arena_memset_cuda", "arena_memcpy_h2d_cuda", "arena_memcpy_d2h_cuda", "arena_memcpy_d2d_cuda",
         "plast_b200_pack", "plast_b200_last_error", "plast_b200_last_error_message",
@@ -116,6 +116,9 @@ def _load() -> C.CDLL:
     lib.plast_b200_chain_forward.argtypes = [C.POINTER(C.POINTER(CTensor)), C.c_int, C.POINTER(CTensor),
                                              C.POINTER(ChainStep), C.c_int]
     lib.plast_b200_chain_forward.restype = None
+    lib.plast_b200_chain_forward_host.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_uint64), C.c_int, C.c_void_p,
+                                                  C.c_uint64, C.POINTER(ChainStep), C.c_int]
+    lib.plast_b200_chain_forward_host.restype = None
     lib.plast_b200_relu_grad_modulate.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_float]
     lib.plast_b200_bias_grad_reduce.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64]
     lib.plast_b200_bias_grad_masked.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_float]
@@ -365,6 +368,25 @@ def chain_forward(inputs, output: Tensor, steps, check: bool = True):
     if check:
         check_error()
     return output
+
+
+def chain_forward_host(host_inputs, output, steps, check: bool = True):
+    """The chain on host buffers: host_inputs are float32 numpy arrays (or (address, elems) pairs
+    for memory owned elsewhere, e.g. a pinned torch tensor) of output.size elements or of 1;
+    output likewise. Copies and kernels of successive chunks overlap; returns once everything is
+    queued: call synchronize() before reading the output."""
+    def addr(a):
+        return (a[0], a[1]) if isinstance(a, tuple) else (a.ctypes.data, a.size)
+    pairs = [addr(a) for a in host_inputs]
+    out_addr, n = addr(output)
+    ptrs = (C.c_void_p * len(pairs))(*[p for p, _ in pairs])
+    elems = (C.c_uint64 * len(pairs))(*[e for _, e in pairs])
+    arr = (ChainStep * len(steps))()
+    for i, (name, a, b, fval) in enumerate(steps):
+        arr[i] = ChainStep(CHAIN_OPCODES[name], a, b, fval)
+    lib.plast_b200_chain_forward_host(ptrs, elems, len(pairs), out_addr, n, arr, len(steps))
+    if check:
+        check_error()
 
 
 def synchronize():

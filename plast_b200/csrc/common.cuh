@@ -56,6 +56,9 @@ bool get_workspace(Workspace *ws);
 
 int sm_count();
 
+// Frees the staging buffers, streams and events of the host-buffer chain (host_pipeline.cu).
+void release_host_pipeline();
+
 // Fills n 32-bit words with a bit pattern on the library stream (helpers.cu).
 void fill32(void *data, unsigned int pattern, u64 n);
 

@@ -245,6 +245,17 @@ static void reduce_plan(IterPlan *plan, const Tensor *a, u64 dim, const u64 *tar
   }
 }
 
+// True when walking the tensor in logical row-major order walks memory front to back.
+static bool row_major_dense(const Tensor *t) {
+  u64 expect = 1;
+  for (u64 d = t->ndim; d-- > 0;) {
+    if (t->shape[d] == 1) continue;
+    if (t->strides[d] != expect) return false;
+    expect *= t->shape[d];
+  }
+  return true;
+}
+
 template <class Op>
 static void reduce_forward(const char *name, const Tensor **inputs, Tensor *output,
                            KernelParams params, bool mean) {
@@ -279,6 +290,32 @@ static void reduce_forward(const char *name, const Tensor **inputs, Tensor *outp
     memcpy(&bits, &start, 4);
     if (std::is_same<Op, ArgMaxOp>::value) bits = 0;
     fill32(output->data, bits, n_out);
+    end_call();
+    return;
+  }
+  if (std::is_same<Op, ArgMaxOp>::value && dim == PLAST_FULL_REDUCE && !row_major_dense(a)) {
+    // The flat index of a full argmax counts elements in the view's logical row-major order
+    // (cpu_utils.c:121-154 walks coordinates), which is not the order a permuted or expanded
+    // view lies in memory. Gather the view into a stream-ordered scratch copy and reduce that.
+    void *packed = nullptr;
+    PB_CUDA(cudaMallocAsync(&packed, numel(a) * sizeof(float), stream()));
+    plast_b200_pack(a, packed);
+    if (!failed()) {
+      Tensor dense = *a;
+      dense.data = packed;
+      u64 s = 1;
+      for (u64 d = a->ndim; d-- > 0;) {
+        dense.strides[d] = s;
+        s *= a->shape[d];
+      }
+      IterPlan plan;
+      reduce_plan(&plan, &dense, dim, tst);
+      const float *ins[1] = {(const float *)packed};
+      launch_reduce<Op, IdentityPro, 1>(plan, (typename Op::Out *)output->data, ins, IdentityPro{}, Op{},
+                                        false, 0.0f);
+    }
+    cudaFreeAsync(packed, stream());
+    if (!failed()) note_kernel("argmax_of_packed_view");
     end_call();
     return;
   }

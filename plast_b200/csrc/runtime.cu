@@ -152,6 +152,7 @@ const char *plast_b200_last_kernel(void) { return pb::t_kernel; }
 const char *plast_b200_version(void) { return "plast_b200 0.1 (sm_100a)"; }
 
 void plast_b200_release_workspace(void) {
+  pb::release_host_pipeline();
   std::lock_guard<std::mutex> lock(pb::g_ws_mutex);
   int cur = 0;
   if (cudaGetDevice(&cur) != cudaSuccess) return;

@@ -75,6 +75,24 @@ def test_empty_and_single_element_reductions(cuda, oracle):
             assert got[0] == 3.5 == ref[0]
 
 
+def test_full_argmax_of_views_counts_in_logical_order(cuda):
+    A = rand_normal(5, (37, 53))
+    A[11, 40] = 9.0
+    tA = cuda.tensor(A)
+    out = cuda.empty((1,), dtype=INT32)
+    for view, ref in ((tA, A), (tA.transpose(0, 1), A.T)):
+        cuda.forward("argmax", [view], out, dim=FULL_REDUCE)
+        assert int(out.numpy()[0]) == int(np.argmax(ref))               # row-major index of the VIEW
+    B = rand_normal(6, (5, 7, 9))
+    B[3, 2, 8] = B[1, 6, 0] = 11.0                                        # a tie: lowest logical index wins
+    tB = cuda.tensor(B)
+    for perm in ((2, 0, 1), (1, 2, 0), (0, 2, 1)):
+        st = [tB.strides[p] for p in perm]
+        sh = [tB.shape[p] for p in perm]
+        cuda.forward("argmax", [tB.view(sh, st)], out, dim=FULL_REDUCE)
+        assert int(out.numpy()[0]) == int(np.argmax(B.transpose(perm))), perm
+
+
 def test_argmax_ties_pick_lowest_index(cuda, oracle):
     A = np.zeros((64, 4096), np.float32)
     A[:, 100] = 5.0; A[:, 3000] = 5.0; A[:, 4095] = 5.0
