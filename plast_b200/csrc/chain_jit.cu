@@ -157,9 +157,10 @@ std::string structure_key(const ChainProgramView &p) {
   return k;
 }
 
-std::string instance_name(const ChainProgramView &p, int vec, bool idx64, bool one_d) {
+std::string instance_name(const ChainProgramView &p, int vec, bool idx64, bool one_d, unsigned cmask = 0) {
   return "pb::ew_kernel<pb::JitF, " + std::to_string(tensor_inputs(p)) + ", " + std::to_string(vec) + ", " +
-         (idx64 ? "unsigned long long" : "unsigned int") + ", " + (one_d ? "true" : "false") + ">";
+         (idx64 ? "unsigned long long" : "unsigned int") + ", " + (one_d ? "true" : "false") + ", " +
+         std::to_string(cmask) + "u>";
 }
 std::string program_source(const ChainProgramView &p, const std::string &inst, bool idx64) {
   const char *idx = idx64 ? "unsigned long long" : "unsigned int";
@@ -171,10 +172,10 @@ std::string program_source(const ChainProgramView &p, const std::string &inst, b
 std::mutex g_mutex;
 std::unordered_map<std::string, CUfunction> g_cache; // nullptr = compile failed, do not retry
 
-CUfunction get_kernel(const ChainProgramView &p, int vec, bool idx64, bool one_d) {
+CUfunction get_kernel(const ChainProgramView &p, int vec, bool idx64, bool one_d, unsigned cmask) {
   Api &a = api();
   if (!a.ok) return nullptr;
-  const std::string inst = instance_name(p, vec, idx64, one_d);
+  const std::string inst = instance_name(p, vec, idx64, one_d, cmask);
   const std::string key = structure_key(p) + inst;
   std::lock_guard<std::mutex> lock(g_mutex);
   auto it = g_cache.find(key);
@@ -240,7 +241,9 @@ bool launch_one(const ChainProgramView &p, const IterPlan &plan, float *out, con
   const u64 per_block = (u64)kEwThreads * kEwUnroll;
   const u64 blocks = (n_items + per_block - 1) / per_block;
   if (blocks > 0x7fffffffull) return false;
-  CUfunction fn = get_kernel(p, c.vec, c.idx64, c.one_d);
+  // same compile-time operand masks as the ahead-of-time engine
+  const unsigned cmask = (NIN >= 2 && c.vec == 4 && !c.idx64 && (vec_mask == 1u || vec_mask == 2u)) ? vec_mask : 0u;
+  CUfunction fn = get_kernel(p, c.vec, c.idx64, c.one_d, cmask);
   if (!fn) return false;
   const bool ok = c.idx64 ? launch_variant<NIN, uint64_t>(fn, plan, out, ins, f, c.vec, n_items, vec_mask, (unsigned)blocks)
                           : launch_variant<NIN, uint32_t>(fn, plan, out, ins, f, c.vec, n_items, vec_mask, (unsigned)blocks);

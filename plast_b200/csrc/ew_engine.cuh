@@ -83,7 +83,26 @@ void launch_ew_one(const IterPlan &plan, float *out, const float *const *ins, co
     else if (c.vec == 2) PB_EW_LAUNCH(2, IDX, ONED);                                               \
     else PB_EW_LAUNCH(1, IDX, ONED);                                                               \
   } while (0)
-  if (c.idx64) {
+  // compile-time operand masks for the two shapes that matter: one streamed operand (the first
+  // or the second) and per-row / constant operands beside it
+  bool launched = false;
+  if constexpr (NIN >= 2) {
+    if (c.vec == 4 && !c.idx64 && (vec_mask == 1u || vec_mask == 2u)) {
+      OffsetCalc<NIN + 1, uint32_t> oc;
+      fill_offset_calc(&oc, plan, 4);
+#define PB_EW_MASKED(ONED, CMASK)                                                                  \
+  ew_kernel<F, NIN, 4, uint32_t, ONED, CMASK><<<grid, block, 0, s>>>(f, out, ip, oc, (uint32_t)n_items, vec_mask)
+      if (vec_mask == 1u) {
+        if (c.one_d) PB_EW_MASKED(true, 1u); else PB_EW_MASKED(false, 1u);
+      } else {
+        if (c.one_d) PB_EW_MASKED(true, 2u); else PB_EW_MASKED(false, 2u);
+      }
+#undef PB_EW_MASKED
+      launched = true;
+    }
+  }
+  if (launched) {
+  } else if (c.idx64) {
     if (c.one_d) PB_EW_BY_VEC(uint64_t, true);
     else PB_EW_BY_VEC(uint64_t, false);
   } else {
