@@ -145,13 +145,17 @@ softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const in
 
     float4 *yr = reinterpret_cast<float4 *>(y + yoff);
     const float lse = (MODE == kLogSoftmax) ? logf(s) : 0.0f;
+    // One correctly rounded reciprocal per row, then a multiply per element: within 1 ulp of the
+    // recipe's exp_x / sum_exp (the exponentials themselves are ~3 ulp), and a tenth of the
+    // instructions of a full-precision division per element.
+    const float inv_s = 1.0f / s;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const u64 j = (u64)tx + (u64)i * tx_n;
       if (live && j < nvec) {
         float4 r;
         if (MODE == kSoftmax) {
-          r.x = v[i].x / s; r.y = v[i].y / s; r.z = v[i].z / s; r.w = v[i].w / s;
+          r.x = v[i].x * inv_s; r.y = v[i].y * inv_s; r.z = v[i].z * inv_s; r.w = v[i].w * inv_s;
         } else {
           r.x = v[i].x - lse; r.y = v[i].y - lse; r.z = v[i].z - lse; r.w = v[i].w - lse;
         }
@@ -266,7 +270,23 @@ cross_entropy_rows_kernel(const float *__restrict__ x, const int *__restrict__ l
     const bool label_ok = label >= 0 && (u64)label < g.cols;
     const float x_label = label_ok ? __ldg(x + ioff[0] + label) : 0.0f;
     MaxSum acc{-FLT_MAX, 0.0f};
+    // start of this warp's next row, for the prefetch below
+    const float4 *xr_next = nullptr;
+    if (row + row_step < g.rows) {
+      u64 yoff2 = 0, ioff2[2] = {0, 0};
+      g.outer.offsets(row + row_step, &yoff2, ioff2);
+      xr_next = reinterpret_cast<const float4 *>(x + ioff2[0]);
+    }
     for (unsigned b = lane; b < nvec + lane; b += kCeBatch * 32) {
+      // While this batch is summed the warp has no load in flight; ask L2 for the next batch (or
+      // the head of the next row) now: lane l takes the l-th 128-byte line of those 4 KiB.
+      {
+        const unsigned next_first = (b - lane) + kCeBatch * 32; // float4 index where the next batch starts
+        const float4 *pf = nullptr;
+        if (next_first + lane * 8 < nvec) pf = xr + next_first + lane * 8;
+        else if (next_first >= nvec && xr_next && lane * 8 < nvec) pf = xr_next + lane * 8;
+        if (pf) asm volatile("prefetch.global.L2 [%0];" ::"l"(pf));
+      }
       float4 v[kCeBatch];
 #pragma unroll
       for (int u = 0; u < kCeBatch; ++u)
