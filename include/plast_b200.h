@@ -180,6 +180,13 @@ void scale_bias_leaky_relu_cuda_backward(Tensor **inputs, const Tensor *output, 
 void add_leaky_relu_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
 void add_leaky_relu_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
 
+/* Forward of the graph `C = leaky_relu(A + b); s = sum(C, last axis)` in one pass over A: both
+ * results are written (the ForwardKernel signature has one output, hence the explicit arguments).
+ * b holds one row ([cols] or [1, cols]) or has A's shape. C is bit-identical to add -> leaky_relu;
+ * s is a tree sum of C's rows (the reference adds left to right). Layouts the one-pass kernel does
+ * not take (views, cols % 4 != 0, unaligned) run as add_leaky_relu followed by sum. */
+void plast_b200_add_leaky_relu_row_sum(const Tensor *a, const Tensor *b, Tensor *c, Tensor *s, float slope);
+
 /* ------------------------------------------------------------------------------------------
  * Fused elementwise chain: what the scheduler's chain fusion issues for a maximal subgraph of
  * same-shape / broadcast elementwise nodes (the reference scheduler runs such a chain node by

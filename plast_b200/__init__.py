@@ -93,6 +93,7 @@ def declared_symbols() -> list[str]:
         "chain_cuda_forward", "chain_cuda_backward",
         "sgd_step_cuda", "adam_step_cuda", "adamw_step_cuda", "plast_b200_adam_state_release",
         "plast_b200_relu_grad_modulate", "plast_b200_bias_grad_reduce", "plast_b200_bias_grad_masked",
+        "plast_b200_add_leaky_relu_row_sum",
     ]
     return syms
 
@@ -119,6 +120,8 @@ def _load() -> C.CDLL:
     lib.plast_b200_chain_forward_host.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_uint64), C.c_int, C.c_void_p,
                                                   C.c_uint64, C.POINTER(ChainStep), C.c_int]
     lib.plast_b200_chain_forward_host.restype = None
+    lib.plast_b200_add_leaky_relu_row_sum.argtypes = [C.POINTER(CTensor)] * 4 + [C.c_float]
+    lib.plast_b200_add_leaky_relu_row_sum.restype = None
     lib.plast_b200_relu_grad_modulate.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_float]
     lib.plast_b200_bias_grad_reduce.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64]
     lib.plast_b200_bias_grad_masked.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_float]

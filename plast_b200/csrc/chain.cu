@@ -77,6 +77,54 @@ struct SblInputGrad { // du * scale
   }
 };
 
+// ---- C = leaky_relu(A + b) and s = sum(C, last axis) in one pass -------------------------------------
+// One warp per row of a contiguous [rows, cols] matrix (cols % 4 == 0, 16-byte aligned): each lane
+// loads float4s of A and of b's row (b is [cols]-like and stays in L1 / L2), stores C and keeps a
+// running sum; a shuffle tree finishes the row. C is bit-identical to the two-op sequence; s is a
+// tree sum of exactly those values.
+constexpr int kRowSumThreads = 256;
+__global__ void __launch_bounds__(kRowSumThreads)
+add_leaky_relu_row_sum_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ c,
+                              float *__restrict__ s, u64 rows, u64 cols, u64 b_row_stride, float alpha) {
+  const unsigned lane = threadIdx.x & 31;
+  const u64 warps = (u64)gridDim.x * (kRowSumThreads / 32);
+  const u64 nvec = cols >> 2;
+  for (u64 row = (u64)blockIdx.x * (kRowSumThreads / 32) + (threadIdx.x >> 5); row < rows; row += warps) {
+    const float4 *ar = reinterpret_cast<const float4 *>(a + row * cols);
+    const float4 *br = reinterpret_cast<const float4 *>(b + row * b_row_stride);
+    float4 *cr = reinterpret_cast<float4 *>(c + row * cols);
+    float acc = 0.0f;
+    for (u64 j0 = 0; j0 < nvec; j0 += 8 * 32) {
+      float4 va[8], vb[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const u64 j = j0 + lane + (u64)u * 32;
+        if (j < nvec) {
+          va[u] = __ldcs(ar + j);
+          vb[u] = __ldg(br + j);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const u64 j = j0 + lane + (u64)u * 32;
+        if (j < nvec) {
+          float4 r;
+          float t;
+          t = va[u].x + vb[u].x; r.x = t > 0.0f ? t : t * alpha;
+          t = va[u].y + vb[u].y; r.y = t > 0.0f ? t : t * alpha;
+          t = va[u].z + vb[u].z; r.z = t > 0.0f ? t : t * alpha;
+          t = va[u].w + vb[u].w; r.w = t > 0.0f ? t : t * alpha;
+          __stcs(cr + j, r);
+          acc += (r.x + r.y) + (r.z + r.w);
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) s[row] = acc;
+  }
+}
+
 // ---- generic chain -------------------------------------------------------------------------------------
 struct ChainProgram {
   int n_inputs, n_steps;
@@ -289,6 +337,66 @@ void scale_bias_leaky_relu_cuda_backward(Tensor **inputs, const Tensor *output, 
   fused_backward_one<SblInputGrad, 3>(name, inputs, output, 0, SblInputGrad{params.fval});
   if (!failed()) fused_backward_one<SblScaleGrad, 3>(name, inputs, output, 1, SblScaleGrad{params.fval});
   if (!failed()) fused_backward_one<SblBiasGrad, 3>(name, inputs, output, 2, SblBiasGrad{params.fval});
+  end_call();
+}
+
+void plast_b200_add_leaky_relu_row_sum(const Tensor *a, const Tensor *b, Tensor *c, Tensor *s, float slope) {
+  const char *name = "add_leaky_relu_row_sum";
+  begin_call();
+  if (!check_tensor(a, name) || !check_tensor(b, name) || !check_tensor(c, name) || !check_tensor(s, name)) return;
+  if (!float_only(a, name) || !float_only(b, name) || !float_only(c, name) || !float_only(s, name)) return;
+  if (a->ndim < 1 || c->ndim != a->ndim) {
+    set_error(PLAST_B200_ERR_SHAPE, "%s: a and c must have the same rank >= 1", name);
+    return;
+  }
+  for (u64 d = 0; d < a->ndim; ++d)
+    if (a->shape[d] != c->shape[d]) {
+      set_error(PLAST_B200_ERR_SHAPE, "%s: a and c differ in dim %llu", name, (unsigned long long)d);
+      return;
+    }
+  const u64 cols = a->shape[a->ndim - 1];
+  const u64 rows = cols ? numel(a) / cols : 0;
+  if (numel(s) != rows) {
+    set_error(PLAST_B200_ERR_SHAPE, "%s: s holds %llu elements, the matrix has %llu rows", name,
+              (unsigned long long)numel(s), (unsigned long long)rows);
+    return;
+  }
+  // b: one row for all (any shape of cols elements, e.g. [1, cols] or [cols]) or a's own shape
+  const bool b_row = numel(b) == cols && b->ndim >= 1 && b->shape[b->ndim - 1] == cols;
+  const bool b_full = numel(b) == numel(a) && b->ndim == a->ndim && b->shape[b->ndim - 1] == cols;
+  auto dense = [](const Tensor *t) {
+    u64 expect = 1;
+    for (u64 d = t->ndim; d-- > 0;) {
+      if (t->shape[d] == 1) continue;
+      if (t->strides[d] != expect) return false;
+      expect *= t->shape[d];
+    }
+    return true;
+  };
+  const bool aligned = ((((uintptr_t)a->data) | ((uintptr_t)b->data) | ((uintptr_t)c->data)) & 15) == 0;
+  const bool fast = (b_row || b_full) && dense(a) && dense(b) && dense(c) && dense(s) && cols % 4 == 0 &&
+                    aligned && rows > 0;
+  if (!fast) {
+    // any other layout: the two entry points one after the other
+    const Tensor *in2[2] = {a, b};
+    KernelParams p = {0, 0, slope};
+    add_leaky_relu_cuda_forward(in2, c, p);
+    if (failed()) return;
+    const Tensor *in1[1] = {c};
+    KernelParams q = {a->ndim - 1, 0, 0.0f};
+    Tensor s_copy = *s; // the reduction rewrites its output's shape; the caller's header stays as given
+    sum_cuda_forward(in1, &s_copy, q);
+    return;
+  }
+  const u64 warps_per_cta = kRowSumThreads / 32;
+  u64 blocks = (rows + warps_per_cta - 1) / warps_per_cta;
+  const u64 cap = (u64)sm_count() * 32;
+  if (blocks > cap) blocks = cap;
+  add_leaky_relu_row_sum_kernel<<<(unsigned)blocks, kRowSumThreads, 0, stream()>>>(
+      (const float *)a->data, (const float *)b->data, (float *)c->data, (float *)s->data, rows, cols,
+      b_full ? cols : 0, slope);
+  count_launch();
+  note_kernel("add_leaky_relu_row_sum");
   end_call();
 }
 

@@ -106,6 +106,9 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
         timeit(1, "row_sum", lambda: pb.forward("sum", [tC], ts, dim=1, check=False), (M * N + M) * F, M * N, ws)
         timeit(1, "fused_add_relu", lambda: pb.forward("add_leaky_relu", [tA, tb], tC, fval=0.0, check=False),
                (2 * M * N + N) * F, M * N, ws)
+        timeit(1, "fused_fwd_C_and_row_sum",
+               lambda: pb.lib.plast_b200_add_leaky_relu_row_sum(C.byref(tA.c), C.byref(tb.c), C.byref(tC.c), C.byref(ts.c), 0.0),
+               (2 * M * N + N + M) * F, M * N, ws)
         tbg = wrap(b); tbg.c.requires_grad = True
         gtb = wrap(gb); tbg.grad = gtb; tbg.c.grad = C.pointer(gtb.c)
         tCg = wrap(Cc); gC = wrap(G); tCg.grad = gC; tCg.c.grad = C.pointer(gC.c)

@@ -9,6 +9,7 @@ Bounds (from the reference's CPU path being the contract):
 import numpy as np
 import pytest
 
+import plast_b200 as pb
 from harness import (FULL_REDUCE, assert_bit_equal, assert_sum_close, assert_ulp, rand_normal,
                      rand_uniform)
 
@@ -237,3 +238,20 @@ def test_error_reporting(cuda):
         cuda.forward("sum", [a], cuda.empty((4,)), dim=5)
     cuda.forward("add", [a, a], out)               # the next good call clears the error
     assert pb.lib.plast_b200_last_error() == 0
+
+
+@pytest.mark.parametrize("shape,bshape", [((1024, 1024), (1, 1024)), ((37, 64), (64,)), ((5, 7, 128), (5, 7, 128)),
+                                          ((33, 1001), (1, 1001)), ((256, 8200), (1, 8200))])
+def test_fused_forward_writes_c_and_its_row_sums(cuda, oracle, shape, bshape):
+    import ctypes as C
+    A, b = rand_uniform(0, shape), rand_uniform(1, bshape)
+    ta, tb = cuda.tensor(A), cuda.tensor(b)
+    c, s = cuda.empty(shape), cuda.empty(shape[:-1])
+    pb.lib.plast_b200_add_leaky_relu_row_sum(C.byref(ta.c), C.byref(tb.c), C.byref(c.c), C.byref(s.c), 0.0)
+    pb.check_error()
+    oa, ob = oracle.tensor(A), oracle.tensor(b)
+    oab, oc = oracle.empty(shape), oracle.empty(shape)
+    oracle.forward("add", [oa, ob], oab); oracle.forward("leaky_relu", [oab], oc, fval=0.0)
+    osum = oracle.empty(shape[:-1]); oracle.forward("sum", [oc], osum, dim=len(shape) - 1)
+    assert_bit_equal(c.numpy(), oc.numpy(), "C of the fused forward")
+    assert_sum_close(s.numpy().reshape(shape[:-1]), osum.numpy().reshape(shape[:-1]), np.abs(oc.numpy()).sum(axis=-1), what="row sums")
