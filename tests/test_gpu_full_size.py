@@ -128,3 +128,34 @@ def test_config5_nchw_epilogue_256x256x56x56(cuda):
     cuda.backward("scale_bias_leaky_relu", [tX, tS, tB], Y, fval=0.0)
     want = (Yv > 0).sum(axis=(0, 2, 3)).astype(np.float32).reshape(pshape)
     assert np.array_equal(tB.grad.numpy(), want)
+
+
+def test_more_than_2_to_31_elements_use_64_bit_indexing(cuda):
+    """8.6 GB per tensor: element offsets no longer fit 32 bits. Everything is generated and checked
+    on the device except a handful of small read-backs."""
+    import ctypes as C
+    R, Cn = (1 << 19) + 1, 4096
+    n = R * Cn                                                            # 2^31 + 4096
+    x, y = pb.Tensor((R, Cn)), pb.Tensor((R, Cn))
+    pb.lib.ones_cuda(C.byref(x.c), n); pb.check_error()
+    plant = np.float32([5.0])
+    pb.lib.arena_memcpy_h2d_cuda(x.c.data + 4 * (n - 3), plant.ctypes.data, 4)   # beyond offset 2^31
+    cuda.forward("add", [x, x], y)                                        # elementwise, 64-bit offsets
+    rows = cuda.empty((R,)); cuda.forward("sum", [y], rows, dim=1)
+    rv = rows.numpy()
+    assert np.all(rv[:-1] == 2.0 * Cn) and rv[-1] == 2.0 * Cn + 8.0
+    cols = cuda.empty((Cn,)); cuda.forward("sum", [y], cols, dim=0)
+    cv = cols.numpy()
+    want = np.full(Cn, 2.0 * R, np.float32); want[Cn - 3] += 8.0          # all exact: integers below 2^24
+    assert np.array_equal(cv, want)
+    mx = cuda.empty((1,)); cuda.forward("max", [y], mx, dim=FULL_REDUCE)
+    assert mx.numpy()[0] == 10.0
+    tot = cuda.empty((1,)); cuda.forward("sum", [y], tot, dim=FULL_REDUCE)
+    assert abs(float(tot.numpy()[0]) - (2.0 * n + 8.0)) <= 1e-6 * 2.0 * n
+    # scalar broadcast and a unary op over the same extent
+    two = cuda.tensor(np.float32(2.0).reshape(()))
+    cuda.forward("div", [y, two], y); cuda.forward("neg", [y], y)
+    cuda.forward("max", [y], mx, dim=FULL_REDUCE)
+    assert mx.numpy()[0] == -1.0
+    cuda.forward("min", [y], mx, dim=FULL_REDUCE)
+    assert mx.numpy()[0] == -5.0
