@@ -193,6 +193,7 @@ struct MomentState {
   Tensor **m, **v;
   Tensor *structs;
   void *slab;
+  int n; // parameters the moments were created for
 };
 static std::mutex g_state_mutex;
 static std::unordered_map<Tensor **, MomentState> g_states; // keyed by the m array
@@ -243,6 +244,7 @@ static bool create_moments(const char *name, Tensor **parameters, int n, Tensor 
       (which == 0 ? st.m : st.v)[i] = t;
     }
   }
+  st.n = n;
   {
     std::lock_guard<std::mutex> lock(g_state_mutex);
     g_states[st.m] = st;
@@ -250,6 +252,17 @@ static bool create_moments(const char *name, Tensor **parameters, int n, Tensor 
   *m_out = st.m;
   *v_out = st.v;
   return true;
+}
+
+// Moments made by this library cover a fixed number of parameters; a later step with a longer list
+// would index past them (the reference has the same limit, silently).
+static bool moments_cover(const char *name, Tensor **m, int num_parameters) {
+  std::lock_guard<std::mutex> lock(g_state_mutex);
+  auto it = g_states.find(m);
+  if (it == g_states.end() || num_parameters <= it->second.n) return true;
+  set_error(PLAST_B200_ERR_SHAPE, "%s: %d parameters, but the moments were created for %d", name, num_parameters,
+            it->second.n);
+  return false;
 }
 
 // adam.c:48-49: float * double sqrt / float, evaluated in double and rounded to float once.
@@ -291,6 +304,7 @@ void adam_step_cuda(Adam *optimizer, Tensor **parameters, int num_parameters) {
   }
   optimizer->t++;
   if (!optimizer->m && !create_moments("adam", parameters, num_parameters, &optimizer->m, &optimizer->v)) return;
+  if (!moments_cover("adam", optimizer->m, num_parameters)) return;
   AdamRule rule = {};
   rule.lr_t = bias_corrected_lr(optimizer->lr, optimizer->beta1, optimizer->beta2, optimizer->t);
   rule.beta1 = optimizer->beta1;
@@ -315,6 +329,7 @@ void adamw_step_cuda(AdamW *optimizer, Tensor **parameters, int num_parameters) 
   }
   optimizer->t++;
   if (!optimizer->m && !create_moments("adamw", parameters, num_parameters, &optimizer->m, &optimizer->v)) return;
+  if (!moments_cover("adamw", optimizer->m, num_parameters)) return;
   AdamRule rule = {};
   rule.lr_t = bias_corrected_lr(optimizer->lr, optimizer->beta1, optimizer->beta2, optimizer->t);
   rule.beta1 = optimizer->beta1;

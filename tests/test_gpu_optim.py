@@ -70,3 +70,15 @@ def test_errors_and_empty_lists():
     pb.lib.sgd_step_cuda(None, O.param_array([]), 0)
     assert pb.lib.plast_b200_last_error() == 3                            # NULL optimizer, as sgd.c:12-15 reports
     pb.lib.plast_b200_clear_error()
+
+
+def test_adam_rejects_a_longer_parameter_list_than_its_moments_cover():
+    ps = [pb.Tensor.from_numpy(np.ones(16, np.float32), requires_grad=True) for _ in range(3)]
+    opt = O.Adam()
+    opt.lr, opt.beta1, opt.beta2, opt.epsilon, opt.t = 1e-3, 0.9, 0.999, 1e-8, 0
+    O.step(opt, ps[:2])
+    pb.lib.adam_step_cuda(C.byref(opt), O.param_array(ps), 3)
+    assert pb.lib.plast_b200_last_error() == 2
+    pb.lib.plast_b200_clear_error()
+    O.step(opt, ps[:1])                                                   # a shorter list is fine
+    O.release_state(opt)
