@@ -339,7 +339,7 @@ def run_ours(args):
         from plast_b200.opbench import per_op_table
         del x_h, y_h, z_h
         per_op = per_op_table(torch, pb, dev, peak, reps=args.op_reps,
-                              configs=tuple(int(c) for c in args.configs.split(",")))
+                              configs=tuple(int(c) for c in args.configs.split(",")), chain_elems=args.elems)
 
     sharded = None
     if world > 1 and not args.no_per_op:
@@ -388,7 +388,7 @@ def run_per_op_only(args):
     pb.lib.plast_b200_set_stream(C.c_void_p(torch.cuda.current_stream().cuda_stream))
     peak, kind = measured_peak()
     cfgs = tuple(int(c) for c in args.configs.split(","))
-    rows = per_op_table(torch, pb, dev, peak, reps=args.op_reps, configs=cfgs)
+    rows = per_op_table(torch, pb, dev, peak, reps=args.op_reps, configs=cfgs, chain_elems=args.elems)
     print(json.dumps({"per_op": rows, "peak_gbs": peak, "peak_source": f"of {kind}"}), flush=True)
 
 

@@ -87,9 +87,9 @@ def global_argmax(dist, torch, local_value, local_index, index_offset: int):
 
 # ---- benchmark of the sharded reductions (rank-parallel, CUDA) -------------------------------------
 def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 10):
-    """Strong-scaling rows for the reductions that need the all-reduce: the FIXED tensors of
-    configs 3, 4 and 5 are split across ranks along their outermost dim; every step is the local
-    kernel followed by the all-reduce, timed with CUDA events, max over ranks."""
+    """Strong-scaling rows: the FIXED tensors of configs 3, 4 and 5 are split across ranks along
+    their outermost dim; a step is the local kernel, followed by the all-reduce where the op needs
+    one (names ending in +allreduce), timed with CUDA events, max over ranks."""
     import numpy as np
 
     world = dist.get_world_size() if dist.is_initialized() else 1
@@ -167,6 +167,39 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
         global_mean(dist, loss, R)
 
     timeit("config3_cross_entropy_mean+allreduce", ce_mean, (R * Cn + R) * 4 + 4)
-    del L
+    # row ops of config 3 on the same row shard: independent per row, no collective
+    rs, Y = torch.empty(sh.count, device=dev), torch.empty_like(L)
+    trs, tY = wrap(rs), wrap(Y)
+    timeit("config3_row_sum", lambda: pb.forward("sum", [tL], trs, dim=1, check=False), (R * Cn + R) * 4)
+    timeit("config3_softmax", lambda: pb.forward("softmax", [tL], tY, dim=1, check=False), 2 * R * Cn * 4)
+    del L, Y
+
+    # config 5: NCHW epilogue, batch-sharded; forward needs no collective, the bias gradient a
+    # 1 KiB all-reduce of the per-GPU channel sums
+    N, Ch, H, W = 256, 256, 56, 56
+    sh = shard_dim(N, rank, world)
+    gen.manual_seed(300 + rank)
+    X = torch.randn((max(sh.count, 1), Ch, H, W), generator=gen, device=dev)
+    G = torch.randn((max(sh.count, 1), Ch, H, W), generator=gen, device=dev)
+    S = torch.rand((1, Ch, 1, 1), generator=gen, device=dev) - 0.5
+    B = torch.rand((1, Ch, 1, 1), generator=gen, device=dev) - 0.5
+    Yv = torch.empty_like(X)
+    gB = torch.zeros((1, Ch, 1, 1), device=dev)
+    tX5, tS, tB, tY5 = wrap(X), wrap(S), wrap(B), wrap(Yv)
+    total = N * Ch * H * W
+    timeit("config5_scale_bias_relu_fwd",
+           lambda: pb.forward("scale_bias_leaky_relu", [tX5, tS, tB], tY5, fval=0.0, check=False), 2 * total * 4 + 2048)
+    import ctypes as C
+    tBg = wrap(B); tBg.c.requires_grad = True
+    tg = wrap(gB); tBg.grad = tg; tBg.c.grad = C.pointer(tg.c)
+    tYg = wrap(Yv); tG = wrap(G); tYg.grad = tG; tYg.c.grad = C.pointer(tG.c)
+
+    def bias_grad():
+        gB.zero_()
+        pb.backward("scale_bias_leaky_relu", [tX5, tS, tBg], tYg, fval=0.0, check=False)
+        all_reduce_sum(dist, gB)
+
+    timeit("config5_bias_grad+allreduce", bias_grad, 2 * total * 4 + 1024)
+    del X, G, Yv
     torch.cuda.synchronize()
     return rows

@@ -18,7 +18,10 @@ import numpy as np
 NOMINAL = 8000.0
 
 
-def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2, 3, 4, 5, 6)):
+def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2, 3, 4, 5, 6),
+                 chain_elems: int = 1 << 28):
+    """chain_elems: length of configuration 2's vectors (2^28 in the benchmark; profiler captures use
+    fewer so that the device memory a multi-pass capture has to save stays small)."""
     gen = torch.Generator(device=dev)
     flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
     rows = []
@@ -116,7 +119,7 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
                (2 * M * N + 2 * N) * F, M * N, ws)
         del A, b, G, AB, Cc, s
     if 2 in configs:
-        n = 1 << 28
+        n = int(chain_elems)
         x, y, z = randn((n,), 0), randn((n,), 1), torch.empty(n, device=dev)
         one = torch.ones((), device=dev)
         tx, ty, tz = wrap(x), wrap(y), wrap(z)
