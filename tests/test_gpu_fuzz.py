@@ -1,0 +1,117 @@
+"""Seeded random layouts through the C ABI against the CPU oracle: random rank (0-8), extents,
+permuted views, broadcast operands (size-1 dims, missing leading dims, stride-0 expands) for the
+elementwise ops, and random axes / keepdim over permuted views for the reductions. The fixed cases
+of the other GPU tests pin named layouts; this one walks the planner's merge / sort / vector-width
+decisions over shapes nobody thought of."""
+import numpy as np
+import pytest
+
+from harness import FULL_REDUCE, INT32, assert_bit_equal, assert_sum_close, assert_ulp
+
+pytestmark = pytest.mark.gpu
+
+BITWISE = ["add", "sub", "mul", "div"]
+UNARY_BIT = ["abs", "neg", "leaky_relu"]
+UNARY_ULP = {"exp": (-5, 5), "sin": (-6, 6), "cos": (-6, 6)}
+
+
+def random_shape(rs, max_ndim=8, max_elems=40000):
+    nd = int(rs.randint(0, max_ndim + 1))
+    shape = []
+    total = 1
+    for _ in range(nd):
+        s = int(rs.choice([1, 2, 3, 4, 5, 7, 8, 16, 33]))
+        if total * s > max_elems:
+            s = 1
+        shape.append(s)
+        total *= s
+    return tuple(shape)
+
+
+def permuted_view(be, arr, perm):
+    """Tensor holding `arr` laid out so that view.transpose(perm-order) == arr: the data is stored
+    in permuted order and viewed back through strides (no copy on the device)."""
+    if arr.ndim < 2:
+        return be.tensor(arr)
+    stored = np.ascontiguousarray(arr.transpose(perm))
+    t = be.tensor(stored)
+    inv = np.argsort(perm)
+    st = [t.strides[i] for i in inv]
+    return t.view(list(arr.shape), st)
+
+
+def broadcast_operand(rs, shape):
+    """A shape that broadcasts to `shape`: some dims collapsed to 1, some leading dims dropped."""
+    b = [1 if rs.rand() < 0.4 else s for s in shape]
+    drop = int(rs.randint(0, len(b) + 1)) if len(b) and rs.rand() < 0.4 else 0
+    while drop and b and b[0] != 1:
+        b[0] = 1
+    return tuple(b[drop:]) if all(x == 1 for x in b[:drop]) else tuple(b)
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_elementwise_random_layouts(cuda, oracle, seed):
+    rs = np.random.RandomState(1000 + seed)
+    shape = random_shape(rs)
+    bshape = broadcast_operand(rs, shape)
+    A = rs.uniform(-2, 2, shape).astype(np.float32)
+    B = (rs.uniform(0.5, 2, bshape) * rs.choice([-1, 1], size=bshape)).astype(np.float32)
+    perm = list(rs.permutation(len(shape)))
+    op = BITWISE[seed % 4]
+    outs = []
+    for be in (cuda, oracle):
+        ta = permuted_view(be, A, perm)
+        tb = be.tensor(B)
+        out = be.empty(shape)
+        be.forward(op, [ta, tb], out)
+        outs.append(out.numpy())
+    assert_bit_equal(outs[0], outs[1], f"{op} {shape} perm {perm} b {bshape}")
+    # unary on the same view
+    uop = (UNARY_BIT + list(UNARY_ULP))[seed % 6]
+    outs = []
+    for be in (cuda, oracle):
+        out = be.empty(shape)
+        be.forward(uop, [permuted_view(be, A, perm)], out, fval=0.0 if seed % 2 else 0.1)
+        outs.append(out.numpy())
+    if uop in UNARY_ULP:
+        assert_ulp(outs[0], outs[1], 2, f"{uop} {shape} perm {perm}")
+    elif uop == "neg":
+        assert np.array_equal(outs[0], outs[1])
+    else:
+        assert_bit_equal(outs[0], outs[1], f"{uop} {shape} perm {perm}")
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_reductions_random_layouts(cuda, oracle, seed):
+    rs = np.random.RandomState(5000 + seed)
+    shape = random_shape(rs, max_ndim=6)
+    if len(shape) == 0:
+        shape = (int(rs.choice([1, 5, 1000])),)
+    A = rs.uniform(-1, 1, shape).astype(np.float32)
+    perm = list(rs.permutation(len(shape)))
+    dim = int(rs.randint(0, len(shape))) if rs.rand() < 0.7 else FULL_REDUCE
+    keepdim = bool(rs.rand() < 0.5)
+    op = ["sum", "mean", "max", "min", "argmax"][seed % 5]
+    res = []
+    for be in (cuda, oracle):
+        ta = permuted_view(be, A, perm)
+        if dim == FULL_REDUCE:
+            out_shape = [1]
+        elif keepdim:
+            out_shape = [1 if i == dim else s for i, s in enumerate(shape)]
+        else:
+            out_shape = [s for i, s in enumerate(shape) if i != dim] or [1]
+        out = be.empty(out_shape, dtype=INT32 if op == "argmax" else 1)
+        be.forward(op, [ta], out, dim=dim, keepdim=int(keepdim))
+        res.append(out.numpy().reshape(-1))
+    what = f"{op} {shape} perm {perm} dim {dim} keepdim {keepdim}"
+    if op == "argmax":
+        want = np.argmax(A) if dim == FULL_REDUCE else np.argmax(A, axis=dim)
+        assert np.array_equal(res[0], np.asarray(want, dtype=np.int32).reshape(-1)), what
+    elif op in ("max", "min"):
+        assert_bit_equal(res[0], res[1], what)
+    else:
+        a64 = np.abs(A.astype(np.float64))
+        n = A.size if dim == FULL_REDUCE else shape[dim]
+        scale = (a64.sum() if dim == FULL_REDUCE else a64.sum(axis=dim)) / (n if op == "mean" else 1)
+        assert_sum_close(res[0], res[1], np.asarray(scale).reshape(-1), what=what)
