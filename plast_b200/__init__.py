@@ -238,11 +238,12 @@ class Tensor:
     # -- construction -------------------------------------------------------------------------
     @staticmethod
     def from_numpy(arr: np.ndarray, device="cuda", requires_grad=False) -> "Tensor":
+        shape = np.shape(arr)                      # ascontiguousarray would turn a 0-dim array into [1]
         arr = np.ascontiguousarray(arr)
         dtype = INT32 if arr.dtype == np.int32 else FLOAT32
         if dtype == FLOAT32:
             arr = arr.astype(np.float32, copy=False)
-        t = Tensor(arr.shape, device=device, dtype=dtype, requires_grad=requires_grad)
+        t = Tensor(shape, device=device, dtype=dtype, requires_grad=requires_grad)
         t.copy_from(arr)
         return t
 

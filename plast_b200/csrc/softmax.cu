@@ -236,7 +236,7 @@ softmax_generic_kernel(const float *x, float *y, const int *labels, SmRows g, fl
 // running (max, sum) pair per lane, re-based whenever a batch raises the maximum. With no row held
 // in registers, 48+ warps fit per SM, which is what a read-only kernel needs to cover HBM latency
 // (the register-resident kernel above tops out near 4.4 TB/s on [65536, 4096]).
-constexpr int kCeBatch = 8;
+constexpr int kCeBatch = 4; // float4 per lane per batch; two batches alternate
 constexpr float kLog2e = 1.4426950408889634f;
 // 2^(x * log2(e) - m2) with m2 = max * log2(e): exp(x - max) for the running sum. The argument is
 // clamped at -150 (2^-150 is 0 in fp32) so a -FLT_MAX start value cannot overflow the product.
@@ -245,6 +245,13 @@ __device__ __forceinline__ float exp2_sum_term(float x, float m2) {
   t = fmaxf(t, -150.0f);
   float r;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+  return r;
+}
+// The same term without the clamps, for callers that keep m2 finite: x = -inf or -FLT_MAX gives
+// 2^(-inf) = 0, never inf - inf.
+__device__ __forceinline__ float exp2_term_fast(float x, float m2) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(__fmaf_rn(x, kLog2e, -m2)));
   return r;
 }
 __global__ void __launch_bounds__(kSmThreads)
@@ -277,20 +284,25 @@ cross_entropy_rows_kernel(const float *__restrict__ x, const int *__restrict__ l
       g.outer.offsets(row + row_step, &yoff2, ioff2);
       xr_next = reinterpret_cast<const float4 *>(x + ioff2[0]);
     }
-    for (unsigned b = lane; b < nvec + lane; b += kCeBatch * 32) {
-      // While this batch is summed the warp has no load in flight; ask L2 for the next batch (or
-      // the head of the next row) now: lane l takes the l-th 128-byte line of those 4 KiB.
-      {
-        const unsigned next_first = (b - lane) + kCeBatch * 32; // float4 index where the next batch starts
-        const float4 *pf = nullptr;
-        if (next_first + lane * 8 < nvec) pf = xr + next_first + lane * 8;
-        else if (next_first >= nvec && xr_next && lane * 8 < nvec) pf = xr_next + lane * 8;
-        if (pf) asm volatile("prefetch.global.L2 [%0];" ::"l"(pf));
-      }
-      float4 v[kCeBatch];
+    // Two batches of kCeBatch float4 per lane alternate: while one is summed the loads of the next
+    // are already in flight, and L2 is asked for the batch after that (lanes 0-15 take one
+    // 128-byte line each of its 2 KiB; past the end of the row it is the head of the next row).
+    const unsigned batch_vecs = kCeBatch * 32;
+    const unsigned nvec_padded = (nvec + batch_vecs - 1) / batch_vecs * batch_vecs;
+    auto load_batch = [&](float4(&v)[kCeBatch], unsigned b) {
 #pragma unroll
       for (int u = 0; u < kCeBatch; ++u)
         if (b + u * 32 < nvec) v[u] = __ldcs(xr + b + u * 32);
+    };
+    auto prefetch_batch = [&](unsigned first) { // first: float4 index where that batch starts
+      if (lane >= 16) return;
+      const unsigned t = first + lane * 8;
+      const float4 *pf = nullptr;
+      if (t < nvec) pf = xr + t;
+      else if (xr_next && t >= nvec_padded && t - nvec_padded < nvec) pf = xr_next + (t - nvec_padded);
+      if (pf) asm volatile("prefetch.global.L2 [%0];" ::"l"(pf));
+    };
+    auto sum_batch = [&](const float4(&v)[kCeBatch], unsigned b) {
       float bm = -FLT_MAX;
 #pragma unroll
       for (int u = 0; u < kCeBatch; ++u)
@@ -302,13 +314,32 @@ cross_entropy_rows_kernel(const float *__restrict__ x, const int *__restrict__ l
       // Only the SUM of the exponentials is needed (its log enters the loss), and terms far below
       // the maximum do not move it, so each term is one FMA + ex2.approx: 2^(x log2e - m log2e).
       // Its relative error grows with |x - m| (about |x - m| * 1e-7) exactly where the term is
-      // negligible; the sum stays within 1e-6 of the accurate one.
-      const float m2 = acc.m * kLog2e;
+      // negligible; the sum stays within 1e-6 of the accurate one. m2 is kept finite so that a row
+      // of -inf cannot produce inf - inf.
+      const float m2 = fmaxf(acc.m * kLog2e, -3.0e38f);
 #pragma unroll
       for (int u = 0; u < kCeBatch; ++u)
         if (b + u * 32 < nvec)
-          acc.s += (exp2_sum_term(v[u].x, m2) + exp2_sum_term(v[u].y, m2)) +
-                   (exp2_sum_term(v[u].z, m2) + exp2_sum_term(v[u].w, m2));
+          acc.s += (exp2_term_fast(v[u].x, m2) + exp2_term_fast(v[u].y, m2)) +
+                   (exp2_term_fast(v[u].z, m2) + exp2_term_fast(v[u].w, m2));
+    };
+    float4 va[kCeBatch], vb[kCeBatch];
+    unsigned b = lane; // b - lane is the same in every lane, so the branches below are uniform
+    load_batch(va, b);
+    while (true) {
+      const unsigned b1 = b + batch_vecs;
+      const bool more1 = b1 - lane < nvec;
+      if (more1) load_batch(vb, b1);
+      prefetch_batch(b1 - lane + batch_vecs);
+      sum_batch(va, b);
+      if (!more1) break;
+      const unsigned b2 = b1 + batch_vecs;
+      const bool more2 = b2 - lane < nvec;
+      if (more2) load_batch(va, b2);
+      prefetch_batch(b2 - lane + batch_vecs);
+      sum_batch(vb, b1);
+      if (!more2) break;
+      b = b2;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
