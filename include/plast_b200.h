@@ -232,6 +232,16 @@ typedef struct PlastChainStep {
 void plast_b200_chain_forward(const Tensor **inputs, int n_inputs, Tensor *output,
                               const PlastChainStep *steps, int n_steps);
 
+/* Backward of the chain: for every input with requires_grad, inputs[i]->grad += d(output)/d(input i)
+ * applied to output->grad, summed over the dims input i broadcasts. The chain's intermediate values
+ * are recomputed from the inputs inside the kernel (nothing was saved by the forward), and every
+ * gradient contribution is applied in the order and with the rounding of the node-by-node backward,
+ * so an input of the output's shape receives the same bits as nine separate backward launches
+ * would give it. Needs the run-time compiler (PLAST_B200_ERR_UNSUPPORTED without libnvrtc /
+ * libcuda). */
+void plast_b200_chain_backward(Tensor **inputs, int n_inputs, const Tensor *output,
+                               const PlastChainStep *steps, int n_steps);
+
 /* The same chain on HOST buffers (what a caller pays when its data starts and ends on the host,
  * the reference's numpy -> tensor -> op -> numpy() round trip, src/python/bindings.cpp:93,144):
  * host_inputs[i] holds input_elems[i] floats, either n or 1 (a constant); host_output receives n
@@ -326,6 +336,12 @@ int plast_b200_chain_source(const PlastChainStep *steps, int n_steps, int n_inpu
                             char *buf, size_t capacity);
 int plast_b200_chain_try_compile(const PlastChainStep *steps, int n_steps, int n_inputs,
                                  unsigned scalar_mask);
+/* The same two hooks for the backward functor of input `wrt` (accumulate != 0: the kernel's last
+ * operand is the input's current gradient and the functor returns the updated one). */
+int plast_b200_chain_backward_source(const PlastChainStep *steps, int n_steps, int n_inputs,
+                                     unsigned scalar_mask, int wrt, int accumulate, char *buf, size_t capacity);
+int plast_b200_chain_backward_try_compile(const PlastChainStep *steps, int n_steps, int n_inputs,
+                                          unsigned scalar_mask, int wrt, int accumulate);
 /* Test hook: runs the host-side iteration planner (drop size-1 dims, order by the strides of
  * argument `sort_arg`, merge dims every argument walks as one run) on caller-supplied metadata.
  * strides / out_strides are [nargs][MAX_NDIM] row-major, outermost dim first on input; the

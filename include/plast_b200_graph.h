@@ -98,9 +98,17 @@ extern "C" {
 u32 plast_b200_fuse_graph(DAG *dag);
 void plast_b200_fusion_release(void);
 
+/* plast_b200_fuse_graph(dag) is plast_b200_fuse_graph_ex(dag, 0). With
+ * PLAST_B200_FUSE_CHAINS_WITH_GRAD the last rule also takes groups whose tensors require grad:
+ * the chain node's backward (plast_b200_chain_backward) recomputes the group inside one kernel per
+ * differentiated input instead of reading saved intermediates, so the gradients of the
+ * intermediates are never materialised. Only taken when the run-time compiler is available. */
+#define PLAST_B200_FUSE_CHAINS_WITH_GRAD 1u
+u32 plast_b200_fuse_graph_ex(DAG *dag, unsigned flags);
+
 /* Kernel of a PLAST_OP_FUSED_CHAIN node: params.dim is the handle of the program the pass
- * registered; inputs are the group's external operands. The backward is a no-op that reports
- * an error if an input requires grad (the pass never fuses such a group). */
+ * registered; inputs are the group's external operands. The backward runs
+ * plast_b200_chain_backward on the same program (nothing to do when no input requires grad). */
 void chain_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
 void chain_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
 

@@ -93,7 +93,8 @@ def declared_symbols() -> list[str]:
         "chain_cuda_forward", "chain_cuda_backward",
         "sgd_step_cuda", "adam_step_cuda", "adamw_step_cuda", "plast_b200_adam_state_release",
         "plast_b200_relu_grad_modulate", "plast_b200_bias_grad_reduce", "plast_b200_bias_grad_masked",
-        "plast_b200_add_leaky_relu_row_sum",
+        "plast_b200_add_leaky_relu_row_sum", "plast_b200_chain_backward", "plast_b200_chain_backward_source",
+        "plast_b200_chain_backward_try_compile", "plast_b200_fuse_graph_ex",
     ]
     return syms
 
@@ -117,6 +118,9 @@ def _load() -> C.CDLL:
     lib.plast_b200_chain_forward.argtypes = [C.POINTER(C.POINTER(CTensor)), C.c_int, C.POINTER(CTensor),
                                              C.POINTER(ChainStep), C.c_int]
     lib.plast_b200_chain_forward.restype = None
+    lib.plast_b200_chain_backward.argtypes = [C.POINTER(C.POINTER(CTensor)), C.c_int, C.POINTER(CTensor),
+                                              C.POINTER(ChainStep), C.c_int]
+    lib.plast_b200_chain_backward.restype = None
     lib.plast_b200_chain_forward_host.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_uint64), C.c_int, C.c_void_p,
                                                   C.c_uint64, C.POINTER(ChainStep), C.c_int]
     lib.plast_b200_chain_forward_host.restype = None
@@ -372,6 +376,17 @@ def chain_forward(inputs, output: Tensor, steps, check: bool = True):
     if check:
         check_error()
     return output
+
+
+def chain_backward(inputs, output: Tensor, steps, check: bool = True):
+    """Accumulates the chain's gradients into inputs[i].grad for every input that requires grad,
+    reading output.grad."""
+    arr = (ChainStep * len(steps))()
+    for i, (name, a, b, fval) in enumerate(steps):
+        arr[i] = ChainStep(CHAIN_OPCODES[name], a, b, fval)
+    lib.plast_b200_chain_backward(_ptr_array(inputs), len(inputs), C.byref(output.c), arr, len(steps))
+    if check:
+        check_error()
 
 
 def chain_forward_host(host_inputs, output, steps, check: bool = True):

@@ -202,8 +202,36 @@ struct ChainProgramView {
   const unsigned char *opcode, *a, *b;
   const float *fval;
   unsigned scalar_mask; // filled by the compiler from the plan
+  int wrt;              // -1 forward; else backward with respect to this input
+  bool accumulate;      // backward: the last operand is the input's current gradient
 };
 bool launch_chain_jit(const ChainProgramView &p, const IterPlan &plan, float *out, const float *const *ins);
+bool chain_jit_available();
+
+static bool read_program(const PlastChainStep *steps, int n_steps, int n_inputs, ChainProgram *prog) {
+  if (n_inputs < 1 || n_inputs > PLAST_CHAIN_MAX_INPUTS || n_steps < 1 || n_steps > PLAST_CHAIN_MAX_STEPS) {
+    set_error(PLAST_B200_ERR_LIMIT, "chain: %d inputs / %d steps (limits %d / %d)", n_inputs, n_steps,
+              PLAST_CHAIN_MAX_INPUTS, PLAST_CHAIN_MAX_STEPS);
+    return false;
+  }
+  prog->n_inputs = n_inputs;
+  prog->n_steps = n_steps;
+  for (int s = 0; s < n_steps; ++s) {
+    const PlastChainStep &st = steps[s];
+    const bool binary = st.opcode <= PLAST_CHAIN_DIV;
+    if (st.opcode < 0 || st.opcode > PLAST_CHAIN_RDIV_SCALAR || st.a < 0 || st.a >= n_inputs + s ||
+        (binary && (st.b < 0 || st.b >= n_inputs + s))) {
+      set_error(PLAST_B200_ERR_SHAPE, "chain: step %d is malformed (opcode %d, a %d, b %d)", s,
+                st.opcode, st.a, st.b);
+      return false;
+    }
+    prog->opcode[s] = (unsigned char)st.opcode;
+    prog->a[s] = (unsigned char)st.a;
+    prog->b[s] = (unsigned char)(binary ? st.b : st.a);
+    prog->fval[s] = st.fval;
+  }
+  return true;
+}
 
 static bool float_only(const Tensor *t, const char *op) {
   if (t->dtype != FLOAT32) {
@@ -408,29 +436,8 @@ void plast_b200_chain_forward(const Tensor **inputs, int n_inputs, Tensor *outpu
     if (!inputs || !steps) set_error(PLAST_B200_ERR_NULL, "chain: NULL inputs or steps");
     return;
   }
-  if (n_inputs < 1 || n_inputs > PLAST_CHAIN_MAX_INPUTS || n_steps < 1 ||
-      n_steps > PLAST_CHAIN_MAX_STEPS) {
-    set_error(PLAST_B200_ERR_LIMIT, "chain: %d inputs / %d steps (limits %d / %d)", n_inputs, n_steps,
-              PLAST_CHAIN_MAX_INPUTS, PLAST_CHAIN_MAX_STEPS);
-    return;
-  }
   ChainProgram prog = {};
-  prog.n_inputs = n_inputs;
-  prog.n_steps = n_steps;
-  for (int s = 0; s < n_steps; ++s) {
-    const PlastChainStep &st = steps[s];
-    const bool binary = st.opcode <= PLAST_CHAIN_DIV;
-    if (st.opcode < 0 || st.opcode > PLAST_CHAIN_RDIV_SCALAR || st.a < 0 || st.a >= n_inputs + s ||
-        (binary && (st.b < 0 || st.b >= n_inputs + s))) {
-      set_error(PLAST_B200_ERR_SHAPE, "chain: step %d is malformed (opcode %d, a %d, b %d)", s,
-                st.opcode, st.a, st.b);
-      return;
-    }
-    prog.opcode[s] = (unsigned char)st.opcode;
-    prog.a[s] = (unsigned char)st.a;
-    prog.b[s] = (unsigned char)(binary ? st.b : st.a);
-    prog.fval[s] = st.fval;
-  }
+  if (!read_program(steps, n_steps, n_inputs, &prog)) return;
   if (is_sigmoid_mul_add_exp_neg_abs(prog)) {
     fused_forward<SigmoidMulAddExpNegAbs, 2>(name, inputs, output, SigmoidMulAddExpNegAbs{});
     if (!failed()) note_kernel("chain_precompiled");
@@ -454,7 +461,7 @@ void plast_b200_chain_forward(const Tensor **inputs, int n_inputs, Tensor *outpu
     }
     IterPlan plan;
     make_plan(&plan, output->shape, output->ndim, n_inputs + 1, st, nullptr, 0);
-    const ChainProgramView view{n_inputs, n_steps, prog.opcode, prog.a, prog.b, prog.fval, 0u};
+    const ChainProgramView view{n_inputs, n_steps, prog.opcode, prog.a, prog.b, prog.fval, 0u, -1, false};
     if (launch_chain_jit(view, plan, (float *)output->data, ins)) {
       note_kernel("chain_jit");
       end_call();
@@ -468,6 +475,102 @@ void plast_b200_chain_forward(const Tensor **inputs, int n_inputs, Tensor *outpu
 #undef PB_INTERP
   }
   if (!failed()) note_kernel("chain_interpreter");
+  end_call();
+}
+
+// Backward of a fused chain: for every input that requires grad, one run-time compiled kernel
+// recomputes the chain's registers from the inputs and sweeps the steps in reverse, applying each
+// gradient contribution in the order and with the rounding of the node-by-node backward
+// (functors.cuh), so full-shape inputs receive bit-identical gradients. An input that broadcasts
+// gets its per-element adjoint written to a stream-ordered scratch buffer, which the
+// broadcast-gradient reduce then sums into its gradient.
+void plast_b200_chain_backward(Tensor **inputs, int n_inputs, const Tensor *output,
+                               const PlastChainStep *steps, int n_steps) {
+  const char *name = "chain backward";
+  begin_call();
+  if (!inputs || !steps || !check_tensor(output, name, false)) {
+    if (!inputs || !steps) set_error(PLAST_B200_ERR_NULL, "chain backward: NULL inputs or steps");
+    return;
+  }
+  ChainProgram prog = {};
+  if (!read_program(steps, n_steps, n_inputs, &prog)) return;
+  bool any = false;
+  for (int a = 0; a < n_inputs; ++a) {
+    if (!check_tensor(inputs[a], name) || !float_only(inputs[a], name)) return;
+    any = any || inputs[a]->requires_grad;
+  }
+  if (!any) return;
+  const Tensor *dout = output->grad;
+  if (!dout || !dout->data) {
+    set_error(PLAST_B200_ERR_NULL, "chain backward: output has no grad tensor");
+    return;
+  }
+  if (!chain_jit_available()) {
+    set_error(PLAST_B200_ERR_UNSUPPORTED, "chain backward needs the run-time compiler (libnvrtc and libcuda)");
+    return;
+  }
+  const u64 nd = dout->ndim;
+  for (int w = 0; w < n_inputs && !failed(); ++w) {
+    Tensor *t = inputs[w];
+    if (!t->requires_grad) continue;
+    if (!t->grad || !t->grad->data) {
+      set_error(PLAST_B200_ERR_NULL, "chain backward: input %d requires grad but has no grad tensor", w);
+      return;
+    }
+    // operand strides aligned to the upstream gradient's shape: [target, g, inputs..., current grad]
+    u64 st[PLAST_CHAIN_MAX_INPUTS + 3][MAX_NDIM] = {};
+    const float *ins[PLAST_CHAIN_MAX_INPUTS + 2] = {};
+    for (u64 d = 0; d < nd; ++d) st[1][d] = dout->strides[d];
+    ins[0] = (const float *)dout->data;
+    for (int a = 0; a < n_inputs; ++a) {
+      if (!broadcast_strides(inputs[a], dout->shape, nd, st[a + 2])) {
+        set_error(PLAST_B200_ERR_SHAPE, "chain backward: input %d does not broadcast to the gradient shape", a);
+        return;
+      }
+      ins[a + 1] = (const float *)inputs[a]->data;
+    }
+    // does input w cover the whole iteration space (no broadcast dim of extent > 1)?
+    u64 gst[MAX_NDIM] = {};
+    Tensor as_grad = *t; // the operand's shape with its gradient's strides
+    for (u64 d = 0; d < t->ndim; ++d) as_grad.strides[d] = t->grad->strides[d];
+    broadcast_strides(&as_grad, dout->shape, nd, gst);
+    bool full = true;
+    for (u64 d = 0; d < nd; ++d) full = full && !(gst[d] == 0 && dout->shape[d] > 1);
+    ChainProgramView view{n_inputs, n_steps, prog.opcode, prog.a, prog.b, prog.fval, 0u, w, full};
+    IterPlan plan;
+    if (full) {
+      for (u64 d = 0; d < nd; ++d) {
+        st[0][d] = gst[d];
+        st[n_inputs + 2][d] = gst[d];
+      }
+      ins[n_inputs + 1] = (const float *)t->grad->data;
+      make_plan(&plan, dout->shape, nd, n_inputs + 3, st, nullptr, 0);
+      if (!launch_chain_jit(view, plan, (float *)t->grad->data, ins)) {
+        set_error(PLAST_B200_ERR_CUDA, "chain backward: the gradient kernel for input %d could not be built or launched", w);
+        return;
+      }
+    } else {
+      float *scratch = nullptr;
+      PB_CUDA(cudaMallocAsync(&scratch, numel(dout) * sizeof(float), stream()));
+      u64 cs = 1;
+      for (u64 d = nd; d-- > 0;) {
+        st[0][d] = cs;
+        cs *= dout->shape[d];
+      }
+      make_plan(&plan, dout->shape, nd, n_inputs + 2, st, nullptr, 0);
+      if (!launch_chain_jit(view, plan, scratch, ins)) {
+        cudaFreeAsync(scratch, stream());
+        set_error(PLAST_B200_ERR_CUDA, "chain backward: the gradient kernel for input %d could not be built or launched", w);
+        return;
+      }
+      u64 in_st[1][MAX_NDIM] = {};
+      for (u64 d = 0; d < nd; ++d) in_st[0][d] = st[0][d];
+      const float *rins[1] = {scratch};
+      accumulate_grad<GradPass, 1>(dout->shape, nd, (float *)t->grad->data, gst, in_st, rins, GradPass{});
+      cudaFreeAsync(scratch, stream());
+    }
+  }
+  if (!failed()) note_kernel("chain_backward_jit");
   end_call();
 }
 

@@ -35,10 +35,17 @@ struct ChainProgramView { // mirrors ChainProgram of chain.cu (kept POD so both 
   // of `1.0 + x`). Such inputs are read once per thread through a pointer in the functor instead
   // of occupying an operand slot of the kernel (registers and a load per element).
   unsigned scalar_mask;
+  // wrt < 0: the forward functor. wrt >= 0: the backward functor for input `wrt`: operand 0 of the
+  // kernel is the upstream gradient, the chain's tensor inputs follow, and with `accumulate` the
+  // last operand is the input's current gradient, which the returned value replaces.
+  int wrt;
+  bool accumulate;
 };
+// Operands of the generated kernel: [upstream gradient] + tensor inputs + [current gradient].
 static int tensor_inputs(const ChainProgramView &p) {
   int n = 0;
   for (int i = 0; i < p.n_inputs; ++i) n += !((p.scalar_mask >> i) & 1u);
+  if (p.wrt >= 0) n += 1 + (p.accumulate ? 1 : 0);
   return n;
 }
 
@@ -124,11 +131,37 @@ const char *step_expr(int opcode) {
   }
 }
 
+// Gradient statements of one step, in the order the standalone backward kernels apply them
+// (first operand, then second; functors.cuh): GA / GB are the adjoint registers of the operands,
+// G the adjoint of the step's result, R the step's forward value.
+const char *step_backward(int opcode) {
+  switch (opcode) {
+  case PLAST_CHAIN_ADD: return "GA = GA + G; GB = GB + G;";
+  case PLAST_CHAIN_SUB: return "GA = GA + G; GB = GB + (-G);";
+  case PLAST_CHAIN_MUL: return "GA = GA + G * B; GB = GB + G * A;";
+  case PLAST_CHAIN_DIV: return "GA = GA + G / B; GB = GB + (-G * A / (B * B));";
+  case PLAST_CHAIN_NEG: return "GA = GA - G;";
+  case PLAST_CHAIN_ABS: return "GA = GA + G * (A > 0.0f ? 1.0f : (A < 0.0f ? -1.0f : 0.0f));";
+  case PLAST_CHAIN_EXP: return "GA = GA + G * R;";
+  case PLAST_CHAIN_LOG: return "GA = GA + G * (1.0f / A);";
+  case PLAST_CHAIN_SIN: return "GA = GA + G * cosf(A);";
+  case PLAST_CHAIN_COS: return "GA = GA + G * (-sinf(A));";
+  case PLAST_CHAIN_TAN: return "GA = GA + G * (1.0f + R * R);";
+  case PLAST_CHAIN_LEAKY_RELU: return "GA = GA + G * (A > 0.0f ? 1.0f : C);";
+  case PLAST_CHAIN_ADD_SCALAR: return "GA = GA + G;";
+  case PLAST_CHAIN_RSUB_SCALAR: return "GA = GA + (-G);";
+  case PLAST_CHAIN_MUL_SCALAR: return "GA = GA + G * C;";
+  default: return "GA = GA + (-G * C / (A * A));"; // PLAST_CHAIN_RDIV_SCALAR
+  }
+}
+
 std::string functor_source(const ChainProgramView &p) {
   std::string s = "namespace pb {\nstruct JitF {\n  float c[" + std::to_string(PLAST_CHAIN_MAX_STEPS) +
                   "];\n  const float *sp[" + std::to_string(PLAST_CHAIN_MAX_INPUTS) +
                   "];\n  __device__ __forceinline__ float operator()(const float *x) const {\n";
-  for (int i = 0, slot = 0, sc = 0; i < p.n_inputs; ++i) {
+  const bool backward = p.wrt >= 0;
+  if (backward) s += "    const float g = x[0];\n";
+  for (int i = 0, slot = backward ? 1 : 0, sc = 0; i < p.n_inputs; ++i) {
     if ((p.scalar_mask >> i) & 1u)
       s += "    const float r" + std::to_string(i) + " = __ldg(sp[" + std::to_string(sc++) + "]);\n";
     else
@@ -146,12 +179,44 @@ std::string functor_source(const ChainProgramView &p) {
     sub("C", "c[" + std::to_string(k) + "]");
     s += "    const float r" + std::to_string(p.n_inputs + k) + " = " + e + ";\n";
   }
-  s += "    return r" + std::to_string(p.n_inputs + p.n_steps - 1) + ";\n  }\n};\n} // namespace pb\n";
+  if (!backward) {
+    s += "    return r" + std::to_string(p.n_inputs + p.n_steps - 1) + ";\n  }\n};\n} // namespace pb\n";
+    return s;
+  }
+  // Reverse sweep. Every adjoint starts at zero and receives its contributions in the order the
+  // node-by-node backward applies them (later nodes first), each rounded on its own, so the
+  // result equals the unfused backward bit for bit; the wanted input's adjoint starts from its
+  // current gradient when that is an operand. Adjoints nobody returns are dead code.
+  const int n_regs = p.n_inputs + p.n_steps;
+  for (int r = 0; r < n_regs; ++r) {
+    std::string init = "0.0f";
+    if (r == p.wrt && p.accumulate) init = "x[" + std::to_string(tensor_inputs(p) - 1) + "]";
+    if (r == n_regs - 1) init = "g";
+    s += "    float a" + std::to_string(r) + " = " + init + ";\n";
+  }
+  for (int k = p.n_steps - 1; k >= 0; --k) {
+    std::string e = step_backward(p.opcode[k]);
+    auto sub = [&](const std::string &from, const std::string &to) {
+      for (size_t pos = 0; (pos = e.find(from, pos)) != std::string::npos; pos += to.size())
+        e.replace(pos, from.size(), to);
+    };
+    // two-letter placeholders first; single capitals never occur in the function names used
+    sub("GA", "a" + std::to_string(p.a[k]));
+    sub("GB", "a" + std::to_string(p.b[k]));
+    sub("G", "a" + std::to_string(p.n_inputs + k));
+    sub("A", "r" + std::to_string(p.a[k]));
+    sub("B", "r" + std::to_string(p.b[k]));
+    sub("R", "r" + std::to_string(p.n_inputs + k));
+    sub("C", "c[" + std::to_string(k) + "]");
+    s += "    " + e + "\n";
+  }
+  s += "    return a" + std::to_string(p.wrt) + ";\n  }\n};\n} // namespace pb\n";
   return s;
 }
 
 std::string structure_key(const ChainProgramView &p) {
-  std::string k = std::to_string(p.n_inputs) + "/" + std::to_string(p.scalar_mask) + ":";
+  std::string k = std::to_string(p.n_inputs) + "/" + std::to_string(p.scalar_mask) + "/" +
+                  std::to_string(p.wrt) + (p.accumulate ? "+" : "") + ":";
   for (int i = 0; i < p.n_steps; ++i)
     k += std::to_string(p.opcode[i]) + "," + std::to_string(p.a[i]) + "," + std::to_string(p.b[i]) + ";";
   return k;
@@ -279,6 +344,9 @@ bool launch_plan(const ChainProgramView &p, const IterPlan &plan, float *out, co
 
 // Returns false when the chain could not be compiled or launched this way; nothing has been
 // launched in that case (a failed tail after a launched body is reported as an error instead).
+//
+// Operand layout of `plan` / `ins`: forward (p.wrt < 0): the chain's inputs. Backward: the upstream
+// gradient, then the chain's inputs, then (p.accumulate) the current gradient of input p.wrt.
 bool launch_chain_jit(const ChainProgramView &p, const IterPlan &plan, float *out, const float *const *ins) {
   static const bool disabled = [] {
     const char *e = getenv("PLAST_B200_CHAIN_JIT");
@@ -292,20 +360,27 @@ bool launch_chain_jit(const ChainProgramView &p, const IterPlan &plan, float *ou
   ChainProgramView q = p;
   q.scalar_mask = 0;
   IterPlan lean = plan;
-  const float *tensor_ins[PLAST_CHAIN_MAX_INPUTS] = {};
+  constexpr int kMaxOperands = PLAST_CHAIN_MAX_INPUTS + 2;
+  const float *tensor_ins[kMaxOperands] = {};
   int n_tensor = 0, n_scalar = 0;
+  auto keep = [&](int arg) { // plan argument `arg` (>= 1) stays a kernel operand
+    for (int d = 0; d < MAX_NDIM; ++d) lean.stride[n_tensor + 1][d] = plan.stride[arg][d];
+    lean.max_offset[n_tensor + 1] = plan.max_offset[arg];
+    tensor_ins[n_tensor++] = ins[arg - 1];
+  };
+  const int first = p.wrt >= 0 ? 1 : 0; // operand index of the chain's input 0
+  if (p.wrt >= 0) keep(1);
   for (int a = 0; a < p.n_inputs; ++a) {
     bool moves = false;
-    for (int d = 0; d < plan.ndim; ++d) moves = moves || plan.stride[a + 1][d] != 0;
+    for (int d = 0; d < plan.ndim; ++d) moves = moves || plan.stride[first + a + 1][d] != 0;
     if (!moves && !(n_tensor == 0 && a == p.n_inputs - 1)) {
       q.scalar_mask |= 1u << a;
-      f.sp[n_scalar++] = ins[a];
+      f.sp[n_scalar++] = ins[first + a];
       continue;
     }
-    for (int d = 0; d < MAX_NDIM; ++d) lean.stride[n_tensor + 1][d] = plan.stride[a + 1][d];
-    lean.max_offset[n_tensor + 1] = plan.max_offset[a + 1];
-    tensor_ins[n_tensor++] = ins[a];
+    keep(first + a + 1);
   }
+  if (p.wrt >= 0 && p.accumulate) keep(first + p.n_inputs + 1);
   lean.nargs = n_tensor + 1;
   switch (n_tensor) {
   case 1: return launch_plan<1>(q, lean, out, tensor_ins, f);
@@ -316,9 +391,13 @@ bool launch_chain_jit(const ChainProgramView &p, const IterPlan &plan, float *ou
   case 6: return launch_plan<6>(q, lean, out, tensor_ins, f);
   case 7: return launch_plan<7>(q, lean, out, tensor_ins, f);
   case 8: return launch_plan<8>(q, lean, out, tensor_ins, f);
+  case 9: return launch_plan<9>(q, lean, out, tensor_ins, f);
+  case 10: return launch_plan<10>(q, lean, out, tensor_ins, f);
   default: return false;
   }
 }
+
+bool chain_jit_available() { return api().ok; }
 
 } // namespace pb
 
@@ -338,7 +417,7 @@ static bool view_of(const PlastChainStep *steps, int n_steps, int n_inputs, unsi
     b[s] = (unsigned char)(binary ? steps[s].b : steps[s].a);
     f[s] = steps[s].fval;
   }
-  *v = pb::ChainProgramView{n_inputs, n_steps, op, a, b, f, scalar_mask};
+  *v = pb::ChainProgramView{n_inputs, n_steps, op, a, b, f, scalar_mask, -1, false};
   return true;
 }
 
@@ -357,12 +436,25 @@ extern "C" int plast_b200_chain_source(const PlastChainStep *steps, int n_steps,
   return (int)src.size();
 }
 
-extern "C" int plast_b200_chain_try_compile(const PlastChainStep *steps, int n_steps, int n_inputs,
-                                            unsigned scalar_mask) {
+extern "C" int plast_b200_chain_backward_source(const PlastChainStep *steps, int n_steps, int n_inputs,
+                                                unsigned scalar_mask, int wrt, int accumulate, char *buf,
+                                                size_t capacity) {
   unsigned char op[PLAST_CHAIN_MAX_STEPS], a[PLAST_CHAIN_MAX_STEPS], b[PLAST_CHAIN_MAX_STEPS];
   float f[PLAST_CHAIN_MAX_STEPS];
   pb::ChainProgramView v;
-  if (!view_of(steps, n_steps, n_inputs, scalar_mask, op, a, b, f, &v)) return -1;
+  if (!view_of(steps, n_steps, n_inputs, scalar_mask, op, a, b, f, &v) || wrt < 0 || wrt >= n_inputs) return -1;
+  v.wrt = wrt;
+  v.accumulate = accumulate != 0;
+  const std::string src = pb::functor_source(v);
+  if (buf && capacity > 0) {
+    const size_t n = src.size() < capacity - 1 ? src.size() : capacity - 1;
+    memcpy(buf, src.data(), n);
+    buf[n] = 0;
+  }
+  return (int)src.size();
+}
+
+static int try_compile_view(const pb::ChainProgramView &v) {
   pb::Api &api = pb::api();
   if (!api.rtc_ok) return -2;
   const std::string inst = pb::instance_name(v, 4, false, true);
@@ -381,4 +473,24 @@ extern "C" int plast_b200_chain_try_compile(const PlastChainStep *steps, int n_s
   }
   api.DestroyProgram(&prog);
   return rc;
+}
+
+extern "C" int plast_b200_chain_try_compile(const PlastChainStep *steps, int n_steps, int n_inputs,
+                                            unsigned scalar_mask) {
+  unsigned char op[PLAST_CHAIN_MAX_STEPS], a[PLAST_CHAIN_MAX_STEPS], b[PLAST_CHAIN_MAX_STEPS];
+  float f[PLAST_CHAIN_MAX_STEPS];
+  pb::ChainProgramView v;
+  if (!view_of(steps, n_steps, n_inputs, scalar_mask, op, a, b, f, &v)) return -1;
+  return try_compile_view(v);
+}
+
+extern "C" int plast_b200_chain_backward_try_compile(const PlastChainStep *steps, int n_steps, int n_inputs,
+                                                     unsigned scalar_mask, int wrt, int accumulate) {
+  unsigned char op[PLAST_CHAIN_MAX_STEPS], a[PLAST_CHAIN_MAX_STEPS], b[PLAST_CHAIN_MAX_STEPS];
+  float f[PLAST_CHAIN_MAX_STEPS];
+  pb::ChainProgramView v;
+  if (!view_of(steps, n_steps, n_inputs, scalar_mask, op, a, b, f, &v) || wrt < 0 || wrt >= n_inputs) return -1;
+  v.wrt = wrt;
+  v.accumulate = accumulate != 0;
+  return try_compile_view(v);
 }

@@ -15,6 +15,7 @@
 #include <vector>
 
 namespace pb {
+bool chain_jit_available(); // chain_jit.cu
 namespace {
 
 struct Program {
@@ -229,11 +230,16 @@ u32 fuse_relu_epilogues(Graph &g) {
   return made;
 }
 
+bool g_with_grad = false; // set for the duration of one pass (under g_pass_mutex)
+std::mutex g_pass_mutex;
+
 bool chain_member(const Node *n) {
   if (!n || chain_opcode(n->op_type) < 0 || n->num_inputs != arity(n->op_type)) return false;
-  if (!on_gpu_f32(n->output) || n->output->requires_grad) return false;
+  if (!on_gpu_f32(n->output) || (n->output->requires_grad && !g_with_grad)) return false;
   for (int k = 0; k < n->num_inputs; ++k)
-    if (!on_gpu_f32(n->inputs[k]) || n->inputs[k]->requires_grad) return false;
+    if (!on_gpu_f32(n->inputs[k]) || (n->inputs[k]->requires_grad && !g_with_grad)) return false;
+  // with gradients, every tensor that takes part needs its grad buffer at backward time
+  if (n->output->requires_grad && !n->output->grad) return false;
   return true;
 }
 
@@ -322,8 +328,12 @@ using namespace pb;
 
 extern "C" {
 
-u32 plast_b200_fuse_graph(DAG *dag) {
+u32 plast_b200_fuse_graph(DAG *dag) { return plast_b200_fuse_graph_ex(dag, 0u); }
+
+u32 plast_b200_fuse_graph_ex(DAG *dag, unsigned flags) {
   if (!dag || !dag->nodes || dag->count < 2) return 0;
+  std::lock_guard<std::mutex> pass_lock(g_pass_mutex);
+  g_with_grad = (flags & PLAST_B200_FUSE_CHAINS_WITH_GRAD) != 0 && chain_jit_available();
   for (u32 i = 0; i < dag->count; ++i)
     if (!dag->nodes[i] || !dag->nodes[i]->output || !dag->nodes[i]->inputs) return 0;
   Graph g(dag);
@@ -373,15 +383,17 @@ void chain_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams para
 }
 
 void chain_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params) {
-  begin_call();
-  (void)output;
-  int n_inputs = 0;
-  if (!plast_b200_fusion_program(params.dim, nullptr, 0, &n_inputs) || !inputs) return;
-  for (int k = 0; k < n_inputs; ++k)
-    if (inputs[k] && inputs[k]->requires_grad) {
-      set_error(PLAST_B200_ERR_UNSUPPORTED, "chain: a fused chain has no backward (input %d requires grad)", k);
+  Program prog;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (params.dim == 0 || params.dim > g_programs.size()) {
+      begin_call();
+      set_error(PLAST_B200_ERR_SHAPE, "chain: unknown program handle %llu", (unsigned long long)params.dim);
       return;
     }
+    prog = g_programs[params.dim - 1];
+  }
+  plast_b200_chain_backward(inputs, prog.n_inputs, output, prog.steps.data(), (int)prog.steps.size());
 }
 
 } // extern "C"

@@ -15,8 +15,8 @@
 
 namespace pb {
 
-constexpr int kMaxArgs = 9; // output + up to 8 operands (the widest fused chain)
-static_assert(PLAST_CHAIN_MAX_INPUTS + 1 <= kMaxArgs, "a chain's operands must fit the planner");
+constexpr int kMaxArgs = 11; // output + up to 10 operands (the widest fused chain's backward)
+static_assert(PLAST_CHAIN_MAX_INPUTS + 3 <= kMaxArgs, "a chain's operands must fit the planner");
 
 struct IterPlan {
   int ndim = 0;  // >= 1 after planning (a single element plans as one dim of size 1)

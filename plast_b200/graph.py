@@ -46,6 +46,9 @@ assert CNode.op_type.offset == 48 and CNode.params.offset == 64 and CDAG.arena.o
 
 lib.plast_b200_fuse_graph.argtypes = [C.POINTER(CDAG)]
 lib.plast_b200_fuse_graph.restype = C.c_uint32
+lib.plast_b200_fuse_graph_ex.argtypes = [C.POINTER(CDAG), C.c_uint]
+lib.plast_b200_fuse_graph_ex.restype = C.c_uint32
+FUSE_CHAINS_WITH_GRAD = 1
 lib.plast_b200_fusion_release.argtypes = []
 lib.plast_b200_fusion_release.restype = None
 lib.plast_b200_fusion_program.argtypes = [C.c_uint64, C.POINTER(ChainStep), C.c_int, C.POINTER(C.c_int)]
@@ -94,8 +97,8 @@ class Graph:
         return d
 
 
-def fuse(dag: CDAG) -> int:
-    return lib.plast_b200_fuse_graph(C.byref(dag))
+def fuse(dag: CDAG, flags: int = 0) -> int:
+    return lib.plast_b200_fuse_graph_ex(C.byref(dag), flags)
 
 
 def dag_forward(dag: CDAG) -> None:

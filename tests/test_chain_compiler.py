@@ -75,3 +75,46 @@ def test_one_element_constants_are_read_through_pointers_and_compile():
     if rc == -2:
         pytest.skip("libnvrtc not available on this machine")
     assert rc == 0
+
+
+def backward_source(prog, n_inputs, mask, wrt, accumulate):
+    h = lib()
+    h.plast_b200_chain_backward_source.argtypes = [C.POINTER(pb.ChainStep), C.c_int, C.c_int, C.c_uint, C.c_int,
+                                                   C.c_int, C.c_char_p, C.c_size_t]
+    h.plast_b200_chain_backward_source.restype = C.c_int
+    buf = C.create_string_buffer(16384)
+    n = h.plast_b200_chain_backward_source(steps_array(prog), len(prog), n_inputs, mask, wrt, accumulate, buf, len(buf))
+    return n, [l.strip() for l in buf.value.decode().splitlines()]
+
+
+def test_backward_functor_sweeps_the_steps_in_reverse_with_one_rounding_per_contribution():
+    # z = (x * y) + exp(x): r2 = r0 * r1, r3 = exp(r0), r4 = r2 + r3
+    prog = [("mul", 0, 1, 0), ("exp", 0, 0, 0), ("add", 2, 3, 0)]
+    n, lines = backward_source(prog, 2, 0, 0, 1)
+    assert n > 0
+    assert "const float g = x[0];" in lines and "const float r0 = x[1];" in lines and "const float r1 = x[2];" in lines
+    assert "float a0 = x[3];" in lines                      # starts from the current gradient of x
+    assert "float a1 = 0.0f;" in lines and "float a4 = g;" in lines
+    body = [l for l in lines if l.startswith("a")]
+    assert body == ["a2 = a2 + a4; a3 = a3 + a4;",           # add
+                    "a0 = a0 + a3 * r3;",                    # exp: g * exp(x), the forward value reused
+                    "a0 = a0 + a2 * r1; a1 = a1 + a2 * r0;"]  # mul
+    assert "return a0;" in lines
+    n, lines = backward_source(prog, 2, 0, 1, 0)            # w.r.t. y, no accumulation operand
+    assert "float a1 = 0.0f;" in lines and "return a1;" in lines
+    assert backward_source(prog, 2, 0, 2, 0)[0] == -1       # no such input
+
+
+def test_every_opcode_backward_compiles_for_sm_100a():
+    prog = [("add", 0, 1, 0), ("sub", 2, 0, 0), ("mul", 3, 1, 0), ("div", 4, 1, 0), ("neg", 5, 0, 0), ("abs", 6, 0, 0),
+            ("exp", 7, 0, 0), ("log", 8, 0, 0), ("sin", 9, 0, 0), ("cos", 10, 0, 0), ("tan", 11, 0, 0),
+            ("leaky_relu", 12, 0, 0.1), ("add_scalar", 13, 0, 1.0), ("rsub_scalar", 14, 0, 2.0),
+            ("mul_scalar", 15, 0, 0.5), ("rdiv_scalar", 16, 0, 3.0)]
+    h = lib()
+    h.plast_b200_chain_backward_try_compile.argtypes = [C.POINTER(pb.ChainStep), C.c_int, C.c_int, C.c_uint, C.c_int, C.c_int]
+    h.plast_b200_chain_backward_try_compile.restype = C.c_int
+    for wrt, acc in ((0, 1), (1, 0)):
+        rc = h.plast_b200_chain_backward_try_compile(steps_array(prog), len(prog), 2, 0, wrt, acc)
+        if rc == -2:
+            pytest.skip("libnvrtc not available on this machine")
+        assert rc == 0

@@ -165,3 +165,65 @@ def test_chain_with_eight_operands_and_constants_in_every_position(cuda):
     assert_bit_equal(res[1], res[0], "eight-operand chain")
     want = xs[4] - (((np.float32(0.5) * xs[0] + xs[1]) - np.float32(-1.25)) * xs[2] / np.float32(3.0) + xs[3])
     assert_bit_equal(res[1], want.astype(np.float32), "eight-operand chain vs numpy")
+
+
+def build_training_chain(cuda, x, y, bias):
+    """z = sigmoid(x) * y + exp(-abs(x)) + bias as ten nodes; x, y and the bias row require grad."""
+    tx, ty = cuda.tensor(x, requires_grad=True), cuda.tensor(y, requires_grad=True)
+    tb = cuda.tensor(bias, requires_grad=True)
+    one_a, one_b = cuda.tensor(np.float32(1.0).reshape(())), cuda.tensor(np.float32(1.0).reshape(()))
+    t = [cuda.empty(x.shape, requires_grad=True) for _ in range(10)]
+    g = G.Graph()
+    g.node("NEG", [tx], t[0]); g.node("EXP", [t[0]], t[1]); g.node("ADD", [one_a, t[1]], t[2])
+    g.node("DIV", [one_b, t[2]], t[3]); g.node("MUL", [t[3], ty], t[4])
+    g.node("ABS", [tx], t[5]); g.node("NEG", [t[5]], t[6]); g.node("EXP", [t[6]], t[7])
+    g.node("ADD", [t[4], t[7]], t[8]); g.node("ADD", [t[8], tb], t[9])
+    return g, tx, ty, tb, t[9]
+
+
+@pytest.mark.parametrize("shape", [(64, 1000), (7, 33), (1 << 20,)])
+def test_training_chain_fused_backward_equals_node_by_node_backward(cuda, shape):
+    x, y = rand_normal(0, shape), rand_normal(1, shape)
+    bias = rand_normal(2, (1,) * (len(shape) - 1) + shape[-1:]) if len(shape) > 1 else rand_normal(2, (1,))
+    gup = rand_normal(3, shape)
+    res = []
+    for fused in (False, True):
+        g, tx, ty, tb, out = build_training_chain(cuda, x, y, bias)
+        dag = g.dag()
+        if fused:
+            assert G.fuse(dag, G.FUSE_CHAINS_WITH_GRAD) == 1 and dag.count == 1
+        G.dag_forward(dag); pb.check_error()
+        out.grad.copy_from(gup)
+        n_bwd = launches(lambda: G.dag_backward(dag))
+        res.append((out.numpy().copy(), tx.grad.numpy().copy(), ty.grad.numpy().copy(), tb.grad.numpy().copy(), n_bwd))
+    assert_bit_equal(res[1][0], res[0][0], "forward")
+    assert_bit_equal(res[1][1], res[0][1], "x.grad: two contributions, applied in the node order")
+    assert_bit_equal(res[1][2], res[0][2], "y.grad")
+    red_axes = tuple(range(len(shape) - 1)) if len(shape) > 1 else (0,)
+    assert_sum_close(res[1][3], res[0][3], np.abs(gup).sum(axis=red_axes, keepdims=True).reshape(res[0][3].shape),
+                     what="bias.grad (reduced over the broadcast dims)")
+    assert res[1][4] < res[0][4]                                          # fewer launches than ten backward nodes
+    # and against float64 calculus
+    x64, y64, g64 = x.astype(np.float64), y.astype(np.float64), gup.astype(np.float64)
+    sg = 1 / (1 + np.exp(-x64))
+    dx = g64 * (sg * (1 - sg) * y64 - np.sign(x64) * np.exp(-np.abs(x64)))
+    np.testing.assert_allclose(res[1][1], dx, rtol=2e-5, atol=2e-6)
+    np.testing.assert_allclose(res[1][2], g64 * sg, rtol=2e-5, atol=2e-6)
+
+
+def test_chain_backward_entry_point_with_scalar_opcodes_and_accumulation(cuda):
+    n = 4099
+    x = rand_uniform(0, (n,), 0.5, 2.0)
+    gup = rand_normal(1, (n,))
+    steps = [("mul_scalar", 0, 0, 3.0), ("add_scalar", 1, 0, 0.5), ("rdiv_scalar", 2, 0, 2.0), ("rsub_scalar", 3, 0, 1.0),
+             ("log", 2, 0, 0.0), ("mul", 4, 5, 0.0)]                        # (1 - 2 / (3x + .5)) * log(3x + .5)
+    tx = cuda.tensor(x, requires_grad=True)
+    tx.grad.copy_from(np.full(n, 0.25, np.float32))                       # accumulates on top of this
+    out = cuda.empty((n,), requires_grad=True)
+    pb.chain_forward([tx], out, steps)
+    out.grad.copy_from(gup)
+    pb.chain_backward([tx], out, steps)
+    assert pb.last_kernel() == "chain_backward_jit"
+    u = 3 * x.astype(np.float64) + 0.5
+    want = 0.25 + gup * 3 * (2 / u ** 2 * np.log(u) + (1 - 2 / u) / u)
+    np.testing.assert_allclose(tx.grad.numpy(), want, rtol=2e-5, atol=2e-6)
