@@ -19,7 +19,8 @@
  * (3) reductions over a transposed view made by the reference's transpose node;
  * (4) z = sigmoid(x) * y + exp(-abs(x)) as the nine nodes plast/tensor.py builds (the two 1.0
  * constants are 0-dim tensors).
- * On CUDA, (1), (2) and (4) run a second time on fresh graphs that go through build_dag, this
+ * (4b) is (4) with requires_grad on every tensor and a backward pass from an upstream gradient.
+ * On CUDA, (1), (2), (4) and (4b) run a second time on fresh graphs that go through build_dag, this
  * library's plast_b200_fuse_graph (the call a maintainer adds after fusion_optimize in
  * src/scheduler/scheduler.c:33) and the reference's dag_forward / dag_backward: the fused DAGs
  * must have 2, 1 and 1 nodes and give the results of the node-by-node runs.
@@ -87,6 +88,9 @@ typedef struct {
   /* the same graphs after plast_b200_fuse_graph (CUDA only) */
   float f_c[M * N], f_s[M], f_grad_b[N], f_softmax[R * K], f_chain[CH];
   unsigned f_nodes[3], f_launches[3];
+  /* the chain as a training graph: gradients of x and y, node by node and (CUDA) fused */
+  float chain_dx[CH], chain_dy[CH], f_chain_dx[CH], f_chain_dy[CH];
+  unsigned f_train_nodes, f_train_bwd_launches;
 } Results;
 
 static Tensor *config1_graph(Ctx *c, const float *A, const float *b, Tensor **tb_out, Tensor **cc_out) {
@@ -107,24 +111,31 @@ static Tensor *softmax_graph(Ctx *c, Tensor *tX) {
   Tensor *se = node1(c, SUM, ex, (u64[]){R, 1}, 2, false, (KernelParams){1, 1, 0.0f});
   return node2(c, DIV, ex, se, (u64[]){R, K}, 2, false);
 }
+static Tensor *chain_graph_rg(Ctx *c, const float *x, const float *y, bool rg, Tensor **tx_out, Tensor **ty_out);
 static Tensor *chain_graph(Ctx *c, const float *x, const float *y) {
+  Tensor *tx, *ty;
+  return chain_graph_rg(c, x, y, false, &tx, &ty);
+}
+static Tensor *chain_graph_rg(Ctx *c, const float *x, const float *y, bool rg, Tensor **tx_out, Tensor **ty_out) {
   const KernelParams none = {0, 0, 0.0f};
   const float one = 1.0f;
-  Tensor *tx = mk(c, (u64[]){CH}, 1, false), *ty = mk(c, (u64[]){CH}, 1, false);
+  Tensor *tx = mk(c, (u64[]){CH}, 1, rg), *ty = mk(c, (u64[]){CH}, 1, rg);
+  *tx_out = tx;
+  *ty_out = ty;
   Tensor *one_a = mk(c, NULL, 0, false), *one_b = mk(c, NULL, 0, false);
   upload(c, tx->data, x, CH);
   upload(c, ty->data, y, CH);
   upload(c, one_a->data, &one, 1);
   upload(c, one_b->data, &one, 1);
-  Tensor *nx = node1(c, NEG, tx, (u64[]){CH}, 1, false, none);
-  Tensor *e = node1(c, EXP, nx, (u64[]){CH}, 1, false, none);
-  Tensor *d = node2(c, ADD, one_a, e, (u64[]){CH}, 1, false);
-  Tensor *sg = node2(c, DIV, one_b, d, (u64[]){CH}, 1, false);
-  Tensor *t = node2(c, MUL, sg, ty, (u64[]){CH}, 1, false);
-  Tensor *ax = node1(c, ABS, tx, (u64[]){CH}, 1, false, none);
-  Tensor *nax = node1(c, NEG, ax, (u64[]){CH}, 1, false, none);
-  Tensor *e2 = node1(c, EXP, nax, (u64[]){CH}, 1, false, none);
-  return node2(c, ADD, t, e2, (u64[]){CH}, 1, false);
+  Tensor *nx = node1(c, NEG, tx, (u64[]){CH}, 1, rg, none);
+  Tensor *e = node1(c, EXP, nx, (u64[]){CH}, 1, rg, none);
+  Tensor *d = node2(c, ADD, one_a, e, (u64[]){CH}, 1, rg);
+  Tensor *sg = node2(c, DIV, one_b, d, (u64[]){CH}, 1, rg);
+  Tensor *t = node2(c, MUL, sg, ty, (u64[]){CH}, 1, rg);
+  Tensor *ax = node1(c, ABS, tx, (u64[]){CH}, 1, rg, none);
+  Tensor *nax = node1(c, NEG, ax, (u64[]){CH}, 1, rg, none);
+  Tensor *e2 = node1(c, EXP, nax, (u64[]){CH}, 1, rg, none);
+  return node2(c, ADD, t, e2, (u64[]){CH}, 1, rg);
 }
 /* What schedule() does in JIT mode (scheduler.c:29-33) with this library's pass added. */
 static DAG *fused_dag(Ctx *c, Tensor *root, unsigned *n_nodes) {
@@ -149,13 +160,14 @@ static void run(DEVICE dev, Results *res) {
   c.data = arena_create(Mib(16), dev);
   c.sched = init_scheduler(jit_create(16));
   unsigned st = 12345;
-  static float A[M * N], b[N], G[M * N], X[R * K], CX[CH], CY[CH];
+  static float A[M * N], b[N], G[M * N], X[R * K], CX[CH], CY[CH], CG[CH];
   for (int i = 0; i < M * N; ++i) A[i] = frand(&st);
   for (int i = 0; i < N; ++i) b[i] = frand(&st);
   for (int i = 0; i < M * N; ++i) G[i] = frand(&st) * 3.0f;
   for (int i = 0; i < R * K; ++i) X[i] = frand(&st) * 4.0f;
   for (int i = 0; i < CH; ++i) CX[i] = frand(&st) * 6.0f;
   for (int i = 0; i < CH; ++i) CY[i] = frand(&st);
+  for (int i = 0; i < CH; ++i) CG[i] = frand(&st) * 2.0f;
 
   /* (1) config 1 */
   Tensor *tb, *cc;
@@ -181,7 +193,35 @@ static void run(DEVICE dev, Results *res) {
   schedule(c.sched, z->creator, FORWARD, &c.meta);
   download(&c, res->chain, z->data, CH);
 
+  /* (4b) the same chain with requires_grad everywhere: backward from an upstream gradient on z */
+  {
+    Tensor *gx, *gy;
+    Tensor *gz = chain_graph_rg(&c, CX, CY, true, &gx, &gy);
+    schedule(c.sched, gz->creator, FORWARD, &c.meta);
+    upload(&c, gz->grad->data, CG, CH);
+    schedule(c.sched, gz->creator, BACKWARD, &c.meta);
+    download(&c, res->chain_dx, gx->grad->data, CH);
+    download(&c, res->chain_dy, gy->grad->data, CH);
+  }
+
   if (dev == CUDA) {
+    {
+      Tensor *gx, *gy;
+      Tensor *gz = chain_graph_rg(&c, CX, CY, true, &gx, &gy);
+      DAG *dg = alloc_dag(MIN_DAG_CAPACITY);
+      dg->arena = &c.meta;
+      build_dag(dg, gz->creator);
+      plast_b200_fuse_graph_ex(dg, PLAST_B200_FUSE_CHAINS_WITH_GRAD);
+      res->f_train_nodes = dg->count;
+      dag_forward(dg);
+      upload(&c, gz->grad->data, CG, CH);
+      const u64 before_bwd = plast_b200_launch_count();
+      dag_backward(dg);
+      res->f_train_bwd_launches = (unsigned)(plast_b200_launch_count() - before_bwd);
+      download(&c, res->f_chain_dx, gx->grad->data, CH);
+      download(&c, res->f_chain_dy, gy->grad->data, CH);
+      dag_release(dg);
+    }
     Tensor *ftb, *fcc;
     Tensor *fs = config1_graph(&c, A, b, &ftb, &fcc);
     DAG *d1 = fused_dag(&c, fs, &res->f_nodes[0]);
@@ -268,6 +308,15 @@ int main(void) {
   bad += close_to("fused: grad_b", cpu.grad_b, gpu.f_grad_b, N, 3.0f * M);
   bad += close_to("fused: softmax", cpu.softmax, gpu.f_softmax, R * K, 1.0f);
   bad += same_bits("fused: chain vs 9 nodes", gpu.chain, gpu.f_chain, CH);
+  bad += close_to("chain dx (9 backward nodes)", cpu.chain_dx, gpu.chain_dx, CH, 4.0f);
+  bad += close_to("chain dy (9 backward nodes)", cpu.chain_dy, gpu.chain_dy, CH, 4.0f);
+  printf("fused training chain: %u node, %u backward launches\n", gpu.f_train_nodes, gpu.f_train_bwd_launches);
+  if (gpu.f_train_nodes != 1 || gpu.f_train_bwd_launches > 4) {
+    printf("fused training chain size      MISMATCH\n");
+    ++bad;
+  }
+  bad += same_bits("fused: chain dx", gpu.chain_dx, gpu.f_chain_dx, CH);
+  bad += same_bits("fused: chain dy", gpu.chain_dy, gpu.f_chain_dy, CH);
   printf(bad ? "DROPIN FAILED\n" : "DROPIN OK\n");
   return bad ? 1 : 0;
 }
