@@ -112,6 +112,21 @@ u32 plast_b200_fuse_graph_ex(DAG *dag, unsigned flags);
 void chain_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
 void chain_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
 
+/* A DAG as one CUDA graph. plast_b200_dag_capture records the kernels of every node (forward
+ * order, or reverse order with the nodes' backward kernels when backward != 0) WITHOUT running
+ * them and returns a handle; plast_b200_dag_replay launches the whole recording on the library
+ * stream. This is what the scheduler's JIT mode wants for a cached DAG it executes again and again
+ * on the same tensors (src/scheduler/scheduler.c:17-27): per replay one launch instead of one
+ * per node, which is the bound for small graphs. Every node must be a CUDA node whose kernel is
+ * an entry point of this library (anything else returns NULL with PLAST_B200_ERR_UNSUPPORTED);
+ * run the DAG once the ordinary way first so that run-time compiled chains and the scratch
+ * workspace exist. The recording holds the tensors' addresses: it is valid while they are. */
+typedef struct PlastDagGraph PlastDagGraph;
+PlastDagGraph *plast_b200_dag_capture(DAG *dag, int backward);
+void plast_b200_dag_replay(PlastDagGraph *graph);
+int plast_b200_dag_graph_kernels(const PlastDagGraph *graph);
+void plast_b200_dag_graph_release(PlastDagGraph *graph);
+
 /* Test hook: copies the program behind a chain handle; returns its step count (0 = unknown
  * handle) and stores its input count. */
 int plast_b200_fusion_program(u64 handle, PlastChainStep *steps, int max_steps, int *n_inputs);

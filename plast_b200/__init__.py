@@ -95,6 +95,8 @@ def declared_symbols() -> list[str]:
         "plast_b200_relu_grad_modulate", "plast_b200_bias_grad_reduce", "plast_b200_bias_grad_masked",
         "plast_b200_add_leaky_relu_row_sum", "plast_b200_chain_backward", "plast_b200_chain_backward_source",
         "plast_b200_chain_backward_try_compile", "plast_b200_fuse_graph_ex",
+        "plast_b200_dag_capture", "plast_b200_dag_replay", "plast_b200_dag_graph_kernels",
+        "plast_b200_dag_graph_release",
     ]
     return syms
 

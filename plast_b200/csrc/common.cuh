@@ -18,6 +18,7 @@ bool failed();
 
 cudaStream_t stream();
 void count_launch(int n = 1);
+bool sync_enabled(); // plast_b200_set_sync state
 void end_call(); // optional device sync (plast_b200_set_sync) + launch error check
 
 #define PB_CUDA(expr)                                                                              \

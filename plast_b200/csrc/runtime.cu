@@ -40,6 +40,7 @@ void begin_call() {
 void note_kernel(const char *name) { t_kernel = name; }
 bool failed() { return t_err != PLAST_B200_OK; }
 cudaStream_t stream() { return g_stream.load(std::memory_order_relaxed); }
+bool sync_enabled() { return g_sync.load(std::memory_order_relaxed) != 0; }
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 
 void end_call() {

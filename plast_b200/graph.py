@@ -58,6 +58,26 @@ for _name in ("chain_cuda_forward", "chain_cuda_backward"):
     getattr(lib, _name).restype = None
 
 
+lib.plast_b200_dag_capture.argtypes = [C.POINTER(CDAG), C.c_int]
+lib.plast_b200_dag_capture.restype = C.c_void_p
+lib.plast_b200_dag_replay.argtypes = [C.c_void_p]
+lib.plast_b200_dag_replay.restype = None
+lib.plast_b200_dag_graph_kernels.argtypes = [C.c_void_p]
+lib.plast_b200_dag_graph_kernels.restype = C.c_int
+lib.plast_b200_dag_graph_release.argtypes = [C.c_void_p]
+lib.plast_b200_dag_graph_release.restype = None
+
+
+def capture(dag: "CDAG", backward: bool = False):
+    """Records the DAG's kernels into a CUDA graph; returns an opaque handle (None on failure,
+    see plast_b200.check_error)."""
+    return lib.plast_b200_dag_capture(C.byref(dag), int(backward))
+
+
+def replay(handle) -> None:
+    lib.plast_b200_dag_replay(handle)
+
+
 def symbol_address(name: str) -> int:
     return C.cast(getattr(lib, name), C.c_void_p).value
 

@@ -112,6 +112,17 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
         timeit(1, "fused_fwd_C_and_row_sum",
                lambda: pb.lib.plast_b200_add_leaky_relu_row_sum(C.byref(tA.c), C.byref(tb.c), C.byref(tC.c), C.byref(ts.c), 0.0),
                (2 * M * N + N + M) * F, M * N, ws)
+        # the whole forward graph (fused add + relu node, row-sum node) replayed as ONE CUDA graph
+        from . import graph as G1
+        g1 = G1.Graph()
+        g1.node("ADD", [tA, tb], tAB); g1.node("LEAKY_RELU", [tAB], tC, fval=0.0); g1.node("SUM", [tC], ts, dim=1)
+        dag1 = g1.dag()
+        G1.fuse(dag1, G1.FUSE_CHAINS_WITH_GRAD)
+        G1.dag_forward(dag1)
+        h1 = G1.capture(dag1)
+        if h1:
+            timeit(1, "forward_dag_as_cuda_graph", lambda: G1.replay(h1), (2 * M * N + N + M * N + M) * F, M * N, ws)
+        timeit(1, "forward_dag_node_by_node", lambda: G1.dag_forward(dag1), (2 * M * N + N + M * N + M) * F, M * N, ws)
         tbg = wrap(b); tbg.c.requires_grad = True
         gtb = wrap(gb); tbg.grad = gtb; tbg.c.grad = C.pointer(gtb.c)
         tCg = wrap(Cc); gC = wrap(G); tCg.grad = gC; tCg.c.grad = C.pointer(gC.c)

@@ -227,3 +227,52 @@ def test_chain_backward_entry_point_with_scalar_opcodes_and_accumulation(cuda):
     u = 3 * x.astype(np.float64) + 0.5
     want = 0.25 + gup * 3 * (2 / u ** 2 * np.log(u) + (1 - 2 / u) / u)
     np.testing.assert_allclose(tx.grad.numpy(), want, rtol=2e-5, atol=2e-6)
+
+
+def test_fused_dag_replayed_as_one_cuda_graph(cuda):
+    A, b = rand_uniform(0, (1024, 1024)), rand_uniform(1, (1, 1024))
+    ta, tb = cuda.tensor(A), cuda.tensor(b, requires_grad=True)
+    ab, c = cuda.empty(A.shape, requires_grad=True), cuda.empty(A.shape, requires_grad=True)
+    s = cuda.empty((1024,), requires_grad=True)
+    g = G.Graph()
+    g.node("ADD", [ta, tb], ab); g.node("LEAKY_RELU", [ab], c, fval=0.0); g.node("SUM", [c], s, dim=1)
+    dag = g.dag()
+    assert G.fuse(dag) == 1 and dag.count == 2
+    G.dag_forward(dag); pb.check_error()
+    handle = G.capture(dag); pb.check_error()
+    assert handle and G.lib.plast_b200_dag_graph_kernels(handle) == 2
+    # new data in the same buffers: the replay computes on it
+    A2 = rand_uniform(5, (1024, 1024))
+    ta.copy_from(A2)
+    assert launches(lambda: G.replay(handle)) == 2
+    want_c = np.where(A2 + b > 0, A2 + b, (A2 + b) * np.float32(0.0))
+    assert_bit_equal(c.numpy(), want_c.astype(np.float32), "C from the replayed graph")
+    G.dag_forward(dag); pb.check_error()
+    eager = s.numpy().copy()
+    G.replay(handle); pb.check_error()
+    assert_bit_equal(s.numpy(), eager, "row sums: replay vs eager")
+    # backward recorded without being run, then replayed
+    Gup = rand_normal(2, (1024, 1024))
+    bwd = G.Graph(); bwd.nodes = [dag.nodes[0].contents]                 # the fused add + relu node only
+    bdag = bwd.dag()
+    hb = G.capture(bdag, backward=True); pb.check_error()
+    c.grad.copy_from(Gup)
+    assert np.all(tb.grad.numpy() == 0)                                   # capturing did not execute anything
+    G.replay(hb); pb.check_error()
+    got = tb.grad.numpy().copy()
+    tb.grad.copy_from(np.zeros_like(got))
+    G.dag_backward(bdag); pb.check_error()
+    assert_bit_equal(got, tb.grad.numpy(), "grad_b: replayed backward vs eager backward")
+    G.lib.plast_b200_dag_graph_release(handle); G.lib.plast_b200_dag_graph_release(hb)
+
+
+def test_capture_refuses_nodes_that_are_not_this_librarys_kernels(cuda):
+    import ctypes as C
+    x, y = cuda.tensor(rand_normal(0, (16,))), cuda.empty((16,))
+    g = G.Graph()
+    n = g.node("EXP", [x], y)
+    n.op.cuda_forward = C.cast(C.CDLL(None).abs, C.c_void_p).value       # some function of another library
+    dag = g.dag()
+    assert G.capture(dag) is None
+    assert pb.lib.plast_b200_last_error() == 5
+    pb.lib.plast_b200_clear_error()
