@@ -38,6 +38,7 @@
 
 #include <math.h>
 #include <stdio.h>
+#include <time.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -91,6 +92,10 @@ typedef struct {
   /* the chain as a training graph: gradients of x and y, node by node and (CUDA) fused */
   float chain_dx[CH], chain_dy[CH], f_chain_dx[CH], f_chain_dy[CH];
   unsigned f_train_nodes, f_train_bwd_launches;
+  /* config 1's fused forward DAG (2 nodes): the reference's dag_forward against one CUDA-graph replay */
+  float replay_s[M];
+  double us_node_by_node, us_replay;
+  int replay_kernels;
 } Results;
 
 static Tensor *config1_graph(Ctx *c, const float *A, const float *b, Tensor **tb_out, Tensor **cc_out) {
@@ -230,6 +235,32 @@ static void run(DEVICE dev, Results *res) {
     res->f_launches[0] = (unsigned)(plast_b200_launch_count() - before);
     download(&c, res->f_c, fcc->data, M * N);
     download(&c, res->f_s, fs->data, M);
+    {
+      /* the same two-node DAG recorded once and replayed; timings are per execution of the DAG */
+      PlastDagGraph *rec = plast_b200_dag_capture(d1, 0);
+      res->replay_kernels = plast_b200_dag_graph_kernels(rec);
+      const int reps = 2000;
+      float sink[1];
+      struct timespec t0, t1;
+      for (int i = 0; i < 50; ++i) dag_forward(d1);
+      download(&c, sink, fs->data, 1);
+      clock_gettime(CLOCK_MONOTONIC, &t0);
+      for (int i = 0; i < reps; ++i) dag_forward(d1);
+      download(&c, sink, fs->data, 1);
+      clock_gettime(CLOCK_MONOTONIC, &t1);
+      res->us_node_by_node = ((t1.tv_sec - t0.tv_sec) * 1e6 + (t1.tv_nsec - t0.tv_nsec) * 1e-3) / reps;
+      if (rec) {
+        for (int i = 0; i < 50; ++i) plast_b200_dag_replay(rec);
+        download(&c, sink, fs->data, 1);
+        clock_gettime(CLOCK_MONOTONIC, &t0);
+        for (int i = 0; i < reps; ++i) plast_b200_dag_replay(rec);
+        download(&c, sink, fs->data, 1);
+        clock_gettime(CLOCK_MONOTONIC, &t1);
+        res->us_replay = ((t1.tv_sec - t0.tv_sec) * 1e6 + (t1.tv_nsec - t0.tv_nsec) * 1e-3) / reps;
+        download(&c, res->replay_s, fs->data, M);
+        plast_b200_dag_graph_release(rec);
+      }
+    }
     upload(&c, fcc->grad->data, G, M * N);
     execute_backward(fcc->creator); /* the fused add + leaky_relu node */
     download(&c, res->f_grad_b, ftb->grad->data, N);
@@ -303,6 +334,13 @@ int main(void) {
     printf("fused DAG sizes                MISMATCH\n");
     ++bad;
   }
+  printf("config 1 forward DAG (2 fused nodes, %d x %d): node by node %.2f us, one CUDA-graph replay (%d kernels) %.2f us\n",
+         M, N, gpu.us_node_by_node, gpu.replay_kernels, gpu.us_replay);
+  if (gpu.replay_kernels != 2) {
+    printf("CUDA-graph recording           MISMATCH\n");
+    ++bad;
+  }
+  bad += same_bits("replayed: sum(C, axis 1)", gpu.f_s, gpu.replay_s, M);
   bad += same_bits("fused: relu(A + b)", gpu.c, gpu.f_c, M * N);
   bad += same_bits("fused: sum(C, axis 1)", gpu.s, gpu.f_s, M);
   bad += close_to("fused: grad_b", cpu.grad_b, gpu.f_grad_b, N, 3.0f * M);

@@ -38,7 +38,7 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
         gen.manual_seed(seed)
         return torch.rand(shape, generator=gen, device=dev, dtype=torch.float32) * (hi - lo) + lo
 
-    def timeit(cfg, name, fn, nbytes, elems, working_set):
+    def timeit(cfg, name, fn, nbytes, elems, working_set, capture=True):
         flush = working_set < (256 << 20)
         fn(); pb.check_error()
         for _ in range(2):
@@ -67,8 +67,20 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
                "frac_of_measured": round(gbs / peak_gbs, 4), "frac_of_nominal": round(gbs / NOMINAL, 4),
                "l2_flushed": flush}
         if flush and reps > 0:
-            # Launch-bound sizes: also time 50 launches replayed from one CUDA graph (no host launch
-            # cost, data stays in L2) - the per-launch cost a graph-capturing scheduler would see.
+            # Launch-bound sizes: the same call 50 times back to back in the stream (data stays in L2) ...
+            bt = []
+            for _ in range(5):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(50):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+                bt.append(e0.elapsed_time(e1) / 50)
+            row["stream_ms_per_call_l2_resident"] = round(float(np.median(bt)), 5)
+        if flush and reps > 0 and capture:
+            # ... and 50 launches replayed from one CUDA graph (no host launch cost) - the
+            # per-launch cost a graph-capturing scheduler would see.
             try:
                 side = torch.cuda.Stream()
                 side.wait_stream(torch.cuda.current_stream())
@@ -121,7 +133,8 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
         G1.dag_forward(dag1)
         h1 = G1.capture(dag1)
         if h1:
-            timeit(1, "forward_dag_as_cuda_graph", lambda: G1.replay(h1), (2 * M * N + N + M * N + M) * F, M * N, ws)
+            timeit(1, "forward_dag_as_cuda_graph", lambda: G1.replay(h1), (2 * M * N + N + M * N + M) * F, M * N, ws,
+                   capture=False)
         timeit(1, "forward_dag_node_by_node", lambda: G1.dag_forward(dag1), (2 * M * N + N + M * N + M) * F, M * N, ws)
         tbg = wrap(b); tbg.c.requires_grad = True
         gtb = wrap(gb); tbg.grad = gtb; tbg.c.grad = C.pointer(gtb.c)
