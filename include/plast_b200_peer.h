@@ -1,0 +1,65 @@
+/*
+ * plast_b200_peer.h — the exchange step of reductions that cross GPUs, over NVLink peer memory.
+ *
+ * The reference has no multi-GPU layer, so nothing here replaces a reference interface. The hot
+ * path shards across the GPUs of one box along the outermost kept dim; full reductions, column
+ * sums of a row-sharded matrix, the cross-entropy mean and bias gradients then need ONE exchange
+ * of a tiny partial (4 bytes to 32 KiB). A library all-reduce costs 25-35 us for such a message on
+ * eight GPUs, several times the local kernel; here every rank stores its partial straight into
+ * every peer's exchange buffer (peer-to-peer stores over NVLink), raises a flag there, waits for
+ * the flags of the others and adds the partials up in rank order — one small kernel, identical
+ * bits on every rank. One process per GPU; buffers are shared through CUDA IPC handles that the
+ * caller passes between the processes (64 opaque bytes per rank, by any transport).
+ */
+#ifndef PLAST_B200_PEER_H
+#define PLAST_B200_PEER_H
+
+#include "plast_b200.h"
+
+#define PLAST_B200_IPC_HANDLE_BYTES 64
+#define PLAST_B200_PEER_MAX_WORLD 8
+#define PLAST_B200_PEER_MAX_FLOATS 8192 /* largest message of one exchange (32 KiB) */
+
+#define PLAST_B200_PEER_SUM 0
+#define PLAST_B200_PEER_MAX 1
+#define PLAST_B200_PEER_MIN 2
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct PlastPeerGroup PlastPeerGroup;
+
+/* Step 1, on every rank: allocates this rank's exchange buffer on the current device (zeroed) and
+ * writes its IPC handle. Returns NULL on failure (see plast_b200_last_error). */
+PlastPeerGroup *plast_b200_peer_group_begin(int rank, int world, unsigned char handle[PLAST_B200_IPC_HANDLE_BYTES]);
+/* Step 2, after the caller gathered every rank's handle (world x 64 bytes, in rank order) and ALL
+ * ranks have completed step 1: maps the peers' buffers. Returns 0 on success. The caller then runs
+ * a barrier of its own before the first exchange (a rank must not store into a buffer whose owner
+ * has not finished step 1). */
+int plast_b200_peer_group_connect(PlastPeerGroup *group, const unsigned char *all_handles);
+/* In-place all-reduce of n <= PLAST_B200_PEER_MAX_FLOATS floats at `data` (device memory of this
+ * rank) on the library stream; every rank must make the same sequence of calls. The partials are
+ * combined in rank order, so every rank ends with the same bits. Waits inside the kernel are
+ * bounded (about a second): if a peer never arrives the kernel gives up, the data is left
+ * unreduced and plast_b200_peer_group_status reports it; nothing hangs. */
+void plast_b200_peer_all_reduce(PlastPeerGroup *group, float *data, u64 n, int op);
+/* 0 = every exchange so far completed; k > 0 = a wait for rank k - 1 ran out (sticky until
+ * plast_b200_peer_group_clear_status). Synchronises the library stream. */
+int plast_b200_peer_group_status(PlastPeerGroup *group);
+void plast_b200_peer_group_clear_status(PlastPeerGroup *group);
+/* Unmaps the peers and frees this rank's buffer. Every rank calls it after its last exchange has
+ * completed on every rank (barrier first). */
+void plast_b200_peer_group_release(PlastPeerGroup *group);
+
+/* Test hooks. A group whose `world` ranks all live in THIS process, rank 0 being the caller and
+ * the others plain local buffers that nobody signals: with world == 1 the exchange completes by
+ * itself; with world > 1 the wait for rank 1 runs out after `max_spins` polls (the bounded-wait
+ * path, exercised without a second GPU and without hanging anything). */
+PlastPeerGroup *plast_b200_peer_group_local(int world, unsigned max_spins);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* PLAST_B200_PEER_H */

@@ -97,6 +97,9 @@ def declared_symbols() -> list[str]:
         "plast_b200_chain_backward_try_compile", "plast_b200_fuse_graph_ex",
         "plast_b200_dag_capture", "plast_b200_dag_replay", "plast_b200_dag_graph_kernels",
         "plast_b200_dag_graph_release",
+        "plast_b200_peer_group_begin", "plast_b200_peer_group_connect", "plast_b200_peer_all_reduce",
+        "plast_b200_peer_group_status", "plast_b200_peer_group_clear_status", "plast_b200_peer_group_release",
+        "plast_b200_peer_group_local",
     ]
     return syms
 

@@ -43,21 +43,93 @@ def shard_dim(total: int, rank: int, world: int) -> Shard:
     return Shard(start, count, total, rank, world)
 
 
+class PeerGroup:
+    """The library's own exchange for tiny partials (include/plast_b200_peer.h): every rank stores
+    its message into every peer's buffer over NVLink and adds the messages up in rank order, in
+    one small kernel. `torch.distributed` only carries the 64-byte IPC handles at set-up.
+
+    Use for messages of at most MAX_FLOATS floats on the GPUs of one box; anything else goes
+    through the process group's all-reduce."""
+
+    MAX_FLOATS = 8192
+    OPS = {"sum": 0, "max": 1, "min": 2}
+
+    def __init__(self, dist, torch, pb):
+        import ctypes as C
+        self._C, self._pb, self._dist = C, pb, dist
+        lib = pb.lib
+        lib.plast_b200_peer_group_begin.argtypes = [C.c_int, C.c_int, C.c_char_p]
+        lib.plast_b200_peer_group_begin.restype = C.c_void_p
+        lib.plast_b200_peer_group_connect.argtypes = [C.c_void_p, C.c_char_p]
+        lib.plast_b200_peer_group_connect.restype = C.c_int
+        lib.plast_b200_peer_all_reduce.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_int]
+        lib.plast_b200_peer_all_reduce.restype = None
+        lib.plast_b200_peer_group_status.argtypes = [C.c_void_p]
+        lib.plast_b200_peer_group_status.restype = C.c_int
+        lib.plast_b200_peer_group_release.argtypes = [C.c_void_p]
+        lib.plast_b200_peer_group_release.restype = None
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        handle = C.create_string_buffer(64)
+        self._g = lib.plast_b200_peer_group_begin(self.rank, self.world, handle)
+        pb.check_error()
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, bytes(handle.raw))      # also orders every rank's step 1 before step 2
+        if lib.plast_b200_peer_group_connect(self._g, b"".join(gathered)) != 0:
+            pb.check_error()
+        dist.barrier()                                            # nobody stores before everybody is mapped
+
+    def all_reduce(self, t, op: str = "sum"):
+        """In place on a contiguous float32 CUDA tensor of at most MAX_FLOATS elements."""
+        assert t.is_contiguous() and t.numel() <= self.MAX_FLOATS
+        self._pb.lib.plast_b200_peer_all_reduce(self._g, self._C.c_void_p(t.data_ptr()), t.numel(), self.OPS[op])
+        return t
+
+    def status(self) -> int:
+        return self._pb.lib.plast_b200_peer_group_status(self._g)
+
+    def close(self):
+        if self._g:
+            self._dist.barrier()
+            self._pb.lib.plast_b200_peer_group_release(self._g)
+            self._g = None
+
+
+_peer_group = None
+
+
+def use_peer_exchange(group) -> None:
+    """Routes all_reduce_sum / max / min of small CUDA tensors through `group` (a PeerGroup), or
+    back to the process group with None."""
+    global _peer_group
+    _peer_group = group
+
+
+def _peer_ok(t) -> bool:
+    return (_peer_group is not None and getattr(t, "is_cuda", False) and t.is_contiguous()
+            and t.numel() <= PeerGroup.MAX_FLOATS and str(t.dtype) == "torch.float32")
+
+
 def all_reduce_sum(dist, t):
     """In place; `t` holds this rank's partial sums (any shape, identical on every rank)."""
     if dist.is_initialized() and dist.get_world_size() > 1:
+        if _peer_ok(t):
+            return _peer_group.all_reduce(t, "sum")
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
     return t
 
 
 def all_reduce_max(dist, t):
     if dist.is_initialized() and dist.get_world_size() > 1:
+        if _peer_ok(t):
+            return _peer_group.all_reduce(t, "max")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return t
 
 
 def all_reduce_min(dist, t):
     if dist.is_initialized() and dist.get_world_size() > 1:
+        if _peer_ok(t):
+            return _peer_group.all_reduce(t, "min")
         dist.all_reduce(t, op=dist.ReduceOp.MIN)
     return t
 

@@ -1,0 +1,70 @@
+"""One rank of the peer-exchange test (launched by tests/test_gpu_peer.py through torchrun on two or
+more GPUs of one box): the library's NVLink exchange against the process group's all-reduce."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+import plast_b200 as pb  # noqa: E402
+from plast_b200.dist import PeerGroup  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
+    os.environ["NCCL_DEBUG"] = "WARN"
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    dist.init_process_group("nccl", device_id=dev)
+    import ctypes as C
+    pb.lib.plast_b200_set_stream(C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    group = PeerGroup(dist, torch, pb)
+    gen = torch.Generator(device=dev)
+    for it, n in enumerate([1, 5, 1000, 4097, 8192] * 8):
+        for op, red in (("sum", dist.ReduceOp.SUM), ("max", dist.ReduceOp.MAX), ("min", dist.ReduceOp.MIN)):
+            gen.manual_seed(1000 * it + rank)
+            x = torch.randn(n, generator=gen, device=dev)
+            want = x.clone()
+            gathered = [torch.empty_like(x) for _ in range(world)]
+            dist.all_gather(gathered, x)
+            acc = gathered[0].clone()
+            for g in gathered[1:]:                                        # rank order, like the kernel
+                acc = acc + g if op == "sum" else (torch.maximum(acc, g) if op == "max" else torch.minimum(acc, g))
+            group.all_reduce(x, op)
+            pb.check_error()
+            torch.cuda.synchronize()
+            assert torch.equal(x, acc), f"rank {rank}: {op} of {n} floats differs from the rank-order result"
+            dist.all_reduce(want, op=red)
+            assert torch.allclose(x, want, rtol=1e-6, atol=1e-6)
+    assert group.status() == 0
+    # timing: exchange of 1 float and of 8192 floats, against the process group's all-reduce
+    def timed(fn, reps=200):
+        for _ in range(10):
+            fn()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e3
+    for n in (1, 8192):
+        x = torch.ones(n, device=dev)
+        t_peer = timed(lambda: group.all_reduce(x, "max"))
+        t_pg = timed(lambda: dist.all_reduce(x, op=dist.ReduceOp.MAX))
+        if rank == 0:
+            print(f"exchange of {n} floats on {world} GPUs: peer kernel {t_peer:.1f} us, process group {t_pg:.1f} us", flush=True)
+    group.close()
+    dist.barrier()
+    if rank == 0:
+        print("PEER OK", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

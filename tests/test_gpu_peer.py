@@ -1,0 +1,85 @@
+"""The NVLink peer exchange (include/plast_b200_peer.h). On one GPU: the degenerate one-rank group
+and the bounded wait (a group whose other ranks never signal: the kernel gives up, reports which
+rank was missing, and the context stays usable). On two or more GPUs: real ranks under torchrun
+against the process group's all-reduce."""
+import ctypes as C
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import plast_b200 as pb
+from harness import rand_normal
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _lib():
+    lib = pb.lib
+    lib.plast_b200_peer_group_local.argtypes = [C.c_int, C.c_uint]
+    lib.plast_b200_peer_group_local.restype = C.c_void_p
+    lib.plast_b200_peer_all_reduce.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_int]
+    lib.plast_b200_peer_all_reduce.restype = None
+    lib.plast_b200_peer_group_status.argtypes = [C.c_void_p]
+    lib.plast_b200_peer_group_status.restype = C.c_int
+    lib.plast_b200_peer_group_clear_status.argtypes = [C.c_void_p]
+    lib.plast_b200_peer_group_release.argtypes = [C.c_void_p]
+    return lib
+
+
+def test_one_rank_group_completes_by_itself(cuda):
+    lib = _lib()
+    g = lib.plast_b200_peer_group_local(1, 1000)
+    pb.check_error()
+    x = rand_normal(0, (8192,))
+    t = cuda.tensor(x)
+    for op in (0, 1, 2, 0, 1):                                            # both parities, several times
+        lib.plast_b200_peer_all_reduce(g, t.c.data, 8192, op)
+        pb.check_error()
+    assert lib.plast_b200_peer_group_status(g) == 0
+    assert np.array_equal(t.numpy(), x)
+    lib.plast_b200_peer_all_reduce(g, t.c.data, 8193, 0)                  # beyond the message limit
+    assert pb.lib.plast_b200_last_error() == 6
+    pb.lib.plast_b200_clear_error()
+    lib.plast_b200_peer_group_release(g)
+
+
+def test_wait_for_a_rank_that_never_arrives_runs_out_and_is_reported(cuda):
+    lib = _lib()
+    g = lib.plast_b200_peer_group_local(3, 2000)                          # ranks 1 and 2 never signal
+    pb.check_error()
+    x = rand_normal(1, (100,))
+    t = cuda.tensor(x)
+    lib.plast_b200_peer_all_reduce(g, t.c.data, 100, 0)
+    pb.check_error()                                                      # the launch itself is fine
+    assert lib.plast_b200_peer_group_status(g) in (2, 3)                  # a wait for rank 1 (or 2) ran out
+    assert np.array_equal(t.numpy(), x)                                   # data left as it was
+    lib.plast_b200_peer_group_clear_status(g)
+    # the context is still usable
+    out = cuda.empty((100,))
+    cuda.forward("neg", [t], out)
+    assert np.array_equal(out.numpy(), -x)
+    lib.plast_b200_peer_group_release(g)
+
+
+def _gpu_count():
+    try:
+        out = subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True, timeout=30).stdout
+        return sum(1 for l in out.splitlines() if l.startswith("GPU "))
+    except Exception:
+        return 0
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs of one box")
+def test_real_ranks_match_the_process_group():
+    n = min(_gpu_count(), 4)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    p = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", "29533", str(ROOT / "tests" / "peer_worker.py")],
+                       capture_output=True, text=True, timeout=300, env=env)
+    print(p.stdout[-2000:], p.stderr[-2000:])
+    assert p.returncode == 0 and "PEER OK" in p.stdout
