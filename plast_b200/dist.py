@@ -221,6 +221,19 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
     timeit("config4_full_sum+allreduce", full_sum, M * M * 4 + 4)
     timeit("config4_full_max+allreduce", full_max, M * M * 4 + 4)
     timeit("config4_sum_axis0+allreduce", sum_axis0, (M * M + M) * 4)
+    # the same three with the library's own NVLink exchange instead of the process group's all-reduce
+    peer = None
+    if world > 1 and world <= 8:
+        try:
+            peer = PeerGroup(dist, torch, pb)
+        except Exception as exc:  # the table must not die with the exchange
+            rows.append({"op": "peer_exchange_unavailable", "n_gpus": world, "error": str(exc)[:200]})
+    if peer is not None:
+        use_peer_exchange(peer)
+        timeit("config4_full_sum+peer_exchange", full_sum, M * M * 4 + 4)
+        timeit("config4_full_max+peer_exchange", full_max, M * M * 4 + 4)
+        timeit("config4_sum_axis0+peer_exchange", sum_axis0, (M * M + M) * 4)
+        use_peer_exchange(None)
     del X
 
     # config 3: cross-entropy mean over row-sharded logits -> 4-byte all-reduce of the loss SUM
@@ -239,6 +252,10 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
         global_mean(dist, loss, R)
 
     timeit("config3_cross_entropy_mean+allreduce", ce_mean, (R * Cn + R) * 4 + 4)
+    if peer is not None:
+        use_peer_exchange(peer)
+        timeit("config3_cross_entropy_mean+peer_exchange", ce_mean, (R * Cn + R) * 4 + 4)
+        use_peer_exchange(None)
     # row ops of config 3 on the same row shard: independent per row, no collective
     rs, Y = torch.empty(sh.count, device=dev), torch.empty_like(L)
     trs, tY = wrap(rs), wrap(Y)
@@ -272,6 +289,14 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
         all_reduce_sum(dist, gB)
 
     timeit("config5_bias_grad+allreduce", bias_grad, 2 * total * 4 + 1024)
+    if peer is not None:
+        use_peer_exchange(peer)
+        timeit("config5_bias_grad+peer_exchange", bias_grad, 2 * total * 4 + 1024)
+        use_peer_exchange(None)
+        status = peer.status()
+        if status != 0:
+            rows.append({"op": "peer_exchange_status", "n_gpus": world, "status": status})
+        peer.close()
     del X, G, Yv
     torch.cuda.synchronize()
     return rows
