@@ -36,8 +36,20 @@ __device__ __forceinline__ void store_flag(unsigned int *p, unsigned int v) {
 }
 
 __global__ void __launch_bounds__(kPeerThreads)
-peer_all_reduce_kernel(PeerPtrs peers, int rank, int world, float *inout, unsigned n, unsigned seq, int op,
-                       unsigned int *status, unsigned max_spins) {
+peer_all_reduce_kernel(PeerPtrs peers, int rank, int world, float *inout, unsigned n, unsigned int *seq_counter,
+                       int op, unsigned int *status, unsigned max_spins) {
+  // The sequence number lives on the device and advances once per launch, so a launch recorded in
+  // a CUDA graph stays correct however often the graph is replayed (every rank makes the same
+  // sequence of launches, so the counters agree). 0 is what empty flags hold and is skipped.
+  __shared__ unsigned seq_shared;
+  if (threadIdx.x == 0) {
+    unsigned next = *seq_counter + 1u;
+    if (next == 0u) next = 2u; // wrapped: keep the parities alternating
+    *seq_counter = next;
+    seq_shared = next;
+  }
+  __syncthreads();
+  const unsigned seq = seq_shared;
   const unsigned par = seq & 1u;
   const size_t my_slot = ((size_t)par * world + rank) * kMaxFloats;
   // (1) my message into everybody's buffer (plain stores; peer addresses go over NVLink)
@@ -92,9 +104,8 @@ struct PlastPeerGroup {
   void *mapped[pb::kMaxWorld];       // peers' buffers (IPC mappings; mapped[rank] == local)
   bool opened[pb::kMaxWorld];
   void *fake[pb::kMaxWorld];         // test groups: local stand-ins for the other ranks
-  unsigned seq;
   unsigned max_spins;
-  unsigned int *status_dev;          // device word the kernel writes on a give-up
+  unsigned int *status_dev;          // device words: [0] set by the kernel on a give-up, [1] the sequence counter
   bool connected;
 };
 
@@ -120,8 +131,8 @@ static PlastPeerGroup *new_group(int rank, int world) {
   g->world = world;
   g->max_spins = 1u << 22; // x 256 ns sleeps: about a second
   if (cudaMalloc(&g->local, kBufferBytes) != cudaSuccess || cudaMemset(g->local, 0, kBufferBytes) != cudaSuccess ||
-      cudaMalloc((void **)&g->status_dev, sizeof(unsigned int)) != cudaSuccess ||
-      cudaMemset(g->status_dev, 0, sizeof(unsigned int)) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+      cudaMalloc((void **)&g->status_dev, 2 * sizeof(unsigned int)) != cudaSuccess ||
+      cudaMemset(g->status_dev, 0, 2 * sizeof(unsigned int)) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
     set_error(PLAST_B200_ERR_CUDA, "peer group: cannot allocate the exchange buffer: %s",
               cudaGetErrorString(cudaGetLastError()));
     if (g->local) cudaFree(g->local);
@@ -209,11 +220,8 @@ void plast_b200_peer_all_reduce(PlastPeerGroup *g, float *data, u64 n, int op) {
     return;
   }
   if (n == 0) return;
-  g->seq += 1; // never 0: the flags start at 0
-  if (g->seq == 0) g->seq = 2; // wrapped: 0 is what empty flags hold; 2 keeps the parities alternating
-  const unsigned threads = kPeerThreads;
-  peer_all_reduce_kernel<<<1, threads, 0, stream()>>>(layout(g), g->rank, g->world, data, (unsigned)n, g->seq, op,
-                                                      g->status_dev, g->max_spins);
+  peer_all_reduce_kernel<<<1, kPeerThreads, 0, stream()>>>(layout(g), g->rank, g->world, data, (unsigned)n,
+                                                           g->status_dev + 1, op, g->status_dev, g->max_spins);
   count_launch();
   note_kernel("peer_all_reduce");
   end_call();
