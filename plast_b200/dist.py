@@ -173,6 +173,8 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
         return pb.Tensor.wrap_pointer(t.data_ptr(), list(t.shape) if shape is None else shape,
                                       dtype=dtype, owner=t)
 
+    import ctypes as C
+
     def timeit(name, fn, total_bytes):
         for _ in range(3):
             fn()
@@ -193,8 +195,50 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
         gbs = total_bytes / (ms * 1e-3) / 1e9
-        rows.append({"op": name, "n_gpus": world, "ms": round(ms, 5), "GBps": round(gbs, 1),
-                     "frac_of_measured_aggregate": round(gbs / (peak_gbs * world), 4)})
+        row = {"op": name, "n_gpus": world, "ms": round(ms, 5), "GBps": round(gbs, 1),
+               "frac_of_measured_aggregate": round(gbs / (peak_gbs * world), 4)}
+        # Steps of a few microseconds are bound by the host's call cost when issued one by one; the
+        # same 20 steps recorded in a CUDA graph and replayed show what the GPUs and the links need.
+        # Every rank must take the same path, so a failure anywhere sends all ranks to the row above.
+        ok = torch.ones(1, device=dev)
+        graph = None
+        main = torch.cuda.current_stream()
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(main)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                pb.lib.plast_b200_set_stream(C.c_void_p(side.cuda_stream))
+                fn()
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(20):
+                        fn()
+        except Exception as exc:
+            ok.zero_()
+            graph = None
+            row["graph_replay_error"] = str(exc)[:160]
+        pb.lib.plast_b200_set_stream(C.c_void_p(main.cuda_stream))
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if graph is not None and float(ok.item()) > 0:
+            graph.replay()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            gt = []
+            for _ in range(reps):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); graph.replay(); e1.record()
+                torch.cuda.synchronize()
+                gt.append(e0.elapsed_time(e1) / 20)
+            g = torch.tensor([float(np.median(gt))], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(g, op=dist.ReduceOp.MAX)
+            gms = float(g.item())
+            row["graph_replay_ms"] = round(gms, 5)
+            row["graph_replay_GBps"] = round(total_bytes / (gms * 1e-3) / 1e9, 1)
+        rows.append(row)
 
     # config 4: X[8192, 8192], rows sharded; full sum / full max -> 4-byte all-reduce,
     # sum over axis 0 -> 32 KiB all-reduce
