@@ -205,27 +205,6 @@ __global__ void __launch_bounds__(256) ew_tiled4_kernel(F f, TiledParams<NIN> p)
     rest = q;
   }
   const unsigned q4 = threadIdx.x & 15, row = threadIdx.x >> 4; // 16 float4 across, 16 rows per pass
-  // Operands that are contiguous along dim 0 are requested first, so that their loads are in
-  // flight together with the transposed tiles' instead of after the barrier.
-  const u64 c0 = t0 * kTile4 + q4 * 4;
-  float4 direct[4][NIN];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const u64 cT = tT * kTile4 + row + j * 16;
-    if (c0 < p.n0 && cT < p.nT) {
-#pragma unroll
-      for (int a = 0; a < NIN; ++a) {
-        if ((p.tmask >> a) & 1u) continue;
-        const float *q = p.in[a] + off[a + 1] + c0 * p.s0[a + 1] + cT * p.sT[a + 1];
-        if (p.s0[a + 1] == 1) {
-          direct[j][a] = __ldcs(reinterpret_cast<const float4 *>(q));
-        } else { // broadcast along dim 0
-          const float sc = __ldg(q);
-          direct[j][a] = make_float4(sc, sc, sc, sc);
-        }
-      }
-    }
-  }
   // phase 1: transposed inputs, float4 along dT, rows along dim 0
 #pragma unroll
   for (int a = 0; a < NIN; ++a) {
@@ -246,7 +225,26 @@ __global__ void __launch_bounds__(256) ew_tiled4_kernel(F f, TiledParams<NIN> p)
     }
   }
   __syncthreads();
-  // phase 2: float4 along dim 0, rows along dT (operands read directly were requested above)
+  // phase 2: float4 along dim 0, rows along dT
+  const u64 c0 = t0 * kTile4 + q4 * 4;
+  float4 direct[4][NIN];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const u64 cT = tT * kTile4 + row + j * 16;
+    if (c0 < p.n0 && cT < p.nT) {
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) {
+        if ((p.tmask >> a) & 1u) continue;
+        const float *q = p.in[a] + off[a + 1] + c0 * p.s0[a + 1] + cT * p.sT[a + 1];
+        if (p.s0[a + 1] == 1) {
+          direct[j][a] = __ldcs(reinterpret_cast<const float4 *>(q));
+        } else { // broadcast along dim 0
+          const float sc = __ldg(q);
+          direct[j][a] = make_float4(sc, sc, sc, sc);
+        }
+      }
+    }
+  }
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const u64 cT = tT * kTile4 + row + j * 16;
