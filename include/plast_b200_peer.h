@@ -6,9 +6,10 @@
  * sums of a row-sharded matrix, the cross-entropy mean and bias gradients then need ONE exchange
  * of a tiny partial (4 bytes to 32 KiB). A library all-reduce costs 25-35 us for such a message on
  * eight GPUs, several times the local kernel; here every rank stores its partial straight into
- * every peer's exchange buffer (peer-to-peer stores over NVLink), raises a flag there, waits for
- * the flags of the others and adds the partials up in rank order — one small kernel, identical
- * bits on every rank. One process per GPU; buffers are shared through CUDA IPC handles that the
+ * every peer's exchange buffer (peer-to-peer stores over NVLink, 8-byte packets that carry the
+ * value and the call's sequence number, so no fence and no separate flag), polls its own buffer
+ * for the packets of the others and adds the values up in rank order — one small kernel,
+ * identical bits on every rank. One process per GPU; buffers are shared through CUDA IPC handles that the
  * caller passes between the processes (64 opaque bytes per rank, by any transport).
  */
 #ifndef PLAST_B200_PEER_H

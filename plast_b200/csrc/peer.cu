@@ -1,15 +1,15 @@
 // All-reduce of tiny partials over NVLink peer memory: see include/plast_b200_peer.h.
 //
-// Layout of one rank's exchange buffer (all ranks use the same layout):
-//   data  [2 parities][world slots][kMaxFloats]   slot r of parity q holds rank r's message of
-//                                                 every call whose sequence number has parity q
-//   flags [2 parities][world]                     flag r of parity q = sequence number of the
-//                                                 last message rank r completed into this buffer
-// A call with sequence number s: (1) store my message into slot `rank` of parity s&1 of EVERY
-// rank's buffer, (2) fence, then store s into flag `rank` of every buffer, (3) wait until all
-// `world` flags of MY buffer show s, (4) add the slots of my buffer in rank order. Two parities
-// are enough: a rank can only begin call s + 2 after completing s + 1, which needs every peer's
-// flag for s + 1, which a peer raises only after it has read everything of call s.
+// One rank's exchange buffer (the same layout on every rank):
+//   packets [2 parities][world slots][kMaxFloats] of 8 bytes: {value bits, sequence number}
+// slot r of parity q receives rank r's message of every call whose sequence number has parity q.
+// A call with sequence number s: (1) store {value, s} for every element into slot `rank` of
+// parity s & 1 of EVERY rank's buffer (one naturally aligned 8-byte store per element and peer:
+// it arrives whole, so the packet validates itself and no fence or separate flag is needed),
+// (2) for every element poll slot 0 .. world-1 of MY buffer until its packet carries s, and add
+// the values in rank order. Two parities are enough: a rank can only begin call s + 2 after
+// completing s + 1, which needs every peer's packets of s + 1, which a peer sends only after its
+// kernel of call s, and with it all its reads of parity s & 1, has finished.
 #include "common.cuh"
 #include "plast_b200_peer.h"
 
@@ -20,19 +20,19 @@ namespace pb {
 constexpr int kPeerThreads = 1024;
 constexpr unsigned kMaxFloats = PLAST_B200_PEER_MAX_FLOATS;
 constexpr int kMaxWorld = PLAST_B200_PEER_MAX_WORLD;
+constexpr int kPerThread = (int)(kMaxFloats / kPeerThreads);
 
 struct PeerPtrs {
-  float *data[kMaxWorld];
-  unsigned int *flags[kMaxWorld];
+  unsigned long long *packets[kMaxWorld];
 };
 
-__device__ __forceinline__ unsigned int load_flag(const unsigned int *p) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long load_packet(const unsigned long long *p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void store_flag(unsigned int *p, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void store_packet(unsigned long long *p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
 __global__ void __launch_bounds__(kPeerThreads)
@@ -40,61 +40,63 @@ peer_all_reduce_kernel(PeerPtrs peers, int rank, int world, float *inout, unsign
                        int op, unsigned int *status, unsigned max_spins) {
   // The sequence number lives on the device and advances once per launch, so a launch recorded in
   // a CUDA graph stays correct however often the graph is replayed (every rank makes the same
-  // sequence of launches, so the counters agree). 0 is what empty flags hold and is skipped.
+  // sequence of launches, so the counters agree). 0 is what an empty buffer holds and is skipped.
   __shared__ unsigned seq_shared;
+  __shared__ int gave_up;
   if (threadIdx.x == 0) {
     unsigned next = *seq_counter + 1u;
     if (next == 0u) next = 2u; // wrapped: keep the parities alternating
     *seq_counter = next;
     seq_shared = next;
+    gave_up = 0;
   }
   __syncthreads();
   const unsigned seq = seq_shared;
-  const unsigned par = seq & 1u;
-  const size_t my_slot = ((size_t)par * world + rank) * kMaxFloats;
-  // (1) my message into everybody's buffer (plain stores; peer addresses go over NVLink)
+  const size_t parity_base = (size_t)(seq & 1u) * world * kMaxFloats;
+  // (1) my message into everybody's buffer
   for (unsigned i = threadIdx.x; i < n; i += kPeerThreads) {
-    const float v = inout[i];
-    for (int p = 0; p < world; ++p) peers.data[p][my_slot + i] = v;
+    const unsigned long long pkt = ((unsigned long long)seq << 32) | (unsigned long long)__float_as_uint(inout[i]);
+    for (int p = 0; p < world; ++p) store_packet(peers.packets[p] + parity_base + (size_t)rank * kMaxFloats + i, pkt);
   }
-  __threadfence_system();
-  __syncthreads();
-  // (2) tell everybody it is complete
-  if (threadIdx.x < (unsigned)world) store_flag(peers.flags[threadIdx.x] + par * world + rank, seq);
-  // (3) wait for everybody's message in MY buffer; every wait is bounded
-  __shared__ int gave_up;
-  if (threadIdx.x == 0) gave_up = 0;
-  __syncthreads();
-  if (threadIdx.x < (unsigned)world) {
-    const unsigned int *f = peers.flags[rank] + par * world + threadIdx.x;
-    unsigned spins = 0;
-    while (load_flag(f) != seq) {
-      if (++spins > max_spins) {
-        atomicCAS(status, 0u, 1u + threadIdx.x); // remember the first rank that never arrived
-        gave_up = 1;
-        break;
+  // (2) everybody's message out of MY buffer, added in rank order: the same bits on every rank.
+  // Every poll loop is bounded; a give-up leaves `inout` untouched and records the missing rank.
+  const unsigned long long *mine = peers.packets[rank] + parity_base;
+  float acc[kPerThread];
+#pragma unroll
+  for (int k = 0; k < kPerThread; ++k) {
+    const unsigned i = threadIdx.x + (unsigned)k * kPeerThreads;
+    acc[k] = 0.0f;
+    if (i >= n) continue;
+    for (int p = 0; p < world; ++p) {
+      const unsigned long long *slot = mine + (size_t)p * kMaxFloats + i;
+      unsigned long long pkt = load_packet(slot);
+      unsigned spins = 0;
+      while ((unsigned)(pkt >> 32) != seq) {
+        if (++spins > max_spins) {
+          atomicCAS(status, 0u, 1u + (unsigned)p);
+          gave_up = 1;
+          break;
+        }
+        __nanosleep(64);
+        pkt = load_packet(slot);
       }
-      __nanosleep(256);
+      const float v = __uint_as_float((unsigned)pkt);
+      acc[k] = p == 0 ? v
+                      : (op == PLAST_B200_PEER_SUM ? acc[k] + v
+                                                   : (op == PLAST_B200_PEER_MAX ? (acc[k] > v ? acc[k] : v)
+                                                                                : (acc[k] < v ? acc[k] : v)));
     }
   }
   __syncthreads();
-  if (gave_up) return; // data stays unreduced; the host reads `status`
-  // (4) combine in rank order: the same bits on every rank. L1 may hold lines of an earlier
-  // call with this parity, so the slots are read past it.
-  const float *mine = peers.data[rank] + (size_t)par * world * kMaxFloats;
-  for (unsigned i = threadIdx.x; i < n; i += kPeerThreads) {
-    float acc = __ldcg(mine + i);
-    for (int p = 1; p < world; ++p) {
-      const float v = __ldcg(mine + (size_t)p * kMaxFloats + i);
-      acc = op == PLAST_B200_PEER_SUM ? acc + v : (op == PLAST_B200_PEER_MAX ? (acc > v ? acc : v) : (acc < v ? acc : v));
-    }
-    inout[i] = acc;
+  if (gave_up) return;
+#pragma unroll
+  for (int k = 0; k < kPerThread; ++k) {
+    const unsigned i = threadIdx.x + (unsigned)k * kPeerThreads;
+    if (i < n) inout[i] = acc[k];
   }
 }
 
-constexpr size_t kDataBytes = (size_t)2 * kMaxWorld * kMaxFloats * sizeof(float);
-constexpr size_t kFlagBytes = (size_t)2 * kMaxWorld * sizeof(unsigned int);
-constexpr size_t kBufferBytes = kDataBytes + 256; // flags live after the data, 256-byte aligned
+constexpr size_t kBufferBytes = (size_t)2 * kMaxWorld * kMaxFloats * sizeof(unsigned long long);
 
 } // namespace pb
 
@@ -113,10 +115,7 @@ using namespace pb;
 
 static PeerPtrs layout(const PlastPeerGroup *g) {
   PeerPtrs p = {};
-  for (int r = 0; r < g->world; ++r) {
-    p.data[r] = (float *)g->mapped[r];
-    p.flags[r] = (unsigned int *)((char *)g->mapped[r] + kDataBytes);
-  }
+  for (int r = 0; r < g->world; ++r) p.packets[r] = (unsigned long long *)g->mapped[r];
   return p;
 }
 
@@ -129,7 +128,7 @@ static PlastPeerGroup *new_group(int rank, int world) {
   memset(g, 0, sizeof(*g));
   g->rank = rank;
   g->world = world;
-  g->max_spins = 1u << 22; // x 256 ns sleeps: about a second
+  g->max_spins = 1u << 23; // polls of ~100 ns each: about a second
   if (cudaMalloc(&g->local, kBufferBytes) != cudaSuccess || cudaMemset(g->local, 0, kBufferBytes) != cudaSuccess ||
       cudaMalloc((void **)&g->status_dev, 2 * sizeof(unsigned int)) != cudaSuccess ||
       cudaMemset(g->status_dev, 0, 2 * sizeof(unsigned int)) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
