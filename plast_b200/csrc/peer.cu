@@ -20,7 +20,6 @@ namespace pb {
 constexpr int kPeerThreads = 1024;
 constexpr unsigned kMaxFloats = PLAST_B200_PEER_MAX_FLOATS;
 constexpr int kMaxWorld = PLAST_B200_PEER_MAX_WORLD;
-constexpr int kPerThread = (int)(kMaxFloats / kPeerThreads);
 
 struct PeerPtrs {
   unsigned long long *packets[kMaxWorld];
@@ -36,63 +35,57 @@ __device__ __forceinline__ void store_packet(unsigned long long *p, unsigned lon
 }
 
 __global__ void __launch_bounds__(kPeerThreads)
-peer_all_reduce_kernel(PeerPtrs peers, int rank, int world, float *inout, unsigned n, unsigned int *seq_counter,
-                       int op, unsigned int *status, unsigned max_spins) {
+peer_all_reduce_kernel(PeerPtrs peers, int rank, int world, float *inout, unsigned n, unsigned int *words, int op,
+                       unsigned max_spins) {
+  // words[0]: status (set on a give-up), words[1]: sequence counter, words[2]: CTA ticket.
   // The sequence number lives on the device and advances once per launch, so a launch recorded in
   // a CUDA graph stays correct however often the graph is replayed (every rank makes the same
-  // sequence of launches, so the counters agree). 0 is what an empty buffer holds and is skipped.
-  __shared__ unsigned seq_shared;
-  __shared__ int gave_up;
-  if (threadIdx.x == 0) {
-    unsigned next = *seq_counter + 1u;
-    if (next == 0u) next = 2u; // wrapped: keep the parities alternating
-    *seq_counter = next;
-    seq_shared = next;
-    gave_up = 0;
-  }
-  __syncthreads();
-  const unsigned seq = seq_shared;
+  // sequence of launches, so the counters agree). Every CTA reads the counter when it starts; the
+  // CTA that finishes last stores the new value, after all the others have read the old one.
+  // 0 is what an empty buffer holds and is skipped.
+  unsigned seq = words[1] + 1u;
+  if (seq == 0u) seq = 2u; // wrapped: keep the parities alternating
   const size_t parity_base = (size_t)(seq & 1u) * world * kMaxFloats;
+  const unsigned i = blockIdx.x * kPeerThreads + threadIdx.x; // one element per thread
   // (1) my message into everybody's buffer
-  for (unsigned i = threadIdx.x; i < n; i += kPeerThreads) {
+  if (i < n) {
     const unsigned long long pkt = ((unsigned long long)seq << 32) | (unsigned long long)__float_as_uint(inout[i]);
     for (int p = 0; p < world; ++p) store_packet(peers.packets[p] + parity_base + (size_t)rank * kMaxFloats + i, pkt);
   }
   // (2) everybody's message out of MY buffer, added in rank order: the same bits on every rank.
-  // Every poll loop is bounded; a give-up leaves `inout` untouched and records the missing rank.
-  const unsigned long long *mine = peers.packets[rank] + parity_base;
-  float acc[kPerThread];
-#pragma unroll
-  for (int k = 0; k < kPerThread; ++k) {
-    const unsigned i = threadIdx.x + (unsigned)k * kPeerThreads;
-    acc[k] = 0.0f;
-    if (i >= n) continue;
-    for (int p = 0; p < world; ++p) {
-      const unsigned long long *slot = mine + (size_t)p * kMaxFloats + i;
+  // Every poll loop is bounded; a give-up leaves the element untouched and records the missing rank.
+  if (i < n) {
+    const unsigned long long *mine = peers.packets[rank] + parity_base + i;
+    float acc = 0.0f;
+    bool complete = true;
+    for (int p = 0; p < world && complete; ++p) {
+      const unsigned long long *slot = mine + (size_t)p * kMaxFloats;
       unsigned long long pkt = load_packet(slot);
       unsigned spins = 0;
       while ((unsigned)(pkt >> 32) != seq) {
         if (++spins > max_spins) {
-          atomicCAS(status, 0u, 1u + (unsigned)p);
-          gave_up = 1;
+          atomicCAS(&words[0], 0u, 1u + (unsigned)p);
+          complete = false;
           break;
         }
         __nanosleep(64);
         pkt = load_packet(slot);
       }
       const float v = __uint_as_float((unsigned)pkt);
-      acc[k] = p == 0 ? v
-                      : (op == PLAST_B200_PEER_SUM ? acc[k] + v
-                                                   : (op == PLAST_B200_PEER_MAX ? (acc[k] > v ? acc[k] : v)
-                                                                                : (acc[k] < v ? acc[k] : v)));
+      acc = p == 0 ? v
+                   : (op == PLAST_B200_PEER_SUM ? acc + v
+                                                : (op == PLAST_B200_PEER_MAX ? (acc > v ? acc : v) : (acc < v ? acc : v)));
     }
+    if (complete) inout[i] = acc;
   }
+  // last CTA out advances the sequence counter and re-arms the ticket
   __syncthreads();
-  if (gave_up) return;
-#pragma unroll
-  for (int k = 0; k < kPerThread; ++k) {
-    const unsigned i = threadIdx.x + (unsigned)k * kPeerThreads;
-    if (i < n) inout[i] = acc[k];
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(&words[2], 1u) == gridDim.x - 1) {
+      words[2] = 0;
+      words[1] = seq;
+    }
   }
 }
 
@@ -107,7 +100,7 @@ struct PlastPeerGroup {
   bool opened[pb::kMaxWorld];
   void *fake[pb::kMaxWorld];         // test groups: local stand-ins for the other ranks
   unsigned max_spins;
-  unsigned int *status_dev;          // device words: [0] set by the kernel on a give-up, [1] the sequence counter
+  unsigned int *status_dev;          // device words: [0] set by the kernel on a give-up, [1] sequence counter, [2] CTA ticket
   bool connected;
 };
 
@@ -130,8 +123,8 @@ static PlastPeerGroup *new_group(int rank, int world) {
   g->world = world;
   g->max_spins = 1u << 23; // polls of ~100 ns each: about a second
   if (cudaMalloc(&g->local, kBufferBytes) != cudaSuccess || cudaMemset(g->local, 0, kBufferBytes) != cudaSuccess ||
-      cudaMalloc((void **)&g->status_dev, 2 * sizeof(unsigned int)) != cudaSuccess ||
-      cudaMemset(g->status_dev, 0, 2 * sizeof(unsigned int)) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+      cudaMalloc((void **)&g->status_dev, 4 * sizeof(unsigned int)) != cudaSuccess ||
+      cudaMemset(g->status_dev, 0, 4 * sizeof(unsigned int)) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
     set_error(PLAST_B200_ERR_CUDA, "peer group: cannot allocate the exchange buffer: %s",
               cudaGetErrorString(cudaGetLastError()));
     if (g->local) cudaFree(g->local);
@@ -219,8 +212,9 @@ void plast_b200_peer_all_reduce(PlastPeerGroup *g, float *data, u64 n, int op) {
     return;
   }
   if (n == 0) return;
-  peer_all_reduce_kernel<<<1, kPeerThreads, 0, stream()>>>(layout(g), g->rank, g->world, data, (unsigned)n,
-                                                           g->status_dev + 1, op, g->status_dev, g->max_spins);
+  const unsigned blocks = (unsigned)((n + kPeerThreads - 1) / kPeerThreads); // at most 8, all resident at once
+  peer_all_reduce_kernel<<<blocks, kPeerThreads, 0, stream()>>>(layout(g), g->rank, g->world, data, (unsigned)n,
+                                                                g->status_dev, op, g->max_spins);
   count_launch();
   note_kernel("peer_all_reduce");
   end_call();
