@@ -242,6 +242,11 @@ void plast_b200_chain_forward(const Tensor **inputs, int n_inputs, Tensor *outpu
 void plast_b200_chain_backward(Tensor **inputs, int n_inputs, const Tensor *output,
                                const PlastChainStep *steps, int n_steps);
 
+/* 1 when chains can be compiled at run time (libnvrtc and libcuda found, PLAST_B200_CHAIN_JIT not
+ * set to 0): then the forward runs as a compiled kernel and the backward exists; 0 = the forward
+ * falls back to the in-kernel interpreter and plast_b200_chain_backward reports UNSUPPORTED. */
+int plast_b200_chain_jit_available(void);
+
 /* The same chain on HOST buffers (what a caller pays when its data starts and ends on the host,
  * the reference's numpy -> tensor -> op -> numpy() round trip, src/python/bindings.cpp:93,144):
  * host_inputs[i] holds input_elems[i] floats, either n or 1 (a constant); host_output receives n

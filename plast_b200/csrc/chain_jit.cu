@@ -347,12 +347,16 @@ bool launch_plan(const ChainProgramView &p, const IterPlan &plan, float *out, co
 //
 // Operand layout of `plan` / `ins`: forward (p.wrt < 0): the chain's inputs. Backward: the upstream
 // gradient, then the chain's inputs, then (p.accumulate) the current gradient of input p.wrt.
-bool launch_chain_jit(const ChainProgramView &p, const IterPlan &plan, float *out, const float *const *ins) {
+static bool jit_disabled_by_env() {
   static const bool disabled = [] {
     const char *e = getenv("PLAST_B200_CHAIN_JIT");
     return e && e[0] == '0';
   }();
-  if (disabled || !api().ok) return false;
+  return disabled;
+}
+
+bool launch_chain_jit(const ChainProgramView &p, const IterPlan &plan, float *out, const float *const *ins) {
+  if (jit_disabled_by_env() || !api().ok) return false;
   JitFHost f = {};
   for (int k = 0; k < p.n_steps; ++k) f.c[k] = p.fval[k];
   // Inputs the plan never advances are constants: hand them to the functor as pointers and plan
@@ -397,7 +401,7 @@ bool launch_chain_jit(const ChainProgramView &p, const IterPlan &plan, float *ou
   }
 }
 
-bool chain_jit_available() { return api().ok; }
+bool chain_jit_available() { return !jit_disabled_by_env() && api().ok; }
 
 } // namespace pb
 
@@ -453,6 +457,8 @@ extern "C" int plast_b200_chain_backward_source(const PlastChainStep *steps, int
   }
   return (int)src.size();
 }
+
+extern "C" int plast_b200_chain_jit_available(void) { return pb::chain_jit_available() ? 1 : 0; }
 
 static int try_compile_view(const pb::ChainProgramView &v) {
   pb::Api &api = pb::api();

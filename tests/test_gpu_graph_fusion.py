@@ -181,6 +181,11 @@ def build_training_chain(cuda, x, y, bias):
     return g, tx, ty, tb, t[9]
 
 
+needs_jit = pytest.mark.skipif(not pb.lib.plast_b200_chain_jit_available(),
+                               reason="the chain backward needs the run-time compiler")
+
+
+@needs_jit
 @pytest.mark.parametrize("shape", [(64, 1000), (7, 33), (1 << 20,)])
 def test_training_chain_fused_backward_equals_node_by_node_backward(cuda, shape):
     x, y = rand_normal(0, shape), rand_normal(1, shape)
@@ -211,6 +216,7 @@ def test_training_chain_fused_backward_equals_node_by_node_backward(cuda, shape)
     np.testing.assert_allclose(res[1][2], g64 * sg, rtol=2e-5, atol=2e-6)
 
 
+@needs_jit
 def test_chain_backward_entry_point_with_scalar_opcodes_and_accumulation(cuda):
     n = 4099
     x = rand_uniform(0, (n,), 0.5, 2.0)
