@@ -45,6 +45,11 @@ int plast_b200_peer_group_connect(PlastPeerGroup *group, const unsigned char *al
  * bounded (about a second): if a peer never arrives the kernel gives up, the data is left
  * unreduced and plast_b200_peer_group_status reports it; nothing hangs. */
 void plast_b200_peer_all_reduce(PlastPeerGroup *group, float *data, u64 n, int op);
+/* The full reduction (op = PLAST_B200_PEER_SUM / MAX / MIN over every element of `input`, this
+ * rank's shard) and the exchange of its result as ONE kernel: output->data[0] receives the value
+ * over all ranks' shards. Counts as one call of the exchange sequence (every rank calls it at the
+ * same point). For a mean, divide the sum by the global element count. */
+void plast_b200_peer_full_reduce(PlastPeerGroup *group, int op, const Tensor *input, Tensor *output);
 /* 0 = every exchange so far completed; k > 0 = a wait for rank k - 1 ran out (sticky until
  * plast_b200_peer_group_clear_status). Synchronises the library stream. */
 int plast_b200_peer_group_status(PlastPeerGroup *group);

@@ -11,7 +11,7 @@
 // completing s + 1, which needs every peer's packets of s + 1, which a peer sends only after its
 // kernel of call s, and with it all its reads of parity s & 1, has finished.
 #include "common.cuh"
-#include "plast_b200_peer.h"
+#include "peer_link.cuh"
 
 #include <string.h>
 
@@ -24,15 +24,6 @@ constexpr int kMaxWorld = PLAST_B200_PEER_MAX_WORLD;
 struct PeerPtrs {
   unsigned long long *packets[kMaxWorld];
 };
-
-__device__ __forceinline__ unsigned long long load_packet(const unsigned long long *p) {
-  unsigned long long v;
-  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void store_packet(unsigned long long *p, unsigned long long v) {
-  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
-}
 
 __global__ void __launch_bounds__(kPeerThreads)
 peer_all_reduce_kernel(PeerPtrs peers, int rank, int world, float *inout, unsigned n, unsigned int *words, int op,
@@ -72,9 +63,7 @@ peer_all_reduce_kernel(PeerPtrs peers, int rank, int world, float *inout, unsign
         pkt = load_packet(slot);
       }
       const float v = __uint_as_float((unsigned)pkt);
-      acc = p == 0 ? v
-                   : (op == PLAST_B200_PEER_SUM ? acc + v
-                                                : (op == PLAST_B200_PEER_MAX ? (acc > v ? acc : v) : (acc < v ? acc : v)));
+      acc = p == 0 ? v : peer_combine(op, acc, v);
     }
     if (complete) inout[i] = acc;
   }
@@ -218,6 +207,43 @@ void plast_b200_peer_all_reduce(PlastPeerGroup *g, float *data, u64 n, int op) {
   count_launch();
   note_kernel("peer_all_reduce");
   end_call();
+}
+
+// Full reduction of this rank's shard AND the exchange of its result in one kernel: the last CTA
+// of the local reduction (the one that combines the per-CTA partials) publishes the value to every
+// peer, polls for theirs and stores the combined result. Shards the single-output kernel does not
+// serve (a few elements, an empty shard) reduce locally and then run the stand-alone exchange, so
+// every rank always makes exactly one call of the exchange sequence.
+void plast_b200_peer_full_reduce(PlastPeerGroup *g, int op, const Tensor *input, Tensor *output) {
+  begin_call();
+  if (!g || !input || !output) {
+    set_error(PLAST_B200_ERR_NULL, "peer full reduce: NULL argument");
+    return;
+  }
+  if (!g->connected || op < PLAST_B200_PEER_SUM || op > PLAST_B200_PEER_MIN) {
+    set_error(PLAST_B200_ERR_UNSUPPORTED, "peer full reduce: group not connected or unknown op %d", op);
+    return;
+  }
+  PeerLink link = {};
+  const PeerPtrs ptrs = layout(g);
+  for (int r = 0; r < g->world; ++r) link.packets[r] = ptrs.packets[r];
+  link.words = g->status_dev;
+  link.rank = g->rank;
+  link.world = g->world;
+  link.max_spins = g->max_spins;
+  const Tensor *ins[1] = {input};
+  const KernelParams full = {PLAST_FULL_REDUCE, 0, 0.0f};
+  arm_peer_link(link);
+  if (op == PLAST_B200_PEER_SUM) sum_cuda_forward(ins, output, full);
+  else if (op == PLAST_B200_PEER_MAX) max_cuda_forward(ins, output, full);
+  else min_cuda_forward(ins, output, full);
+  const bool fused = disarm_peer_link();
+  if (plast_b200_last_error() != PLAST_B200_OK) return;
+  if (fused) {
+    note_kernel("reduce_seg_with_peer_exchange");
+    return;
+  }
+  plast_b200_peer_all_reduce(g, (float *)output->data, 1, op);
 }
 
 int plast_b200_peer_group_status(PlastPeerGroup *g) {

@@ -21,6 +21,7 @@
 
 #include "common.cuh"
 #include "iter.h"
+#include "peer_link.cuh"
 
 #include <float.h>
 
@@ -33,6 +34,7 @@ struct SumOp {
   using T = float;
   using Out = float;
   static constexpr bool kIndexed = false;
+  static constexpr int kPeerOp = PLAST_B200_PEER_SUM; // combine of the cross-GPU exchange (-1: none)
   __device__ __forceinline__ static T identity() { return 0.0f; }
   __device__ __forceinline__ static T step(T acc, float v, unsigned) { return acc + v; }
   __device__ __forceinline__ static T combine(T a, T b) { return a + b; }
@@ -50,6 +52,7 @@ struct MaxOp {
   using T = float;
   using Out = float;
   static constexpr bool kIndexed = false;
+  static constexpr int kPeerOp = PLAST_B200_PEER_MAX;
   __device__ __forceinline__ static T identity() { return -FLT_MAX; }
   __device__ __forceinline__ static T step(T acc, float v, unsigned) { return acc > v ? acc : v; }
   __device__ __forceinline__ static T combine(T a, T b) { return a > b ? a : b; }
@@ -63,6 +66,7 @@ struct MinOp {
   using T = float;
   using Out = float;
   static constexpr bool kIndexed = false;
+  static constexpr int kPeerOp = PLAST_B200_PEER_MIN;
   __device__ __forceinline__ static T identity() { return FLT_MAX; }
   __device__ __forceinline__ static T step(T acc, float v, unsigned) { return acc < v ? acc : v; }
   __device__ __forceinline__ static T combine(T a, T b) { return a < b ? a : b; }
@@ -80,6 +84,7 @@ struct ArgMaxOp {
   };
   using Out = int;
   static constexpr bool kIndexed = true;
+  static constexpr int kPeerOp = -1;
   __device__ __forceinline__ static T identity() { return T{-INFINITY, 0xffffffffu}; }
   // a thread visits its elements in increasing index order, so only a strictly greater value
   // replaces the running best
@@ -156,7 +161,17 @@ template <int NIN> struct RedParams {
   float post_div;
   unsigned int *counters;
   void *partials;
+  PeerLink peer; // world > 0: the thread that holds the single final value exchanges it across GPUs
 };
+
+// The final value of a single-output reduction, combined across GPUs when a link is attached.
+template <class Op>
+__device__ __forceinline__ typename Op::T across_gpus(const PeerLink &link, typename Op::T v) {
+  if constexpr (Op::kPeerOp >= 0) {
+    if (link.world > 0) return peer_exchange_scalar(link, v, Op::kPeerOp);
+  }
+  return v;
+}
 
 template <int VEC>
 __device__ __forceinline__ void red_load(const float *p, bool vec, float *v) {
@@ -386,7 +401,8 @@ __global__ void __launch_bounds__(kRedThreads) reduce_seg_kernel(RedParams<NIN> 
   r = block_reduce<Op>(r);
 
   if (p.splits == 1) {
-    if (threadIdx.x == 0) Op::store((typename Op::Out *)p.out + toff, r, p.accumulate, p.post_div);
+    if (threadIdx.x == 0)
+      Op::store((typename Op::Out *)p.out + toff, across_gpus<Op>(p.peer, r), p.accumulate, p.post_div);
     return;
   }
   T *partials = (T *)p.partials + out_idx * p.splits;
@@ -399,7 +415,8 @@ __global__ void __launch_bounds__(kRedThreads) reduce_seg_kernel(RedParams<NIN> 
   for (unsigned c = threadIdx.x; c < p.splits; c += kRedThreads) v = Op::combine(v, Op::load_cg(partials + c));
   __syncthreads(); // block_reduce's scratch was used above
   v = block_reduce<Op>(v);
-  if (threadIdx.x == 0) Op::store((typename Op::Out *)p.out + toff, v, p.accumulate, p.post_div);
+  if (threadIdx.x == 0)
+    Op::store((typename Op::Out *)p.out + toff, across_gpus<Op>(p.peer, v), p.accumulate, p.post_div);
 }
 
 // ---- cols: CTA per (strip of 32*VEC outputs along dim 0, outer kept index, chunk of reduced) ---------
@@ -742,6 +759,10 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   p.post_div = post_div;
   p.counters = nullptr;
   p.partials = nullptr;
+  p.peer = PeerLink{};
+  // a pending cross-GPU exchange rides on the kernel whose last CTA holds THE final value
+  if (Op::kPeerOp >= 0 && g.kind == kRedSeg && !g.stream && g.n_kept == 1 && !take_peer_link(&p.peer))
+    p.peer = PeerLink{};
   Workspace ws = {};
   if (g.splits > 1 || g.stream) {
     if (!get_workspace(&ws)) return;

@@ -1,5 +1,6 @@
 // Library state: last-error record, launch stream, launch counter, per-device scratch.
 #include "common.cuh"
+#include "peer_link.cuh"
 
 #include <atomic>
 #include <mutex>
@@ -22,6 +23,27 @@ Workspace g_ws[kMaxDevices] = {};
 volatile unsigned int *g_gave_up_host[kMaxDevices] = {};
 int g_sm_count[kMaxDevices] = {};
 } // namespace
+
+namespace {
+thread_local PeerLink t_link;
+thread_local bool t_link_armed = false, t_link_taken = false;
+} // namespace
+void arm_peer_link(const PeerLink &link) {
+  t_link = link;
+  t_link_armed = true;
+  t_link_taken = false;
+}
+bool take_peer_link(PeerLink *out) {
+  if (!t_link_armed || t_link_taken) return false;
+  *out = t_link;
+  t_link_taken = true;
+  return true;
+}
+bool disarm_peer_link() {
+  const bool taken = t_link_taken;
+  t_link_armed = t_link_taken = false;
+  return taken;
+}
 
 void set_error(int code, const char *fmt, ...) {
   if (t_err != PLAST_B200_OK) return; // keep the first error of a call

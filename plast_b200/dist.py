@@ -84,6 +84,16 @@ class PeerGroup:
         self._pb.lib.plast_b200_peer_all_reduce(self._g, self._C.c_void_p(t.data_ptr()), t.numel(), self.OPS[op])
         return t
 
+    def full_reduce(self, t, out, op: str = "sum"):
+        """Full reduction of this rank's shard `t` and the exchange of the result in one kernel;
+        `t` and `out` are plast_b200.Tensor objects (out holds one float)."""
+        C = self._C
+        fn = self._pb.lib.plast_b200_peer_full_reduce
+        fn.argtypes = [C.c_void_p, C.c_int, C.POINTER(self._pb.CTensor), C.POINTER(self._pb.CTensor)]
+        fn.restype = None
+        fn(self._g, self.OPS[op], C.byref(t.c), C.byref(out.c))
+        return out
+
     def status(self) -> int:
         return self._pb.lib.plast_b200_peer_group_status(self._g)
 

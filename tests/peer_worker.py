@@ -40,6 +40,24 @@ def main():
             assert torch.equal(x, acc), f"rank {rank}: {op} of {n} floats differs from the rank-order result"
             dist.all_reduce(want, op=red)
             assert torch.allclose(x, want, rtol=1e-6, atol=1e-6)
+    # the full reduction of a shard with the exchange inside the reduction kernel
+    for it, n in enumerate([5, 1 << 16, (1 << 22) + 3, 1 << 23]):
+        gen.manual_seed(7000 + 10 * it + rank)
+        shard = torch.randn(n, generator=gen, device=dev)
+        t_shard = pb.Tensor.wrap_pointer(shard.data_ptr(), [n], owner=shard)
+        for op in ("sum", "max", "min"):
+            local = pb.Tensor((1,)); pb.forward(op, [t_shard], local, dim=pb.FULL_REDUCE)
+            lv = torch.from_numpy(local.numpy().copy()).to(dev)
+            gathered = [torch.empty_like(lv) for _ in range(world)]
+            dist.all_gather(gathered, lv)
+            acc = gathered[0].clone()
+            for g in gathered[1:]:
+                acc = acc + g if op == "sum" else (torch.maximum(acc, g) if op == "max" else torch.minimum(acc, g))
+            out = pb.Tensor((1,))
+            group.full_reduce(t_shard, out, op)
+            pb.check_error()
+            torch.cuda.synchronize()
+            assert out.numpy()[0] == acc.item(), f"rank {rank}: fused {op} of {n} floats: {out.numpy()[0]} vs {acc.item()}"
     assert group.status() == 0
     # timing: exchange of 1 float and of 8192 floats, against the process group's all-reduce
     def timed(fn, reps=200):
@@ -86,6 +104,28 @@ def main():
         if rank == 0:
             print(f"exchange of {n} floats on {world} GPUs: peer kernel {t_peer:.1f} us per call from Python, "
                   f"{t_peer_graph:.1f} us replayed from a CUDA graph; process group {t_pg:.1f} us per call", flush=True)
+    # a 32 MiB shard (config 4 on eight GPUs): local full sum + all-reduce against the single fused kernel
+    shard = torch.randn(1 << 23, device=dev)
+    t_shard = pb.Tensor.wrap_pointer(shard.data_ptr(), [1 << 23], owner=shard)
+    one = torch.zeros(1, device=dev)
+    t_one = pb.Tensor.wrap_pointer(one.data_ptr(), [1], owner=one)
+
+    def two_step():
+        pb.forward("sum", [t_shard], t_one, dim=pb.FULL_REDUCE, check=False)
+        group.all_reduce(one, "sum")
+
+    def with_process_group():
+        pb.forward("sum", [t_shard], t_one, dim=pb.FULL_REDUCE, check=False)
+        dist.all_reduce(one, op=dist.ReduceOp.SUM)
+
+    t_fused = graph_timed(lambda: group.full_reduce(t_shard, t_one, "sum"), inner=20)
+    t_two = graph_timed(two_step, inner=20)
+    t_pg = timed(with_process_group)
+    if rank == 0:
+        print(f"full sum of a 32 MiB shard on {world} GPUs: one kernel with the exchange inside {t_fused:.1f} us, "
+              f"reduce then exchange kernel {t_two:.1f} us (both replayed from a CUDA graph); "
+              f"reduce then process-group all-reduce {t_pg:.1f} us per call", flush=True)
+    assert group.status() == 0
     group.close()
     dist.barrier()
     if rank == 0:

@@ -66,6 +66,38 @@ def test_wait_for_a_rank_that_never_arrives_runs_out_and_is_reported(cuda):
     lib.plast_b200_peer_group_release(g)
 
 
+def test_full_reduce_with_the_exchange_inside_the_reduction_kernel(cuda):
+    lib = _lib()
+    lib.plast_b200_peer_full_reduce.argtypes = [C.c_void_p, C.c_int, C.POINTER(pb.CTensor), C.POINTER(pb.CTensor)]
+    lib.plast_b200_peer_full_reduce.restype = None
+    g = lib.plast_b200_peer_group_local(1, 1000)                          # one rank: publishes to and polls itself
+    pb.check_error()
+    x = rand_normal(3, (1 << 22,))
+    t = cuda.tensor(x)
+    for op, name in ((0, "sum"), (1, "max"), (2, "min"), (0, "sum")):
+        want = cuda.empty((1,)); cuda.forward(name, [t], want, dim=pb.FULL_REDUCE)
+        got = cuda.empty((1,))
+        lib.plast_b200_peer_full_reduce(g, op, C.byref(t.c), C.byref(got.c))
+        pb.check_error()
+        assert pb.last_kernel() == "reduce_seg_with_peer_exchange"
+        assert got.numpy()[0] == want.numpy()[0]                          # same kernel, same bits
+    small = cuda.tensor(x[:5].copy())                                     # served by another kernel: exchange follows it
+    got = cuda.empty((1,))
+    lib.plast_b200_peer_full_reduce(g, 1, C.byref(small.c), C.byref(got.c))
+    pb.check_error()
+    assert pb.last_kernel() == "peer_all_reduce" and got.numpy()[0] == x[:5].max()
+    assert lib.plast_b200_peer_group_status(g) == 0
+    lib.plast_b200_peer_group_release(g)
+    # bounded wait inside the reduction kernel: ranks 1 and 2 never publish
+    g = lib.plast_b200_peer_group_local(3, 2000)
+    got = cuda.empty((1,))
+    lib.plast_b200_peer_full_reduce(g, 1, C.byref(t.c), C.byref(got.c))
+    pb.check_error()
+    assert lib.plast_b200_peer_group_status(g) == 2
+    assert got.numpy()[0] == x.max()                                      # the local value, flagged as unreduced
+    lib.plast_b200_peer_group_release(g)
+
+
 def _gpu_count():
     try:
         out = subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True, timeout=30).stdout
