@@ -288,6 +288,9 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
         timeit("config4_full_max+peer_exchange", full_max, M * M * 4 + 4)
         timeit("config4_sum_axis0+peer_exchange", sum_axis0, (M * M + M) * 4)
         use_peer_exchange(None)
+        # ... and with the exchange inside the reduction kernel (one launch per step)
+        timeit("config4_full_sum_fused_with_exchange", lambda: peer.full_reduce(tX, tone, "sum"), M * M * 4 + 4)
+        timeit("config4_full_max_fused_with_exchange", lambda: peer.full_reduce(tX, tone, "max"), M * M * 4 + 4)
     del X
 
     # config 3: cross-entropy mean over row-sharded logits -> 4-byte all-reduce of the loss SUM
