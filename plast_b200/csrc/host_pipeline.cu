@@ -130,7 +130,6 @@ extern "C" void plast_b200_chain_forward_host(const float *const *host_inputs, c
   Tensor in_t[PLAST_CHAIN_MAX_INPUTS] = {};
   const Tensor *in_ptr[PLAST_CHAIN_MAX_INPUTS];
   int slot_of_input[PLAST_CHAIN_MAX_INPUTS];
-  bool any_constant = false;
   for (int a = 0, k = 0; a < n_inputs; ++a) {
     in_t[a].dtype = FLOAT32;
     in_t[a].device = CUDA;
@@ -144,10 +143,8 @@ extern "C" void plast_b200_chain_forward_host(const float *const *host_inputs, c
       in_t[a].ndim = 0;
       in_t[a].data = p->constants + a;
       PB_CUDA(cudaMemcpyAsync(p->constants + a, host_inputs[a], sizeof(float), cudaMemcpyHostToDevice, p->in));
-      any_constant = true;
     }
   }
-  (void)any_constant;
   const int operands = n_streamed + 1;
   const u64 n_chunks = (n + kChunkElems - 1) / kChunkElems;
   Tensor out_t = {};
