@@ -188,3 +188,20 @@ int main(void) {
         subprocess.run(["gcc", "-std=c11", *flags, str(src), "-o", str(tmp_path / "p")], check=True)
         out.append(subprocess.run([str(tmp_path / "p")], check=True, capture_output=True, text=True).stdout.strip())
     assert out[0] == out[1] == out[2] == "32 88 0 8 16 48 52 64 32 8 16 24 0 5 23 27"
+
+
+def test_training_chains_are_fused_only_when_a_backward_can_be_generated():
+    x, t, out = T((16,), True), T((16,), True), T((16,), True)
+    for tensor in (x, t, out):                       # the pass wants grad buffers on tensors that require grad
+        g_ = pb.Tensor((16,), device="cuda", _ptr=0x2000)
+        tensor.grad, tensor.c.grad = g_, C.pointer(g_.c)
+    g = G.Graph()
+    g.node("EXP", [x], t); g.node("NEG", [t], out)
+    dag = g.dag()
+    assert G.fuse(dag) == 0 and dag.count == 2                            # default: forward-only groups
+    can = bool(pb.lib.plast_b200_chain_jit_available())                   # needs libnvrtc AND the driver library
+    assert G.fuse(dag, G.FUSE_CHAINS_WITH_GRAD) == (1 if can else 0)
+    if can:
+        node = dag.nodes[0].contents
+        assert node.op_type == G.OP["FUSED_CHAIN"]
+        assert node.op.cuda_backward == G.symbol_address("chain_cuda_backward")
