@@ -364,7 +364,7 @@ def run_ours(args):
 
     cpu_info = None
     if rank == 0 and world == 1:
-        _, cpu_info, _ = cpu_chain_baseline(1 << 25, 3)
+        _, cpu_info, _ = cpu_chain_baseline(1 << 25, 40)   # about 12 s of CPU work
 
     sharded = None
     if world > 1 and not args.no_per_op:
