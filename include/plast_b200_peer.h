@@ -50,6 +50,12 @@ void plast_b200_peer_all_reduce(PlastPeerGroup *group, float *data, u64 n, int o
  * over all ranks' shards. Counts as one call of the exchange sequence (every rank calls it at the
  * same point). For a mean, divide the sum by the global element count. */
 void plast_b200_peer_full_reduce(PlastPeerGroup *group, int op, const Tensor *input, Tensor *output);
+/* Mean cross-entropy over row-sharded logits (this rank holds `logits` [rows_here, C] and their
+ * INT32 `labels`; global_rows = rows over all ranks): the loss sums of the ranks are exchanged
+ * inside the cross-entropy kernel and divided by global_rows; output->data[0] receives the same
+ * mean on every rank. One call of the exchange sequence. */
+void plast_b200_peer_cross_entropy_mean(PlastPeerGroup *group, const Tensor *logits, const Tensor *labels,
+                                        Tensor *output, u64 global_rows);
 /* 0 = every exchange so far completed; k > 0 = a wait for rank k - 1 ran out (sticky until
  * plast_b200_peer_group_clear_status). Synchronises the library stream. */
 int plast_b200_peer_group_status(PlastPeerGroup *group);

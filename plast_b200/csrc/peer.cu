@@ -125,6 +125,19 @@ static PlastPeerGroup *new_group(int rank, int world) {
   return g;
 }
 
+static PeerLink link_of(const PlastPeerGroup *g) {
+  PeerLink link = {};
+  const PeerPtrs ptrs = layout(g);
+  for (int r = 0; r < g->world; ++r) link.packets[r] = ptrs.packets[r];
+  link.words = g->status_dev;
+  link.rank = g->rank;
+  link.world = g->world;
+  link.max_spins = g->max_spins;
+  return link;
+}
+
+__global__ void scale_one_kernel(float *v, float factor) { v[0] = v[0] * factor; }
+
 extern "C" {
 
 PlastPeerGroup *plast_b200_peer_group_begin(int rank, int world, unsigned char handle[PLAST_B200_IPC_HANDLE_BYTES]) {
@@ -224,13 +237,7 @@ void plast_b200_peer_full_reduce(PlastPeerGroup *g, int op, const Tensor *input,
     set_error(PLAST_B200_ERR_UNSUPPORTED, "peer full reduce: group not connected or unknown op %d", op);
     return;
   }
-  PeerLink link = {};
-  const PeerPtrs ptrs = layout(g);
-  for (int r = 0; r < g->world; ++r) link.packets[r] = ptrs.packets[r];
-  link.words = g->status_dev;
-  link.rank = g->rank;
-  link.world = g->world;
-  link.max_spins = g->max_spins;
+  const PeerLink link = link_of(g);
   const Tensor *ins[1] = {input};
   const KernelParams full = {PLAST_FULL_REDUCE, 0, 0.0f};
   arm_peer_link(link);
@@ -244,6 +251,50 @@ void plast_b200_peer_full_reduce(PlastPeerGroup *g, int op, const Tensor *input,
     return;
   }
   plast_b200_peer_all_reduce(g, (float *)output->data, 1, op);
+}
+
+// Cross-entropy mean over row-sharded logits: this rank's rows go through the streaming
+// cross-entropy kernel, whose last CTA exchanges the loss sum and divides by the global row count.
+// Layouts that kernel does not take compute the local mean first, turn it back into a sum,
+// exchange it with the stand-alone kernel and divide.
+void plast_b200_peer_cross_entropy_mean(PlastPeerGroup *g, const Tensor *logits, const Tensor *labels,
+                                        Tensor *output, u64 global_rows) {
+  begin_call();
+  if (!g || !logits || !labels || !output || !output->data) {
+    set_error(PLAST_B200_ERR_NULL, "peer cross entropy: NULL argument");
+    return;
+  }
+  if (!g->connected || global_rows == 0 || logits->ndim != 2) {
+    set_error(PLAST_B200_ERR_UNSUPPORTED, "peer cross entropy: group not connected, no rows, or logits not [N, C]");
+    return;
+  }
+  PeerLink link = link_of(g);
+  link.global_count = (float)global_rows;
+  const Tensor *ins[2] = {logits, labels};
+  const KernelParams none = {0, 0, 0.0f};
+  const u64 local_rows = logits->shape[0];
+  bool fused = false;
+  if (local_rows > 0) {
+    arm_peer_link(link);
+    cross_entropy_cuda_forward(ins, output, none);
+    fused = disarm_peer_link();
+    if (plast_b200_last_error() != PLAST_B200_OK) return;
+  } else {
+    fill32(output->data, 0u, 1); // an empty shard contributes a zero sum
+  }
+  if (fused) {
+    note_kernel("cross_entropy_rows_with_peer_exchange");
+    return;
+  }
+  if (local_rows > 0) {
+    scale_one_kernel<<<1, 1, 0, stream()>>>((float *)output->data, (float)local_rows); // mean -> sum
+    count_launch();
+  }
+  plast_b200_peer_all_reduce(g, (float *)output->data, 1, PLAST_B200_PEER_SUM);
+  if (plast_b200_last_error() != PLAST_B200_OK) return;
+  scale_one_kernel<<<1, 1, 0, stream()>>>((float *)output->data, 1.0f / (float)global_rows);
+  count_launch();
+  end_call();
 }
 
 int plast_b200_peer_group_status(PlastPeerGroup *g) {

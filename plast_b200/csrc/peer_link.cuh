@@ -13,6 +13,7 @@ struct PeerLink {
   unsigned int *words; // [0] status, [1] sequence counter, [2] CTA ticket of the exchange kernel
   int rank, world;     // world == 0: no exchange
   unsigned max_spins;
+  float global_count;  // kernels that end in a mean divide the exchanged sum by this (0: not a mean)
 };
 
 #ifdef __CUDACC__

@@ -94,6 +94,17 @@ class PeerGroup:
         fn(self._g, self.OPS[op], C.byref(t.c), C.byref(out.c))
         return out
 
+    def cross_entropy_mean(self, logits, labels, out, global_rows: int):
+        """Mean cross-entropy over row-sharded logits with the exchange inside the loss kernel;
+        arguments are plast_b200.Tensor objects (labels INT32, out one float)."""
+        C = self._C
+        fn = self._pb.lib.plast_b200_peer_cross_entropy_mean
+        T = C.POINTER(self._pb.CTensor)
+        fn.argtypes = [C.c_void_p, T, T, T, C.c_uint64]
+        fn.restype = None
+        fn(self._g, C.byref(logits.c), C.byref(labels.c), C.byref(out.c), global_rows)
+        return out
+
     def status(self) -> int:
         return self._pb.lib.plast_b200_peer_group_status(self._g)
 
@@ -313,6 +324,8 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
         use_peer_exchange(peer)
         timeit("config3_cross_entropy_mean+peer_exchange", ce_mean, (R * Cn + R) * 4 + 4)
         use_peer_exchange(None)
+        timeit("config3_cross_entropy_mean_fused_with_exchange",
+               lambda: peer.cross_entropy_mean(tL, tl, tloss, R), (R * Cn + R) * 4 + 4)
     # row ops of config 3 on the same row shard: independent per row, no collective
     rs, Y = torch.empty(sh.count, device=dev), torch.empty_like(L)
     trs, tY = wrap(rs), wrap(Y)

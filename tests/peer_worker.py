@@ -58,6 +58,22 @@ def main():
             pb.check_error()
             torch.cuda.synchronize()
             assert out.numpy()[0] == acc.item(), f"rank {rank}: fused {op} of {n} floats: {out.numpy()[0]} vs {acc.item()}"
+    # mean cross-entropy over row-sharded logits, the exchange inside the loss kernel
+    rows_here, cols = 1024 + 8 * rank, 4096
+    total_rows = sum(1024 + 8 * r for r in range(world))
+    gen.manual_seed(9000 + rank)
+    logits = torch.randn((rows_here, cols), generator=gen, device=dev) * 2
+    labels = torch.randint(0, cols, (rows_here,), generator=gen, device=dev, dtype=torch.int32)
+    t_logits = pb.Tensor.wrap_pointer(logits.data_ptr(), [rows_here, cols], owner=logits)
+    t_labels = pb.Tensor.wrap_pointer(labels.data_ptr(), [rows_here], dtype=pb.INT32, owner=labels)
+    out = pb.Tensor((1,))
+    group.cross_entropy_mean(t_logits, t_labels, out, total_rows)
+    pb.check_error()
+    torch.cuda.synchronize()
+    ref = torch.nn.functional.cross_entropy(logits.double(), labels.long(), reduction="sum")
+    dist.all_reduce(ref)
+    assert abs(out.numpy()[0] - ref.item() / total_rows) <= 2e-6 * abs(ref.item() / total_rows) + 1e-6, \
+        f"rank {rank}: fused cross-entropy mean {out.numpy()[0]} vs {ref.item() / total_rows}"
     assert group.status() == 0
     # timing: exchange of 1 float and of 8192 floats, against the process group's all-reduce
     def timed(fn, reps=200):

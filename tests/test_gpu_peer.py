@@ -98,6 +98,33 @@ def test_full_reduce_with_the_exchange_inside_the_reduction_kernel(cuda):
     lib.plast_b200_peer_group_release(g)
 
 
+def test_cross_entropy_mean_with_the_exchange_inside_the_loss_kernel(cuda):
+    lib = _lib()
+    T = C.POINTER(pb.CTensor)
+    lib.plast_b200_peer_cross_entropy_mean.argtypes = [C.c_void_p, T, T, T, C.c_uint64]
+    lib.plast_b200_peer_cross_entropy_mean.restype = None
+    g = lib.plast_b200_peer_group_local(1, 1000)
+    pb.check_error()
+    for rows, cols in ((512, 4096), (37, 1000), (64, 10)):                # streaming kernel, and two other layouts
+        X = rand_normal(rows, (rows, cols), std=2.0)
+        lab = np.random.RandomState(1).randint(0, cols, size=rows).astype(np.int32)
+        tx, tl = cuda.tensor(X), cuda.tensor(lab)
+        want = cuda.empty((1,)); cuda.forward("cross_entropy", [tx, tl], want)
+        got = cuda.empty((1,))
+        lib.plast_b200_peer_cross_entropy_mean(g, C.byref(tx.c), C.byref(tl.c), C.byref(got.c), rows)
+        pb.check_error()
+        if cols % 4 == 0 and cols >= 4096:
+            assert pb.last_kernel() == "cross_entropy_rows_with_peer_exchange"
+            assert got.numpy()[0] == want.numpy()[0]
+        np.testing.assert_allclose(got.numpy()[0], want.numpy()[0], rtol=1e-6)
+        # a global row count larger than the local one: the sum is divided by it
+        lib.plast_b200_peer_cross_entropy_mean(g, C.byref(tx.c), C.byref(tl.c), C.byref(got.c), 4 * rows)
+        pb.check_error()
+        np.testing.assert_allclose(got.numpy()[0], want.numpy()[0] / 4, rtol=1e-6)
+    assert lib.plast_b200_peer_group_status(g) == 0
+    lib.plast_b200_peer_group_release(g)
+
+
 def _gpu_count():
     try:
         out = subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True, timeout=30).stdout
