@@ -89,6 +89,7 @@ struct PlastPeerGroup {
   bool opened[pb::kMaxWorld];
   void *fake[pb::kMaxWorld];         // test groups: local stand-ins for the other ranks
   unsigned max_spins;
+  pb::PeerLink *link_dev;            // the link as kernels see it (device memory), made when connected
   unsigned int *status_dev;          // device words: [0] set by the kernel on a give-up, [1] sequence counter, [2] CTA ticket
   bool connected;
 };
@@ -135,6 +136,12 @@ static PeerLink link_of(const PlastPeerGroup *g) {
   link.max_spins = g->max_spins;
   return link;
 }
+// Called once every peer is mapped: the device copy of the link that fused kernels read.
+static bool publish_link(PlastPeerGroup *g) {
+  const PeerLink link = link_of(g);
+  if (!g->link_dev && cudaMalloc((void **)&g->link_dev, sizeof(PeerLink)) != cudaSuccess) return false;
+  return cudaMemcpy(g->link_dev, &link, sizeof(PeerLink), cudaMemcpyHostToDevice) == cudaSuccess;
+}
 
 __global__ void scale_one_kernel(float *v, float factor) { v[0] = v[0] * factor; }
 
@@ -176,6 +183,10 @@ int plast_b200_peer_group_connect(PlastPeerGroup *g, const unsigned char *all_ha
     }
     g->opened[r] = true;
   }
+  if (!publish_link(g)) {
+    set_error(PLAST_B200_ERR_CUDA, "peer group connect: cannot store the link on the device");
+    return 1;
+  }
   g->connected = true;
   return 0;
 }
@@ -194,6 +205,11 @@ PlastPeerGroup *plast_b200_peer_group_local(int world, unsigned max_spins) {
   }
   cudaDeviceSynchronize();
   g->max_spins = max_spins ? max_spins : 1u;
+  if (!publish_link(g)) {
+    set_error(PLAST_B200_ERR_CUDA, "peer group: cannot store the link on the device");
+    plast_b200_peer_group_release(g);
+    return nullptr;
+  }
   g->connected = true;
   return g;
 }
@@ -237,10 +253,9 @@ void plast_b200_peer_full_reduce(PlastPeerGroup *g, int op, const Tensor *input,
     set_error(PLAST_B200_ERR_UNSUPPORTED, "peer full reduce: group not connected or unknown op %d", op);
     return;
   }
-  const PeerLink link = link_of(g);
   const Tensor *ins[1] = {input};
   const KernelParams full = {PLAST_FULL_REDUCE, 0, 0.0f};
-  arm_peer_link(link);
+  arm_peer_link(g->link_dev, 0.0f);
   if (op == PLAST_B200_PEER_SUM) sum_cuda_forward(ins, output, full);
   else if (op == PLAST_B200_PEER_MAX) max_cuda_forward(ins, output, full);
   else min_cuda_forward(ins, output, full);
@@ -268,14 +283,12 @@ void plast_b200_peer_cross_entropy_mean(PlastPeerGroup *g, const Tensor *logits,
     set_error(PLAST_B200_ERR_UNSUPPORTED, "peer cross entropy: group not connected, no rows, or logits not [N, C]");
     return;
   }
-  PeerLink link = link_of(g);
-  link.global_count = (float)global_rows;
   const Tensor *ins[2] = {logits, labels};
   const KernelParams none = {0, 0, 0.0f};
   const u64 local_rows = logits->shape[0];
   bool fused = false;
   if (local_rows > 0) {
-    arm_peer_link(link);
+    arm_peer_link(g->link_dev, (float)global_rows);
     cross_entropy_cuda_forward(ins, output, none);
     fused = disarm_peer_link();
     if (plast_b200_last_error() != PLAST_B200_OK) return;
@@ -319,6 +332,7 @@ void plast_b200_peer_group_release(PlastPeerGroup *g) {
   }
   if (g->local) cudaFree(g->local);
   if (g->status_dev) cudaFree(g->status_dev);
+  if (g->link_dev) cudaFree(g->link_dev);
   delete g;
 }
 

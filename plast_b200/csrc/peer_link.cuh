@@ -11,10 +11,11 @@ namespace pb {
 struct PeerLink {
   unsigned long long *packets[PLAST_B200_PEER_MAX_WORLD]; // every rank's buffer, as mapped here
   unsigned int *words; // [0] status, [1] sequence counter, [2] CTA ticket of the exchange kernel
-  int rank, world;     // world == 0: no exchange
+  int rank, world;
   unsigned max_spins;
-  float global_count;  // kernels that end in a mean divide the exchanged sum by this (0: not a mean)
 };
+// Kernels receive a POINTER to the link (in device memory, NULL = no exchange): a by-value copy
+// would be indexed dynamically (packets[p]) and end up on every thread's local stack.
 
 #ifdef __CUDACC__
 __device__ __forceinline__ unsigned long long load_packet(const unsigned long long *p) {
@@ -66,11 +67,12 @@ __device__ __forceinline__ float peer_exchange_scalar(const PeerLink &link, floa
 }
 #endif
 
-// Host side (runtime.cu): a reduction entry point called between arm and disarm hands the link to
-// the first eligible launch (a segmented reduction with a single output); fused() tells whether
-// that happened.
-void arm_peer_link(const PeerLink &link);
-bool take_peer_link(PeerLink *out); // true once per armed link
-bool disarm_peer_link();            // returns whether a launch took it
+// Host side (runtime.cu): a reduction entry point called between arm and disarm hands the link
+// (a device pointer) to the first eligible launch (a segmented reduction with a single output, the
+// streaming cross-entropy kernel); disarm tells whether that happened. global_count: what a kernel
+// that ends in a mean divides the exchanged sum by.
+void arm_peer_link(const PeerLink *device_link, float global_count);
+bool take_peer_link(const PeerLink **out, float *global_count); // true once per armed link
+bool disarm_peer_link();                                        // returns whether a launch took it
 
 } // namespace pb

@@ -161,14 +161,14 @@ template <int NIN> struct RedParams {
   float post_div;
   unsigned int *counters;
   void *partials;
-  PeerLink peer; // world > 0: the thread that holds the single final value exchanges it across GPUs
+  const PeerLink *peer; // not NULL: the thread that holds the single final value exchanges it across GPUs
 };
 
 // The final value of a single-output reduction, combined across GPUs when a link is attached.
 template <class Op>
-__device__ __forceinline__ typename Op::T across_gpus(const PeerLink &link, typename Op::T v) {
+__device__ __forceinline__ typename Op::T across_gpus(const PeerLink *link, typename Op::T v) {
   if constexpr (Op::kPeerOp >= 0) {
-    if (link.world > 0) return peer_exchange_scalar(link, v, Op::kPeerOp);
+    if (link != nullptr) return peer_exchange_scalar(*link, v, Op::kPeerOp);
   }
   return v;
 }
@@ -759,10 +759,10 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   p.post_div = post_div;
   p.counters = nullptr;
   p.partials = nullptr;
-  p.peer = PeerLink{};
+  p.peer = nullptr;
   // a pending cross-GPU exchange rides on the kernel whose last CTA holds THE final value
-  if (Op::kPeerOp >= 0 && g.kind == kRedSeg && !g.stream && g.n_kept == 1 && !take_peer_link(&p.peer))
-    p.peer = PeerLink{};
+  if (Op::kPeerOp >= 0 && g.kind == kRedSeg && !g.stream && g.n_kept == 1 && !take_peer_link(&p.peer, nullptr))
+    p.peer = nullptr;
   Workspace ws = {};
   if (g.splits > 1 || g.stream) {
     if (!get_workspace(&ws)) return;

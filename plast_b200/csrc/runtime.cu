@@ -25,23 +25,27 @@ int g_sm_count[kMaxDevices] = {};
 } // namespace
 
 namespace {
-thread_local PeerLink t_link;
+thread_local const PeerLink *t_link = nullptr;
+thread_local float t_link_count = 0.0f;
 thread_local bool t_link_armed = false, t_link_taken = false;
 } // namespace
-void arm_peer_link(const PeerLink &link) {
-  t_link = link;
+void arm_peer_link(const PeerLink *device_link, float global_count) {
+  t_link = device_link;
+  t_link_count = global_count;
   t_link_armed = true;
   t_link_taken = false;
 }
-bool take_peer_link(PeerLink *out) {
+bool take_peer_link(const PeerLink **out, float *global_count) {
   if (!t_link_armed || t_link_taken) return false;
   *out = t_link;
+  if (global_count) *global_count = t_link_count;
   t_link_taken = true;
   return true;
 }
 bool disarm_peer_link() {
   const bool taken = t_link_taken;
   t_link_armed = t_link_taken = false;
+  t_link = nullptr;
   return taken;
 }
 

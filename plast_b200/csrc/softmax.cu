@@ -256,7 +256,8 @@ __device__ __forceinline__ float exp2_term_fast(float x, float m2) {
 }
 __global__ void __launch_bounds__(kSmThreads)
 cross_entropy_rows_kernel(const float *__restrict__ x, const int *__restrict__ labels, SmRows g,
-                          float *__restrict__ mean_out, unsigned int *counter, float *partials, PeerLink peer) {
+                          float *__restrict__ mean_out, unsigned int *counter, float *partials, const PeerLink *peer,
+                          float global_count) {
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float warp_loss = 0.0f; // lane 0: sum of the losses of this warp's rows
   const unsigned warps_per_cta = kSmThreads / 32;
@@ -364,7 +365,7 @@ cross_entropy_rows_kernel(const float *__restrict__ x, const int *__restrict__ l
   if (threadIdx.x == 0) {
     // Row-sharded logits: the loss SUMS of all ranks are exchanged right here (one thread, after
     // the grid has retired) and divided by the global row count: never a mean of means.
-    if (peer.world > 0) mean_out[0] = peer_exchange_scalar(peer, tot, PLAST_B200_PEER_SUM) / peer.global_count;
+    if (peer != nullptr) mean_out[0] = peer_exchange_scalar(*peer, tot, PLAST_B200_PEER_SUM) / global_count;
     else mean_out[0] = tot / (float)g.rows; // src/kernels/cpu/reduce_ops.c:13
   }
 }
@@ -550,9 +551,11 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
     if (ce_grid > ce_cap) ce_grid = ce_cap;
     Workspace ws;
     if (!get_workspace(&ws)) return;
-    PeerLink link = {};
-    if (!take_peer_link(&link)) link = PeerLink{};
-    cross_entropy_rows_kernel<<<(unsigned)ce_grid, kSmThreads, 0, s>>>(xd, labels, g, y, ws.counters, ws.partials, link);
+    const PeerLink *link = nullptr;
+    float global_count = 0.0f;
+    if (!take_peer_link(&link, &global_count)) link = nullptr;
+    cross_entropy_rows_kernel<<<(unsigned)ce_grid, kSmThreads, 0, s>>>(xd, labels, g, y, ws.counters, ws.partials, link,
+                                                                      global_count);
     count_launch();
     note_kernel("cross_entropy_rows");
     end_call();
