@@ -148,7 +148,10 @@ void argmax_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams par
  * any other layout / axis gives PLAST_B200_ERR_UNSUPPORTED. All calls on a device share the array
  * (it keeps the previous call's contents; what must start at zero is cleared per call): calls
  * whose kernels overlap on the GPU race, so issue them on one stream. The first call on each
- * device looks up the array's device address; make that call before any stream capture. */
+ * device looks up the array's device address; make that call before any stream capture. Under
+ * CUDA's default lazy module loading that first call is also when the driver claims the array's
+ * memory on the device: make it BEFORE handing the rest of device memory to an arena (or set
+ * CUDA_MODULE_LOADING=EAGER); no later call asks the driver for memory. */
 void sum_axis0_noalloc_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
 
 /* ------------------------------------------------------------------------------------------

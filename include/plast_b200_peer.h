@@ -25,6 +25,10 @@
 #define PLAST_B200_PEER_MAX 1
 #define PLAST_B200_PEER_MIN 2
 
+/* plast_b200_peer_group_status value for "the local part of a fused call failed on this rank":
+ * the rank still made its call of the exchange sequence, with an invalid contribution. */
+#define PLAST_B200_PEER_STATUS_LOCAL_FAILURE 0x100
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -56,8 +60,10 @@ void plast_b200_peer_full_reduce(PlastPeerGroup *group, int op, const Tensor *in
  * mean on every rank. One call of the exchange sequence. */
 void plast_b200_peer_cross_entropy_mean(PlastPeerGroup *group, const Tensor *logits, const Tensor *labels,
                                         Tensor *output, u64 global_rows);
-/* 0 = every exchange so far completed; k > 0 = a wait for rank k - 1 ran out (sticky until
- * plast_b200_peer_group_clear_status). Synchronises the library stream. */
+/* 0 = every exchange so far completed; 1 <= k <= world: a wait for rank k - 1 ran out;
+ * PLAST_B200_PEER_STATUS_LOCAL_FAILURE: a fused call's local kernel could not run here (see
+ * plast_b200_last_error at that call) and the exchanged value is invalid. Sticky until
+ * plast_b200_peer_group_clear_status. Synchronises the library stream. */
 int plast_b200_peer_group_status(PlastPeerGroup *group);
 void plast_b200_peer_group_clear_status(PlastPeerGroup *group);
 /* Unmaps the peers and frees this rank's buffer. Every rank calls it after its last exchange has

@@ -49,7 +49,6 @@ void end_call(); // optional device sync (plast_b200_set_sync) + launch error ch
 struct Workspace {
   unsigned int *counters; // kCounters tickets
   float *partials;        // kPartialFloats floats
-  unsigned int *gave_up;  // host-mapped word a kernel sets when a bounded wait ran out
 };
 constexpr size_t kCounters = 1 << 16;
 constexpr size_t kPartialFloats = (size_t)8 << 20; // 32 MiB

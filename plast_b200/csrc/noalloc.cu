@@ -12,7 +12,12 @@
 // The price is a hard size limit and shared state:
 //   * cols <= kNoAllocMaxCols (16384) and rows < 2^31; larger inputs are rejected with
 //     PLAST_B200_ERR_LIMIT and nothing is launched;
-//   * every GPU that loads the library holds the ~1 MiB array until the process exits;
+//   * every GPU that uses the library holds the ~1 MiB array until the process exits. With CUDA's
+//     default lazy module loading the driver claims that memory when the array is first touched,
+//     which is the first call of this entry point on the device, not the moment the library is
+//     loaded. A caller that is about to hand ALL device memory to its own arena must therefore
+//     make one call (any small input will do) BEFORE that grab, or run with
+//     CUDA_MODULE_LOADING=EAGER; afterwards no call needs memory from the driver;
 //   * all calls on a device share the array and it keeps the previous call's contents: the ticket
 //     counters are cleared at the start of every call, partials are always written before they
 //     are read. Two calls whose kernels overlap on the GPU (different streams) race on it — issue
@@ -153,7 +158,14 @@ extern "C" void sum_axis0_noalloc_cuda_forward(const Tensor **inputs, Tensor *ou
     output->shape[0] = cols;
     output->strides[0] = 1;
   }
-  if (rows == 0 || cols == 0) return;
+  if (cols == 0) return;
+  if (rows == 0) {
+    // nothing to add: every column sum is the start value of the CPU loop, 0
+    // (src/kernels/cpu/reduce_ops.c:53), exactly what sum_cuda_forward stores for an empty input
+    PB_CUDA(cudaMemsetAsync(output->data, 0, cols * sizeof(float), stream()));
+    end_call();
+    return;
+  }
   unsigned char *scratch = noalloc_scratch_address();
   if (!scratch) return;
   const unsigned strips = (unsigned)((cols + kNoAllocStripCols - 1) / kNoAllocStripCols);

@@ -21,13 +21,13 @@ constexpr int kPeerThreads = 1024;
 constexpr unsigned kMaxFloats = PLAST_B200_PEER_MAX_FLOATS;
 constexpr int kMaxWorld = PLAST_B200_PEER_MAX_WORLD;
 
-struct PeerPtrs {
-  unsigned long long *packets[kMaxWorld];
-};
-
+// The mapped buffers arrive through a pointer to the group's PeerLink in device memory: a table
+// passed by value and indexed with a run-time rank would be copied to every thread's local stack.
 __global__ void __launch_bounds__(kPeerThreads)
-peer_all_reduce_kernel(PeerPtrs peers, int rank, int world, float *inout, unsigned n, unsigned int *words, int op,
-                       unsigned max_spins) {
+peer_all_reduce_kernel(const PeerLink *__restrict__ link, float *inout, unsigned n, int op) {
+  const int rank = link->rank, world = link->world;
+  unsigned int *words = link->words;
+  const unsigned max_spins = link->max_spins;
   // words[0]: status (set on a give-up), words[1]: sequence counter, words[2]: CTA ticket.
   // The sequence number lives on the device and advances once per launch, so a launch recorded in
   // a CUDA graph stays correct however often the graph is replayed (every rank makes the same
@@ -41,12 +41,12 @@ peer_all_reduce_kernel(PeerPtrs peers, int rank, int world, float *inout, unsign
   // (1) my message into everybody's buffer
   if (i < n) {
     const unsigned long long pkt = ((unsigned long long)seq << 32) | (unsigned long long)__float_as_uint(inout[i]);
-    for (int p = 0; p < world; ++p) store_packet(peers.packets[p] + parity_base + (size_t)rank * kMaxFloats + i, pkt);
+    for (int p = 0; p < world; ++p) store_packet(link->packets[p] + parity_base + (size_t)rank * kMaxFloats + i, pkt);
   }
   // (2) everybody's message out of MY buffer, added in rank order: the same bits on every rank.
   // Every poll loop is bounded; a give-up leaves the element untouched and records the missing rank.
   if (i < n) {
-    const unsigned long long *mine = peers.packets[rank] + parity_base + i;
+    const unsigned long long *mine = link->packets[rank] + parity_base + i;
     float acc = 0.0f;
     bool complete = true;
     for (int p = 0; p < world && complete; ++p) {
@@ -96,12 +96,6 @@ struct PlastPeerGroup {
 
 using namespace pb;
 
-static PeerPtrs layout(const PlastPeerGroup *g) {
-  PeerPtrs p = {};
-  for (int r = 0; r < g->world; ++r) p.packets[r] = (unsigned long long *)g->mapped[r];
-  return p;
-}
-
 static PlastPeerGroup *new_group(int rank, int world) {
   if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world) {
     set_error(PLAST_B200_ERR_LIMIT, "peer group: rank %d / world %d (at most %d ranks)", rank, world, kMaxWorld);
@@ -128,8 +122,7 @@ static PlastPeerGroup *new_group(int rank, int world) {
 
 static PeerLink link_of(const PlastPeerGroup *g) {
   PeerLink link = {};
-  const PeerPtrs ptrs = layout(g);
-  for (int r = 0; r < g->world; ++r) link.packets[r] = ptrs.packets[r];
+  for (int r = 0; r < g->world; ++r) link.packets[r] = (unsigned long long *)g->mapped[r];
   link.words = g->status_dev;
   link.rank = g->rank;
   link.world = g->world;
@@ -144,6 +137,24 @@ static bool publish_link(PlastPeerGroup *g) {
 }
 
 __global__ void scale_one_kernel(float *v, float factor) { v[0] = v[0] * factor; }
+__global__ void raise_status_kernel(unsigned int *words, unsigned code) { atomicCAS(&words[0], 0u, code); }
+
+// One call of the exchange sequence on the library stream (arguments already checked).
+static void launch_exchange(PlastPeerGroup *g, float *data, unsigned n, int op) {
+  const unsigned blocks = (n + kPeerThreads - 1) / kPeerThreads; // at most 8, all resident at once
+  peer_all_reduce_kernel<<<blocks, kPeerThreads, 0, stream()>>>(g->link_dev, data, n, op);
+  count_launch();
+}
+// The local part of a fused call failed on THIS rank (the error is already recorded). The peers
+// still make their call of the sequence, so this rank makes it too, with whatever the output
+// holds, and raises the group's status word: packets are matched on the sequence number, and a
+// rank that skipped a call would leave every later exchange of every rank waiting until it times
+// out. The result of this exchange is not valid on any rank; the status word says so.
+static void keep_sequence_after_local_failure(PlastPeerGroup *g, Tensor *output, int op) {
+  if (!output || !output->data) return;
+  raise_status_kernel<<<1, 1, 0, stream()>>>(g->status_dev, (unsigned)PLAST_B200_PEER_STATUS_LOCAL_FAILURE);
+  launch_exchange(g, (float *)output->data, 1, op);
+}
 
 extern "C" {
 
@@ -230,10 +241,7 @@ void plast_b200_peer_all_reduce(PlastPeerGroup *g, float *data, u64 n, int op) {
     return;
   }
   if (n == 0) return;
-  const unsigned blocks = (unsigned)((n + kPeerThreads - 1) / kPeerThreads); // at most 8, all resident at once
-  peer_all_reduce_kernel<<<blocks, kPeerThreads, 0, stream()>>>(layout(g), g->rank, g->world, data, (unsigned)n,
-                                                                g->status_dev, op, g->max_spins);
-  count_launch();
+  launch_exchange(g, data, (unsigned)n, op);
   note_kernel("peer_all_reduce");
   end_call();
 }
@@ -255,17 +263,22 @@ void plast_b200_peer_full_reduce(PlastPeerGroup *g, int op, const Tensor *input,
   }
   const Tensor *ins[1] = {input};
   const KernelParams full = {PLAST_FULL_REDUCE, 0, 0.0f};
-  arm_peer_link(g->link_dev, 0.0f);
+  arm_peer_link(g->link_dev, kPeerFullReduce, 0.0f);
   if (op == PLAST_B200_PEER_SUM) sum_cuda_forward(ins, output, full);
   else if (op == PLAST_B200_PEER_MAX) max_cuda_forward(ins, output, full);
   else min_cuda_forward(ins, output, full);
   const bool fused = disarm_peer_link();
-  if (plast_b200_last_error() != PLAST_B200_OK) return;
-  if (fused) {
-    note_kernel("reduce_seg_with_peer_exchange");
+  if (fused) { // the kernel that took the link made this call of the sequence
+    if (!failed()) note_kernel("reduce_seg_with_peer_exchange");
     return;
   }
-  plast_b200_peer_all_reduce(g, (float *)output->data, 1, op);
+  if (failed()) {
+    keep_sequence_after_local_failure(g, output, op);
+    return;
+  }
+  launch_exchange(g, (float *)output->data, 1, op);
+  note_kernel("peer_all_reduce");
+  end_call();
 }
 
 // Cross-entropy mean over row-sharded logits: this rank's rows go through the streaming
@@ -288,10 +301,13 @@ void plast_b200_peer_cross_entropy_mean(PlastPeerGroup *g, const Tensor *logits,
   const u64 local_rows = logits->shape[0];
   bool fused = false;
   if (local_rows > 0) {
-    arm_peer_link(g->link_dev, (float)global_rows);
+    arm_peer_link(g->link_dev, kPeerCrossEntropy, (float)global_rows);
     cross_entropy_cuda_forward(ins, output, none);
     fused = disarm_peer_link();
-    if (plast_b200_last_error() != PLAST_B200_OK) return;
+    if (failed()) {
+      if (!fused) keep_sequence_after_local_failure(g, output, PLAST_B200_PEER_SUM);
+      return;
+    }
   } else {
     fill32(output->data, 0u, 1); // an empty shard contributes a zero sum
   }
@@ -303,8 +319,7 @@ void plast_b200_peer_cross_entropy_mean(PlastPeerGroup *g, const Tensor *logits,
     scale_one_kernel<<<1, 1, 0, stream()>>>((float *)output->data, (float)local_rows); // mean -> sum
     count_launch();
   }
-  plast_b200_peer_all_reduce(g, (float *)output->data, 1, PLAST_B200_PEER_SUM);
-  if (plast_b200_last_error() != PLAST_B200_OK) return;
+  launch_exchange(g, (float *)output->data, 1, PLAST_B200_PEER_SUM);
   scale_one_kernel<<<1, 1, 0, stream()>>>((float *)output->data, 1.0f / (float)global_rows);
   count_launch();
   end_call();

@@ -67,12 +67,15 @@ __device__ __forceinline__ float peer_exchange_scalar(const PeerLink &link, floa
 }
 #endif
 
-// Host side (runtime.cu): a reduction entry point called between arm and disarm hands the link
-// (a device pointer) to the first eligible launch (a segmented reduction with a single output, the
-// streaming cross-entropy kernel); disarm tells whether that happened. global_count: what a kernel
-// that ends in a mean divides the exchanged sum by.
-void arm_peer_link(const PeerLink *device_link, float global_count);
-bool take_peer_link(const PeerLink **out, float *global_count); // true once per armed link
+// Host side (runtime.cu): an entry point called between arm and disarm hands the link (a device
+// pointer) to the first launch of the kind it was armed FOR: the single-output segmented reduction
+// of a full reduce, or the streaming cross-entropy kernel (which divides the exchanged sum by
+// global_count). A launch of the other kind never takes it: the row-loss reduction behind the
+// cross-entropy fallback kernels would otherwise exchange a sum and divide it by the LOCAL row
+// count. disarm tells whether a launch took the link.
+enum PeerConsumer { kPeerFullReduce = 0, kPeerCrossEntropy = 1 };
+void arm_peer_link(const PeerLink *device_link, PeerConsumer consumer, float global_count);
+bool take_peer_link(PeerConsumer consumer, const PeerLink **out, float *global_count); // true once per armed link
 bool disarm_peer_link();                                        // returns whether a launch took it
 
 } // namespace pb

@@ -9,14 +9,6 @@
 
 namespace pb {
 
-bool stream_reductions_enabled() {
-  static const bool on = [] {
-    const char *e = getenv("PLAST_B200_STREAM");
-    return e && e[0] == '1';
-  }();
-  return on;
-}
-
 static u64 ceil_div(u64 a, u64 b) { return (a + b - 1) / b; }
 static int log2_ceil(u64 v) {
   int l = 0;
@@ -25,8 +17,7 @@ static int log2_ceil(u64 v) {
 }
 
 bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int nin,
-                          size_t elem_bytes, bool indexed, const RedOccupancy &occ, bool allow_stream,
-                          RedGeometry *g) {
+                          size_t elem_bytes, bool indexed, const RedOccupancy &occ, RedGeometry *g) {
   // Vector width along dim 0 (same rule as the elementwise engine, inputs only).
   g->vec = 1;
   g->vec_mask = 0;
@@ -81,17 +72,6 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
   g->splits = 1;
   g->seg_len = g->nsplit0 = g->nseg = g->per_chunk = 0;
   g->log_tx = 5;
-  // Streamed variant (bulk copies into a shared-memory ring): float4 inputs only; its CTAs are
-  // limited by shared memory (64 KiB each), three per SM.
-  g->stream = false;
-  g->n_streamed = 0;
-  for (int a = 0; a < nin; ++a) g->n_streamed += (g->vec_mask >> a) & 1u;
-  int streamed_pow2 = 1;
-  while (streamed_pow2 < g->n_streamed) streamed_pow2 <<= 1;
-  g->tile_items = 1024u / (unsigned)streamed_pow2;
-  g->rows_per_tile = 0;
-  const bool can_stream = allow_stream && g->vec == 4 && g->n_streamed >= 1 && g->n_streamed <= 4;
-  const u64 stream_ctas = sms * 3;
 
   if (dim0_reduced) {
     if (indexed && plan.size[0] * (g->n_red) > 0xffffffffull) {
@@ -111,9 +91,7 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
       return true;
     }
     g->kind = kRedSeg;
-    // stream when a segment is at least 1 KiB (bulk copies of a few bytes would only add latency)
-    g->stream = can_stream && g->len0_items >= 64;
-    const u64 seg_cap = g->stream ? (u64)g->tile_items : (u64)kRedThreads * (nin == 1 ? 8 : 4);
+    const u64 seg_cap = (u64)kRedThreads * (nin == 1 ? 8 : 4);
     if (g->len0_items <= seg_cap) {
       // whole runs as segments: a row-worker of ~1/16 of the run's items walks it in several
       // full load batches; the other row-workers of the CTA take the next runs
@@ -123,20 +101,18 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
       if (g->log_tx < 5 && g->len0_items >= 32) g->log_tx = 5;
       if (g->log_tx > 8) g->log_tx = 8;
     } else {
-      // one trip of the load batch (or one stage of the ring) per segment
+      // one trip of the load batch per segment
       g->seg_len = seg_cap;
       g->nsplit0 = ceil_div(g->len0_items, g->seg_len);
       g->log_tx = 8;
     }
-    if (g->stream) g->log_tx = 8; // the whole CTA consumes one segment at a time
     g->nseg = g->nsplit0 * g->n_red;
     const u64 ty_n = (u64)kRedThreads >> g->log_tx;
     // a chunk should give every row-worker >= 2 segments and move >= ~64 KiB
     u64 min_per = ty_n * 2;
     const u64 seg_bytes = g->seg_len * vec * sizeof(float);
     if (min_per * seg_bytes < (64u << 10)) min_per = ceil_div(64u << 10, seg_bytes);
-    if (g->stream) min_per = 2 * 4; // at least two rounds of the four-stage ring
-    u64 splits = ceil_div(g->stream ? stream_ctas : target_ctas, g->n_kept);
+    u64 splits = ceil_div(target_ctas, g->n_kept);
     const u64 max_splits = g->nseg / min_per > 0 ? g->nseg / min_per : 1;
     if (splits > max_splits) splits = max_splits;
     if (splits > 1 && (g->n_kept > kCounters ||
@@ -158,13 +134,10 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
     const u64 tx_n = (u64)1 << g->log_tx, ty_n = (u64)kRedThreads >> g->log_tx;
     const u64 strips = ceil_div(g->len0_items, tx_n);
     const u64 tiles = g->n_kept * strips;
-    g->stream = can_stream && g->n_red_dims <= 1 && g->n_red >= 16;
-    g->rows_per_tile = g->tile_items >> g->log_tx;
     // four CTAs' worth of work per SM measured best for the column sweep
-    u64 splits = ceil_div(g->stream ? stream_ctas : sms * 4, tiles);
-    // every row-worker of a chunk should get at least two full load batches (streamed: two
-    // rounds of the ring)
-    const u64 min_per = g->stream ? (u64)g->rows_per_tile * 8 : ty_n * 4 * 2;
+    u64 splits = ceil_div(sms * 4, tiles);
+    // every row-worker of a chunk should get at least two full load batches
+    const u64 min_per = ty_n * 4 * 2;
     const u64 max_splits = g->n_red / min_per > 0 ? g->n_red / min_per : 1;
     if (splits > max_splits) splits = max_splits;
     if (splits > 1 && (tiles > kCounters || tiles * splits * tx_n * vec * elem_bytes >

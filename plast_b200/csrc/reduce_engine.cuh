@@ -610,12 +610,6 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
   }
 }
 
-} // namespace pb
-
-#include "reduce_stream.cuh" // streamed (bulk-copy) variants of the seg and cols kernels
-
-namespace pb {
-
 // ---- host side ----------------------------------------------------------------------------------------
 enum RedKind { kRedRows = 0, kRedSeg = 1, kRedCols = 2 };
 
@@ -636,23 +630,13 @@ struct RedGeometry {
   unsigned splits;
   int kept_dims[MAX_NDIM], n_kept_dims; // plan dim indices in each sub-space
   int red_dims[MAX_NDIM], n_red_dims;
-  // streamed (bulk-copy) variant, see reduce_stream.cuh
-  bool stream;
-  int n_streamed;
-  unsigned tile_items, rows_per_tile;
 };
 // Resident CTAs per SM of each kernel shape ([kind][vec 1,2,4]), from the occupancy calculator.
 struct RedOccupancy {
   int ctas_per_sm[3][3];
 };
 bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int nin,
-                          size_t elem_bytes, bool indexed, const RedOccupancy &occ, bool allow_stream,
-                          RedGeometry *g);
-
-// PLAST_B200_STREAM=1 in the environment routes eligible reductions through the bulk-copy kernels
-// of reduce_stream.cuh (an A/B switch; the register-staged kernels measured faster on B200 and
-// are the default).
-bool stream_reductions_enabled();
+                          size_t elem_bytes, bool indexed, const RedOccupancy &occ, RedGeometry *g);
 
 template <class Op, class Pro, int NIN> const RedOccupancy &reduce_occupancy() {
   static RedOccupancy occ = [] {
@@ -687,7 +671,7 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   const void *ptrs[NIN];
   for (int a = 0; a < NIN; ++a) ptrs[a] = ins[a];
   if (!plan_reduce_geometry(plan, ptrs, NIN, sizeof(typename Op::T), Op::kIndexed,
-                            reduce_occupancy<Op, Pro, NIN>(), stream_reductions_enabled(), &g))
+                            reduce_occupancy<Op, Pro, NIN>(), &g))
     return;
 
   // Several reduced dims around long contiguous runs (N, H, W of an NCHW channel gradient) with
@@ -761,46 +745,16 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   p.partials = nullptr;
   p.peer = nullptr;
   // a pending cross-GPU exchange rides on the kernel whose last CTA holds THE final value
-  if (Op::kPeerOp >= 0 && g.kind == kRedSeg && !g.stream && g.n_kept == 1 && !take_peer_link(&p.peer, nullptr))
+  if (Op::kPeerOp >= 0 && g.kind == kRedSeg && g.n_kept == 1 && !take_peer_link(kPeerFullReduce, &p.peer, nullptr))
     p.peer = nullptr;
   Workspace ws = {};
-  if (g.splits > 1 || g.stream) {
+  if (g.splits > 1) {
     if (!get_workspace(&ws)) return;
     p.counters = ws.counters;
     p.partials = ws.partials;
   }
   cudaStream_t s = stream();
   dim3 grid((unsigned)g.grid), block(kRedThreads);
-  if (g.stream) {
-    StreamParams<NIN> sp;
-    int next = 0;
-    for (int a = 0; a < NIN; ++a) sp.slot[a] = ((g.vec_mask >> a) & 1u) ? next++ : -1;
-    sp.n_streamed = g.n_streamed;
-    sp.tile_items = g.tile_items;
-    sp.rows_per_tile = g.rows_per_tile;
-    sp.gave_up = ws.gave_up;
-    // dynamic shared memory beyond 48 KiB has to be opted into once per kernel
-    static bool seg_ready = false, cols_ready = false;
-    if (g.kind == kRedSeg) {
-      if (!seg_ready) {
-        PB_CUDA(cudaFuncSetAttribute(reduce_seg_stream_kernel<Op, Pro, NIN>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStreamSmemBytes));
-        seg_ready = true;
-      }
-      reduce_seg_stream_kernel<Op, Pro, NIN><<<grid, block, kStreamSmemBytes, s>>>(p, sp, pro);
-      note_kernel("reduce_seg_stream");
-    } else {
-      if (!cols_ready) {
-        PB_CUDA(cudaFuncSetAttribute(reduce_cols_stream_kernel<Op, Pro, NIN>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kStreamSmemBytes));
-        cols_ready = true;
-      }
-      reduce_cols_stream_kernel<Op, Pro, NIN><<<grid, block, kStreamSmemBytes, s>>>(p, sp, pro);
-      note_kernel("reduce_cols_stream");
-    }
-    count_launch();
-    return;
-  }
 #define PB_RED_LAUNCH(KERNEL)                                                                      \
   do {                                                                                             \
     if (g.vec == 4) KERNEL<Op, Pro, NIN, 4><<<grid, block, 0, s>>>(p, pro);                        \

@@ -20,7 +20,6 @@ std::atomic<unsigned long long> g_launches{0};
 constexpr int kMaxDevices = 64;
 std::mutex g_ws_mutex;
 Workspace g_ws[kMaxDevices] = {};
-volatile unsigned int *g_gave_up_host[kMaxDevices] = {};
 int g_sm_count[kMaxDevices] = {};
 } // namespace
 
@@ -28,15 +27,17 @@ namespace {
 thread_local const PeerLink *t_link = nullptr;
 thread_local float t_link_count = 0.0f;
 thread_local bool t_link_armed = false, t_link_taken = false;
+thread_local PeerConsumer t_link_consumer = kPeerFullReduce;
 } // namespace
-void arm_peer_link(const PeerLink *device_link, float global_count) {
+void arm_peer_link(const PeerLink *device_link, PeerConsumer consumer, float global_count) {
   t_link = device_link;
+  t_link_consumer = consumer;
   t_link_count = global_count;
   t_link_armed = true;
   t_link_taken = false;
 }
-bool take_peer_link(const PeerLink **out, float *global_count) {
-  if (!t_link_armed || t_link_taken) return false;
+bool take_peer_link(PeerConsumer consumer, const PeerLink **out, float *global_count) {
+  if (!t_link_armed || t_link_taken || consumer != t_link_consumer) return false;
   *out = t_link;
   if (global_count) *global_count = t_link_count;
   t_link_taken = true;
@@ -113,35 +114,8 @@ bool get_workspace(Workspace *ws) {
       set_error(PLAST_B200_ERR_CUDA, "workspace memset failed: %s", cudaGetErrorString(e));
       return false;
     }
-    // one pinned, device-visible word: kernels with bounded waits report a give-up through it
-    void *flag = nullptr;
-    e = cudaHostAlloc(&flag, sizeof(unsigned int), cudaHostAllocMapped);
-    if (e != cudaSuccess) {
-      cudaFree(p);
-      set_error(PLAST_B200_ERR_CUDA, "workspace flag allocation failed: %s", cudaGetErrorString(e));
-      return false;
-    }
-    *(volatile unsigned int *)flag = 0;
-    void *flag_dev = nullptr;
-    e = cudaHostGetDevicePointer(&flag_dev, flag, 0);
-    if (e != cudaSuccess) {
-      cudaFreeHost(flag);
-      cudaFree(p);
-      set_error(PLAST_B200_ERR_CUDA, "workspace flag mapping failed: %s", cudaGetErrorString(e));
-      return false;
-    }
-    g_gave_up_host[dev] = (volatile unsigned int *)flag;
-    g_ws[dev].gave_up = (unsigned int *)flag_dev;
     g_ws[dev].counters = (unsigned int *)p;
     g_ws[dev].partials = (float *)((char *)p + kCounters * sizeof(unsigned int));
-  }
-  if (g_gave_up_host[dev] && *g_gave_up_host[dev]) {
-    // A streamed reduction of an EARLIER call stopped waiting for its bulk copies: its output is
-    // not valid. Report it on this call (the earliest point the host looks) and re-arm.
-    *g_gave_up_host[dev] = 0;
-    cudaMemsetAsync(g_ws[dev].counters, 0, kCounters * sizeof(unsigned int), stream());
-    set_error(PLAST_B200_ERR_CUDA, "an earlier reduction kernel gave up waiting for its bulk copies");
-    return false;
   }
   *ws = g_ws[dev];
   return true;
@@ -187,8 +161,6 @@ void plast_b200_release_workspace(void) {
     if (pb::g_ws[d].counters) {
       cudaSetDevice(d);
       cudaFree(pb::g_ws[d].counters);
-      if (pb::g_gave_up_host[d]) cudaFreeHost((void *)pb::g_gave_up_host[d]);
-      pb::g_gave_up_host[d] = nullptr;
       pb::g_ws[d] = pb::Workspace{};
     }
   }

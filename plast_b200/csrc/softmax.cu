@@ -553,7 +553,7 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
     if (!get_workspace(&ws)) return;
     const PeerLink *link = nullptr;
     float global_count = 0.0f;
-    if (!take_peer_link(&link, &global_count)) link = nullptr;
+    if (!take_peer_link(kPeerCrossEntropy, &link, &global_count)) link = nullptr;
     cross_entropy_rows_kernel<<<(unsigned)ce_grid, kSmThreads, 0, s>>>(xd, labels, g, y, ws.counters, ws.partials, link,
                                                                       global_count);
     count_launch();

@@ -80,8 +80,9 @@ class PeerGroup:
 
     def all_reduce(self, t, op: str = "sum"):
         """In place on a contiguous float32 CUDA tensor of at most MAX_FLOATS elements."""
-        assert t.is_contiguous() and t.numel() <= self.MAX_FLOATS
+        assert t.is_contiguous() and t.numel() <= self.MAX_FLOATS and str(t.dtype) == "torch.float32"
         self._pb.lib.plast_b200_peer_all_reduce(self._g, self._C.c_void_p(t.data_ptr()), t.numel(), self.OPS[op])
+        self._pb.check_error()
         return t
 
     def full_reduce(self, t, out, op: str = "sum"):
@@ -92,6 +93,7 @@ class PeerGroup:
         fn.argtypes = [C.c_void_p, C.c_int, C.POINTER(self._pb.CTensor), C.POINTER(self._pb.CTensor)]
         fn.restype = None
         fn(self._g, self.OPS[op], C.byref(t.c), C.byref(out.c))
+        self._pb.check_error()
         return out
 
     def cross_entropy_mean(self, logits, labels, out, global_rows: int):
@@ -103,6 +105,7 @@ class PeerGroup:
         fn.argtypes = [C.c_void_p, T, T, T, C.c_uint64]
         fn.restype = None
         fn(self._g, C.byref(logits.c), C.byref(labels.c), C.byref(out.c), global_rows)
+        self._pb.check_error()
         return out
 
     def status(self) -> int:

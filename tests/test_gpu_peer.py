@@ -125,6 +125,67 @@ def test_cross_entropy_mean_with_the_exchange_inside_the_loss_kernel(cuda):
     lib.plast_b200_peer_group_release(g)
 
 
+def test_cross_entropy_mean_fallback_layouts_divide_by_the_global_count(cuda):
+    """Layouts the streaming kernel does not take (cols % 4 != 0, a logits pointer that is not
+    16-byte aligned) write per-row losses and take their mean with a segmented full reduce once
+    there are more than 1024 local rows. That reduce must NOT pick up the link armed for the
+    cross-entropy kernel: it would exchange the sum and divide by the local row count."""
+    lib = _lib()
+    T = C.POINTER(pb.CTensor)
+    lib.plast_b200_peer_cross_entropy_mean.argtypes = [C.c_void_p, T, T, T, C.c_uint64]
+    lib.plast_b200_peer_cross_entropy_mean.restype = None
+    g = lib.plast_b200_peer_group_local(1, 1000)
+    pb.check_error()
+    rows = 4096
+    lab = np.random.RandomState(7).randint(0, 1000, size=rows).astype(np.int32)
+    tl = cuda.tensor(lab)
+    X = rand_normal(11, (rows, 1000), std=2.0)                            # cols % 4 == 0 but see below
+    X3 = rand_normal(12, (rows, 1003), std=2.0)                           # cols % 4 != 0
+    cases = [("odd columns", cuda.tensor(X3))]
+    # a misaligned logits pointer: the matrix starts one float into its allocation
+    base = cuda.empty((rows * 1000 + 4,))
+    base.copy_from(np.concatenate([np.zeros(1, np.float32), X.ravel(), np.zeros(3, np.float32)]))
+    shifted = pb.Tensor.wrap_pointer(base.c.data + 4, (rows, 1000), owner=base)
+    cases.append(("misaligned pointer", shifted))
+    for what, tx in cases:
+        want = cuda.empty((1,)); cuda.forward("cross_entropy", [tx, tl], want)
+        assert pb.last_kernel() != "cross_entropy_rows", what
+        got = cuda.empty((1,))
+        lib.plast_b200_peer_cross_entropy_mean(g, C.byref(tx.c), C.byref(tl.c), C.byref(got.c), rows)
+        pb.check_error()
+        np.testing.assert_allclose(got.numpy()[0], want.numpy()[0], rtol=1e-6, err_msg=what)
+        lib.plast_b200_peer_cross_entropy_mean(g, C.byref(tx.c), C.byref(tl.c), C.byref(got.c), 4 * rows)
+        pb.check_error()
+        np.testing.assert_allclose(got.numpy()[0], want.numpy()[0] / 4, rtol=1e-6, err_msg=what)
+    assert lib.plast_b200_peer_group_status(g) == 0
+    lib.plast_b200_peer_group_release(g)
+
+
+def test_a_local_failure_still_makes_its_call_of_the_exchange_sequence(cuda):
+    """A rank whose local kernel cannot run (here: labels of the wrong dtype) still advances the
+    sequence counter, so later exchanges of the group do not wait for a packet that never comes,
+    and the group's status word says that this exchange carried an invalid value."""
+    lib = _lib()
+    T = C.POINTER(pb.CTensor)
+    lib.plast_b200_peer_cross_entropy_mean.argtypes = [C.c_void_p, T, T, T, C.c_uint64]
+    lib.plast_b200_peer_cross_entropy_mean.restype = None
+    g = lib.plast_b200_peer_group_local(1, 1000)
+    pb.check_error()
+    X = rand_normal(5, (64, 4096))
+    tx, bad_labels, out = cuda.tensor(X), cuda.tensor(np.zeros(64, np.float32)), cuda.empty((1,))
+    lib.plast_b200_peer_cross_entropy_mean(g, C.byref(tx.c), C.byref(bad_labels.c), C.byref(out.c), 64)
+    assert pb.lib.plast_b200_last_error() == 1                            # DTYPE: reported to the caller
+    pb.lib.plast_b200_clear_error()
+    assert lib.plast_b200_peer_group_status(g) == 0x100                   # ... and on the group
+    lib.plast_b200_peer_group_clear_status(g)
+    x = rand_normal(6, (16,))
+    t = cuda.tensor(x)
+    lib.plast_b200_peer_all_reduce(g, t.c.data, 16, 0)                    # the sequence is intact
+    pb.check_error()
+    assert lib.plast_b200_peer_group_status(g) == 0 and np.array_equal(t.numpy(), x)
+    lib.plast_b200_peer_group_release(g)
+
+
 def _gpu_count():
     try:
         out = subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True, timeout=30).stdout

@@ -33,6 +33,18 @@ def test_matches_the_allocating_entry_point_twice_in_a_row(cuda, rows, cols):
         assert_sum_close(got, A.astype(np.float64).sum(axis=0), scale, what="vs fp64")
 
 
+def test_no_rows_gives_zeros_like_the_allocating_entry_point(cuda):
+    """[0, cols]: nothing to add, every column sum is 0; the output must be written, not left stale."""
+    A = np.zeros((0, 8), np.float32)
+    out = cuda.empty((8,))
+    out.copy_from(np.full(8, 7.0, np.float32))            # stale contents that must disappear
+    cuda.forward("sum_axis0_noalloc", [cuda.tensor(A)], out, dim=0)
+    want = cuda.empty((8,))
+    want.copy_from(np.full(8, 7.0, np.float32))
+    cuda.forward("sum", [cuda.tensor(A)], want, dim=0)
+    assert np.array_equal(out.numpy(), want.numpy()) and np.all(out.numpy() == 0.0)
+
+
 def test_keepdim_and_reproducibility(cuda):
     A = rand_normal(2, (3000, 2048))
     a, shape = column_sums(cuda, A, keepdim=1)
