@@ -531,16 +531,18 @@ void oracle_adamw_step(float *data, const float *grad, float *m_data, float *v_d
 }
 
 /* ---- backward pieces of the fused GEMM epilogues ---------------------------------------------------
- * src/kernels/cuda/matmul_relu.cu:137-144 (the only definition: these kernels have no CPU twin) */
+ * src/kernels/cpu/fused_ops.c:105-109 (relu_grad_modulate_contig_kernel; its CUDA twin is
+ * src/kernels/cuda/matmul_relu.cu:137-144). Pinned by tests/golden/epilogue_pieces.npz, recorded
+ * through the reference's matmul_bias_relu_cpu_backward. */
 void oracle_relu_grad_modulate(const float *dout, const float *out_data, float *dc, u64 n, float alpha) {
   for (u64 i = 0; i < n; ++i) {
     float o = out_data[i];
     dc[i] = dout[i] * (o > 0.0f ? 1.0f : alpha);
   }
 }
-/* src/kernels/cuda/matmul_bias_relu.cu:143-151 after the cudaMemset of line 220: dbias[i % cols]
- * receives every dc_mod[i]; the reference's order of additions is whatever the atomics give, here
- * rows are added in order. */
+/* src/kernels/cpu/fused_ops.c:288-299: dbias is zeroed, then every dc_mod[row][col] is added to
+ * dbias[col], rows in order (the CUDA twin, src/kernels/cuda/matmul_bias_relu.cu:143-151, adds in
+ * whatever order its atomics give). */
 void oracle_bias_grad_reduce(const float *dc_mod, float *dbias, u64 num_elements, u64 cols) {
   for (u64 c = 0; c < cols; ++c) dbias[c] = 0.0f;
   for (u64 i = 0; i < num_elements; ++i) dbias[i % cols] += dc_mod[i];

@@ -182,10 +182,22 @@ def global_argmax(dist, torch, local_value, local_index, index_offset: int):
 
 
 # ---- benchmark of the sharded reductions (rank-parallel, CUDA) -------------------------------------
-def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 10):
+def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 10, deadline=None):
     """Strong-scaling rows: the FIXED tensors of configs 3, 4 and 5 are split across ranks along
     their outermost dim; a step is the local kernel, followed by the all-reduce where the op needs
-    one (names ending in +allreduce), timed with CUDA events, max over ranks."""
+    one (names ending in +allreduce), timed with CUDA events, max over ranks.
+
+    Rows that use the library's own NVLink exchange (+peer_exchange, _fused_with_exchange) are
+    first VERIFIED, outside the timed region: their result is compared with the process group's
+    all-reduce of the same per-rank partials (bitwise for max; for sums |a - b| <= 1e-5 * the
+    all-reduced sum of |terms|, since the two add the ranks in different orders) and the row
+    carries "verified" and the exchange's status word.
+
+    deadline (time.monotonic() value): checked between rows, agreed on by all ranks through the
+    process group; rows past it are listed as skipped, so no rank leaves while another is still
+    inside an exchange."""
+    import time
+
     import numpy as np
 
     world = dist.get_world_size() if dist.is_initialized() else 1
@@ -199,7 +211,17 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
 
     import ctypes as C
 
-    def timeit(name, fn, total_bytes):
+    def out_of_time():
+        late = torch.tensor([1.0 if (deadline is not None and time.monotonic() > deadline) else 0.0], device=dev)
+        if world > 1:
+            dist.all_reduce(late, op=dist.ReduceOp.MAX)
+        return float(late.item()) > 0
+
+    def timeit(name, fn, total_bytes, check=None):
+        if out_of_time():
+            rows.append({"op": name, "n_gpus": world, "skipped": "time limit of the table reached"})
+            return
+        checked = check() if check is not None else {}
         for _ in range(3):
             fn()
         torch.cuda.synchronize()
@@ -221,6 +243,7 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
         gbs = total_bytes / (ms * 1e-3) / 1e9
         row = {"op": name, "n_gpus": world, "ms": round(ms, 5), "GBps": round(gbs, 1),
                "frac_of_measured_aggregate": round(gbs / (peak_gbs * world), 4)}
+        row.update(checked)
         # Steps of a few microseconds are bound by the host's call cost when issued one by one; the
         # same 20 steps recorded in a CUDA graph and replayed show what the GPUs and the links need.
         # Every rank must take the same path, so a failure anywhere sends all ranks to the row above.
@@ -286,11 +309,42 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
         pb.forward("sum", [tX], tcol, dim=0, check=False)
         all_reduce_sum(dist, col)
 
+    def verify(run, result, local, op, abs_terms=None):
+        """run(): the step under test, leaves its answer in `result`. local(): leaves THIS rank's
+        partial in `result` (no exchange). The expected answer is the process group's all-reduce of
+        the partials. Returns the fields the row carries."""
+        def check():
+            if peer is None:
+                return {}
+            peer_ok = {"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX}[op]
+            local(); torch.cuda.synchronize()
+            expect = result.clone()
+            dist.all_reduce(expect, op=peer_ok)
+            run(); torch.cuda.synchronize()
+            got = result.clone()
+            if op == "max":
+                ok = bool(torch.equal(got, expect))
+                worst = 0.0 if ok else 1e30
+            else:
+                scale = abs_terms().clone()
+                dist.all_reduce(scale, op=dist.ReduceOp.SUM)
+                worst = float(((got.double() - expect.double()).abs() / (1e-5 * scale.double() + 1e-30)).max().item())
+                ok = worst <= 1.0
+            flag = torch.tensor([1.0 if ok else 0.0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)          # verified only if every rank agrees
+            return {"verified": bool(flag.item() > 0), "max_err_over_bound": round(worst, 4), "peer_status": peer.status()}
+        return check
+
+    def local_full(op):
+        return lambda: pb.forward(op, [tX], tone, dim=pb.FULL_REDUCE, check=False)
+
+    abs_all = lambda: X.abs().sum().reshape(1)
+    abs_cols = lambda: X.abs().sum(dim=0)
+    peer = None
     timeit("config4_full_sum+allreduce", full_sum, M * M * 4 + 4)
     timeit("config4_full_max+allreduce", full_max, M * M * 4 + 4)
     timeit("config4_sum_axis0+allreduce", sum_axis0, (M * M + M) * 4)
     # the same three with the library's own NVLink exchange instead of the process group's all-reduce
-    peer = None
     if world > 1 and world <= 8:
         try:
             peer = PeerGroup(dist, torch, pb)
@@ -298,13 +352,19 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
             rows.append({"op": "peer_exchange_unavailable", "n_gpus": world, "error": str(exc)[:200]})
     if peer is not None:
         use_peer_exchange(peer)
-        timeit("config4_full_sum+peer_exchange", full_sum, M * M * 4 + 4)
-        timeit("config4_full_max+peer_exchange", full_max, M * M * 4 + 4)
-        timeit("config4_sum_axis0+peer_exchange", sum_axis0, (M * M + M) * 4)
+        timeit("config4_full_sum+peer_exchange", full_sum, M * M * 4 + 4,
+               verify(full_sum, one, local_full("sum"), "sum", abs_all))
+        timeit("config4_full_max+peer_exchange", full_max, M * M * 4 + 4, verify(full_max, one, local_full("max"), "max"))
+        timeit("config4_sum_axis0+peer_exchange", sum_axis0, (M * M + M) * 4,
+               verify(sum_axis0, col, lambda: pb.forward("sum", [tX], tcol, dim=0, check=False), "sum", abs_cols))
         use_peer_exchange(None)
         # ... and with the exchange inside the reduction kernel (one launch per step)
-        timeit("config4_full_sum_fused_with_exchange", lambda: peer.full_reduce(tX, tone, "sum"), M * M * 4 + 4)
-        timeit("config4_full_max_fused_with_exchange", lambda: peer.full_reduce(tX, tone, "max"), M * M * 4 + 4)
+        fused_sum = lambda: peer.full_reduce(tX, tone, "sum")
+        fused_max = lambda: peer.full_reduce(tX, tone, "max")
+        timeit("config4_full_sum_fused_with_exchange", fused_sum, M * M * 4 + 4,
+               verify(fused_sum, one, local_full("sum"), "sum", abs_all))
+        timeit("config4_full_max_fused_with_exchange", fused_max, M * M * 4 + 4,
+               verify(fused_max, one, local_full("max"), "max"))
     del X
 
     # config 3: cross-entropy mean over row-sharded logits -> 4-byte all-reduce of the loss SUM
@@ -322,13 +382,22 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
         loss.mul_(float(sh.count))                                   # back to the local sum
         global_mean(dist, loss, R)
 
+    def ce_local_share():
+        # this rank's share of the global mean: local loss sum / global row count
+        pb.forward("cross_entropy", [tL, tl], tloss, check=False)
+        loss.mul_(float(sh.count) / float(R))
+
+    # per-row losses are positive, so sum|terms| of the mean is the mean itself
+    ce_terms = lambda: (ce_local_share(), loss.clone())[1]
     timeit("config3_cross_entropy_mean+allreduce", ce_mean, (R * Cn + R) * 4 + 4)
     if peer is not None:
         use_peer_exchange(peer)
-        timeit("config3_cross_entropy_mean+peer_exchange", ce_mean, (R * Cn + R) * 4 + 4)
+        timeit("config3_cross_entropy_mean+peer_exchange", ce_mean, (R * Cn + R) * 4 + 4,
+               verify(ce_mean, loss, ce_local_share, "sum", ce_terms))
         use_peer_exchange(None)
-        timeit("config3_cross_entropy_mean_fused_with_exchange",
-               lambda: peer.cross_entropy_mean(tL, tl, tloss, R), (R * Cn + R) * 4 + 4)
+        ce_fused = lambda: peer.cross_entropy_mean(tL, tl, tloss, R)
+        timeit("config3_cross_entropy_mean_fused_with_exchange", ce_fused, (R * Cn + R) * 4 + 4,
+               verify(ce_fused, loss, ce_local_share, "sum", ce_terms))
     # row ops of config 3 on the same row shard: independent per row, no collective
     rs, Y = torch.empty(sh.count, device=dev), torch.empty_like(L)
     trs, tY = wrap(rs), wrap(Y)
@@ -361,10 +430,19 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
         pb.backward("scale_bias_leaky_relu", [tX5, tS, tBg], tYg, fval=0.0, check=False)
         all_reduce_sum(dist, gB)
 
+    def bias_grad_local():
+        gB.zero_()
+        pb.backward("scale_bias_leaky_relu", [tX5, tS, tBg], tYg, fval=0.0, check=False)
+
+    def bias_terms():
+        pb.forward("scale_bias_leaky_relu", [tX5, tS, tB], tY5, fval=0.0, check=False)
+        return (G.abs() * (Yv > 0)).sum(dim=(0, 2, 3)).reshape(1, Ch, 1, 1)
+
     timeit("config5_bias_grad+allreduce", bias_grad, 2 * total * 4 + 1024)
     if peer is not None:
         use_peer_exchange(peer)
-        timeit("config5_bias_grad+peer_exchange", bias_grad, 2 * total * 4 + 1024)
+        timeit("config5_bias_grad+peer_exchange", bias_grad, 2 * total * 4 + 1024,
+               verify(bias_grad, gB, bias_grad_local, "sum", bias_terms))
         use_peer_exchange(None)
         status = peer.status()
         if status != 0:

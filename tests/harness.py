@@ -147,6 +147,53 @@ class OracleRecipes:
         return z
 
 
+def cpu_recipe_graph(be, mode, X, G=None, labels=None):
+    """Forward AND backward of softmax / log_softmax / cross_entropy as the op sequence plast builds
+    from primitives (plast/nn/functional.py:77-86, 89-97, 312-333, 391-396), every node run through
+    the CPU entry points of `be` in graph order and its backward in reverse order
+    (src/core/graph.c:57-65; kernels: src/kernels/cpu/reduce_ops.c:90-262,
+    include/kernels/kernel_macros.h:273-325). X is [rows, cols], the axis is 1.
+    Returns (forward result, d/dX): G is the upstream gradient of softmax / log_softmax; the
+    cross-entropy mean is seeded with 1 (what backward() does, src/core/tensor.c:143-152)."""
+    R, Cn = X.shape
+    x = be.tensor(X, requires_grad=True)
+    m = be.empty((R, 1), requires_grad=True); be.forward("max", [x], m, dim=1, keepdim=1)
+    sh = be.empty((R, Cn), requires_grad=True); be.forward("sub", [x, m], sh)
+    e = be.empty((R, Cn), requires_grad=True); be.forward("exp", [sh], e)
+    s = be.empty((R, 1), requires_grad=True); be.forward("sum", [e], s, dim=1, keepdim=1)
+
+    def head_backward():
+        be.backward("sum", [e], s, dim=1, keepdim=1); be.backward("exp", [sh], e)
+        be.backward("sub", [x, m], sh); be.backward("max", [x], m, dim=1, keepdim=1)
+
+    if mode == "softmax":
+        y = be.empty((R, Cn), requires_grad=True); be.forward("div", [e, s], y)
+        y.grad.copy_from(G)
+        be.backward("div", [e, s], y)
+        head_backward()
+        return y.numpy(), x.grad.numpy()
+    ls = be.empty((R, 1), requires_grad=True); be.forward("log", [s], ls)
+    y = be.empty((R, Cn), requires_grad=True); be.forward("sub", [sh, ls], y)
+    if mode == "log_softmax":
+        y.grad.copy_from(G)
+        be.backward("sub", [sh, ls], y); be.backward("log", [s], ls)
+        head_backward()
+        return y.numpy(), x.grad.numpy()
+    assert mode == "cross_entropy"
+    onehot = np.zeros((R, Cn), np.float32); onehot[np.arange(R), labels] = 1.0
+    oh = be.tensor(onehot)
+    prod = be.empty((R, Cn), requires_grad=True); be.forward("mul", [y, oh], prod)
+    rs = be.empty((R,), requires_grad=True); be.forward("sum", [prod], rs, dim=1)
+    ng = be.empty((R,), requires_grad=True); be.forward("neg", [rs], ng)
+    loss = be.empty((1,), requires_grad=True); be.forward("mean", [ng], loss, dim=FULL_REDUCE)
+    loss.grad.copy_from(np.ones(1, np.float32))
+    be.backward("mean", [ng], loss, dim=FULL_REDUCE); be.backward("neg", [rs], ng)
+    be.backward("sum", [prod], rs, dim=1); be.backward("mul", [y, oh], prod)
+    be.backward("sub", [sh, ls], y); be.backward("log", [s], ls)
+    head_backward()
+    return loss.numpy(), x.grad.numpy()
+
+
 # ---- comparison helpers ------------------------------------------------------------------------
 def bits(a: np.ndarray) -> np.ndarray:
     return np.ascontiguousarray(a, np.float32).view(np.uint32)

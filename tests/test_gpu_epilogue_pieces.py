@@ -45,6 +45,23 @@ def test_modulate_and_bias_grad(rows, cols, alpha):
     assert_sum_close(tbias2.numpy(), want_bias, scale, what="bias_grad_masked")
 
 
+def test_against_the_outputs_recorded_from_the_reference_backward():
+    """tests/golden/epilogue_pieces.npz holds what the reference's matmul_bias_relu_cpu_backward
+    produced on these cases (src/kernels/cpu/fused_ops.c:105-109, 288-299)."""
+    import epilogue_cases
+    from harness import GOLDEN_DIR
+    golden = np.load(GOLDEN_DIR / "epilogue_pieces.npz")
+    for i, (rows, cols, _) in enumerate(epilogue_cases.CASES):
+        dout, out, alpha = epilogue_cases.inputs(i)
+        n = rows * cols
+        td, ty, tmod, tbias = pb.Tensor.from_numpy(dout), pb.Tensor.from_numpy(out), pb.Tensor((n,)), pb.Tensor((cols,))
+        pb.lib.plast_b200_relu_grad_modulate(td.c.data, ty.c.data, tmod.c.data, n, alpha); pb.check_error()
+        assert np.array_equal(tmod.numpy().reshape(rows, cols), golden[f"case{i}/dc_mod"])
+        pb.lib.plast_b200_bias_grad_masked(td.c.data, ty.c.data, tbias.c.data, n, cols, alpha); pb.check_error()
+        scale = np.abs(golden[f"case{i}/dc_mod"]).sum(axis=0)
+        assert_sum_close(tbias.numpy(), golden[f"case{i}/dbias"], scale, what=f"case {i} bias gradient")
+
+
 def test_bad_arguments_are_reported():
     t = pb.Tensor((8,))
     pb.lib.plast_b200_bias_grad_reduce(t.c.data, t.c.data, 8, 3)

@@ -259,27 +259,51 @@ def test_cross_entropy(cuda, recipes, rows, cols):
     assert_sum_close(out.numpy(), want, np.abs(per_row).sum() / rows, what="ce mean")
 
 
-def test_softmax_family_backward(cuda):
-    rows, cols = 33, 200
+@pytest.mark.parametrize("rows,cols", [(33, 200), (16, 4096), (5, 1003)])
+def test_softmax_family_backward(cuda, oracle, rows, cols):
+    """Against the reference's OWN backward: the op sequence of plast/nn/functional.py run node by
+    node through the CPU kernels, forward and then backward in reverse (harness.cpu_recipe_graph).
+    The fused kernels evaluate the closed forms, so the bound is the fp32 accumulation bound of the
+    row sums they contain: |gpu - cpu| <= 1e-5 * sum of the |terms| that make up the element."""
+    from harness import cpu_recipe_graph
     X, G = rand_normal(0, (rows, cols)), rand_normal(1, (rows, cols))
     x64, g64 = X.astype(np.float64), G.astype(np.float64)
     p = np.exp(x64 - x64.max(1, keepdims=True)); p /= p.sum(1, keepdims=True)
-    for op, want in (("softmax", p * (g64 - (g64 * p).sum(1, keepdims=True))),
-                     ("log_softmax", g64 - p * g64.sum(1, keepdims=True))):
+    scales = {"softmax": p * (np.abs(g64) + (np.abs(g64) * p).sum(1, keepdims=True)),
+              "log_softmax": np.abs(g64) + p * np.abs(g64).sum(1, keepdims=True)}
+    # The op sequence also sends a gradient through the row maximum (sub -> max backward): the sum
+    # of the whole row's gradients, zero in exact arithmetic, lands on the argmax element with the
+    # rounding of that sum, so that element's bound carries the row's terms as well.
+    top = (np.arange(rows), X.argmax(axis=1))
+
+    def with_max_path(scale):
+        scale = scale.copy()
+        scale[top] += scale.sum(axis=1)
+        return scale
+    scales = {k: with_max_path(v) for k, v in scales.items()}
+    for op in ("softmax", "log_softmax"):
+        _, want = cpu_recipe_graph(oracle, op, X, G)
         tx = cuda.tensor(X, requires_grad=True)
         out = cuda.empty((rows, cols), requires_grad=True)
         cuda.forward(op, [tx], out, dim=1)
         out.grad.copy_from(G)
         cuda.backward(op, [tx], out, dim=1)
-        np.testing.assert_allclose(tx.grad.numpy(), want, rtol=1e-4, atol=1e-5)
+        assert_sum_close(tx.grad.numpy(), want, scales[op], what=f"{op} backward vs the op-sequence backward")
+        # and against the closed form in fp64
+        closed = p * (g64 - (g64 * p).sum(1, keepdims=True)) if op == "softmax" else g64 - p * g64.sum(1, keepdims=True)
+        assert_sum_close(tx.grad.numpy(), closed, scales[op], what=f"{op} backward vs fp64")
     labels = np.random.RandomState(2).randint(0, cols, size=rows).astype(np.int32)
+    loss_want, want = cpu_recipe_graph(oracle, "cross_entropy", X, labels=labels)
     tx = cuda.tensor(X, requires_grad=True)
     out = cuda.empty((1,), requires_grad=True)
     cuda.forward("cross_entropy", [tx, cuda.tensor(labels)], out)
+    np.testing.assert_allclose(out.numpy(), loss_want, rtol=1e-5)
     out.grad.copy_from(np.ones(1, np.float32))
     cuda.backward("cross_entropy", [tx, cuda.tensor(labels)], out)
     onehot = np.eye(cols)[labels]
-    np.testing.assert_allclose(tx.grad.numpy(), (p - onehot) / rows, rtol=1e-4, atol=1e-7)
+    ce_scale = with_max_path((p + onehot) / rows)
+    assert_sum_close(tx.grad.numpy(), want, ce_scale, what="cross-entropy backward vs the op-sequence backward")
+    assert_sum_close(tx.grad.numpy(), (p - onehot) / rows, ce_scale, what="cross-entropy backward vs fp64")
 
 
 def test_sigmoid_and_chain(cuda, recipes):
