@@ -179,6 +179,9 @@ def cpu_per_op_baselines(rows):
     smp2 = "2^24 of 2^28 elements"
     for op in ("neg", "exp", "abs"):
         fns[(2, op)] = (lambda op=op: be.forward(op, [x], t2[0]), n2 / full2, smp2)
+    fns[(2, "neg_with_reference_arena_fill")] = (lambda: (C.memset(t2[0].c.data, 0, n2 * 4), be.forward("neg", [x], t2[0])),
+                                                 n2 / full2, smp2 + ", output zero-filled first as the arena does")
+    fns[(2, "neg_with_output_fill_skipped")] = (lambda: be.forward("neg", [x], t2[0]), n2 / full2, smp2)
     fns[(2, "add_scalar")] = (lambda: be.forward("add", [x, one], t2[0]), n2 / full2, smp2)
     fns[(2, "rdiv_scalar")] = (lambda: be.forward("div", [one, x], t2[0]), n2 / full2, smp2)
     fns[(2, "mul")] = (lambda: be.forward("mul", [x, y], t2[0]), n2 / full2, smp2)
@@ -493,7 +496,7 @@ def run_ours(args):
         got = z_d[sl].cpu().numpy().astype(np.float64)
         x64, y64 = xs.astype(np.float64), ys.astype(np.float64)
         terms = np.abs(y64) / (1 + np.exp(-x64)) + np.exp(-np.abs(x64))  # z = t + e2 may cancel
-        assert (np.abs(got - want) <= 4 * 2.0 ** -23 * terms).all(), "bench: fused chain disagrees with the oracle"
+        assert (np.abs(got - want) <= 3 * 2.0 ** -23 * terms).all(), "bench: fused chain disagrees with the oracle"
 
     for _ in range(max(args.warmup, 3)):
         step()

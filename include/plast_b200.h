@@ -281,6 +281,20 @@ void transpose_backward_cuda(float *da, const float *dout, const u64 *a_shape,
 void *arena_alloc_cuda(u64 size);
 void arena_free_cuda(void *ptr);
 void arena_memset_cuda(void *ptr, int value, u64 size);
+/* Fill policy of arena_memset_cuda for the calling thread (no counterpart in the reference).
+ * The reference's arena zero-fills every allocation (src/core/arena.c:94-102): the output of a
+ * forward op is written twice (4 extra bytes per element of HBM traffic on top of the op's own
+ * 8 - 12) and a gradient twin is zeroed twice (src/core/tensor.c:82-90 calls zeros_cuda after the
+ * arena's fill). With PLAST_B200_ARENA_SKIP_FILL, arena_memset_cuda(ptr, 0, size) returns without
+ * touching memory; zeros_cuda / ones_cuda / zero_grad_cuda still fill, so gradients start at zero,
+ * filled once. The caller sets it around allocations whose first use overwrites them completely
+ * (every forward entry point of this library does) and restores PLAST_B200_ARENA_FILL afterwards;
+ * the default is the reference's behaviour. plast_b200_arena_fill_stats reports the bytes filled and
+ * the bytes skipped since the library was loaded. */
+#define PLAST_B200_ARENA_FILL 0
+#define PLAST_B200_ARENA_SKIP_FILL 1
+void plast_b200_arena_fill_policy(int policy);
+void plast_b200_arena_fill_stats(u64 *filled_bytes, u64 *skipped_bytes);
 void arena_memcpy_h2d_cuda(void *dest, const void *src, u64 size);
 void arena_memcpy_d2h_cuda(void *dest, const void *src, u64 size);
 void arena_memcpy_d2d_cuda(void *dest, const void *src, u64 size);
@@ -350,6 +364,12 @@ int plast_b200_chain_backward_source(const PlastChainStep *steps, int n_steps, i
                                      unsigned scalar_mask, int wrt, int accumulate, char *buf, size_t capacity);
 int plast_b200_chain_backward_try_compile(const PlastChainStep *steps, int n_steps, int n_inputs,
                                           unsigned scalar_mask, int wrt, int accumulate);
+/* Tuning hook: overrides one launch-geometry choice of the reductions for the whole process
+ * (key 0: log2 of the lanes across a strip of the column reduce, 1: resident CTAs per SM the
+ * column reduce plans for, 2: load batches per row-worker below which a column reduce is not split
+ * further, 3: resident CTAs per SM the segmented reduce plans for); a negative value restores the
+ * built-in choice. Results do not depend on the geometry beyond the order of additions. */
+void plast_b200_tune(int key, long value);
 /* Test hook: runs the host-side iteration planner (drop size-1 dims, order by the strides of
  * argument `sort_arg`, merge dims every argument walks as one run) on caller-supplied metadata.
  * strides / out_strides are [nargs][MAX_NDIM] row-major, outermost dim first on input; the

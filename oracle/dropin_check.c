@@ -24,6 +24,12 @@
  * library's plast_b200_fuse_graph (the call a maintainer adds after fusion_optimize in
  * src/scheduler/scheduler.c:33) and the reference's dag_forward / dag_backward: the fused DAGs
  * must have 2, 1 and 1 nodes and give the results of the node-by-node runs.
+ * (5) CUDA only: the arena's zero-fill (src/core/arena.c:94-102). The nine-node training chain runs
+ * node by node twice in an arena whose memory was dirtied first: once as the reference allocates
+ * (every allocation filled, gradients filled a second time by zeros_cuda, src/core/tensor.c:82-90)
+ * and once with the three-line caller patch this library offers: plast_b200_arena_fill_policy(SKIP)
+ * around the allocation of an op's output. Results and gradients must be the same bits, every
+ * gradient buffer must still start at zero, and the fill counters must show the outputs skipped.
  */
 #include "core/arena.h"
 #include "core/graph.h"
@@ -49,12 +55,24 @@ typedef struct {
   Arena meta, data;
   DEVICE dev;
   Scheduler *sched;
+  bool skip_output_fill;     /* (5): allocate op outputs without the arena's zero-fill */
+  Tensor *outputs[64];       /* (5): every op output allocated through node1 / node2 */
+  int n_outputs;
 } Ctx;
 
 static Tensor *mk(Ctx *c, const u64 *shape, u64 nd, bool rg) {
   u64 sh[MAX_NDIM];
   memcpy(sh, shape, nd * sizeof(u64));
   return init(&c->meta, &c->data, c->dev, FLOAT32, sh, nd, rg, NULL);
+}
+/* An op's output: its forward kernel overwrites every element, so the arena's fill is wasted on
+ * it. This is the whole caller-side patch: the policy call before and after the allocation. */
+static Tensor *mk_output(Ctx *c, const u64 *shape, u64 nd, bool rg) {
+  if (c->skip_output_fill) plast_b200_arena_fill_policy(PLAST_B200_ARENA_SKIP_FILL);
+  Tensor *t = mk(c, shape, nd, rg);
+  if (c->skip_output_fill) plast_b200_arena_fill_policy(PLAST_B200_ARENA_FILL);
+  if (c->n_outputs < 64) c->outputs[c->n_outputs++] = t;
+  return t;
 }
 static void upload(Ctx *c, void *dst, const float *src, u64 n) {
   if (c->dev == CUDA) arena_memcpy_h2d_cuda(dst, src, n * 4);
@@ -65,14 +83,14 @@ static void download(Ctx *c, float *dst, const void *src, u64 n) {
   else memcpy(dst, src, n * 4);
 }
 static Tensor *node1(Ctx *c, OP_TYPE op, Tensor *a, const u64 *shape, u64 nd, bool rg, KernelParams p) {
-  Tensor *out = mk(c, shape, nd, rg);
+  Tensor *out = mk_output(c, shape, nd, rg);
   Tensor **in = (Tensor **)arena_alloc(&c->meta, sizeof(Tensor *), 8);
   in[0] = a;
   arena_node_alloc(&c->meta, in, 1, out, get_op_impl(op), op, p);
   return out;
 }
 static Tensor *node2(Ctx *c, OP_TYPE op, Tensor *a, Tensor *b, const u64 *shape, u64 nd, bool rg) {
-  Tensor *out = mk(c, shape, nd, rg);
+  Tensor *out = mk_output(c, shape, nd, rg);
   Tensor **in = (Tensor **)arena_alloc(&c->meta, 2 * sizeof(Tensor *), 8);
   in[0] = a;
   in[1] = b;
@@ -92,6 +110,10 @@ typedef struct {
   /* the chain as a training graph: gradients of x and y, node by node and (CUDA) fused */
   float chain_dx[CH], chain_dy[CH], f_chain_dx[CH], f_chain_dy[CH];
   unsigned f_train_nodes, f_train_bwd_launches;
+  /* (5) the training chain in a dirtied arena: [0] every allocation filled, [1] op outputs unfilled */
+  float fill_z[2][CH], fill_dx[2][CH], fill_dy[2][CH];
+  int fill_grads_nonzero[2];
+  unsigned long long fill_filled[2], fill_skipped[2];
   /* config 1's fused forward DAG (2 nodes): the reference's dag_forward against one CUDA-graph replay */
   float replay_s[M];
   double us_node_by_node, us_replay;
@@ -158,8 +180,48 @@ static float frand(unsigned *st) {
   return ((float)((*st >> 8) & 0xffff) / 32768.0f - 1.0f) * 0.7317519f;
 }
 
+/* (5): see the header comment. */
+static void run_arena_fill(Results *res, const float *CX, const float *CY, const float *CG) {
+  for (int pass = 0; pass < 2; ++pass) {
+    Ctx c;
+    memset(&c, 0, sizeof(c));
+    c.dev = CUDA;
+    c.meta = arena_create(Mib(4), CPU);
+    c.data = arena_create(Mib(16), CUDA);
+    c.sched = init_scheduler(jit_create(16));
+    /* dirty the block, then hand it out again from the start */
+    Tensor *junk = mk(&c, (u64[]){Mib(3)}, 1, false);
+    ones(junk, Mib(3));
+    arena_reset(&c.data);
+    c.skip_output_fill = pass == 1;
+    u64 f0, s0, f1, s1;
+    plast_b200_arena_fill_stats(&f0, &s0);
+    Tensor *gx, *gy;
+    Tensor *gz = chain_graph_rg(&c, CX, CY, true, &gx, &gy);
+    plast_b200_arena_fill_stats(&f1, &s1);
+    res->fill_filled[pass] = f1 - f0;
+    res->fill_skipped[pass] = s1 - s0;
+    /* every gradient buffer of an op output starts at zero although its memory was dirty */
+    static float g[CH];
+    res->fill_grads_nonzero[pass] = 0;
+    for (int i = 0; i < c.n_outputs; ++i) {
+      download(&c, g, c.outputs[i]->grad->data, CH);
+      for (int j = 0; j < CH; ++j) res->fill_grads_nonzero[pass] += g[j] != 0.0f;
+    }
+    schedule(c.sched, gz->creator, FORWARD, &c.meta);
+    download(&c, res->fill_z[pass], gz->data, CH);
+    upload(&c, gz->grad->data, CG, CH);
+    schedule(c.sched, gz->creator, BACKWARD, &c.meta);
+    download(&c, res->fill_dx[pass], gx->grad->data, CH);
+    download(&c, res->fill_dy[pass], gy->grad->data, CH);
+    arena_release(&c.data);
+    arena_release(&c.meta);
+  }
+}
+
 static void run(DEVICE dev, Results *res) {
   Ctx c;
+  memset(&c, 0, sizeof(c));
   c.dev = dev;
   c.meta = arena_create(Mib(4), CPU); /* metadata always lives on the host */
   c.data = arena_create(Mib(16), dev);
@@ -297,6 +359,7 @@ static void run(DEVICE dev, Results *res) {
 
   arena_release(&c.data);
   arena_release(&c.meta);
+  if (dev == CUDA) run_arena_fill(res, CX, CY, CG);
 }
 
 static int same_bits(const char *what, const float *a, const float *b, int n) {
@@ -355,6 +418,21 @@ int main(void) {
   }
   bad += same_bits("fused: chain dx", gpu.chain_dx, gpu.f_chain_dx, CH);
   bad += same_bits("fused: chain dy", gpu.chain_dy, gpu.f_chain_dy, CH);
+  bad += same_bits("arena: chain, all filled", gpu.chain, gpu.fill_z[0], CH);
+  bad += same_bits("arena: chain, outputs unfilled", gpu.chain, gpu.fill_z[1], CH);
+  bad += same_bits("arena: dx, outputs unfilled", gpu.fill_dx[0], gpu.fill_dx[1], CH);
+  bad += same_bits("arena: dy, outputs unfilled", gpu.fill_dy[0], gpu.fill_dy[1], CH);
+  printf("arena fill, nine-node training chain of %d elements: as the reference allocates %llu bytes filled by the "
+         "arena, %llu skipped; with the caller patch %llu filled, %llu skipped; non-zero gradient words at start: %d / %d\n",
+         CH, gpu.fill_filled[0], gpu.fill_skipped[0], gpu.fill_filled[1], gpu.fill_skipped[1],
+         gpu.fill_grads_nonzero[0], gpu.fill_grads_nonzero[1]);
+  /* nine outputs, data and gradient twin each, are not filled by the arena any more */
+  if (gpu.fill_grads_nonzero[0] || gpu.fill_grads_nonzero[1] || gpu.fill_skipped[0] != 0 ||
+      gpu.fill_skipped[1] != (unsigned long long)9 * 2 * CH * 4 ||
+      gpu.fill_filled[0] != gpu.fill_filled[1] + gpu.fill_skipped[1]) {
+    printf("arena fill policy              MISMATCH\n");
+    ++bad;
+  }
   printf(bad ? "DROPIN FAILED\n" : "DROPIN OK\n");
   return bad ? 1 : 0;
 }

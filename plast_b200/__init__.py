@@ -88,7 +88,8 @@ def declared_symbols() -> list[str]:
         "plast_b200_clear_error", "plast_b200_set_stream", "plast_b200_get_stream",
         "plast_b200_set_sync", "plast_b200_launch_count", "plast_b200_last_kernel",
         "plast_b200_release_workspace", "plast_b200_version", "plast_b200_plan_debug",
-        "sum_axis0_noalloc_cuda_forward", "plast_b200_chain_source", "plast_b200_chain_try_compile",
+        "sum_axis0_noalloc_cuda_forward", "plast_b200_chain_source", "plast_b200_chain_try_compile", "plast_b200_tune",
+        "plast_b200_arena_fill_policy", "plast_b200_arena_fill_stats",
         "plast_b200_fuse_graph", "plast_b200_fusion_release", "plast_b200_fusion_program",
         "chain_cuda_forward", "chain_cuda_backward",
         "sgd_step_cuda", "adam_step_cuda", "adamw_step_cuda", "plast_b200_adam_state_release",
@@ -168,6 +169,12 @@ def _load() -> C.CDLL:
     lib.plast_b200_launch_count.restype = C.c_uint64
     lib.plast_b200_last_kernel.restype = C.c_char_p
     lib.plast_b200_version.restype = C.c_char_p
+    lib.plast_b200_arena_fill_policy.argtypes = [C.c_int]
+    lib.plast_b200_arena_fill_policy.restype = None
+    lib.plast_b200_arena_fill_stats.argtypes = [C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+    lib.plast_b200_arena_fill_stats.restype = None
+    lib.plast_b200_tune.argtypes = [C.c_int, C.c_long]
+    lib.plast_b200_tune.restype = None
     return lib
 
 

@@ -86,6 +86,8 @@ constexpr int kRowSumThreads = 256;
 __global__ void __launch_bounds__(kRowSumThreads)
 add_leaky_relu_row_sum_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ c,
                               float *__restrict__ s, u64 rows, u64 cols, u64 b_row_stride, float alpha) {
+  pdl_wait();
+  pdl_launch_dependents();
   const unsigned lane = threadIdx.x & 31;
   const u64 warps = (u64)gridDim.x * (kRowSumThreads / 32);
   const u64 nvec = cols >> 2;
@@ -420,9 +422,9 @@ void plast_b200_add_leaky_relu_row_sum(const Tensor *a, const Tensor *b, Tensor 
   u64 blocks = (rows + warps_per_cta - 1) / warps_per_cta;
   const u64 cap = (u64)sm_count() * 32;
   if (blocks > cap) blocks = cap;
-  add_leaky_relu_row_sum_kernel<<<(unsigned)blocks, kRowSumThreads, 0, stream()>>>(
-      (const float *)a->data, (const float *)b->data, (float *)c->data, (float *)s->data, rows, cols,
-      b_full ? cols : 0, slope);
+  launch_k(add_leaky_relu_row_sum_kernel, dim3((unsigned)blocks), dim3(kRowSumThreads), 0, stream(),
+           (const float *)a->data, (const float *)b->data, (float *)c->data, (float *)s->data, rows, cols,
+           b_full ? cols : (u64)0, slope);
   count_launch();
   note_kernel("add_leaky_relu_row_sum");
   end_call();

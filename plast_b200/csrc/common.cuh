@@ -56,6 +56,36 @@ bool get_workspace(Workspace *ws);
 
 int sm_count();
 
+// Geometry knobs a test or a tuning run may override (plast_b200_tune); negative = built-in choice.
+enum TuneKey { kTuneColsLogTx = 0, kTuneColsCtasPerSm = 1, kTuneColsMinBatches = 2, kTuneSegCtasPerSm = 3, kTuneKeys = 8 };
+long tuned(int key);
+
+// ---- launches ------------------------------------------------------------------------------------
+// Kernels in a stream cost ~4 us from the end of one to the start of the next, a tenth of the time a
+// 268 MB tensor needs at HBM speed. The streaming kernels of this library are therefore launched
+// with programmatic stream serialization: the grid may become resident while its predecessor in the
+// stream is still draining, and waits (pdl_wait(), the first statement of every such kernel, before
+// any global memory access) until that predecessor has completed and its writes are visible. The
+// early start hides launch latency and block scheduling only; ordering of memory is unchanged.
+// PLAST_B200_PDL=0 in the environment turns the attribute off (plain stream order).
+bool pdl_enabled();
+
+template <class... KArgs, class... Args>
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                            Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Frees the staging buffers, streams and events of the host-buffer chain (host_pipeline.cu).
 void release_host_pipeline();
 

@@ -74,8 +74,8 @@ void launch_ew_one(const IterPlan &plan, float *out, const float *const *ins, co
   do {                                                                                             \
     OffsetCalc<NIN + 1, IDX> oc;                                                                   \
     fill_offset_calc(&oc, plan, VEC);                                                              \
-    ew_kernel<F, NIN, VEC, IDX, ONED><<<grid, block, 0, s>>>(f, out, ip, oc, (IDX)n_items,        \
-                                                              vec_mask);                           \
+    launch_k(ew_kernel<F, NIN, VEC, IDX, ONED>, grid, block, 0, s, f, out, ip, oc, (IDX)n_items,  \
+             vec_mask);                                                                            \
   } while (0)
 #define PB_EW_BY_VEC(IDX, ONED)                                                                    \
   do {                                                                                             \
@@ -91,7 +91,7 @@ void launch_ew_one(const IterPlan &plan, float *out, const float *const *ins, co
       OffsetCalc<NIN + 1, uint32_t> oc;
       fill_offset_calc(&oc, plan, 4);
 #define PB_EW_MASKED(ONED, CMASK)                                                                  \
-  ew_kernel<F, NIN, 4, uint32_t, ONED, CMASK><<<grid, block, 0, s>>>(f, out, ip, oc, (uint32_t)n_items, vec_mask)
+  launch_k(ew_kernel<F, NIN, 4, uint32_t, ONED, CMASK>, grid, block, 0, s, f, out, ip, oc, (uint32_t)n_items, vec_mask)
       if (vec_mask == 1u) {
         if (c.one_d) PB_EW_MASKED(true, 1u); else PB_EW_MASKED(false, 1u);
       } else {
@@ -143,6 +143,8 @@ template <int NIN> struct TiledParams {
 template <class F, int NIN>
 __global__ void __launch_bounds__(kTileDim * kTileRows) ew_tiled_kernel(F f, TiledParams<NIN> p) {
   __shared__ float tile[NIN][kTileDim][kTileDim + 1];
+  pdl_wait();
+  pdl_launch_dependents();
   const u64 t0 = blockIdx.x % p.tiles0, tT = blockIdx.x / p.tiles0;
   u64 off[NIN + 1];
 #pragma unroll
@@ -193,6 +195,8 @@ constexpr int kTile4 = 64;
 template <class F, int NIN>
 __global__ void __launch_bounds__(256) ew_tiled4_kernel(F f, TiledParams<NIN> p) {
   extern __shared__ float tile4_smem[]; // [NIN][64][65]
+  pdl_wait();
+  pdl_launch_dependents();
   const u64 t0 = blockIdx.x % p.tiles0, tT = blockIdx.x / p.tiles0;
   u64 off[NIN + 1];
 #pragma unroll
@@ -205,50 +209,54 @@ __global__ void __launch_bounds__(256) ew_tiled4_kernel(F f, TiledParams<NIN> p)
     rest = q;
   }
   const unsigned q4 = threadIdx.x & 15, row = threadIdx.x >> 4; // 16 float4 across, 16 rows per pass
-  // phase 1: transposed inputs, float4 along dT, rows along dim 0
+  // Every load of the tile is issued before anything waits: the transposed inputs as float4 along dT
+  // (rows along dim 0), the others as float4 along dim 0 (rows along dT), 4 x NIN vectors in flight
+  // per thread and ONE trip to memory per tile instead of one per phase.
+  const u64 c0v = t0 * kTile4 + q4 * 4; // phase-2 position of this thread along dim 0
+  float4 v[4][NIN];
 #pragma unroll
   for (int a = 0; a < NIN; ++a) {
-    if (!((p.tmask >> a) & 1u)) continue;
-    float *tl = tile4_smem + (size_t)a * kTile4 * (kTile4 + 1);
-    const u64 cT = tT * kTile4 + q4 * 4;
-    float4 v[4];
+    if ((p.tmask >> a) & 1u) {
+      const u64 cT = tT * kTile4 + q4 * 4;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const u64 c0 = t0 * kTile4 + row + j * 16;
-      if (cT < p.nT && c0 < p.n0)
-        v[j] = __ldcs(reinterpret_cast<const float4 *>(p.in[a] + off[a + 1] + c0 * p.s0[a + 1] + cT));
-    }
+      for (int j = 0; j < 4; ++j) {
+        const u64 c0 = t0 * kTile4 + row + j * 16;
+        if (cT < p.nT && c0 < p.n0)
+          v[j][a] = __ldcs(reinterpret_cast<const float4 *>(p.in[a] + off[a + 1] + c0 * p.s0[a + 1] + cT));
+      }
+    } else {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float *dst = tl + (row + j * 16) * (kTile4 + 1) + q4 * 4;
-      dst[0] = v[j].x; dst[1] = v[j].y; dst[2] = v[j].z; dst[3] = v[j].w;
-    }
-  }
-  __syncthreads();
-  // phase 2: float4 along dim 0, rows along dT
-  const u64 c0 = t0 * kTile4 + q4 * 4;
-  float4 direct[4][NIN];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const u64 cT = tT * kTile4 + row + j * 16;
-    if (c0 < p.n0 && cT < p.nT) {
-#pragma unroll
-      for (int a = 0; a < NIN; ++a) {
-        if ((p.tmask >> a) & 1u) continue;
-        const float *q = p.in[a] + off[a + 1] + c0 * p.s0[a + 1] + cT * p.sT[a + 1];
-        if (p.s0[a + 1] == 1) {
-          direct[j][a] = __ldcs(reinterpret_cast<const float4 *>(q));
-        } else { // broadcast along dim 0
-          const float sc = __ldg(q);
-          direct[j][a] = make_float4(sc, sc, sc, sc);
+      for (int j = 0; j < 4; ++j) {
+        const u64 cT = tT * kTile4 + row + j * 16;
+        if (c0v < p.n0 && cT < p.nT) {
+          const float *q = p.in[a] + off[a + 1] + c0v * p.s0[a + 1] + cT * p.sT[a + 1];
+          if (p.s0[a + 1] == 1) {
+            v[j][a] = __ldcs(reinterpret_cast<const float4 *>(q));
+          } else { // broadcast along dim 0
+            const float sc = __ldg(q);
+            v[j][a] = make_float4(sc, sc, sc, sc);
+          }
         }
       }
     }
   }
+  // phase 1: park the transposed inputs in shared memory, [dim 0][dT] with a one-float pad
+#pragma unroll
+  for (int a = 0; a < NIN; ++a) {
+    if (!((p.tmask >> a) & 1u)) continue;
+    float *tl = tile4_smem + (size_t)a * kTile4 * (kTile4 + 1);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float *dst = tl + (row + j * 16) * (kTile4 + 1) + q4 * 4;
+      dst[0] = v[j][a].x; dst[1] = v[j][a].y; dst[2] = v[j][a].z; dst[3] = v[j][a].w;
+    }
+  }
+  __syncthreads();
+  // phase 2: float4 along dim 0, rows along dT
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const u64 cT = tT * kTile4 + row + j * 16;
-    if (c0 < p.n0 && cT < p.nT) {
+    if (c0v < p.n0 && cT < p.nT) {
       float r[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -258,13 +266,13 @@ __global__ void __launch_bounds__(256) ew_tiled4_kernel(F f, TiledParams<NIN> p)
           if ((p.tmask >> a) & 1u) {
             x[a] = tile4_smem[(size_t)a * kTile4 * (kTile4 + 1) + (q4 * 4 + k) * (kTile4 + 1) + row + j * 16];
           } else {
-            const float4 d = direct[j][a];
+            const float4 d = v[j][a];
             x[a] = k == 0 ? d.x : (k == 1 ? d.y : (k == 2 ? d.z : d.w));
           }
         }
         r[k] = f(x);
       }
-      __stcs(reinterpret_cast<float4 *>(p.out + off[0] + c0 + cT * p.sT[0]), make_float4(r[0], r[1], r[2], r[3]));
+      __stcs(reinterpret_cast<float4 *>(p.out + off[0] + c0v + cT * p.sT[0]), make_float4(r[0], r[1], r[2], r[3]));
     }
   }
 }
@@ -319,7 +327,7 @@ bool launch_ew_tiled(const IterPlan &plan, float *out, const float *const *ins, 
         ready = true;
       }
       dim3 grid((unsigned)(p.tiles0 * tilesT), (unsigned)outer);
-      ew_tiled4_kernel<F, NIN><<<grid, 256, smem4, stream()>>>(f, p);
+      launch_k(ew_tiled4_kernel<F, NIN>, grid, dim3(256), smem4, stream(), f, p);
       count_launch();
       note_kernel("ew_tiled_transpose");
       return true;
@@ -329,7 +337,7 @@ bool launch_ew_tiled(const IterPlan &plan, float *out, const float *const *ins, 
   const u64 tilesT = (p.nT + kTileDim - 1) / kTileDim;
   if (p.tiles0 * tilesT > 0x7fffffffull) return false;
   dim3 grid((unsigned)(p.tiles0 * tilesT), (unsigned)outer), block(kTileDim, kTileRows);
-  ew_tiled_kernel<F, NIN><<<grid, block, 0, stream()>>>(f, p);
+  launch_k(ew_tiled_kernel<F, NIN>, grid, block, 0, stream(), f, p);
   count_launch();
   note_kernel("ew_tiled_transpose");
   return true;

@@ -17,6 +17,12 @@ namespace pb {
 constexpr int kEwThreads = 256;
 constexpr int kEwUnroll = 4;
 
+// Programmatic dependent launch: pdl_wait() returns once the grid this one depends on has completed
+// and its memory is visible (at once for a plain launch); pdl_launch_dependents() lets the next
+// grid in the stream become resident early (it waits the same way before touching memory).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 template <int VEC> struct VecOf;
 template <> struct VecOf<4> { using type = float4; };
 template <> struct VecOf<2> { using type = float2; };
@@ -86,6 +92,8 @@ template <class F, int NIN, int VEC, typename index_t, bool ONE_D, uint32_t CMAS
 __global__ void __launch_bounds__(kEwThreads)
 ew_kernel(F f, float *out, InPtrs<NIN> in, OffsetCalc<NIN + 1, index_t> oc, index_t n_items,
           uint32_t vec_mask_arg) {
+  pdl_wait();
+  pdl_launch_dependents();
   const uint32_t vec_mask = CMASK ? CMASK : vec_mask_arg;
   const index_t tile = (index_t)blockIdx.x * (kEwThreads * kEwUnroll) + threadIdx.x;
   float v[kEwUnroll][NIN][VEC];

@@ -1,5 +1,6 @@
 // Symbols the reference's core, arena, shape ops and Python extension link against:
 // fills, arena memory calls, view-gradient accumulation and the strided -> contiguous pack.
+#include <atomic>
 #include "ew_engine.cuh"
 #include "functors.cuh"
 #include "grad_accum.cuh"
@@ -181,9 +182,29 @@ void *arena_alloc_cuda(u64 size) {
   return p;
 }
 void arena_free_cuda(void *ptr) { PB_FATAL(cudaFree(ptr)); }
-// Stream-ordered on the library stream, so a fill never races the kernels around it.
+// The reference's arena zero-fills EVERY allocation (src/core/arena.c:94-102), also the output of
+// a forward op that is about to be overwritten (+4 bytes per element of HBM traffic on top of the
+// op's own 8-12) and the gradient twin that src/core/tensor.c:82-90 zeroes again through
+// zeros_cuda. The fill is stream-ordered on the library stream, so it never races the kernels
+// around it and never stalls the host; and the caller can switch it off around allocations whose
+// first use is a full overwrite (plast_b200_arena_fill_policy): gradients are still zeroed, once,
+// by zeros_cuda.
+static thread_local int t_fill_policy = PLAST_B200_ARENA_FILL;
+static std::atomic<unsigned long long> g_fill_bytes{0}, g_fill_skipped_bytes{0};
 void arena_memset_cuda(void *ptr, int value, u64 size) {
+  if (t_fill_policy == PLAST_B200_ARENA_SKIP_FILL && value == 0) {
+    g_fill_skipped_bytes.fetch_add(size, std::memory_order_relaxed);
+    return;
+  }
+  g_fill_bytes.fetch_add(size, std::memory_order_relaxed);
   PB_FATAL(cudaMemsetAsync(ptr, value, size, stream()));
+}
+void plast_b200_arena_fill_policy(int policy) {
+  t_fill_policy = policy == PLAST_B200_ARENA_SKIP_FILL ? PLAST_B200_ARENA_SKIP_FILL : PLAST_B200_ARENA_FILL;
+}
+void plast_b200_arena_fill_stats(u64 *filled_bytes, u64 *skipped_bytes) {
+  if (filled_bytes) *filled_bytes = g_fill_bytes.load(std::memory_order_relaxed);
+  if (skipped_bytes) *skipped_bytes = g_fill_skipped_bytes.load(std::memory_order_relaxed);
 }
 void arena_memcpy_h2d_cuda(void *dest, const void *src, u64 size) {
   PB_FATAL(cudaMemcpyAsync(dest, src, size, cudaMemcpyHostToDevice, stream()));

@@ -127,25 +127,44 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
       return false;
     }
     g->kind = kRedCols;
-    // strip width: one warp across dim 0 (32 lanes x float4 = 512 B per row) and eight
-    // row-workers per CTA measured as fast as wider strips and leaves more tiles, hence fewer
-    // chunks to combine at the end
-    g->log_tx = 5;
-    const u64 tx_n = (u64)1 << g->log_tx, ty_n = (u64)kRedThreads >> g->log_tx;
-    const u64 strips = ceil_div(g->len0_items, tx_n);
-    const u64 tiles = g->n_kept * strips;
-    // four CTAs' worth of work per SM measured best for the column sweep
-    u64 splits = ceil_div(sms * 4, tiles);
-    // every row-worker of a chunk should get at least two full load batches
-    const u64 min_per = ty_n * 4 * 2;
-    const u64 max_splits = g->n_red / min_per > 0 ? g->n_red / min_per : 1;
-    if (splits > max_splits) splits = max_splits;
-    if (splits > 1 && (tiles > kCounters || tiles * splits * tx_n * vec * elem_bytes >
-                                                kPartialFloats / 2 * sizeof(float)))
-      splits = 1;
-    g->per_chunk = ceil_div(g->n_red, splits);
-    g->splits = (unsigned)ceil_div(g->n_red, g->per_chunk);
-    g->grid = tiles * g->splits;
+    // A CTA sweeps a strip of tx_n lanes (x VEC outputs) with 256 / tx_n row-workers; the reduced
+    // dim is cut into `splits` chunks so that ONE resident wave of equally loaded CTAs covers the
+    // tensor (CTAs beyond the wave would run as a second, mostly empty one). Strips one warp wide
+    // (512 B per row with float4, eight row-workers) measured fastest by a wide margin on B200:
+    // 46 us for the column sum of 8192 x 8192 against 49 / 62 / 113 us with 64 / 128 / 256 lanes,
+    // whichever way the wave was filled; wider strips are only for plast_b200_tune.
+    u64 ctas_per_sm = (u64)occ.ctas_per_sm[kRedCols][vi] < 4 ? (u64)occ.ctas_per_sm[kRedCols][vi] : 4;
+    if (tuned(kTuneColsCtasPerSm) > 0) ctas_per_sm = (u64)tuned(kTuneColsCtasPerSm);
+    const u64 wave = sms * ctas_per_sm;
+    // a chunk gives every row-worker at least this many full load batches of four rows
+    u64 min_batches = 2; // (one batch per row-worker, i.e. twice the CTAs, measured slower even at 4 MiB)
+    if (tuned(kTuneColsMinBatches) > 0) min_batches = (u64)tuned(kTuneColsMinBatches);
+    double best_fill = -1.0;
+    const int forced_ltx = tuned(kTuneColsLogTx) >= 5 && tuned(kTuneColsLogTx) <= 8 ? (int)tuned(kTuneColsLogTx) : 5;
+    for (int ltx = forced_ltx; ltx <= forced_ltx; ++ltx) {
+      const u64 tx_n = (u64)1 << ltx, ty_n = (u64)kRedThreads >> ltx;
+      const u64 strips = ceil_div(g->len0_items, tx_n);
+      const u64 tiles = g->n_kept * strips;
+      u64 splits = wave / tiles > 0 ? wave / tiles : 1;
+      const u64 min_per = ty_n * 4 * min_batches;
+      const u64 max_splits = g->n_red / min_per > 0 ? g->n_red / min_per : 1;
+      if (splits > max_splits) splits = max_splits;
+      if (splits > 1 && (tiles > kCounters || tiles * splits * tx_n * vec * elem_bytes >
+                                                  kPartialFloats / 2 * sizeof(float)))
+        splits = 1;
+      const u64 per_chunk = ceil_div(g->n_red, splits);
+      splits = ceil_div(g->n_red, per_chunk);
+      const u64 ctas = tiles * splits;
+      const double fill = (double)ctas / (double)(ceil_div(ctas, wave) * wave) *
+                          ((double)g->len0_items / (double)(strips * tx_n));
+      if (fill > best_fill + 0.015) {
+        best_fill = fill;
+        g->log_tx = ltx;
+        g->per_chunk = per_chunk;
+        g->splits = (unsigned)splits;
+        g->grid = ctas;
+      }
+    }
   }
   if (g->grid == 0 || g->grid > 0x7fffffffull) {
     set_error(PLAST_B200_ERR_LIMIT, "reduction needs %llu blocks", (unsigned long long)g->grid);

@@ -20,6 +20,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "ew_kernel_device.cuh" // pdl_wait / pdl_launch_dependents
 #include "iter.h"
 #include "peer_link.cuh"
 
@@ -295,6 +296,8 @@ __device__ __forceinline__ void accumulate_run(const RedParams<NIN> &p, const Pr
 template <class Op, class Pro, int NIN, int VEC, int NS = NIN>
 __global__ void __launch_bounds__(kRedThreads) reduce_rows_kernel(RedParams<NIN> p, Pro pro) {
   using T = typename Op::T;
+  pdl_wait();
+  pdl_launch_dependents();
   const unsigned tx_n = 1u << p.log_tx;
   const unsigned tx = threadIdx.x & (tx_n - 1), ty = threadIdx.x >> p.log_tx;
   const unsigned ty_n = kRedThreads >> p.log_tx;
@@ -334,6 +337,8 @@ __device__ __forceinline__ bool take_ticket(unsigned int *counter, unsigned spli
 template <class Op, class Pro, int NIN, int VEC, int NS = NIN>
 __global__ void __launch_bounds__(kRedThreads) reduce_seg_kernel(RedParams<NIN> p, Pro pro) {
   using T = typename Op::T;
+  pdl_wait();
+  pdl_launch_dependents();
   const u64 out_idx = blockIdx.x / p.splits;
   const unsigned chunk = blockIdx.x % p.splits;
   const unsigned tx_n = 1u << p.log_tx;
@@ -423,6 +428,8 @@ __global__ void __launch_bounds__(kRedThreads) reduce_seg_kernel(RedParams<NIN> 
 template <class Op, class Pro, int NIN, int VEC>
 __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN> p, Pro pro) {
   using T = typename Op::T;
+  pdl_wait();
+  pdl_launch_dependents();
   // tx_n lanes across dim 0 (a strip of tx_n * VEC outputs, one coalesced run per reduced index),
   // ty_n row-workers striding over the reduced indices. Wide strips (up to 256 lanes = 4 KiB per
   // row) keep every DRAM page access long; narrow ones serve small dim 0.
@@ -757,9 +764,9 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   dim3 grid((unsigned)g.grid), block(kRedThreads);
 #define PB_RED_LAUNCH(KERNEL)                                                                      \
   do {                                                                                             \
-    if (g.vec == 4) KERNEL<Op, Pro, NIN, 4><<<grid, block, 0, s>>>(p, pro);                        \
-    else if (g.vec == 2) KERNEL<Op, Pro, NIN, 2><<<grid, block, 0, s>>>(p, pro);                   \
-    else KERNEL<Op, Pro, NIN, 1><<<grid, block, 0, s>>>(p, pro);                                   \
+    if (g.vec == 4) launch_k(KERNEL<Op, Pro, NIN, 4>, grid, block, 0, s, p, pro);                  \
+    else if (g.vec == 2) launch_k(KERNEL<Op, Pro, NIN, 2>, grid, block, 0, s, p, pro);             \
+    else launch_k(KERNEL<Op, Pro, NIN, 1>, grid, block, 0, s, p, pro);                             \
   } while (0)
   // float4 plans whose inputs are "the first m vary along the run, the rest are constant"
   // (m = 1 or 2 < NIN) get the kernel that knows this at compile time (fewer registers).
@@ -768,8 +775,8 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   const bool prefix = g.vec == 4 && lead < NIN && g.vec_mask == ((1u << lead) - 1u) && (lead == 1 || lead == 2);
 #define PB_RED_LAUNCH_NS(KERNEL)                                                                   \
   do {                                                                                             \
-    if (prefix && lead == 1) KERNEL<Op, Pro, NIN, 4, (NIN > 1 ? 1 : NIN)><<<grid, block, 0, s>>>(p, pro); \
-    else if (prefix && lead == 2) KERNEL<Op, Pro, NIN, 4, (NIN > 2 ? 2 : NIN)><<<grid, block, 0, s>>>(p, pro); \
+    if (prefix && lead == 1) launch_k(KERNEL<Op, Pro, NIN, 4, (NIN > 1 ? 1 : NIN)>, grid, block, 0, s, p, pro); \
+    else if (prefix && lead == 2) launch_k(KERNEL<Op, Pro, NIN, 4, (NIN > 2 ? 2 : NIN)>, grid, block, 0, s, p, pro); \
     else PB_RED_LAUNCH(KERNEL);                                                                    \
   } while (0)
   if (g.kind == kRedRows) {

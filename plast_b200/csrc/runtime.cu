@@ -5,6 +5,7 @@
 #include <atomic>
 #include <mutex>
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 namespace pb {
@@ -84,6 +85,24 @@ void end_call() {
   }
 }
 
+namespace {
+std::atomic<long> g_tune[kTuneKeys];
+struct TuneInit {
+  TuneInit() {
+    for (int i = 0; i < kTuneKeys; ++i) g_tune[i].store(-1);
+  }
+} g_tune_init;
+} // namespace
+long tuned(int key) { return key >= 0 && key < kTuneKeys ? g_tune[key].load(std::memory_order_relaxed) : -1; }
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char *e = getenv("PLAST_B200_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 int sm_count() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
@@ -151,6 +170,10 @@ void plast_b200_set_sync(int on) { pb::g_sync.store(on ? 1 : 0); }
 u64 plast_b200_launch_count(void) { return (u64)pb::g_launches.load(); }
 const char *plast_b200_last_kernel(void) { return pb::t_kernel; }
 const char *plast_b200_version(void) { return "plast_b200 0.1 (sm_100a)"; }
+
+void plast_b200_tune(int key, long value) {
+  if (key >= 0 && key < pb::kTuneKeys) pb::g_tune[key].store(value);
+}
 
 void plast_b200_release_workspace(void) {
   pb::release_host_pipeline();

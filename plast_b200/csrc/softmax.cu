@@ -79,6 +79,8 @@ __global__ void __launch_bounds__(kSmThreads, 4)
 softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const int *__restrict__ labels,
                     SmRows g, int log_tx, float *row_loss) {
   __shared__ float red_smem[kSmThreads / 32];
+  pdl_wait();
+  pdl_launch_dependents();
   const int tx_n = 1 << log_tx;
   const int tx = threadIdx.x & (tx_n - 1), ty = threadIdx.x >> log_tx;
   const int rows_per_cta = kSmThreads >> log_tx;
@@ -194,6 +196,8 @@ __device__ __forceinline__ MaxSum ms_block_reduce(MaxSum v) {
 template <int MODE>
 __global__ void __launch_bounds__(kSmThreads)
 softmax_generic_kernel(const float *x, float *y, const int *labels, SmRows g, float *row_loss) {
+  pdl_wait();
+  pdl_launch_dependents();
   for (u64 row = blockIdx.x; row < g.rows; row += gridDim.x) {
     u64 yoff = 0, ioff[2] = {0, 0};
     g.outer.offsets(row, &yoff, ioff);
@@ -258,6 +262,8 @@ __global__ void __launch_bounds__(kSmThreads)
 cross_entropy_rows_kernel(const float *__restrict__ x, const int *__restrict__ labels, SmRows g,
                           float *__restrict__ mean_out, unsigned int *counter, float *partials, const PeerLink *peer,
                           float global_count) {
+  pdl_wait();
+  pdl_launch_dependents();
   const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float warp_loss = 0.0f; // lane 0: sum of the losses of this warp's rows
   const unsigned warps_per_cta = kSmThreads / 32;
@@ -378,6 +384,8 @@ cross_entropy_rows_kernel(const float *__restrict__ x, const int *__restrict__ l
 template <int MODE>
 __global__ void __launch_bounds__(kSmThreads)
 softmax_backward_kernel(const float *y_or_x, const float *dy, float *dx, const int *labels, SmRows g) {
+  pdl_wait();
+  pdl_launch_dependents();
   for (u64 row = blockIdx.x; row < g.rows; row += gridDim.x) {
     u64 doff = 0, ioff[2] = {0, 0};
     g.outer.offsets(row, &doff, ioff);
@@ -554,8 +562,8 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
     const PeerLink *link = nullptr;
     float global_count = 0.0f;
     if (!take_peer_link(kPeerCrossEntropy, &link, &global_count)) link = nullptr;
-    cross_entropy_rows_kernel<<<(unsigned)ce_grid, kSmThreads, 0, s>>>(xd, labels, g, y, ws.counters, ws.partials, link,
-                                                                      global_count);
+    launch_k(cross_entropy_rows_kernel, dim3((unsigned)ce_grid), dim3(kSmThreads), 0, s, xd, labels, g, y, ws.counters,
+             ws.partials, link, global_count);
     count_launch();
     note_kernel("cross_entropy_rows");
     end_call();
@@ -564,13 +572,13 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
     int v = 1;
     while (v < vpt) v <<= 1;
     switch (v) {
-    case 1: softmax_fast_kernel<MODE, 1><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, row_loss); break;
-    case 2: softmax_fast_kernel<MODE, 2><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, row_loss); break;
-    case 4: softmax_fast_kernel<MODE, 4><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, row_loss); break;
-    default: softmax_fast_kernel<MODE, 8><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, log_tx, row_loss); break;
+    case 1: launch_k(softmax_fast_kernel<MODE, 1>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); break;
+    case 2: launch_k(softmax_fast_kernel<MODE, 2>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); break;
+    case 4: launch_k(softmax_fast_kernel<MODE, 4>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); break;
+    default: launch_k(softmax_fast_kernel<MODE, 8>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); break;
     }
   } else {
-    softmax_generic_kernel<MODE><<<(unsigned)grid, kSmThreads, 0, s>>>(xd, y, labels, g, row_loss);
+    launch_k(softmax_generic_kernel<MODE>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, row_loss);
   }
   count_launch();
   if (MODE == kCrossEntropy) {
@@ -629,8 +637,8 @@ static void softmax_family_backward(const char *name, Tensor **inputs, const Ten
   u64 grid = g.rows;
   const u64 cap = (u64)sm_count() * 16;
   if (grid > cap) grid = cap;
-  softmax_backward_kernel<MODE><<<(unsigned)grid, kSmThreads, 0, stream()>>>(
-      a, (const float *)output->grad->data, (float *)x->grad->data, labels, g);
+  launch_k(softmax_backward_kernel<MODE>, dim3((unsigned)grid), dim3(kSmThreads), 0, stream(), a,
+           (const float *)output->grad->data, (float *)x->grad->data, labels, g);
   count_launch();
   note_kernel("softmax_backward");
   end_call();

@@ -46,9 +46,15 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
         torch.cuda.synchronize()
         kernel = pb.last_kernel()
         # Working sets beyond L2 are timed as `inner` back-to-back launches per event pair, so the
-        # few microseconds between an event and a launch are not billed to a 40 us kernel; small
-        # working sets need the flush before every launch and are timed one launch at a time.
-        inner = 1 if flush else 5
+        # few microseconds between an event and the first launch after it are not billed to a 40 us
+        # kernel (20 launches for kernels under 100 us, 5 for longer ones); small working sets need
+        # the flush before every launch and are timed one launch at a time.
+        inner = 1
+        if not flush:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); fn(); e1.record()
+            torch.cuda.synchronize()
+            inner = 20 if e0.elapsed_time(e1) / 2 < 0.1 else 5
         times = []
         for _ in range(reps):
             if flush:
@@ -65,7 +71,7 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
         row = {"config": cfg, "op": name, "kernel": kernel, "ms": round(ms, 5),
                "bytes": int(nbytes), "GBps": round(gbs, 1), "elements_per_s": elems / (ms * 1e-3),
                "frac_of_measured": round(gbs / peak_gbs, 4), "frac_of_nominal": round(gbs / NOMINAL, 4),
-               "l2_flushed": flush}
+               "l2_flushed": flush, "launches_per_timed_region": inner}
         if flush and reps > 0:
             # Launch-bound sizes: the same call 50 times back to back in the stream (data stays in L2) ...
             bt = []
@@ -163,6 +169,17 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
         timeit(2, "mul", lambda: pb.forward("mul", [tx, ty], tz, check=False), 3 * n * F, n, ws)
         timeit(2, "add", lambda: pb.forward("add", [tx, ty], tz, check=False), 3 * n * F, n, ws)
         timeit(2, "sigmoid_fused", lambda: pb.forward("sigmoid", [tx], tz, check=False), 2 * n * F, n, ws)
+        # What the reference's arena adds on the caller's side of every op (src/core/arena.c:94-102:
+        # each output is zero-filled when allocated, then overwritten by its op): the fill call
+        # followed by the op, with the reference's fill policy and with the fill skipped for op
+        # outputs (plast_b200_arena_fill_policy). Same 8 algorithmic bytes per element in both rows.
+        def neg_after_arena_fill(policy):
+            pb.lib.plast_b200_arena_fill_policy(policy)
+            pb.lib.arena_memset_cuda(C.c_void_p(z.data_ptr()), 0, n * F)
+            pb.lib.plast_b200_arena_fill_policy(0)
+            pb.forward("neg", [tx], tz, check=False)
+        timeit(2, "neg_with_reference_arena_fill", lambda: neg_after_arena_fill(0), 2 * n * F, n, ws)
+        timeit(2, "neg_with_output_fill_skipped", lambda: neg_after_arena_fill(1), 2 * n * F, n, ws)
         steps = [("neg", 0, 0, 0.0), ("exp", 2, 0, 0.0), ("add_scalar", 3, 0, 1.0), ("rdiv_scalar", 4, 0, 1.0),
                  ("mul", 5, 1, 0.0), ("abs", 0, 0, 0.0), ("neg", 7, 0, 0.0), ("exp", 8, 0, 0.0), ("add", 6, 9, 0.0)]
         timeit(2, "fused_chain", lambda: pb.chain_forward([tx, ty], tz, steps, check=False), 3 * n * F, n, ws)

@@ -15,8 +15,9 @@ Bounds (the benchmark's): bit-exact for add, mul, div, abs, neg, relu, max, argm
 exp / log; |gpu - cpu| <= 1e-5 * sum|terms| for sums, means and gradient reductions (the CPU adds
 left to right, the GPU as a tree; the reference's own broadcast-gradient order is whatever its
 atomics give); relative 1e-5 for softmax / log-softmax outputs and the cross-entropy mean. sigmoid
-and the nine-op chain are compositions: exp within 2 ulp of glibc's moves 1/(1+e) by up to 3 ulp,
-and z = t + e2 can cancel, so their bounds are the measured worst cases stated at the asserts.
+and the nine-op chain are compositions: exp within 2 ulp of glibc's moves 1/(1+e) by up to 4 ulp,
+and z = t + e2 can cancel, so their bounds are the measured worst cases stated at the asserts
+(sigmoid 4 ulp; chain 3 * 2^-23 * (|t| + |e2|)).
 
 Every test records the largest error it saw; the last test prints the table (and leaves it in
 gpurun_out/parity_table.json when that folder can be written).
@@ -168,13 +169,16 @@ def test_config2_every_op_and_the_chain_on_2p28_elements(cuda, cpu, recipes):
     cuda.forward("exp", [tx], tz); cpu.forward("exp", [hx], hz)
     u = max_ulp(tz.numpy(), want); assert u <= 2
     record(2, "exp", u, 2, "ulp")
-    # sigmoid = neg -> exp -> +1 -> 1/. : exp within 2 ulp of glibc's; for x << 0 the +1 does not
-    # absorb that, and the reciprocal rounds once more: at most 3 ulp (measured worst case)
+    # sigmoid = neg -> exp -> +1 -> 1/. : exp is within 2 ulp of glibc's; where e = exp(-x) is not
+    # small against 1 the sum 1 + e inherits that difference (up to 2 ulp of a value in [1, 2), i.e.
+    # 2^-22 relative), and the reciprocal lands in (0.5, 1], where one ulp is 2^-24 relative: up to
+    # 4 ulp between the two results. Measured worst case over the 2^28 inputs of this configuration: 4.
     cuda.forward("sigmoid", [tx], tz)
     u = max_ulp(tz.numpy(), recipes.sigmoid(x)); assert u <= 4
-    record(2, "sigmoid (4-op recipe)", u, 3, "ulp")
+    record(2, "sigmoid (4-op recipe)", u, 4, "ulp")
     # the chain: z = t + e2 with t = sigmoid(x) * y, e2 = exp(-|x|); t and e2 can cancel, so the
-    # bound is in ulps of the terms: |gpu - cpu| <= k * 2^-23 * (|t| + |e2|), k = 3 measured worst case
+    # bound is in ulps of the terms: |gpu - cpu| <= k * 2^-23 * (|t| + |e2|); measured worst case over
+    # the 2^28 inputs: k = 2.69, asserted: 3
     steps = [("neg", 0, 0, 0), ("exp", 2, 0, 0), ("add_scalar", 3, 0, 1.0), ("rdiv_scalar", 4, 0, 1.0),
              ("mul", 5, 1, 0), ("abs", 0, 0, 0), ("neg", 7, 0, 0), ("exp", 8, 0, 0), ("add", 6, 9, 0)]
     pb.chain_forward([tx, ty], tz, steps)
@@ -185,7 +189,7 @@ def test_config2_every_op_and_the_chain_on_2p28_elements(cuda, cpu, recipes):
         terms = np.abs(y64) / (1 + np.exp(-x64)) + np.exp(-np.abs(x64))
         d = np.abs(got[i:i + CHUNK].astype(np.float64) - ref[i:i + CHUNK]) / (2.0 ** -23 * terms)
         worst = max(worst, float(d.max()))
-    assert worst <= 4.0
+    assert worst <= 3.0
     record(2, "fused chain z = sigmoid(x)*y + exp(-|x|)", worst, 3.0, "|gpu-cpu| / (2^-23 * (|t|+|e2|))")
 
 

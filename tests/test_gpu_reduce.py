@@ -311,7 +311,9 @@ def test_sigmoid_and_chain(cuda, recipes):
     X, Y = rand_normal(0, (n,)), rand_normal(1, (n,))
     out = cuda.empty((n,))
     cuda.forward("sigmoid", [cuda.tensor(X)], out)
-    # exp is <= 2 ulp off glibc's; the +1 and the reciprocal each round once more
+    # exp is <= 2 ulp off glibc's: 1 + e carries up to 2 ulp of [1, 2), the reciprocal lies in
+    # (0.5, 1] where an ulp is half as large: up to 4 ulp (also the measured worst case over the
+    # 2^28 N(0,1) inputs of the benchmark's configuration 2)
     assert_ulp(out.numpy(), recipes.sigmoid(X), 4, "sigmoid")
     import plast_b200 as pb
     steps = [("neg", 0, 0, 0), ("exp", 2, 0, 0), ("add_scalar", 3, 0, 1.0), ("rdiv_scalar", 4, 0, 1.0),
@@ -324,7 +326,8 @@ def test_sigmoid_and_chain(cuda, recipes):
     # oracle's, which moves t and e2 by <= ~3 ulp each
     x64, y64 = X.astype(np.float64), Y.astype(np.float64)
     terms = np.abs(y64) / (1 + np.exp(-x64)) + np.exp(-np.abs(x64))
-    assert (np.abs(z.numpy().astype(np.float64) - want) <= 4 * 2.0 ** -23 * terms).all(), "fused chain"
+    # (measured worst case on the benchmark's 2^28 inputs: 2.69 in these units)
+    assert (np.abs(z.numpy().astype(np.float64) - want) <= 3 * 2.0 ** -23 * terms).all(), "fused chain"
     # the same program with one step changed takes the interpreter and must agree with it
     steps2 = steps[:-1] + [("sub", 6, 9, 0)]
     z2 = cuda.empty((n,))
