@@ -60,6 +60,22 @@ void plast_b200_peer_full_reduce(PlastPeerGroup *group, int op, const Tensor *in
  * mean on every rank. One call of the exchange sequence. */
 void plast_b200_peer_cross_entropy_mean(PlastPeerGroup *group, const Tensor *logits, const Tensor *labels,
                                         Tensor *output, u64 global_rows);
+/* Bracket for reductions that cross the sharded dim. Every final reduction that entry points called
+ * by THIS host thread launch between _begin and _end is combined across the ranks, in launch order:
+ * a forward sum / max / min over the sharded axis (the column sum of a row-sharded matrix), the
+ * broadcast-gradient reduce of a backward call (the bias / scale gradient of a batch-sharded
+ * activation: inputs[i]->grad += the sum over ALL ranks' shards). Where the reduction kernel ends
+ * with one thread or one row of strip owners holding the final values (full reductions, column
+ * reductions onto contiguous outputs) the exchange happens inside that kernel; any other shape is
+ * followed by the stand-alone exchange kernel on a parked copy, so the result is the same either
+ * way and each reduction is exactly one call of the exchange sequence. Every rank must issue the
+ * same calls in the same order. Limits: at most PLAST_B200_PEER_MAX_FLOATS contiguous outputs per
+ * reduction; sum, max and min only (a mean would divide by the local count: take the sum and divide
+ * by the global count), otherwise the call fails with PLAST_B200_ERR_UNSUPPORTED and launches
+ * nothing. _end returns the number of exchanges made since _begin (0 means the bracketed calls
+ * contained no reduction). */
+void plast_b200_peer_reduce_begin(PlastPeerGroup *group);
+int plast_b200_peer_reduce_end(PlastPeerGroup *group);
 /* 0 = every exchange so far completed; 1 <= k <= world: a wait for rank k - 1 ran out;
  * PLAST_B200_PEER_STATUS_LOCAL_FAILURE: a fused call's local kernel could not run here (see
  * plast_b200_last_error at that call) and the exchanged value is invalid. Sticky until

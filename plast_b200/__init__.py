@@ -101,6 +101,7 @@ def declared_symbols() -> list[str]:
         "plast_b200_peer_group_begin", "plast_b200_peer_group_connect", "plast_b200_peer_all_reduce",
         "plast_b200_peer_group_status", "plast_b200_peer_group_clear_status", "plast_b200_peer_group_release",
         "plast_b200_peer_group_local", "plast_b200_chain_jit_available", "plast_b200_peer_full_reduce", "plast_b200_peer_cross_entropy_mean",
+        "plast_b200_peer_reduce_begin", "plast_b200_peer_reduce_end",
     ]
     return syms
 

@@ -49,15 +49,20 @@ void end_call(); // optional device sync (plast_b200_set_sync) + launch error ch
 struct Workspace {
   unsigned int *counters; // kCounters tickets
   float *partials;        // kPartialFloats floats
+  float *parked;          // kParkedFloats floats: a local result waiting for its cross-GPU exchange
 };
 constexpr size_t kCounters = 1 << 16;
 constexpr size_t kPartialFloats = (size_t)8 << 20; // 32 MiB
+constexpr size_t kParkedFloats = 8192;             // = PLAST_B200_PEER_MAX_FLOATS
 bool get_workspace(Workspace *ws);
 
 int sm_count();
 
 // Geometry knobs a test or a tuning run may override (plast_b200_tune); negative = built-in choice.
-enum TuneKey { kTuneColsLogTx = 0, kTuneColsCtasPerSm = 1, kTuneColsMinBatches = 2, kTuneSegCtasPerSm = 3, kTuneKeys = 8 };
+enum TuneKey {
+  kTuneColsLogTx = 0, kTuneColsCtasPerSm = 1, kTuneColsMinBatches = 2, kTuneSegCtasPerSm = 3,
+  kTuneKeepInL2MiB = 4, kTuneColsTileMajor = 5, kTuneKeys = 8
+};
 long tuned(int key);
 
 // ---- launches ------------------------------------------------------------------------------------

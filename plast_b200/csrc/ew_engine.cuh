@@ -31,6 +31,10 @@ struct EwChoice {
 
 EwChoice choose_ew(const IterPlan &plan, const void *const *ptrs, int nargs, u64 *n_items,
                    uint32_t *vec_mask);
+// True when everything the plan touches is small against L2 (the default bound is 32 MiB over all
+// operands; plast_b200_tune key 4 overrides it in MiB): such kernels use the default cache policy
+// so that the next kernel of a graph finds the data in L2.
+bool keep_in_l2(const IterPlan &plan, int nargs);
 
 template <int NARGS, typename index_t>
 void fill_offset_calc(OffsetCalc<NARGS, index_t> *oc, const IterPlan &plan, int vec) {
@@ -60,6 +64,7 @@ void launch_ew_one(const IterPlan &plan, float *out, const float *const *ins, co
   u64 n_items = 0;
   uint32_t vec_mask = 0;
   EwChoice c = choose_ew(plan, ptrs, NIN + 1, &n_items, &vec_mask);
+  const uint32_t policy = keep_in_l2(plan, NIN + 1) ? kEwKeepInL2 : 0u;
   InPtrs<NIN> ip;
   for (int a = 0; a < NIN; ++a) ip.p[a] = ins[a];
   const u64 per_block = (u64)kEwThreads * kEwUnroll;
@@ -75,7 +80,7 @@ void launch_ew_one(const IterPlan &plan, float *out, const float *const *ins, co
     OffsetCalc<NIN + 1, IDX> oc;                                                                   \
     fill_offset_calc(&oc, plan, VEC);                                                              \
     launch_k(ew_kernel<F, NIN, VEC, IDX, ONED>, grid, block, 0, s, f, out, ip, oc, (IDX)n_items,  \
-             vec_mask);                                                                            \
+             vec_mask | policy);                                                                   \
   } while (0)
 #define PB_EW_BY_VEC(IDX, ONED)                                                                    \
   do {                                                                                             \
@@ -91,7 +96,7 @@ void launch_ew_one(const IterPlan &plan, float *out, const float *const *ins, co
       OffsetCalc<NIN + 1, uint32_t> oc;
       fill_offset_calc(&oc, plan, 4);
 #define PB_EW_MASKED(ONED, CMASK)                                                                  \
-  launch_k(ew_kernel<F, NIN, 4, uint32_t, ONED, CMASK>, grid, block, 0, s, f, out, ip, oc, (uint32_t)n_items, vec_mask)
+  launch_k(ew_kernel<F, NIN, 4, uint32_t, ONED, CMASK>, grid, block, 0, s, f, out, ip, oc, (uint32_t)n_items, vec_mask | policy)
       if (vec_mask == 1u) {
         if (c.one_d) PB_EW_MASKED(true, 1u); else PB_EW_MASKED(false, 1u);
       } else {
@@ -137,6 +142,7 @@ template <int NIN> struct TiledParams {
   u64 outer_size[MAX_NDIM];
   u64 outer_stride[NIN + 1][MAX_NDIM];
   unsigned tmask;         // bit a: input a is contiguous along dT (goes through shared memory)
+  bool keep;              // default cache policy instead of streaming accesses (small working set)
   u64 tiles0;             // tiles along dim 0 (blockIdx.x = tile0 + tiles0 * tileT)
 };
 
@@ -222,7 +228,7 @@ __global__ void __launch_bounds__(256) ew_tiled4_kernel(F f, TiledParams<NIN> p)
       for (int j = 0; j < 4; ++j) {
         const u64 c0 = t0 * kTile4 + row + j * 16;
         if (cT < p.nT && c0 < p.n0)
-          v[j][a] = __ldcs(reinterpret_cast<const float4 *>(p.in[a] + off[a + 1] + c0 * p.s0[a + 1] + cT));
+          v[j][a] = ld_bulk(reinterpret_cast<const float4 *>(p.in[a] + off[a + 1] + c0 * p.s0[a + 1] + cT), p.keep);
       }
     } else {
 #pragma unroll
@@ -231,7 +237,7 @@ __global__ void __launch_bounds__(256) ew_tiled4_kernel(F f, TiledParams<NIN> p)
         if (c0v < p.n0 && cT < p.nT) {
           const float *q = p.in[a] + off[a + 1] + c0v * p.s0[a + 1] + cT * p.sT[a + 1];
           if (p.s0[a + 1] == 1) {
-            v[j][a] = __ldcs(reinterpret_cast<const float4 *>(q));
+            v[j][a] = ld_bulk(reinterpret_cast<const float4 *>(q), p.keep);
           } else { // broadcast along dim 0
             const float sc = __ldg(q);
             v[j][a] = make_float4(sc, sc, sc, sc);
@@ -272,7 +278,7 @@ __global__ void __launch_bounds__(256) ew_tiled4_kernel(F f, TiledParams<NIN> p)
         }
         r[k] = f(x);
       }
-      __stcs(reinterpret_cast<float4 *>(p.out + off[0] + c0v + cT * p.sT[0]), make_float4(r[0], r[1], r[2], r[3]));
+      st_bulk(reinterpret_cast<float4 *>(p.out + off[0] + c0v + cT * p.sT[0]), make_float4(r[0], r[1], r[2], r[3]), p.keep);
     }
   }
 }
@@ -288,6 +294,7 @@ bool launch_ew_tiled(const IterPlan &plan, float *out, const float *const *ins, 
   p.n0 = plan.size[0];
   p.nT = plan.size[dT];
   p.tmask = tmask;
+  p.keep = keep_in_l2(plan, NIN + 1);
   p.n_outer = 0;
   u64 outer = 1;
   for (int d = 1; d < plan.ndim; ++d) {
@@ -343,6 +350,72 @@ bool launch_ew_tiled(const IterPlan &plan, float *out, const float *const *ins, 
   return true;
 }
 
+// Inputs that are contiguous along two DIFFERENT dims other than the output's (x.transpose(0, 2) +
+// y.transpose(1, 2) on 3-D tensors): one tile transpose can only turn one of those dims. The inputs
+// that do not share the first such dim are gathered, each by one pass of the tile kernel, into
+// stream-ordered scratch laid out like the output; the op then reads the scratch. That costs 8 more
+// bytes per element and gathered input; reading such an input in place would touch a 32-byte
+// sector for every 4-byte element. Returns the number of inputs replaced (0: nothing to do or not
+// applicable), fills `plan2` / `ins2` and the scratch pointers to free after the launch.
+struct EwCopy {
+  __device__ __forceinline__ float operator()(const float *x) const { return x[0]; }
+};
+template <class F, int NIN> bool launch_ew_tiled(const IterPlan &plan, float *out, const float *const *ins, const F &f);
+template <int NIN>
+int gather_second_transposed_inputs(const IterPlan &plan, const float *const *ins, IterPlan *plan2,
+                                    const float **ins2, void **scratch) {
+  if (plan.ndim < 3 || plan.stride[0][0] != 1) return 0;
+  int unit_dim[NIN], first = -1, n_other = 0;
+  for (int a = 0; a < NIN; ++a) {
+    unit_dim[a] = -1;
+    if (plan.stride[a + 1][0] <= 1) continue;
+    bool expands = false;
+    for (int d = 0; d < plan.ndim; ++d) {
+      if (plan.stride[a + 1][d] == 0) expands = true;
+      if (d >= 1 && plan.stride[a + 1][d] == 1 && plan.size[d] > 1) unit_dim[a] = d;
+    }
+    if (expands) unit_dim[a] = -1; // a broadcasting view would be blown up by the gather
+    if (unit_dim[a] < 0) continue;
+    if (first < 0) first = unit_dim[a];
+    else if (unit_dim[a] != first) ++n_other;
+  }
+  if (n_other == 0) return 0;
+  *plan2 = plan;
+  u64 dense[MAX_NDIM], run = 1;
+  for (int d = 0; d < plan.ndim; ++d) {
+    dense[d] = run;
+    run *= plan.size[d];
+  }
+  int replaced = 0;
+  for (int a = 0; a < NIN; ++a) {
+    ins2[a] = ins[a];
+    if (unit_dim[a] < 0 || unit_dim[a] == first) continue;
+    void *buf = nullptr;
+    if (cudaMallocAsync(&buf, plan.numel * sizeof(float), stream()) != cudaSuccess) {
+      cudaGetLastError();
+      continue; // no scratch: this input stays where it is, the generic kernel reads it in place
+    }
+    IterPlan copy;
+    copy.ndim = plan.ndim;
+    copy.nargs = 2;
+    copy.numel = plan.numel;
+    for (int d = 0; d < plan.ndim; ++d) {
+      copy.size[d] = plan.size[d];
+      copy.stride[0][d] = dense[d];
+      copy.stride[1][d] = plan.stride[a + 1][d];
+    }
+    copy.max_offset[0] = plan.numel - 1;
+    copy.max_offset[1] = plan.max_offset[a + 1];
+    const float *src[1] = {ins[a]};
+    if (!launch_ew_tiled<EwCopy, 1>(copy, (float *)buf, src, EwCopy{})) launch_ew_one<EwCopy, 1>(copy, (float *)buf, src, EwCopy{});
+    for (int d = 0; d < plan.ndim; ++d) plan2->stride[a + 1][d] = dense[d];
+    plan2->max_offset[a + 1] = plan.numel - 1;
+    ins2[a] = (const float *)buf;
+    scratch[replaced++] = buf;
+  }
+  return replaced;
+}
+
 // Public entry: 1-D plans whose length is not a multiple of 4 run as a vector body plus a
 // <= 3 element tail, so an odd element count does not force the whole tensor onto scalar loads.
 template <class F, int NIN>
@@ -369,6 +442,18 @@ void launch_ew(const IterPlan &plan, float *out, const float *const *ins, const 
     }
   }
   if (plan.numel != 0 && launch_ew_tiled<F, NIN>(plan, out, ins, f)) return;
+  if (plan.numel != 0) {
+    IterPlan plan2;
+    const float *ins2[NIN];
+    void *scratch[NIN];
+    const int replaced = gather_second_transposed_inputs<NIN>(plan, ins, &plan2, ins2, scratch);
+    if (replaced > 0) {
+      if (!failed() && !launch_ew_tiled<F, NIN>(plan2, out, ins2, f)) launch_ew_one<F, NIN>(plan2, out, ins2, f);
+      for (int i = 0; i < replaced; ++i) cudaFreeAsync(scratch[i], stream());
+      if (!failed()) note_kernel("ew_gather_then_tiled_transpose");
+      return;
+    }
+  }
   launch_ew_one<F, NIN>(plan, out, ins, f);
 }
 

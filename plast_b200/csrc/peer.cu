@@ -139,11 +139,28 @@ static bool publish_link(PlastPeerGroup *g) {
 __global__ void scale_one_kernel(float *v, float factor) { v[0] = v[0] * factor; }
 __global__ void raise_status_kernel(unsigned int *words, unsigned code) { atomicCAS(&words[0], 0u, code); }
 
+__global__ void add_parked_kernel(float *dst, const float *parked, unsigned n, bool accumulate) {
+  const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = accumulate ? dst[i] + parked[i] : parked[i];
+}
+
+namespace pb {
+void launch_peer_exchange(const PeerLink *device_link, float *data, unsigned n, int op) {
+  if (n == 0) return;
+  const unsigned blocks = (n + kPeerThreads - 1) / kPeerThreads; // at most 8, all resident at once
+  peer_all_reduce_kernel<<<blocks, kPeerThreads, 0, stream()>>>(device_link, data, n, op);
+  count_launch();
+}
+void launch_add_parked(float *dst, const float *parked, unsigned n, bool accumulate) {
+  if (n == 0) return;
+  add_parked_kernel<<<(n + 255) / 256, 256, 0, stream()>>>(dst, parked, n, accumulate);
+  count_launch();
+}
+} // namespace pb
+
 // One call of the exchange sequence on the library stream (arguments already checked).
 static void launch_exchange(PlastPeerGroup *g, float *data, unsigned n, int op) {
-  const unsigned blocks = (n + kPeerThreads - 1) / kPeerThreads; // at most 8, all resident at once
-  peer_all_reduce_kernel<<<blocks, kPeerThreads, 0, stream()>>>(g->link_dev, data, n, op);
-  count_launch();
+  launch_peer_exchange(g->link_dev, data, n, op);
 }
 // The local part of a fused call failed on THIS rank (the error is already recorded). The peers
 // still make their call of the sequence, so this rank makes it too, with whatever the output
@@ -323,6 +340,24 @@ void plast_b200_peer_cross_entropy_mean(PlastPeerGroup *g, const Tensor *logits,
   scale_one_kernel<<<1, 1, 0, stream()>>>((float *)output->data, 1.0f / (float)global_rows);
   count_launch();
   end_call();
+}
+
+// Bracket mode: every final reduction the entry points of this thread launch until _end is combined
+// across the ranks (reduce_engine.cuh decides per launch whether the exchange runs inside the
+// reduction kernel or right behind it).
+void plast_b200_peer_reduce_begin(PlastPeerGroup *g) {
+  begin_call();
+  if (!g || !g->connected) {
+    set_error(g ? PLAST_B200_ERR_UNSUPPORTED : PLAST_B200_ERR_NULL, "peer reduce begin: no connected group");
+    return;
+  }
+  arm_peer_link(g->link_dev, kPeerEveryReduction, 0.0f);
+}
+int plast_b200_peer_reduce_end(PlastPeerGroup *g) {
+  (void)g;
+  const int n = peer_bracket_exchanges();
+  disarm_peer_link();
+  return n;
 }
 
 int plast_b200_peer_group_status(PlastPeerGroup *g) {

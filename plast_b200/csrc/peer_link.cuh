@@ -65,6 +65,59 @@ __device__ __forceinline__ float peer_exchange_scalar(const PeerLink &link, floa
   link.words[1] = seq;
   return complete ? acc : v;
 }
+
+// The exchange of a STRIP of a multi-output reduction, run by the threads that hold the strip's
+// final local values (one thread per VEC consecutive outputs, first output index `elem`): every
+// value goes to slot [rank][elem + k] of every peer, then the world's packets for the same
+// elements are polled and combined in rank order. All strips of the launch together form ONE call
+// of the exchange sequence: every exchanging thread reads the sequence counter, which cannot move
+// before peer_exchange_strip_done has been called for all `n_strips` strips of the grid.
+template <int VEC>
+__device__ __forceinline__ void peer_exchange_strip(const PeerLink &link, float (&v)[VEC], unsigned elem, int op) {
+  unsigned seq = *(volatile unsigned int *)&link.words[1] + 1u;
+  if (seq == 0u) seq = 2u;
+  const size_t parity_base = (size_t)(seq & 1u) * link.world * PLAST_B200_PEER_MAX_FLOATS;
+  for (int p = 0; p < link.world; ++p) {
+    unsigned long long *dst = link.packets[p] + parity_base + (size_t)link.rank * PLAST_B200_PEER_MAX_FLOATS + elem;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k)
+      store_packet(dst + k, ((unsigned long long)seq << 32) | (unsigned long long)__float_as_uint(v[k]));
+  }
+  const unsigned long long *mine = link.packets[link.rank] + parity_base + elem;
+#pragma unroll
+  for (int k = 0; k < VEC; ++k) {
+    float acc = 0.0f;
+    bool complete = true;
+    for (int p = 0; p < link.world && complete; ++p) {
+      const unsigned long long *slot = mine + (size_t)p * PLAST_B200_PEER_MAX_FLOATS + k;
+      unsigned long long got = load_packet(slot);
+      unsigned spins = 0;
+      while ((unsigned)(got >> 32) != seq) {
+        if (++spins > link.max_spins) {
+          atomicCAS(&link.words[0], 0u, 1u + (unsigned)p);
+          complete = false;
+          break;
+        }
+        __nanosleep(64);
+        got = load_packet(slot);
+      }
+      const float x = __uint_as_float((unsigned)got);
+      acc = p == 0 ? x : peer_combine(op, acc, x);
+    }
+    if (complete) v[k] = acc; // a give-up leaves the local value and raises the status word
+  }
+}
+// One thread per strip, after every thread of the strip has returned from peer_exchange_strip
+// (a barrier in between): the last strip of the grid advances the sequence counter.
+__device__ __forceinline__ void peer_exchange_strip_done(const PeerLink &link, unsigned n_strips) {
+  unsigned seq = *(volatile unsigned int *)&link.words[1] + 1u;
+  if (seq == 0u) seq = 2u;
+  __threadfence();
+  if (atomicAdd(&link.words[2], 1u) == n_strips - 1) {
+    link.words[2] = 0;
+    link.words[1] = seq;
+  }
+}
 #endif
 
 // Host side (runtime.cu): an entry point called between arm and disarm hands the link (a device
@@ -73,9 +126,27 @@ __device__ __forceinline__ float peer_exchange_scalar(const PeerLink &link, floa
 // global_count). A launch of the other kind never takes it: the row-loss reduction behind the
 // cross-entropy fallback kernels would otherwise exchange a sum and divide it by the LOCAL row
 // count. disarm tells whether a launch took the link.
-enum PeerConsumer { kPeerFullReduce = 0, kPeerCrossEntropy = 1 };
+//
+// kPeerEveryReduction is the bracket mode (plast_b200_peer_reduce_begin / _end): EVERY final
+// reduction launched while it is armed is combined across the ranks, in launch order, fused into
+// the kernel where the kernel shape allows it and by the stand-alone exchange kernel right behind
+// the reduction otherwise; the link can be taken any number of times. Reductions that are internal
+// steps (the first stage of a two-stage reduction, tie counts, per-row losses) suspend the link
+// around themselves.
+enum PeerConsumer { kPeerFullReduce = 0, kPeerCrossEntropy = 1, kPeerEveryReduction = 2 };
 void arm_peer_link(const PeerLink *device_link, PeerConsumer consumer, float global_count);
 bool take_peer_link(PeerConsumer consumer, const PeerLink **out, float *global_count); // true once per armed link
 bool disarm_peer_link();                                        // returns whether a launch took it
+bool peer_bracket_open();                // armed for kPeerEveryReduction and not suspended
+const PeerLink *peer_bracket_take();     // the link of the open bracket; counts one exchange
+int peer_bracket_exchanges();            // exchanges made since the bracket was armed
+struct PeerSuspend {                     // scope guard: reductions inside are local steps
+  PeerSuspend();
+  ~PeerSuspend();
+};
+// peer.cu: one stand-alone exchange of n floats (n <= PLAST_B200_PEER_MAX_FLOATS) at `data` on the
+// library stream, through the link in device memory; then dst (+)= data for a parked result.
+void launch_peer_exchange(const PeerLink *device_link, float *data, unsigned n, int op);
+void launch_add_parked(float *dst, const float *parked, unsigned n, bool accumulate);
 
 } // namespace pb

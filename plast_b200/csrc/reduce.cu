@@ -419,6 +419,7 @@ static void max_min_backward(const char *name, Tensor **inputs, const Tensor *ou
     make_plan(&plan, a->shape, a->ndim, 3, st, red, 1);
     if (dim == PLAST_FULL_REDUCE) plan.reduced[0] = true;
     const float *ins[2] = {(const float *)a->data, (const float *)output->data};
+    PeerSuspend local_step; // tie counts are scratch of this call, not a result that crosses GPUs
     launch_reduce<SumOp, EqualsPro, 2>(plan, ties, ins, EqualsPro{}, SumOp{}, false, 0.0f);
     if (failed()) return;
   }

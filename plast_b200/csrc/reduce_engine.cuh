@@ -163,6 +163,8 @@ template <int NIN> struct RedParams {
   unsigned int *counters;
   void *partials;
   const PeerLink *peer; // not NULL: the thread that holds the single final value exchanges it across GPUs
+  bool keep;            // default cache policy instead of streaming loads (inputs small against L2)
+  bool strip_major;     // cols: consecutive CTAs take neighbouring strips of the same chunk of rows
 };
 
 // The final value of a single-output reduction, combined across GPUs when a link is attached.
@@ -175,12 +177,12 @@ __device__ __forceinline__ typename Op::T across_gpus(const PeerLink *link, type
 }
 
 template <int VEC>
-__device__ __forceinline__ void red_load(const float *p, bool vec, float *v) {
+__device__ __forceinline__ void red_load(const float *p, bool vec, float *v, bool keep) {
   if (VEC == 4 && vec) {
-    const float4 t = __ldcs(reinterpret_cast<const float4 *>(p));
+    const float4 t = ld_bulk(reinterpret_cast<const float4 *>(p), keep);
     v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
   } else if (VEC == 2 && vec) {
-    const float2 t = __ldcs(reinterpret_cast<const float2 *>(p));
+    const float2 t = ld_bulk(reinterpret_cast<const float2 *>(p), keep);
     v[0] = t.x; v[1] = t.y;
   } else {
     const float s = __ldg(p);
@@ -251,10 +253,10 @@ __device__ __forceinline__ void accumulate_run(const RedParams<NIN> &p, const Pr
   auto load_item = [&](int a, unsigned i, float *v) {
     if (!kStatic && p.istride0[a] == 0) return;
     if (VEC == 4) {
-      const float4 t = __ldcs(reinterpret_cast<const float4 *>(base[a]) + i);
+      const float4 t = ld_bulk(reinterpret_cast<const float4 *>(base[a]) + i, p.keep);
       v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
     } else if (VEC == 2) {
-      const float2 t = __ldcs(reinterpret_cast<const float2 *>(base[a]) + i);
+      const float2 t = ld_bulk(reinterpret_cast<const float2 *>(base[a]) + i, p.keep);
       v[0] = t.x; v[1] = t.y;
     } else {
       v[0] = __ldg(base[a] + (u64)i * p.istride0[a]);
@@ -437,8 +439,11 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
   const unsigned lane = threadIdx.x & (tx_n - 1), ty = threadIdx.x >> p.log_tx;
   const unsigned ty_n = kRedThreads >> p.log_tx;
   const u64 strips = (p.len0 + tx_n - 1) >> p.log_tx;
-  const u64 tile = blockIdx.x / p.splits; // (outer kept, strip)
-  const unsigned chunk = blockIdx.x % p.splits;
+  // (outer kept, strip) and chunk of the reduced dim; either the chunks of a tile or the tiles of a
+  // chunk are neighbours in launch order
+  const unsigned n_tiles = gridDim.x / p.splits;
+  const u64 tile = p.strip_major ? blockIdx.x % n_tiles : blockIdx.x / p.splits;
+  const unsigned chunk = p.strip_major ? blockIdx.x / n_tiles : blockIdx.x % p.splits;
   const u64 outer = tile / strips;
   const u64 strip = tile - outer * strips;
   const u64 item = (strip << p.log_tx) + lane;
@@ -476,10 +481,10 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
     auto load_row = [&](const float *q, int a, float *v) {
       if ((p.vec_mask >> a) & 1u) {
         if (VEC == 4) {
-          const float4 t = __ldcs(reinterpret_cast<const float4 *>(q));
+          const float4 t = ld_bulk(reinterpret_cast<const float4 *>(q), p.keep);
           v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
         } else if (VEC == 2) {
-          const float2 t = __ldcs(reinterpret_cast<const float2 *>(q));
+          const float2 t = ld_bulk(reinterpret_cast<const float2 *>(q), p.keep);
           v[0] = t.x; v[1] = t.y;
         } else {
           v[0] = __ldg(q);
@@ -537,7 +542,7 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
           p.red.offsets(r_begin + r, &dummy, ioff);
 #pragma unroll
           for (int a = 0; a < NIN; ++a)
-            red_load<VEC>(p.in[a] + ioff[a], (p.vec_mask >> a) & 1u, v[u][a]);
+            red_load<VEC>(p.in[a] + ioff[a], (p.vec_mask >> a) & 1u, v[u][a], p.keep);
         }
       }
 #pragma unroll
@@ -575,7 +580,22 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
     for (int k = 0; k < VEC; ++k) r[k] = acc[k];
   }
   typename Op::Out *out = (typename Op::Out *)p.out;
+  // With a link attached (the host only does that for a single row of strips whose outputs are
+  // contiguous, at most PLAST_B200_PEER_MAX_FLOATS of them) the threads that hold a strip's final
+  // local values exchange them across the GPUs before they store: reduce and all-reduce are one
+  // kernel. Every thread of the CTA reaches this point together (a CTA that is not the last of its
+  // tile has returned as a whole).
+  auto across_gpus_strip = [&](T(&vals)[VEC]) {
+    if constexpr (Op::kPeerOp >= 0 && !Op::kIndexed) {
+      if (p.peer != nullptr) {
+        if (ty == 0 && live) peer_exchange_strip<VEC>(*p.peer, vals, (unsigned)(item * VEC), Op::kPeerOp);
+        __syncthreads();
+        if (threadIdx.x == 0) peer_exchange_strip_done(*p.peer, (unsigned)strips);
+      }
+    }
+  };
   if (p.splits == 1) {
+    across_gpus_strip(r);
     if (ty == 0 && live) {
 #pragma unroll
       for (int k = 0; k < VEC; ++k)
@@ -611,6 +631,7 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
           fin[k] = Op::combine(fin[k], strip_vals[((t * VEC + k) << p.log_tx) + lane]);
     }
   }
+  across_gpus_strip(fin);
   if (ty == 0 && live) {
 #pragma unroll
     for (int k = 0; k < VEC; ++k) Op::store(out + toff + (u64)k * p.tstride0, fin[k], p.accumulate, p.post_div);
@@ -708,7 +729,10 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
     }
     first.stride[0][0] = 0;
     first.max_offset[0] = g.n_kept * g.n_red - 1;
-    launch_reduce<Op, Pro, NIN>(first, (typename Op::Out *)scratch, ins, pro, Op{}, false, 0.0f);
+    {
+      PeerSuspend local_step; // partial sums into scratch: only the second stage's result crosses GPUs
+      launch_reduce<Op, Pro, NIN>(first, (typename Op::Out *)scratch, ins, pro, Op{}, false, 0.0f);
+    }
     if (failed()) return;
     IterPlan second;
     make_plan(&second, sh2, (u64)(plan.ndim - 1), 2, st2, red2, 1);
@@ -751,9 +775,48 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   p.counters = nullptr;
   p.partials = nullptr;
   p.peer = nullptr;
+  {
+    u64 in_bytes = 0;
+    for (int a = 0; a < NIN; ++a) in_bytes += (plan.max_offset[a + 1] + 1) * sizeof(float);
+    const u64 bound = tuned(kTuneKeepInL2MiB) >= 0 ? (u64)tuned(kTuneKeepInL2MiB) << 20 : (u64)32 << 20;
+    p.keep = in_bytes <= bound;
+  }
+  p.strip_major = tuned(kTuneColsTileMajor) != 0; // default (-1) and 1: strips of a chunk are neighbours
   // a pending cross-GPU exchange rides on the kernel whose last CTA holds THE final value
   if (Op::kPeerOp >= 0 && g.kind == kRedSeg && g.n_kept == 1 && !take_peer_link(kPeerFullReduce, &p.peer, nullptr))
     p.peer = nullptr;
+  // Bracket mode: this reduction's result is combined across the ranks. Inside the kernel where one
+  // thread (single output) or the strip owners (column reduce over one row of strips, contiguous
+  // outputs) hold the final values; otherwise the local result is parked in scratch, exchanged by
+  // the stand-alone kernel right behind this launch and then stored / accumulated at its place.
+  // Either way it is exactly one call of the exchange sequence, at this point of the launch order.
+  float *parked_for = nullptr;
+  unsigned parked_n = 0;
+  bool parked_accumulate = false;
+  if constexpr (Op::kPeerOp >= 0 && !Op::kIndexed) {
+    if (peer_bracket_open()) {
+      u64 n_out = g.n_kept * (plan.reduced[0] ? 1 : plan.size[0]);
+      if (post_div > 0.0f || n_out > kParkedFloats || plan.max_offset[0] != n_out - 1) {
+        set_error(PLAST_B200_ERR_UNSUPPORTED,
+                  "a reduction inside plast_b200_peer_reduce_begin/_end must be a sum, max or min (a mean divides by the "
+                  "local count) onto at most %llu contiguous outputs", (unsigned long long)kParkedFloats);
+        return;
+      }
+      const bool single = g.kind == kRedSeg && g.n_kept == 1;
+      const bool strips_row = g.kind == kRedCols && g.n_kept == 1 && plan.stride[0][0] == 1;
+      if (single || strips_row) {
+        p.peer = peer_bracket_take();
+      } else {
+        Workspace wsp;
+        if (!get_workspace(&wsp)) return;
+        parked_for = (float *)out;
+        parked_n = (unsigned)n_out;
+        parked_accumulate = accumulate;
+        p.out = wsp.parked;
+        p.accumulate = false;
+      }
+    }
+  }
   Workspace ws = {};
   if (g.splits > 1) {
     if (!get_workspace(&ws)) return;
@@ -792,6 +855,10 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
 #undef PB_RED_LAUNCH_NS
 #undef PB_RED_LAUNCH
   count_launch();
+  if (parked_for != nullptr) {
+    launch_peer_exchange(peer_bracket_take(), (float *)p.out, parked_n, Op::kPeerOp);
+    launch_add_parked(parked_for, (const float *)p.out, parked_n, parked_accumulate);
+  }
 }
 
 } // namespace pb

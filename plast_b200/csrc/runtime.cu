@@ -29,6 +29,7 @@ thread_local const PeerLink *t_link = nullptr;
 thread_local float t_link_count = 0.0f;
 thread_local bool t_link_armed = false, t_link_taken = false;
 thread_local PeerConsumer t_link_consumer = kPeerFullReduce;
+thread_local int t_link_suspended = 0, t_bracket_exchanges = 0;
 } // namespace
 void arm_peer_link(const PeerLink *device_link, PeerConsumer consumer, float global_count) {
   t_link = device_link;
@@ -36,6 +37,7 @@ void arm_peer_link(const PeerLink *device_link, PeerConsumer consumer, float glo
   t_link_count = global_count;
   t_link_armed = true;
   t_link_taken = false;
+  t_bracket_exchanges = 0;
 }
 bool take_peer_link(PeerConsumer consumer, const PeerLink **out, float *global_count) {
   if (!t_link_armed || t_link_taken || consumer != t_link_consumer) return false;
@@ -50,6 +52,15 @@ bool disarm_peer_link() {
   t_link = nullptr;
   return taken;
 }
+bool peer_bracket_open() { return t_link_armed && t_link_consumer == kPeerEveryReduction && t_link_suspended == 0; }
+const PeerLink *peer_bracket_take() {
+  t_link_taken = true;
+  ++t_bracket_exchanges;
+  return t_link;
+}
+int peer_bracket_exchanges() { return t_bracket_exchanges; }
+PeerSuspend::PeerSuspend() { ++t_link_suspended; }
+PeerSuspend::~PeerSuspend() { --t_link_suspended; }
 
 void set_error(int code, const char *fmt, ...) {
   if (t_err != PLAST_B200_OK) return; // keep the first error of a call
@@ -125,7 +136,7 @@ bool get_workspace(Workspace *ws) {
   std::lock_guard<std::mutex> lock(g_ws_mutex);
   if (!g_ws[dev].counters) {
     void *p = nullptr;
-    size_t bytes = kCounters * sizeof(unsigned int) + kPartialFloats * sizeof(float);
+    size_t bytes = kCounters * sizeof(unsigned int) + (kPartialFloats + kParkedFloats) * sizeof(float);
     PB_CUDA_RET(cudaMalloc(&p, bytes), false);
     cudaError_t e = cudaMemset(p, 0, kCounters * sizeof(unsigned int));
     if (e != cudaSuccess) {
@@ -135,6 +146,7 @@ bool get_workspace(Workspace *ws) {
     }
     g_ws[dev].counters = (unsigned int *)p;
     g_ws[dev].partials = (float *)((char *)p + kCounters * sizeof(unsigned int));
+    g_ws[dev].parked = g_ws[dev].partials + kPartialFloats;
   }
   *ws = g_ws[dev];
   return true;

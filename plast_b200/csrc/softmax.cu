@@ -591,6 +591,7 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
     make_plan(&plan, shape, 1, 2, st, red, 1);
     plan.reduced[0] = true;
     const float *ins[1] = {row_loss};
+    PeerSuspend local_step; // a mean over THIS rank's rows; sharded callers use plast_b200_peer_cross_entropy_mean
     launch_reduce<SumOp, IdentityPro, 1>(plan, y, ins, IdentityPro{}, SumOp{}, false, (float)g.rows);
   }
   if (!failed())

@@ -108,6 +108,32 @@ class PeerGroup:
         self._pb.check_error()
         return out
 
+    def reducing(self):
+        """Context manager: every final reduction that plast_b200 entry points launch inside the
+        block (a sum over the sharded axis, the broadcast-gradient reduce of a backward call) is
+        combined across the ranks, inside the reduction kernel where its shape allows it
+        (plast_b200_peer_reduce_begin / _end). `exchanges` holds the count afterwards."""
+        group = self
+
+        class _Bracket:
+            exchanges = 0
+
+            def __enter__(self):
+                lib = group._pb.lib
+                lib.plast_b200_peer_reduce_begin.argtypes = [group._C.c_void_p]
+                lib.plast_b200_peer_reduce_begin.restype = None
+                lib.plast_b200_peer_reduce_end.argtypes = [group._C.c_void_p]
+                lib.plast_b200_peer_reduce_end.restype = group._C.c_int
+                lib.plast_b200_peer_reduce_begin(group._g)
+                group._pb.check_error()
+                return self
+
+            def __exit__(self, *exc):
+                self.exchanges = group._pb.lib.plast_b200_peer_reduce_end(group._g)
+                return False
+
+        return _Bracket()
+
     def status(self) -> int:
         return self._pb.lib.plast_b200_peer_group_status(self._g)
 

@@ -253,6 +253,17 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
                3 * M * M * F, M * M, 3 * ws)
         timeit(4, "pack_transposed_view", lambda: pb.lib.plast_b200_pack(C.byref(tXT.c), C.c_void_p(Z2.data_ptr())),
                2 * M * M * F, M * M, 2 * ws)
+        tY2T = wrap(Y2, shape=[M, M], strides=[1, M])
+        timeit(4, "add_of_two_transposed_views", lambda: pb.forward("add", [tXT, tY2T], tZ2, check=False),
+               3 * M * M * F, M * M, 3 * ws)
+        # 3-D, the two inputs contiguous along two DIFFERENT dims, neither of them the output's:
+        # out[i, j, k] = a.transpose(0, 2) + b.transpose(1, 2) on [128, 512, 1024] (same 2^26 elements)
+        I3, J3, K3 = 128, 512, 1024
+        t3a = wrap(X, shape=[I3, J3, K3], strides=[1, I3, I3 * J3])          # memory order [K, J, I]
+        t3b = wrap(Y2, shape=[I3, J3, K3], strides=[K3 * J3, 1, J3])          # memory order [I, K, J]
+        t3z = wrap(Z2, shape=[I3, J3, K3])
+        timeit(4, "add_inputs_transposed_along_two_different_dims", lambda: pb.forward("add", [t3a, t3b], t3z, check=False),
+               3 * M * M * F, M * M, 3 * ws)
         del X, Y2, Z2
     if 5 in configs:
         shape, pshape = (256, 256, 56, 56), (1, 256, 1, 1)

@@ -75,6 +75,66 @@ def main():
     assert abs(out.numpy()[0] - ref.item() / total_rows) <= 2e-6 * abs(ref.item() / total_rows) + 1e-6, \
         f"rank {rank}: fused cross-entropy mean {out.numpy()[0]} vs {ref.item() / total_rows}"
     assert group.status() == 0
+    # reductions that cross the sharded dim, inside the bracket: the column sum of a row-sharded
+    # matrix (exchange inside the column-reduce kernel), row sums as a many-output stand-in for the
+    # parked route, and the bias / scale gradients of a batch-sharded NCHW activation
+    rows_here = 512 + 16 * rank
+    gen.manual_seed(11000 + rank)
+    Mx = torch.randn((rows_here, 4096), generator=gen, device=dev)
+    t_m = pb.Tensor.wrap_pointer(Mx.data_ptr(), [rows_here, 4096], owner=Mx)
+    col = torch.zeros(4096, device=dev)
+    t_col = pb.Tensor.wrap_pointer(col.data_ptr(), [4096], owner=col)
+    pb.forward("sum", [t_m], t_col, dim=0)
+    want = col.clone(); dist.all_reduce(want)
+    scale = Mx.abs().sum(dim=0); dist.all_reduce(scale)
+    with group.reducing() as br:
+        pb.forward("sum", [t_m], t_col, dim=0)
+    torch.cuda.synchronize()
+    assert br.exchanges == 1 and pb.last_kernel().startswith("reduce_cols")
+    assert bool(((col - want).abs() <= 1e-5 * scale).all()), f"rank {rank}: fused column sum"
+    everyone = [torch.empty_like(col) for _ in range(world)]
+    dist.all_gather(everyone, col)
+    assert all(torch.equal(everyone[0], e) for e in everyone), "every rank must hold the same bits"
+    Mr = torch.randn((3000, 256), generator=gen, device=dev)             # 3000 outputs: the parked route
+    t_r = pb.Tensor.wrap_pointer(Mr.data_ptr(), [3000, 256], owner=Mr)
+    rs = torch.zeros(3000, device=dev)
+    t_rs = pb.Tensor.wrap_pointer(rs.data_ptr(), [3000], owner=rs)
+    pb.forward("max", [t_r], t_rs, dim=1)
+    want = rs.clone(); dist.all_reduce(want, op=dist.ReduceOp.MAX)
+    with group.reducing() as br:
+        pb.forward("max", [t_r], t_rs, dim=1)
+    torch.cuda.synchronize()
+    assert br.exchanges == 1 and torch.equal(rs, want), f"rank {rank}: parked row max"
+    nb = 4 + rank
+    gen.manual_seed(12000 + rank)
+    X5 = torch.randn((nb, 64, 56, 56), generator=gen, device=dev)
+    G5 = torch.randn((nb, 64, 56, 56), generator=gen, device=dev)
+    gen.manual_seed(12999)
+    S5 = torch.rand((1, 64, 1, 1), generator=gen, device=dev) - 0.5
+    B5 = torch.rand((1, 64, 1, 1), generator=gen, device=dev) - 0.5
+    Y5 = torch.empty_like(X5)
+    gS, gB = torch.ones((1, 64, 1, 1), device=dev), torch.full((1, 64, 1, 1), -2.0, device=dev)
+
+    def wrap(t, grad=None):
+        w = pb.Tensor.wrap_pointer(t.data_ptr(), list(t.shape), owner=t)
+        if grad is not None:
+            w.grad = pb.Tensor.wrap_pointer(grad.data_ptr(), list(grad.shape), owner=grad)
+            w.c.grad = C.pointer(w.grad.c); w.c.requires_grad = True
+        return w
+    tX5, tS5, tB5, tY5 = wrap(X5), wrap(S5, gS), wrap(B5, gB), wrap(Y5, G5)
+    pb.forward("scale_bias_leaky_relu", [tX5, tS5, tB5], tY5, fval=0.0)
+    mask = (Y5 > 0).float()
+    wantB = (G5 * mask).sum(dim=(0, 2, 3)).reshape(1, 64, 1, 1); dist.all_reduce(wantB)
+    wantS = (G5 * mask * X5).sum(dim=(0, 2, 3)).reshape(1, 64, 1, 1); dist.all_reduce(wantS)
+    sclB = (G5 * mask).abs().sum(dim=(0, 2, 3)).reshape(1, 64, 1, 1); dist.all_reduce(sclB)
+    sclS = (G5 * mask * X5).abs().sum(dim=(0, 2, 3)).reshape(1, 64, 1, 1); dist.all_reduce(sclS)
+    with group.reducing() as br:
+        pb.backward("scale_bias_leaky_relu", [tX5, tS5, tB5], tY5, fval=0.0)
+    torch.cuda.synchronize()
+    assert br.exchanges == 2
+    assert bool(((gB - (-2.0 + wantB)).abs() <= 1e-5 * sclB + 1e-6).all()), f"rank {rank}: bias gradient over all ranks"
+    assert bool(((gS - (1.0 + wantS)).abs() <= 1e-5 * sclS + 1e-6).all()), f"rank {rank}: scale gradient over all ranks"
+    assert group.status() == 0
     # timing: exchange of 1 float and of 8192 floats, against the process group's all-reduce
     def timed(fn, reps=200):
         for _ in range(10):

@@ -21,4 +21,4 @@ def test_reference_runtime_drives_the_library():
     # A + b, relu(A + b), max(X.T); fused relu(A + b), row sums and chain against the node-by-node runs
     # ... and the gradients of the fused training chain against its nine backward nodes
     # ... and the row sums of the DAG replayed as one CUDA graph
-    assert p.stdout.count("bit-exact") == 9
+    assert p.stdout.count("bit-exact") == 13          # + the four comparisons of the arena-fill runs

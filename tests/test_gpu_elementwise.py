@@ -105,6 +105,38 @@ def test_binary_transposed_and_expanded_views(cuda, oracle):
     assert_bit_equal(outs[0], outs[1], "tiled 3-D")
 
 
+def test_inputs_contiguous_along_two_different_dims(cuda, oracle):
+    """out[i, j, k] = a.transpose(0, 2)[i, j, k] op b.transpose(1, 2)[i, j, k]: a is contiguous along
+    i, b along j, the output along k. Any stride combination is one code path in the reference
+    (include/kernels/kernel_macros.h:213-220); here the input that does not share the first
+    transposed dim is gathered through the tile kernel first."""
+    import plast_b200 as pb
+    for shape in [(24, 40, 56), (9, 33, 130), (64, 64, 64)]:
+        I, J, K = shape
+        a, b = rand_normal(7, (K, J, I)), rand_normal(8, (I, K, J))
+        small = rand_uniform(9, (1, J, 1), 0.5, 2.0)
+        for op in BINARY:
+            outs = []
+            for be in (cuda, oracle):
+                out = be.empty(shape)
+                be.forward(op, [be.tensor(a).transpose(0, 2), be.tensor(b).transpose(1, 2)], out)
+                outs.append(out.numpy())
+            assert pb.last_kernel() == "ew_gather_then_tiled_transpose", shape
+            assert_bit_equal(outs[0], outs[1], f"{op} {shape}: two transposed inputs")
+        # three operands through a fused entry point: x transposed one way, scale the other, bias broadcast
+        outs = []
+        for be, name in ((cuda, "scale_bias_leaky_relu"), (oracle, None)):
+            ta, tb, ts = be.tensor(a).transpose(0, 2), be.tensor(b).transpose(1, 2), be.tensor(small)
+            out = be.empty(shape)
+            if name:
+                be.forward(name, [ta, tb, ts], out, fval=0.1)
+            else:
+                m, u = be.empty(shape), be.empty(shape)
+                be.forward("mul", [ta, tb], m); be.forward("add", [m, ts], u); be.forward("leaky_relu", [u], out, fval=0.1)
+            outs.append(out.numpy())
+        assert_bit_equal(outs[0], outs[1], f"fused epilogue {shape}: two transposed inputs")
+
+
 def test_relu_negative_zero_and_config1_forward(cuda, oracle):
     # config 1: C = relu(A + b); s = sum(C, axis=1). relu is leaky_relu(slope 0): x <= 0 -> x * 0
     A, b = rand_uniform(0, (1024, 1024)), rand_uniform(1, (1, 1024))

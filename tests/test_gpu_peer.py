@@ -186,6 +186,107 @@ def test_a_local_failure_still_makes_its_call_of_the_exchange_sequence(cuda):
     lib.plast_b200_peer_group_release(g)
 
 
+def _bracket(lib):
+    lib.plast_b200_peer_reduce_begin.argtypes = [C.c_void_p]
+    lib.plast_b200_peer_reduce_begin.restype = None
+    lib.plast_b200_peer_reduce_end.argtypes = [C.c_void_p]
+    lib.plast_b200_peer_reduce_end.restype = C.c_int
+
+
+def test_reductions_inside_the_bracket_are_exchanged_fused_or_parked(cuda):
+    """One-rank group: the exchange returns the local value, so every result must equal the plain
+    call's bits, and the launch count tells which route a reduction took (1 = exchange inside the
+    reduction kernel, 3 = reduce into scratch + exchange kernel + store)."""
+    lib = _lib(); _bracket(lib)
+    g = lib.plast_b200_peer_group_local(1, 1000)
+    pb.check_error()
+
+    def launches(fn):
+        n0 = pb.lib.plast_b200_launch_count(); fn(); return pb.lib.plast_b200_launch_count() - n0
+
+    A = rand_normal(0, (4096, 2048))
+    ta = cuda.tensor(A)
+    want = cuda.empty((2048,)); cuda.forward("sum", [ta], want, dim=0)
+    got = cuda.empty((2048,))
+    lib.plast_b200_peer_reduce_begin(g)
+    n = launches(lambda: cuda.forward("sum", [ta], got, dim=0))          # column reduce: strip owners exchange
+    assert lib.plast_b200_peer_reduce_end(g) == 1 and n == 1
+    assert np.array_equal(got.numpy(), want.numpy())
+    for op in ("max", "min"):
+        cuda.forward(op, [ta], want, dim=0)
+        lib.plast_b200_peer_reduce_begin(g); cuda.forward(op, [ta], got, dim=0)
+        assert lib.plast_b200_peer_reduce_end(g) == 1 and np.array_equal(got.numpy(), want.numpy())
+    # a full reduction: one thread exchanges
+    w1, g1 = cuda.empty((1,)), cuda.empty((1,))
+    cuda.forward("sum", [ta], w1, dim=pb.FULL_REDUCE)
+    lib.plast_b200_peer_reduce_begin(g)
+    n = launches(lambda: cuda.forward("sum", [ta], g1, dim=pb.FULL_REDUCE))
+    assert lib.plast_b200_peer_reduce_end(g) == 1 and n == 1 and g1.numpy()[0] == w1.numpy()[0]
+    # row sums (many outputs, one warp each): parked, exchanged by the stand-alone kernel, stored
+    B = rand_normal(1, (3000, 512))
+    tb = cuda.tensor(B)
+    want = cuda.empty((3000,)); cuda.forward("sum", [tb], want, dim=1)
+    got = cuda.empty((3000,))
+    lib.plast_b200_peer_reduce_begin(g)
+    n = launches(lambda: cuda.forward("sum", [tb], got, dim=1))
+    assert lib.plast_b200_peer_reduce_end(g) == 1 and n == 3
+    assert np.array_equal(got.numpy(), want.numpy())
+    # a backward call: both broadcast gradients are exchanged and ACCUMULATED onto what was there
+    shape, pshape = (6, 16, 14, 14), (1, 16, 1, 1)
+    X, S, Bi, G = rand_normal(2, shape), rand_normal(3, pshape), rand_normal(4, pshape), rand_normal(5, shape)
+    res = []
+    for bracket in (False, True):
+        tx, ts, tbias = cuda.tensor(X), cuda.tensor(S, requires_grad=True), cuda.tensor(Bi, requires_grad=True)
+        y = cuda.empty(shape, requires_grad=True)
+        cuda.forward("scale_bias_leaky_relu", [tx, ts, tbias], y, fval=0.0)
+        y.grad.copy_from(G)
+        ts.grad.copy_from(np.full(16, 2.0, np.float32)); tbias.grad.copy_from(np.full(16, -3.0, np.float32))
+        if bracket:
+            lib.plast_b200_peer_reduce_begin(g)
+        cuda.backward("scale_bias_leaky_relu", [tx, ts, tbias], y, fval=0.0)
+        if bracket:
+            assert lib.plast_b200_peer_reduce_end(g) == 2
+        res.append((ts.grad.numpy(), tbias.grad.numpy()))
+    assert np.array_equal(res[0][0], res[1][0]) and np.array_equal(res[0][1], res[1][1])
+    # the config-5 shape in small takes the two-stage route: only its second stage is exchanged
+    shape, pshape = (32, 128, 28, 28), (1, 128, 1, 1)
+    X, S, Bi, G = rand_normal(6, shape), rand_normal(7, pshape), rand_normal(8, pshape), rand_normal(9, shape)
+    res = []
+    for bracket in (False, True):
+        tx, ts, tbias = cuda.tensor(X), cuda.tensor(S), cuda.tensor(Bi, requires_grad=True)
+        y = cuda.empty(shape, requires_grad=True)
+        cuda.forward("scale_bias_leaky_relu", [tx, ts, tbias], y, fval=0.0)
+        y.grad.copy_from(G)
+        if bracket:
+            lib.plast_b200_peer_reduce_begin(g)
+        n = launches(lambda: cuda.backward("scale_bias_leaky_relu", [tx, ts, tbias], y, fval=0.0))
+        if bracket:
+            assert lib.plast_b200_peer_reduce_end(g) == 1 and n == 2     # rows stage + column stage with the exchange inside
+        res.append(tbias.grad.numpy())
+    assert np.array_equal(res[0], res[1])
+    # what the bracket cannot serve is refused, nothing is launched
+    lib.plast_b200_peer_reduce_begin(g)
+    n = launches(lambda: cuda.forward("mean", [ta], cuda.empty((2048,)), dim=0, check=False))
+    assert n == 0 and pb.lib.plast_b200_last_error() == 5
+    wide = cuda.tensor(rand_normal(10, (4, 9000)))
+    n = launches(lambda: cuda.forward("sum", [wide], cuda.empty((9000,)), dim=0, check=False))
+    assert n == 0 and pb.lib.plast_b200_last_error() == 5
+    assert lib.plast_b200_peer_reduce_end(g) == 0
+    pb.lib.plast_b200_clear_error()
+    # after the bracket, reductions are local again
+    n = launches(lambda: cuda.forward("sum", [tb], got, dim=1))
+    assert n == 1
+    assert lib.plast_b200_peer_group_status(g) == 0
+    lib.plast_b200_peer_group_release(g)
+    # bounded wait inside the column reduce: the other ranks never publish
+    g = lib.plast_b200_peer_group_local(3, 2000)
+    want = cuda.empty((2048,)); cuda.forward("sum", [ta], want, dim=0)
+    lib.plast_b200_peer_reduce_begin(g); cuda.forward("sum", [ta], got, dim=0); lib.plast_b200_peer_reduce_end(g)
+    assert lib.plast_b200_peer_group_status(g) == 2
+    assert np.array_equal(got.numpy(), want.numpy())                      # local values, flagged as unreduced
+    lib.plast_b200_peer_group_release(g)
+
+
 def _gpu_count():
     try:
         out = subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True, timeout=30).stdout
