@@ -367,9 +367,8 @@ int plast_b200_chain_backward_try_compile(const PlastChainStep *steps, int n_ste
 /* Tuning hook: overrides one launch-geometry choice of the reductions for the whole process
  * (key 0: log2 of the lanes across a strip of the column reduce, 1: resident CTAs per SM the
  * column reduce plans for, 2: load batches per row-worker below which a column reduce is not split
- * further, 3: resident CTAs per SM the segmented reduce plans for, 4: working-set size in MiB up to
- * which kernels use the default cache policy instead of streaming accesses, 5: order of the column
- * reduce's CTAs); a negative value restores the built-in choice. Results do not depend on the geometry beyond the order of additions. */
+ * further, 3: resident CTAs per SM the segmented reduce plans for, 5: order of the column reduce's
+ * CTAs); a negative value restores the built-in choice. Results do not depend on the geometry beyond the order of additions. */
 void plast_b200_tune(int key, long value);
 /* Test hook: runs the host-side iteration planner (drop size-1 dims, order by the strides of
  * argument `sort_arg`, merge dims every argument walks as one run) on caller-supplied metadata.

@@ -85,7 +85,7 @@ struct SblInputGrad { // du * scale
 constexpr int kRowSumThreads = 256;
 __global__ void __launch_bounds__(kRowSumThreads)
 add_leaky_relu_row_sum_kernel(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ c,
-                              float *__restrict__ s, u64 rows, u64 cols, u64 b_row_stride, float alpha, bool keep) {
+                              float *__restrict__ s, u64 rows, u64 cols, u64 b_row_stride, float alpha) {
   pdl_wait();
   pdl_launch_dependents();
   const unsigned lane = threadIdx.x & 31;
@@ -102,7 +102,7 @@ add_leaky_relu_row_sum_kernel(const float *__restrict__ a, const float *__restri
       for (int u = 0; u < 8; ++u) {
         const u64 j = j0 + lane + (u64)u * 32;
         if (j < nvec) {
-          va[u] = ld_bulk(ar + j, keep);
+          va[u] = __ldcs(ar + j);
           vb[u] = __ldg(br + j);
         }
       }
@@ -116,7 +116,7 @@ add_leaky_relu_row_sum_kernel(const float *__restrict__ a, const float *__restri
           t = va[u].y + vb[u].y; r.y = t > 0.0f ? t : t * alpha;
           t = va[u].z + vb[u].z; r.z = t > 0.0f ? t : t * alpha;
           t = va[u].w + vb[u].w; r.w = t > 0.0f ? t : t * alpha;
-          st_bulk(cr + j, r, keep);
+          __stcs(cr + j, r);
           acc += (r.x + r.y) + (r.z + r.w);
         }
       }
@@ -424,7 +424,7 @@ void plast_b200_add_leaky_relu_row_sum(const Tensor *a, const Tensor *b, Tensor 
   if (blocks > cap) blocks = cap;
   launch_k(add_leaky_relu_row_sum_kernel, dim3((unsigned)blocks), dim3(kRowSumThreads), 0, stream(),
            (const float *)a->data, (const float *)b->data, (float *)c->data, (float *)s->data, rows, cols,
-           b_full ? cols : (u64)0, slope, rows * cols * 2 * sizeof(float) <= ((u64)32 << 20));
+           b_full ? cols : (u64)0, slope);
   count_launch();
   note_kernel("add_leaky_relu_row_sum");
   end_call();
@@ -553,7 +553,7 @@ void plast_b200_chain_backward(Tensor **inputs, int n_inputs, const Tensor *outp
       }
     } else {
       float *scratch = nullptr;
-      PB_CUDA(cudaMallocAsync(&scratch, numel(dout) * sizeof(float), stream()));
+      PB_CUDA(scratch_alloc_async((void **)&scratch, numel(dout) * sizeof(float)));
       u64 cs = 1;
       for (u64 d = nd; d-- > 0;) {
         st[0][d] = cs;

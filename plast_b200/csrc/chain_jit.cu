@@ -303,7 +303,6 @@ bool launch_one(const ChainProgramView &p, const IterPlan &plan, float *out, con
   u64 n_items = 0;
   uint32_t vec_mask = 0;
   const EwChoice c = choose_ew(plan, ptrs, NIN + 1, &n_items, &vec_mask);
-  const uint32_t policy = keep_in_l2(plan, NIN + 1) ? kEwKeepInL2 : 0u;
   const u64 per_block = (u64)kEwThreads * kEwUnroll;
   const u64 blocks = (n_items + per_block - 1) / per_block;
   if (blocks > 0x7fffffffull) return false;
@@ -311,8 +310,8 @@ bool launch_one(const ChainProgramView &p, const IterPlan &plan, float *out, con
   const unsigned cmask = (NIN >= 2 && c.vec == 4 && !c.idx64 && (vec_mask == 1u || vec_mask == 2u)) ? vec_mask : 0u;
   CUfunction fn = get_kernel(p, c.vec, c.idx64, c.one_d, cmask);
   if (!fn) return false;
-  const bool ok = c.idx64 ? launch_variant<NIN, uint64_t>(fn, plan, out, ins, f, c.vec, n_items, vec_mask | policy, (unsigned)blocks)
-                          : launch_variant<NIN, uint32_t>(fn, plan, out, ins, f, c.vec, n_items, vec_mask | policy, (unsigned)blocks);
+  const bool ok = c.idx64 ? launch_variant<NIN, uint64_t>(fn, plan, out, ins, f, c.vec, n_items, vec_mask, (unsigned)blocks)
+                          : launch_variant<NIN, uint32_t>(fn, plan, out, ins, f, c.vec, n_items, vec_mask, (unsigned)blocks);
   if (ok) count_launch();
   return ok;
 }

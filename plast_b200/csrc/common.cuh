@@ -58,10 +58,17 @@ bool get_workspace(Workspace *ws);
 
 int sm_count();
 
+// Stream-ordered scratch on the library stream (cudaMallocAsync from the device's default pool;
+// release with cudaFreeAsync). The first call on a device tells the pool to keep freed memory
+// instead of returning it to the driver at the next synchronisation, so that a kernel sequence
+// that needs scratch every call (gathering a transposed operand, the argmax of a view) does not
+// pay a device allocation each time. plast_b200_release_workspace trims the pool.
+cudaError_t scratch_alloc_async(void **p, size_t bytes);
+
 // Geometry knobs a test or a tuning run may override (plast_b200_tune); negative = built-in choice.
 enum TuneKey {
   kTuneColsLogTx = 0, kTuneColsCtasPerSm = 1, kTuneColsMinBatches = 2, kTuneSegCtasPerSm = 3,
-  kTuneKeepInL2MiB = 4, kTuneColsTileMajor = 5, kTuneKeys = 8
+  kTuneColsTileMajor = 5, kTuneKeys = 8
 };
 long tuned(int key);
 

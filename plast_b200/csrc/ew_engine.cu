@@ -49,13 +49,6 @@ EwChoice choose_ew(const IterPlan &plan, const void *const *ptrs, int nargs, u64
   return c;
 }
 
-bool keep_in_l2(const IterPlan &plan, int nargs) {
-  u64 bytes = 0;
-  for (int a = 0; a < nargs; ++a) bytes += (plan.max_offset[a] + 1) * sizeof(float);
-  const u64 bound = tuned(kTuneKeepInL2MiB) >= 0 ? (u64)tuned(kTuneKeepInL2MiB) << 20 : (u64)32 << 20;
-  return bytes <= bound;
-}
-
 int choose_tiled_dim(const IterPlan &plan, int nargs, unsigned *tmask) {
   *tmask = 0;
   if (plan.ndim < 2 || plan.stride[0][0] != 1) return -1; // output must run along dim 0

@@ -31,10 +31,7 @@ struct EwChoice {
 
 EwChoice choose_ew(const IterPlan &plan, const void *const *ptrs, int nargs, u64 *n_items,
                    uint32_t *vec_mask);
-// True when everything the plan touches is small against L2 (the default bound is 32 MiB over all
-// operands; plast_b200_tune key 4 overrides it in MiB): such kernels use the default cache policy
-// so that the next kernel of a graph finds the data in L2.
-bool keep_in_l2(const IterPlan &plan, int nargs);
+
 
 template <int NARGS, typename index_t>
 void fill_offset_calc(OffsetCalc<NARGS, index_t> *oc, const IterPlan &plan, int vec) {
@@ -64,7 +61,6 @@ void launch_ew_one(const IterPlan &plan, float *out, const float *const *ins, co
   u64 n_items = 0;
   uint32_t vec_mask = 0;
   EwChoice c = choose_ew(plan, ptrs, NIN + 1, &n_items, &vec_mask);
-  const uint32_t policy = keep_in_l2(plan, NIN + 1) ? kEwKeepInL2 : 0u;
   InPtrs<NIN> ip;
   for (int a = 0; a < NIN; ++a) ip.p[a] = ins[a];
   const u64 per_block = (u64)kEwThreads * kEwUnroll;
@@ -80,7 +76,7 @@ void launch_ew_one(const IterPlan &plan, float *out, const float *const *ins, co
     OffsetCalc<NIN + 1, IDX> oc;                                                                   \
     fill_offset_calc(&oc, plan, VEC);                                                              \
     launch_k(ew_kernel<F, NIN, VEC, IDX, ONED>, grid, block, 0, s, f, out, ip, oc, (IDX)n_items,  \
-             vec_mask | policy);                                                                   \
+             vec_mask);                                                                            \
   } while (0)
 #define PB_EW_BY_VEC(IDX, ONED)                                                                    \
   do {                                                                                             \
@@ -96,7 +92,7 @@ void launch_ew_one(const IterPlan &plan, float *out, const float *const *ins, co
       OffsetCalc<NIN + 1, uint32_t> oc;
       fill_offset_calc(&oc, plan, 4);
 #define PB_EW_MASKED(ONED, CMASK)                                                                  \
-  launch_k(ew_kernel<F, NIN, 4, uint32_t, ONED, CMASK>, grid, block, 0, s, f, out, ip, oc, (uint32_t)n_items, vec_mask | policy)
+  launch_k(ew_kernel<F, NIN, 4, uint32_t, ONED, CMASK>, grid, block, 0, s, f, out, ip, oc, (uint32_t)n_items, vec_mask)
       if (vec_mask == 1u) {
         if (c.one_d) PB_EW_MASKED(true, 1u); else PB_EW_MASKED(false, 1u);
       } else {
@@ -142,7 +138,6 @@ template <int NIN> struct TiledParams {
   u64 outer_size[MAX_NDIM];
   u64 outer_stride[NIN + 1][MAX_NDIM];
   unsigned tmask;         // bit a: input a is contiguous along dT (goes through shared memory)
-  bool keep;              // default cache policy instead of streaming accesses (small working set)
   u64 tiles0;             // tiles along dim 0 (blockIdx.x = tile0 + tiles0 * tileT)
 };
 
@@ -228,7 +223,7 @@ __global__ void __launch_bounds__(256) ew_tiled4_kernel(F f, TiledParams<NIN> p)
       for (int j = 0; j < 4; ++j) {
         const u64 c0 = t0 * kTile4 + row + j * 16;
         if (cT < p.nT && c0 < p.n0)
-          v[j][a] = ld_bulk(reinterpret_cast<const float4 *>(p.in[a] + off[a + 1] + c0 * p.s0[a + 1] + cT), p.keep);
+          v[j][a] = __ldcs(reinterpret_cast<const float4 *>(p.in[a] + off[a + 1] + c0 * p.s0[a + 1] + cT));
       }
     } else {
 #pragma unroll
@@ -237,7 +232,7 @@ __global__ void __launch_bounds__(256) ew_tiled4_kernel(F f, TiledParams<NIN> p)
         if (c0v < p.n0 && cT < p.nT) {
           const float *q = p.in[a] + off[a + 1] + c0v * p.s0[a + 1] + cT * p.sT[a + 1];
           if (p.s0[a + 1] == 1) {
-            v[j][a] = ld_bulk(reinterpret_cast<const float4 *>(q), p.keep);
+            v[j][a] = __ldcs(reinterpret_cast<const float4 *>(q));
           } else { // broadcast along dim 0
             const float sc = __ldg(q);
             v[j][a] = make_float4(sc, sc, sc, sc);
@@ -278,7 +273,7 @@ __global__ void __launch_bounds__(256) ew_tiled4_kernel(F f, TiledParams<NIN> p)
         }
         r[k] = f(x);
       }
-      st_bulk(reinterpret_cast<float4 *>(p.out + off[0] + c0v + cT * p.sT[0]), make_float4(r[0], r[1], r[2], r[3]), p.keep);
+      __stcs(reinterpret_cast<float4 *>(p.out + off[0] + c0v + cT * p.sT[0]), make_float4(r[0], r[1], r[2], r[3]));
     }
   }
 }
@@ -294,7 +289,6 @@ bool launch_ew_tiled(const IterPlan &plan, float *out, const float *const *ins, 
   p.n0 = plan.size[0];
   p.nT = plan.size[dT];
   p.tmask = tmask;
-  p.keep = keep_in_l2(plan, NIN + 1);
   p.n_outer = 0;
   u64 outer = 1;
   for (int d = 1; d < plan.ndim; ++d) {
@@ -391,7 +385,7 @@ int gather_second_transposed_inputs(const IterPlan &plan, const float *const *in
     ins2[a] = ins[a];
     if (unit_dim[a] < 0 || unit_dim[a] == first) continue;
     void *buf = nullptr;
-    if (cudaMallocAsync(&buf, plan.numel * sizeof(float), stream()) != cudaSuccess) {
+    if (scratch_alloc_async(&buf, plan.numel * sizeof(float)) != cudaSuccess) {
       cudaGetLastError();
       continue; // no scratch: this input stays where it is, the generic kernel reads it in place
     }

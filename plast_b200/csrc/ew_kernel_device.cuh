@@ -28,40 +28,29 @@ template <> struct VecOf<4> { using type = float4; };
 template <> struct VecOf<2> { using type = float2; };
 template <> struct VecOf<1> { using type = float; };
 
-// Cache policy of the bulk traffic. Tensors far larger than L2 are read and written once per
-// kernel: streaming (evict-first) accesses keep them from pushing everything else out. Tensors
-// that fit L2 several times over are what the NEXT kernel of a graph reads (the output of add is
-// the input of relu): with `keep` the accesses use the default policy and the data stays in L2.
-__device__ __forceinline__ float4 ld_bulk(const float4 *p, bool keep) { return keep ? *p : __ldcs(p); }
-__device__ __forceinline__ float2 ld_bulk(const float2 *p, bool keep) { return keep ? *p : __ldcs(p); }
-__device__ __forceinline__ void st_bulk(float4 *p, float4 v, bool keep) {
-  if (keep) *p = v; else __stcs(p, v);
-}
-__device__ __forceinline__ void st_bulk(float2 *p, float2 v, bool keep) {
-  if (keep) *p = v; else __stcs(p, v);
-}
-// Bit 31 of the kernel's vec_mask argument carries the policy (the low bits are the operand mask).
-constexpr uint32_t kEwKeepInL2 = 0x80000000u;
-
-template <int VEC> __device__ __forceinline__ void load_stream(const float *p, float *v, bool keep);
-template <> __device__ __forceinline__ void load_stream<4>(const float *p, float *v, bool keep) {
-  float4 t = ld_bulk(reinterpret_cast<const float4 *>(p), keep);
+// Bulk traffic is streaming (evict-first): tensors are read and written once per kernel. A policy
+// switched per launch by working-set size (default caching for tensors that fit L2) was measured:
+// no gain on 4 MiB tensors in a stream or a graph, and the extra predicated instructions cost the
+// compute-heaviest fused chain 4 % at 1 GiB, so there is none.
+template <int VEC> __device__ __forceinline__ void load_stream(const float *p, float *v);
+template <> __device__ __forceinline__ void load_stream<4>(const float *p, float *v) {
+  float4 t = __ldcs(reinterpret_cast<const float4 *>(p));
   v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
 }
-template <> __device__ __forceinline__ void load_stream<2>(const float *p, float *v, bool keep) {
-  float2 t = ld_bulk(reinterpret_cast<const float2 *>(p), keep);
+template <> __device__ __forceinline__ void load_stream<2>(const float *p, float *v) {
+  float2 t = __ldcs(reinterpret_cast<const float2 *>(p));
   v[0] = t.x; v[1] = t.y;
 }
-template <> __device__ __forceinline__ void load_stream<1>(const float *p, float *v, bool) { v[0] = *p; }
+template <> __device__ __forceinline__ void load_stream<1>(const float *p, float *v) { v[0] = *p; }
 
-template <int VEC> __device__ __forceinline__ void store_stream(float *p, const float *v, bool keep);
-template <> __device__ __forceinline__ void store_stream<4>(float *p, const float *v, bool keep) {
-  st_bulk(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]), keep);
+template <int VEC> __device__ __forceinline__ void store_stream(float *p, const float *v);
+template <> __device__ __forceinline__ void store_stream<4>(float *p, const float *v) {
+  __stcs(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]));
 }
-template <> __device__ __forceinline__ void store_stream<2>(float *p, const float *v, bool keep) {
-  st_bulk(reinterpret_cast<float2 *>(p), make_float2(v[0], v[1]), keep);
+template <> __device__ __forceinline__ void store_stream<2>(float *p, const float *v) {
+  __stcs(reinterpret_cast<float2 *>(p), make_float2(v[0], v[1]));
 }
-template <> __device__ __forceinline__ void store_stream<1>(float *p, const float *v, bool) { *p = v[0]; }
+template <> __device__ __forceinline__ void store_stream<1>(float *p, const float *v) { *p = v[0]; }
 
 // Offsets of one item for NARGS operands. index_t = uint32_t when every count and offset fits
 // in 31 bits (multiply-shift division), uint64_t otherwise (hardware-emulated division).
@@ -109,8 +98,7 @@ ew_kernel(F f, float *out, InPtrs<NIN> in, OffsetCalc<NIN + 1, index_t> oc, inde
           uint32_t vec_mask_arg) {
   pdl_wait();
   pdl_launch_dependents();
-  const uint32_t vec_mask = CMASK ? CMASK : (vec_mask_arg & ~kEwKeepInL2);
-  const bool keep = (vec_mask_arg & kEwKeepInL2) != 0;
+  const uint32_t vec_mask = CMASK ? CMASK : vec_mask_arg;
   const index_t tile = (index_t)blockIdx.x * (kEwThreads * kEwUnroll) + threadIdx.x;
   float v[kEwUnroll][NIN][VEC];
   index_t out_off[kEwUnroll];
@@ -132,7 +120,7 @@ ew_kernel(F f, float *out, InPtrs<NIN> in, OffsetCalc<NIN + 1, index_t> oc, inde
         if (VEC == 1) {
           v[u][a][0] = *p;
         } else if (vec_mask & (1u << a)) {
-          load_stream<VEC>(p, v[u][a], keep);
+          load_stream<VEC>(p, v[u][a]);
         } else {
           const float s = __ldg(p);
 #pragma unroll
@@ -153,7 +141,7 @@ ew_kernel(F f, float *out, InPtrs<NIN> in, OffsetCalc<NIN + 1, index_t> oc, inde
         for (int a = 0; a < NIN; ++a) x[a] = v[u][a][k];
         r[k] = f(x);
       }
-      store_stream<VEC>(out + out_off[u], r, keep);
+      store_stream<VEC>(out + out_off[u], r);
     }
   }
 }

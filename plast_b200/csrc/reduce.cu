@@ -140,7 +140,27 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
     u64 min_batches = 2; // (one batch per row-worker, i.e. twice the CTAs, measured slower even at 4 MiB)
     if (tuned(kTuneColsMinBatches) > 0) min_batches = (u64)tuned(kTuneColsMinBatches);
     double best_fill = -1.0;
-    const int forced_ltx = tuned(kTuneColsLogTx) >= 5 && tuned(kTuneColsLogTx) <= 8 ? (int)tuned(kTuneColsLogTx) : 5;
+    int forced_ltx = 5;
+    {
+      // Inputs that fit L2 with a short reduced dim (the bias gradient of a 1024 x 1024 layer) are
+      // bound by the latencies of a split reduction: partial store, fence, ticket, second pass.
+      // Narrow strips (2+ lanes of float4, the other threads of the CTA as row-workers) give the
+      // same number of CTAs without a split: every CTA reduces its columns over ALL rows in at most
+      // four load batches per thread and stores the result itself.
+      u64 in_bytes = 0;
+      for (int a = 0; a < nin; ++a) in_bytes += (plan.max_offset[a + 1] + 1) * sizeof(float);
+      if (in_bytes <= ((u64)32 << 20) && g->n_red_dims <= 1) {
+        for (int ltx = 1; ltx < 5; ++ltx) {
+          const u64 tx_n = (u64)1 << ltx, ty_n = (u64)kRedThreads >> ltx;
+          const u64 tiles = g->n_kept * ceil_div(g->len0_items, tx_n);
+          if (tiles <= 2 * sms && tiles * 4 >= sms && ceil_div(g->n_red, ty_n) <= 16) {
+            forced_ltx = ltx;
+            break;
+          }
+        }
+      }
+    }
+    if (tuned(kTuneColsLogTx) >= 0 && tuned(kTuneColsLogTx) <= 8) forced_ltx = (int)tuned(kTuneColsLogTx);
     for (int ltx = forced_ltx; ltx <= forced_ltx; ++ltx) {
       const u64 tx_n = (u64)1 << ltx, ty_n = (u64)kRedThreads >> ltx;
       const u64 strips = ceil_div(g->len0_items, tx_n);
@@ -290,7 +310,7 @@ static void reduce_forward(const char *name, const Tensor **inputs, Tensor *outp
     // (cpu_utils.c:121-154 walks coordinates), which is not the order a permuted or expanded
     // view lies in memory. Gather the view into a stream-ordered scratch copy and reduce that.
     void *packed = nullptr;
-    PB_CUDA(cudaMallocAsync(&packed, numel(a) * sizeof(float), stream()));
+    PB_CUDA(scratch_alloc_async(&packed, numel(a) * sizeof(float)));
     plast_b200_pack(a, packed);
     if (!failed()) {
       Tensor dense = *a;

@@ -163,7 +163,6 @@ template <int NIN> struct RedParams {
   unsigned int *counters;
   void *partials;
   const PeerLink *peer; // not NULL: the thread that holds the single final value exchanges it across GPUs
-  bool keep;            // default cache policy instead of streaming loads (inputs small against L2)
   bool strip_major;     // cols: consecutive CTAs take neighbouring strips of the same chunk of rows
 };
 
@@ -177,12 +176,12 @@ __device__ __forceinline__ typename Op::T across_gpus(const PeerLink *link, type
 }
 
 template <int VEC>
-__device__ __forceinline__ void red_load(const float *p, bool vec, float *v, bool keep) {
+__device__ __forceinline__ void red_load(const float *p, bool vec, float *v) {
   if (VEC == 4 && vec) {
-    const float4 t = ld_bulk(reinterpret_cast<const float4 *>(p), keep);
+    const float4 t = __ldcs(reinterpret_cast<const float4 *>(p));
     v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
   } else if (VEC == 2 && vec) {
-    const float2 t = ld_bulk(reinterpret_cast<const float2 *>(p), keep);
+    const float2 t = __ldcs(reinterpret_cast<const float2 *>(p));
     v[0] = t.x; v[1] = t.y;
   } else {
     const float s = __ldg(p);
@@ -253,10 +252,10 @@ __device__ __forceinline__ void accumulate_run(const RedParams<NIN> &p, const Pr
   auto load_item = [&](int a, unsigned i, float *v) {
     if (!kStatic && p.istride0[a] == 0) return;
     if (VEC == 4) {
-      const float4 t = ld_bulk(reinterpret_cast<const float4 *>(base[a]) + i, p.keep);
+      const float4 t = __ldcs(reinterpret_cast<const float4 *>(base[a]) + i);
       v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
     } else if (VEC == 2) {
-      const float2 t = ld_bulk(reinterpret_cast<const float2 *>(base[a]) + i, p.keep);
+      const float2 t = __ldcs(reinterpret_cast<const float2 *>(base[a]) + i);
       v[0] = t.x; v[1] = t.y;
     } else {
       v[0] = __ldg(base[a] + (u64)i * p.istride0[a]);
@@ -481,10 +480,10 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
     auto load_row = [&](const float *q, int a, float *v) {
       if ((p.vec_mask >> a) & 1u) {
         if (VEC == 4) {
-          const float4 t = ld_bulk(reinterpret_cast<const float4 *>(q), p.keep);
+          const float4 t = __ldcs(reinterpret_cast<const float4 *>(q));
           v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
         } else if (VEC == 2) {
-          const float2 t = ld_bulk(reinterpret_cast<const float2 *>(q), p.keep);
+          const float2 t = __ldcs(reinterpret_cast<const float2 *>(q));
           v[0] = t.x; v[1] = t.y;
         } else {
           v[0] = __ldg(q);
@@ -542,7 +541,7 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
           p.red.offsets(r_begin + r, &dummy, ioff);
 #pragma unroll
           for (int a = 0; a < NIN; ++a)
-            red_load<VEC>(p.in[a] + ioff[a], (p.vec_mask >> a) & 1u, v[u][a], p.keep);
+            red_load<VEC>(p.in[a] + ioff[a], (p.vec_mask >> a) & 1u, v[u][a]);
         }
       }
 #pragma unroll
@@ -560,25 +559,34 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
       }
     }
   }
-  // Combine the row-workers in shared memory: worker t holds reduced indices = t (mod ty_n).
+  // Combine the row-workers in shared memory (worker t holds reduced indices = t (mod ty_n)) as a
+  // tree in a fixed order: a narrow strip has up to 256 workers, too many for one thread to walk.
+  // The result is valid in the threads of worker 0.
   __shared__ T strip_vals[kRedThreads * VEC];
-  T r[VEC];
-  if (ty_n > 1) {
+  auto combine_workers = [&](T(&vals)[VEC]) {
+    if (ty_n == 1) return;
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) strip_vals[((ty * VEC + k) << p.log_tx) + lane] = acc[k];
+    for (int k = 0; k < VEC; ++k) strip_vals[((ty * VEC + k) << p.log_tx) + lane] = vals[k];
     __syncthreads();
+    for (unsigned s = ty_n >> 1; s > 0; s >>= 1) {
+      if (ty < s) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          const unsigned mine = ((ty * VEC + k) << p.log_tx) + lane, other = (((ty + s) * VEC + k) << p.log_tx) + lane;
+          strip_vals[mine] = Op::combine(strip_vals[mine], strip_vals[other]);
+        }
+      }
+      __syncthreads();
+    }
     if (ty == 0) {
 #pragma unroll
-      for (int k = 0; k < VEC; ++k) {
-        r[k] = strip_vals[(k << p.log_tx) + lane];
-        for (unsigned t = 1; t < ty_n; ++t)
-          r[k] = Op::combine(r[k], strip_vals[((t * VEC + k) << p.log_tx) + lane]);
-      }
+      for (int k = 0; k < VEC; ++k) vals[k] = strip_vals[(k << p.log_tx) + lane];
     }
-  } else {
+  };
+  T r[VEC];
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) r[k] = acc[k];
-  }
+  for (int k = 0; k < VEC; ++k) r[k] = acc[k];
+  combine_workers(r);
   typename Op::Out *out = (typename Op::Out *)p.out;
   // With a link attached (the host only does that for a single row of strips whose outputs are
   // contiguous, at most PLAST_B200_PEER_MAX_FLOATS of them) the threads that hold a strip's final
@@ -619,18 +627,8 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
       for (unsigned c = ty; c < p.splits; c += ty_n)
         fin[k] = Op::combine(fin[k], Op::load_cg(partials + (((u64)c * VEC + k) << p.log_tx) + lane));
   }
-  if (ty_n > 1) {
-    __syncthreads();
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) strip_vals[((ty * VEC + k) << p.log_tx) + lane] = fin[k];
-    __syncthreads();
-    if (ty == 0) {
-#pragma unroll
-      for (int k = 0; k < VEC; ++k)
-        for (unsigned t = 1; t < ty_n; ++t)
-          fin[k] = Op::combine(fin[k], strip_vals[((t * VEC + k) << p.log_tx) + lane]);
-    }
-  }
+  __syncthreads(); // the shared strip is reused
+  combine_workers(fin);
   across_gpus_strip(fin);
   if (ty == 0 && live) {
 #pragma unroll
@@ -775,13 +773,7 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   p.counters = nullptr;
   p.partials = nullptr;
   p.peer = nullptr;
-  {
-    u64 in_bytes = 0;
-    for (int a = 0; a < NIN; ++a) in_bytes += (plan.max_offset[a + 1] + 1) * sizeof(float);
-    const u64 bound = tuned(kTuneKeepInL2MiB) >= 0 ? (u64)tuned(kTuneKeepInL2MiB) << 20 : (u64)32 << 20;
-    p.keep = in_bytes <= bound;
-  }
-  p.strip_major = tuned(kTuneColsTileMajor) != 0; // default (-1) and 1: strips of a chunk are neighbours
+  p.strip_major = tuned(kTuneColsTileMajor) > 0; // measured: the order of the CTAs makes no difference
   // a pending cross-GPU exchange rides on the kernel whose last CTA holds THE final value
   if (Op::kPeerOp >= 0 && g.kind == kRedSeg && g.n_kept == 1 && !take_peer_link(kPeerFullReduce, &p.peer, nullptr))
     p.peer = nullptr;

@@ -114,6 +114,21 @@ bool pdl_enabled() {
   return on;
 }
 
+cudaError_t scratch_alloc_async(void **p, size_t bytes) {
+  static bool configured[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && !configured[dev]) {
+    cudaMemPool_t pool = nullptr;
+    if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+      unsigned long long keep_all = ~0ull;
+      cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep_all);
+    }
+    cudaGetLastError();
+    configured[dev] = true;
+  }
+  return cudaMallocAsync(p, bytes ? bytes : 1, stream());
+}
+
 int sm_count() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
@@ -195,6 +210,11 @@ void plast_b200_release_workspace(void) {
   for (int d = 0; d < pb::kMaxDevices; ++d) {
     if (pb::g_ws[d].counters) {
       cudaSetDevice(d);
+      cudaMemPool_t pool = nullptr;
+      if (cudaDeviceGetDefaultMemPool(&pool, d) == cudaSuccess) {
+        cudaDeviceSynchronize();
+        cudaMemPoolTrimTo(pool, 0);
+      }
       cudaFree(pb::g_ws[d].counters);
       pb::g_ws[d] = pb::Workspace{};
     }

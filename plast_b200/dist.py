@@ -391,7 +391,25 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
                verify(fused_sum, one, local_full("sum"), "sum", abs_all))
         timeit("config4_full_max_fused_with_exchange", fused_max, M * M * 4 + 4,
                verify(fused_max, one, local_full("max"), "max"))
+
+        def fused_axis0():
+            with peer.reducing():
+                pb.forward("sum", [tX], tcol, dim=0, check=False)
+        timeit("config4_sum_axis0_fused_with_exchange", fused_axis0, (M * M + M) * 4,
+               verify(fused_axis0, col, lambda: pb.forward("sum", [tX], tcol, dim=0, check=False), "sum", abs_cols))
     del X
+    # ... and sharded along the KEPT dim instead (columns): every rank sums its own strip of columns
+    # of the row-major matrix, a strided view [M, M / world] with row stride M; no exchange at all
+    cs = shard_dim(M, rank, world)
+    gen.manual_seed(150)
+    Xfull = torch.rand((M, M), generator=gen, device=dev) * 2 - 1
+    tXc = pb.Tensor.wrap_pointer(Xfull.data_ptr() + 4 * cs.start, [M, cs.count], strides=[M, 1], owner=Xfull)
+    colc = torch.zeros(max(cs.count, 1), device=dev)
+    tcolc = wrap(colc, shape=[cs.count])
+    if cs.count > 0:
+        timeit("config4_sum_axis0_column_sharded_no_exchange",
+               lambda: pb.forward("sum", [tXc], tcolc, dim=0, check=False), (M * M + M) * 4)
+    del Xfull
 
     # config 3: cross-entropy mean over row-sharded logits -> 4-byte all-reduce of the loss SUM
     R, Cn = 65536, 4096
@@ -470,10 +488,41 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
         timeit("config5_bias_grad+peer_exchange", bias_grad, 2 * total * 4 + 1024,
                verify(bias_grad, gB, bias_grad_local, "sum", bias_terms))
         use_peer_exchange(None)
+
+        def bias_grad_fused():
+            gB.zero_()
+            with peer.reducing():
+                pb.backward("scale_bias_leaky_relu", [tX5, tS, tBg], tYg, fval=0.0, check=False)
+        timeit("config5_bias_grad_fused_with_exchange", bias_grad_fused, 2 * total * 4 + 1024,
+               verify(bias_grad_fused, gB, bias_grad_local, "sum", bias_terms))
         status = peer.status()
         if status != 0:
             rows.append({"op": "peer_exchange_status", "n_gpus": world, "status": status})
         peer.close()
     del X, G, Yv
+    # ... and sharded along the KEPT dim instead (channels): a strided view [N, Ch / world, H, W] of
+    # the full activation; every rank reduces its own channels over (N, H, W); no exchange at all
+    ch = shard_dim(Ch, rank, world)
+    if ch.count > 0 and not out_of_time():
+        gen.manual_seed(350)
+        Gf = torch.randn((N, Ch, H, W), generator=gen, device=dev)
+        Yf = torch.randn((N, Ch, H, W), generator=gen, device=dev)
+        Xf = Yf                                                      # only read when the scale needs a gradient
+        full_strides = [Ch * H * W, H * W, W, 1]
+        view = lambda t: pb.Tensor.wrap_pointer(t.data_ptr() + 4 * ch.start * H * W, [N, ch.count, H, W],
+                                                strides=full_strides, owner=t)
+        Sc = torch.rand((1, ch.count, 1, 1), generator=gen, device=dev) - 0.5
+        Bc = torch.rand((1, ch.count, 1, 1), generator=gen, device=dev) - 0.5
+        gBc = torch.zeros((1, ch.count, 1, 1), device=dev)
+        tXf, tSc = view(Xf), wrap(Sc)
+        tBc = wrap(Bc); tBc.c.requires_grad = True
+        tgc = wrap(gBc); tBc.grad = tgc; tBc.c.grad = C.pointer(tgc.c)
+        tYf = view(Yf); tGf = view(Gf); tYf.grad = tGf; tYf.c.grad = C.pointer(tGf.c)
+
+        def bias_grad_channels():
+            gBc.zero_()
+            pb.backward("scale_bias_leaky_relu", [tXf, tSc, tBc], tYf, fval=0.0, check=False)
+        timeit("config5_bias_grad_channel_sharded_no_exchange", bias_grad_channels, 2 * total * 4 + 1024)
+        del Gf, Yf
     torch.cuda.synchronize()
     return rows

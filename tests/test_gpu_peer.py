@@ -266,10 +266,10 @@ def test_reductions_inside_the_bracket_are_exchanged_fused_or_parked(cuda):
     assert np.array_equal(res[0], res[1])
     # what the bracket cannot serve is refused, nothing is launched
     lib.plast_b200_peer_reduce_begin(g)
-    n = launches(lambda: cuda.forward("mean", [ta], cuda.empty((2048,)), dim=0, check=False))
+    n = launches(lambda: pb.forward("mean", [ta], cuda.empty((2048,)), dim=0, check=False))
     assert n == 0 and pb.lib.plast_b200_last_error() == 5
     wide = cuda.tensor(rand_normal(10, (4, 9000)))
-    n = launches(lambda: cuda.forward("sum", [wide], cuda.empty((9000,)), dim=0, check=False))
+    n = launches(lambda: pb.forward("sum", [wide], cuda.empty((9000,)), dim=0, check=False))
     assert n == 0 and pb.lib.plast_b200_last_error() == 5
     assert lib.plast_b200_peer_reduce_end(g) == 0
     pb.lib.plast_b200_clear_error()
