@@ -112,9 +112,10 @@ u32 plast_b200_fuse_graph_ex(DAG *dag, unsigned flags);
 void chain_cuda_forward(const Tensor **inputs, Tensor *output, KernelParams params);
 void chain_cuda_backward(Tensor **inputs, const Tensor *output, KernelParams params);
 
-/* A DAG as one CUDA graph. plast_b200_dag_capture records the kernels of every node (forward
- * order, or reverse order with the nodes' backward kernels when backward != 0) WITHOUT running
- * them and returns a handle; plast_b200_dag_replay launches the whole recording on the library
+/* A DAG as one CUDA graph. plast_b200_dag_capture records the kernels of every node (backward == 0:
+ * forward order; 1: reverse order with the nodes' backward kernels; 2: the forward pass followed by
+ * the backward pass, a whole training step whose upstream gradient is already in place) WITHOUT
+ * running them and returns a handle; plast_b200_dag_replay launches the whole recording on the library
  * stream. This is what the scheduler's JIT mode wants for a cached DAG it executes again and again
  * on the same tensors (src/scheduler/scheduler.c:17-27): per replay one launch instead of one
  * per node, which is the bound for small graphs. Every node must be a CUDA node whose kernel is

@@ -43,8 +43,9 @@ PlastDagGraph *plast_b200_dag_capture(DAG *dag, int backward) {
   }
   for (u32 i = 0; i < dag->count; ++i) {
     const Node *n = dag->nodes[i];
-    const void *fn = n ? (backward ? (const void *)n->op.cuda_backward : (const void *)n->op.cuda_forward) : nullptr;
-    if (!n || !n->output || n->output->device != CUDA || !ours(fn)) {
+    const bool fwd_ok = n && (backward == 1 || ours((const void *)n->op.cuda_forward));
+    const bool bwd_ok = n && (backward == 0 || ours((const void *)n->op.cuda_backward));
+    if (!n || !n->output || n->output->device != CUDA || !fwd_ok || !bwd_ok) {
       set_error(PLAST_B200_ERR_UNSUPPORTED, "dag capture: node %u is not a CUDA node of this library", i);
       return nullptr;
     }
@@ -65,13 +66,18 @@ PlastDagGraph *plast_b200_dag_capture(DAG *dag, int backward) {
   int failed_node = -1;
   char failed_message[256] = "";
   if (ok) {
-    for (u32 k = 0; k < dag->count && failed_node < 0; ++k) {
-      Node *n = dag->nodes[backward ? dag->count - 1 - k : k];
-      if (backward) n->op.cuda_backward(n->inputs, n->output, n->params);
-      else n->op.cuda_forward((const Tensor **)n->inputs, n->output, n->params);
-      if (plast_b200_last_error() != PLAST_B200_OK) {
-        failed_node = (int)k;
-        strncpy(failed_message, plast_b200_last_error_message(), sizeof(failed_message) - 1);
+    // mode 0: forward pass; 1: backward pass; 2: forward pass followed by the backward pass
+    for (int pass = 0; pass < 2; ++pass) {
+      const bool run_backward = pass == 1;
+      if ((run_backward && backward == 0) || (!run_backward && backward == 1)) continue;
+      for (u32 k = 0; k < dag->count && failed_node < 0; ++k) {
+        Node *n = dag->nodes[run_backward ? dag->count - 1 - k : k];
+        if (run_backward) n->op.cuda_backward(n->inputs, n->output, n->params);
+        else n->op.cuda_forward((const Tensor **)n->inputs, n->output, n->params);
+        if (plast_b200_last_error() != PLAST_B200_OK) {
+          failed_node = (int)k;
+          strncpy(failed_message, plast_b200_last_error_message(), sizeof(failed_message) - 1);
+        }
       }
     }
     const cudaError_t e = cudaStreamEndCapture(capture_stream, &graph);

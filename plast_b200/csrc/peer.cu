@@ -27,7 +27,7 @@ __global__ void __launch_bounds__(kPeerThreads)
 peer_all_reduce_kernel(const PeerLink *__restrict__ link, float *inout, unsigned n, int op) {
   const int rank = link->rank, world = link->world;
   unsigned int *words = link->words;
-  const unsigned max_spins = link->max_spins;
+  const unsigned max_spins = peer_spin_limit(*link);
   // words[0]: status (set on a give-up), words[1]: sequence counter, words[2]: CTA ticket.
   // The sequence number lives on the device and advances once per launch, so a launch recorded in
   // a CUDA graph stays correct however often the graph is replayed (every rank makes the same

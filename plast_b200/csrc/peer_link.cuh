@@ -26,6 +26,12 @@ __device__ __forceinline__ unsigned long long load_packet(const unsigned long lo
 __device__ __forceinline__ void store_packet(unsigned long long *p, unsigned long long v) {
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+// Polls allowed per wait. Once a wait of this group has run out (the status word is set) every
+// later wait gives up after a few polls: a peer that is gone stays gone, and a step that would
+// otherwise spend a second per packet finishes at once with its local values and the status set.
+__device__ __forceinline__ unsigned peer_spin_limit(const PeerLink &link) {
+  return *(volatile unsigned int *)&link.words[0] != 0u ? 256u : link.max_spins;
+}
 __device__ __forceinline__ float peer_combine(int op, float a, float b) {
   return op == PLAST_B200_PEER_SUM ? a + b : (op == PLAST_B200_PEER_MAX ? (a > b ? a : b) : (a < b ? a : b));
 }
@@ -46,12 +52,13 @@ __device__ __forceinline__ float peer_exchange_scalar(const PeerLink &link, floa
   const unsigned long long *mine = link.packets[link.rank] + parity_base;
   float acc = 0.0f;
   bool complete = true;
+  const unsigned spin_limit = peer_spin_limit(link);
   for (int p = 0; p < link.world && complete; ++p) {
     const unsigned long long *slot = mine + (size_t)p * PLAST_B200_PEER_MAX_FLOATS;
     unsigned long long got = load_packet(slot);
     unsigned spins = 0;
     while ((unsigned)(got >> 32) != seq) {
-      if (++spins > link.max_spins) {
+      if (++spins > spin_limit) {
         atomicCAS(&link.words[0], 0u, 1u + (unsigned)p);
         complete = false;
         break;
@@ -86,6 +93,7 @@ __device__ __forceinline__ void peer_exchange_strip(const PeerLink &link, float 
   const unsigned long long *mine = link.packets[link.rank] + parity_base + elem;
 #pragma unroll
   for (int k = 0; k < VEC; ++k) {
+    const unsigned spin_limit = peer_spin_limit(link);
     float acc = 0.0f;
     bool complete = true;
     for (int p = 0; p < link.world && complete; ++p) {
@@ -93,7 +101,7 @@ __device__ __forceinline__ void peer_exchange_strip(const PeerLink &link, float 
       unsigned long long got = load_packet(slot);
       unsigned spins = 0;
       while ((unsigned)(got >> 32) != seq) {
-        if (++spins > link.max_spins) {
+        if (++spins > spin_limit) {
           atomicCAS(&link.words[0], 0u, 1u + (unsigned)p);
           complete = false;
           break;

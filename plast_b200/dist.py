@@ -469,6 +469,8 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
     tg = wrap(gB); tBg.grad = tg; tBg.c.grad = C.pointer(tg.c)
     tYg = wrap(Yv); tG = wrap(G); tYg.grad = tG; tYg.c.grad = C.pointer(tG.c)
 
+    # The backward ACCUMULATES into bias.grad; a step that all-reduces the gradient buffer itself
+    # needs it zeroed first (one more small kernel), the bracket form exchanges only the new sum.
     def bias_grad():
         gB.zero_()
         pb.backward("scale_bias_leaky_relu", [tX5, tS, tBg], tYg, fval=0.0, check=False)
@@ -490,11 +492,14 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
         use_peer_exchange(None)
 
         def bias_grad_fused():
-            gB.zero_()
             with peer.reducing():
                 pb.backward("scale_bias_leaky_relu", [tX5, tS, tBg], tYg, fval=0.0, check=False)
+
+        def bias_grad_fused_from_zero():
+            gB.zero_()
+            bias_grad_fused()
         timeit("config5_bias_grad_fused_with_exchange", bias_grad_fused, 2 * total * 4 + 1024,
-               verify(bias_grad_fused, gB, bias_grad_local, "sum", bias_terms))
+               verify(bias_grad_fused_from_zero, gB, bias_grad_local, "sum", bias_terms))
         status = peer.status()
         if status != 0:
             rows.append({"op": "peer_exchange_status", "n_gpus": world, "status": status})
@@ -520,7 +525,6 @@ def sharded_reduction_table(torch, dist, pb, dev, peak_gbs: float, reps: int = 1
         tYf = view(Yf); tGf = view(Gf); tYf.grad = tGf; tYf.c.grad = C.pointer(tGf.c)
 
         def bias_grad_channels():
-            gBc.zero_()
             pb.backward("scale_bias_leaky_relu", [tXf, tSc, tBc], tYf, fval=0.0, check=False)
         timeit("config5_bias_grad_channel_sharded_no_exchange", bias_grad_channels, 2 * total * 4 + 1024)
         del Gf, Yf

@@ -68,9 +68,10 @@ lib.plast_b200_dag_graph_release.argtypes = [C.c_void_p]
 lib.plast_b200_dag_graph_release.restype = None
 
 
-def capture(dag: "CDAG", backward: bool = False):
-    """Records the DAG's kernels into a CUDA graph; returns an opaque handle (None on failure,
-    see plast_b200.check_error)."""
+def capture(dag: "CDAG", backward=False):
+    """Records the DAG's kernels into a CUDA graph (backward: False / 0 forward pass, True / 1
+    backward pass, 2 forward then backward); returns an opaque handle (None on failure, see
+    plast_b200.check_error)."""
     return lib.plast_b200_dag_capture(C.byref(dag), int(backward))
 
 

@@ -149,6 +149,29 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
             timeit(1, "forward_dag_as_cuda_graph", lambda: G1.replay(h1), (2 * M * N + N + M * N + M) * F, M * N, ws,
                    capture=False)
         timeit(1, "forward_dag_node_by_node", lambda: G1.dag_forward(dag1), (2 * M * N + N + M * N + M) * F, M * N, ws)
+        # the whole training step of the configuration (forward C and s, backward from the upstream
+        # gradient on C into b.grad) as ONE replayed CUDA graph: fused add + relu, row sum, their two
+        # backward nodes (the sum's contributes a zero gradient here)
+        gb2, gs2 = torch.zeros((1, N), device=dev), torch.zeros(M, device=dev)
+        tb2 = wrap(b); tb2.c.requires_grad = True
+        gtb2 = wrap(gb2); tb2.grad = gtb2; tb2.c.grad = C.pointer(gtb2.c)
+        tAB2 = wrap(AB); tAB2.c.requires_grad = True
+        gAB2 = wrap(torch.zeros_like(A)); tAB2.grad = gAB2; tAB2.c.grad = C.pointer(gAB2.c)
+        tC2 = wrap(Cc); tC2.c.requires_grad = True
+        gC2 = wrap(G); tC2.grad = gC2; tC2.c.grad = C.pointer(gC2.c)
+        ts2 = wrap(s); ts2.c.requires_grad = True
+        gts2 = wrap(gs2); ts2.grad = gts2; ts2.c.grad = C.pointer(gts2.c)
+        g2 = G1.Graph()
+        g2.node("ADD", [tA, tb2], tAB2); g2.node("LEAKY_RELU", [tAB2], tC2, fval=0.0); g2.node("SUM", [tC2], ts2, dim=1)
+        dag2 = g2.dag()
+        G1.fuse(dag2, G1.FUSE_CHAINS_WITH_GRAD)
+        G1.dag_forward(dag2); G1.dag_backward(dag2)
+        h2 = G1.capture(dag2, 2)
+        step_bytes = (2 * M * N + N + M * N + M) * F + (M * N + M) * F + (2 * M * N + 2 * N) * F
+        if h2:
+            timeit(1, "forward_and_backward_dag_as_cuda_graph", lambda: G1.replay(h2), step_bytes, M * N, ws, capture=False)
+        timeit(1, "forward_and_backward_dag_node_by_node", lambda: (G1.dag_forward(dag2), G1.dag_backward(dag2)),
+               step_bytes, M * N, ws)
         tbg = wrap(b); tbg.c.requires_grad = True
         gtb = wrap(gb); tbg.grad = gtb; tbg.c.grad = C.pointer(gtb.c)
         tCg = wrap(Cc); gC = wrap(G); tCg.grad = gC; tCg.c.grad = C.pointer(gC.c)
