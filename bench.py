@@ -168,8 +168,11 @@ def cpu_per_op_baselines(rows):
     fns[(1, "fused_add_relu")] = (lambda: (add1(), relu1()), 1.0, full1 + ", as add -> leaky_relu")
     for name in ("fused_fwd_C_and_row_sum", "forward_dag_as_cuda_graph", "forward_dag_node_by_node"):
         fns[(1, name)] = (lambda: (add1(), relu1(), sum1()), 1.0, full1 + ", as add -> leaky_relu -> sum")
-    fns[(1, "fused_bwd_grad_b")] = (lambda: (be.backward("leaky_relu", [AB], Cc, fval=0.0), be.backward("add", [A, b], AB)),
-                                    1.0, full1 + ", as leaky_relu backward -> add backward")
+    bwd1 = lambda: (be.backward("leaky_relu", [AB], Cc, fval=0.0), be.backward("add", [A, b], AB))
+    fns[(1, "fused_bwd_grad_b")] = (bwd1, 1.0, full1 + ", as leaky_relu backward -> add backward")
+    for name in ("forward_and_backward_dag_as_cuda_graph", "forward_and_backward_dag_node_by_node"):
+        fns[(1, name)] = (lambda: (add1(), relu1(), sum1(), bwd1()), 1.0,
+                          full1 + ", as add -> leaky_relu -> sum, then leaky_relu backward -> add backward")
 
     # config 2: 2^24 of the 2^28 elements
     n2, full2 = 1 << 24, float(1 << 28)
@@ -245,6 +248,14 @@ def cpu_per_op_baselines(rows):
         fns[(4, "full_sum" + name)] = (lambda tin=tin: be.forward("sum", [tin], sc3, dim=FULL), frac4, smp4)
         fns[(4, "full_max" + name)] = (lambda tin=tin: be.forward("max", [tin], sc3, dim=FULL), frac4, smp4)
     fns[(4, "add_transposed_view_plus_contiguous")] = (lambda: be.forward("add", [X4T, Y4], Z4), frac4, smp4)
+    Y4T = Y4.transpose(0, 1)
+    fns[(4, "add_of_two_transposed_views")] = (lambda: be.forward("add", [X4T, Y4T], Z4), frac4, smp4)
+    I3, J3, K3 = 64, 256, 1024                       # the same 2^24 elements seen as a 3-D tensor
+    a3 = X4.view([I3, J3, K3], [1, I3, I3 * J3])
+    b3 = Y4.view([I3, J3, K3], [K3 * J3, 1, J3])
+    z3 = Z4.view([I3, J3, K3], [J3 * K3, K3, 1])
+    fns[(4, "add_inputs_transposed_along_two_different_dims")] = (lambda: be.forward("add", [a3, b3], z3), frac4,
+                                                                  smp4 + " seen as [64, 256, 1024]")
     if kind == "reference":
         class Pack(C.Structure):
             _fields_ = [("data", C.c_void_p), ("_buf", C.c_void_p)]
