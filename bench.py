@@ -45,8 +45,8 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM traffic of ONE launch of the chain kernel, from an ncu capture of this file's own command at
 # --elems 67108864 (dram__bytes_read.sum / dram__bytes_write.sum, three launches averaged; the
 # 2^28-element launch holds 3 GiB, beyond what a multi-pass capture may save and restore):
-NCU_READ_BYTES_AT_2P26 = 536_896_683      # algorithmic 536 870 912: every operand byte crosses DRAM once
-NCU_WRITE_BYTES_AT_2P26 = 224_318_720     # algorithmic 268 435 456: the rest is still dirty in L2 at kernel end
+NCU_READ_BYTES_AT_2P26 = 536_909_227      # algorithmic 536 870 912: every operand byte crosses DRAM once
+NCU_WRITE_BYTES_AT_2P26 = 224_770_048     # algorithmic 268 435 456: the rest is still dirty in L2 at kernel end
 L2_DIRTY_RESIDUE_BYTES = (1 << 28) - NCU_WRITE_BYTES_AT_2P26   # ~44 MB, bounded by L2, does not grow with n
 
 CHAIN_STEPS = [("neg", 0, 0, 0.0), ("exp", 2, 0, 0.0), ("add_scalar", 3, 0, 1.0),

@@ -216,6 +216,15 @@ def test_reductions_inside_the_bracket_are_exchanged_fused_or_parked(cuda):
         cuda.forward(op, [ta], want, dim=0)
         lib.plast_b200_peer_reduce_begin(g); cuda.forward(op, [ta], got, dim=0)
         assert lib.plast_b200_peer_reduce_end(g) == 1 and np.array_equal(got.numpy(), want.numpy())
+    # a small matrix takes narrow strips (two lanes per CTA, no split): the two strip owners exchange
+    S = rand_normal(11, (1024, 1024))
+    tsm = cuda.tensor(S)
+    want = cuda.empty((1024,)); cuda.forward("sum", [tsm], want, dim=0)
+    got_s = cuda.empty((1024,))
+    lib.plast_b200_peer_reduce_begin(g)
+    n = launches(lambda: cuda.forward("sum", [tsm], got_s, dim=0))
+    assert lib.plast_b200_peer_reduce_end(g) == 1 and n == 1
+    assert np.array_equal(got_s.numpy(), want.numpy())
     # a full reduction: one thread exchanges
     w1, g1 = cuda.empty((1,)), cuda.empty((1,))
     cuda.forward("sum", [ta], w1, dim=pb.FULL_REDUCE)
