@@ -164,6 +164,7 @@ template <int NIN> struct RedParams {
   void *partials;
   const PeerLink *peer; // not NULL: the thread that holds the single final value exchanges it across GPUs
   bool strip_major;     // cols: consecutive CTAs take neighbouring strips of the same chunk of rows
+  unsigned prefetch_batches; // cols: load batches ahead of which a row-worker asks L2 for its rows (0 = off)
 };
 
 // The final value of a single-output reduction, combined across GPUs when a link is attached.
@@ -495,7 +496,21 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
       }
     };
     unsigned rb = ty;
+    // bytes of one row of the strip (the last strip of a row may be narrower)
+    const unsigned strip_bytes =
+        (unsigned)((p.len0 - (strip << p.log_tx) < tx_n ? p.len0 - (strip << p.log_tx) : tx_n) * VEC * sizeof(float));
     for (; rb + (kRedUnroll - 1) * ty_n < n; rb += kRedUnroll * ty_n) {
+      if (VEC == 4 && p.prefetch_batches != 0 && lane == 0) {
+        // the rows this worker reads `prefetch_batches` batches from now, one bulk prefetch per row
+        const unsigned ahead = p.prefetch_batches * kRedUnroll;
+#pragma unroll
+        for (int u = 0; u < kRedUnroll; ++u)
+          if (rb + (ahead + u) * ty_n < n) {
+#pragma unroll
+            for (int a = 0; a < NIN; ++a)
+              if ((p.vec_mask >> a) & 1u) prefetch_l2(ptr[a] + (u64)(ahead + u) * step[a], strip_bytes);
+          }
+      }
       float v[kRedUnroll][NIN][VEC];
 #pragma unroll
       for (int u = 0; u < kRedUnroll; ++u)
@@ -774,6 +789,7 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   p.partials = nullptr;
   p.peer = nullptr;
   p.strip_major = tuned(kTuneColsTileMajor) > 0; // measured: the order of the CTAs makes no difference
+  p.prefetch_batches = tuned(kTuneColsPrefetch) > 0 ? (unsigned)tuned(kTuneColsPrefetch) : 0u;
   // a pending cross-GPU exchange rides on the kernel whose last CTA holds THE final value
   if (Op::kPeerOp >= 0 && g.kind == kRedSeg && g.n_kept == 1 && !take_peer_link(kPeerFullReduce, &p.peer, nullptr))
     p.peer = nullptr;

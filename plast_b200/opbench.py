@@ -66,7 +66,10 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
             e1.record()
             torch.cuda.synchronize()
             times.append(e0.elapsed_time(e1) / inner)
-        ms = float(np.median(times)) if times else float('nan')
+        if not times:   # --op-reps 0: every op launched, nothing timed (the profiler-capture mode)
+            rows.append({"config": cfg, "op": name, "kernel": kernel, "bytes": int(nbytes), "timed": False})
+            return
+        ms = float(np.median(times))
         gbs = nbytes / (ms * 1e-3) / 1e9
         row = {"config": cfg, "op": name, "kernel": kernel, "ms": round(ms, 5),
                "bytes": int(nbytes), "GBps": round(gbs, 1), "elements_per_s": elems / (ms * 1e-3),
