@@ -368,7 +368,9 @@ int plast_b200_chain_backward_try_compile(const PlastChainStep *steps, int n_ste
  * (key 0: log2 of the lanes across a strip of the column reduce, 1: resident CTAs per SM the
  * column reduce plans for, 2: load batches per row-worker below which a column reduce is not split
  * further, 3: resident CTAs per SM the segmented reduce plans for, 5: order of the column reduce's
- * CTAs); a negative value restores the built-in choice. Results do not depend on the geometry beyond the order of additions. */
+ * CTAs, 6 / 7: L2 prefetch distance of the column sweep in load batches and the number of batches
+ * per chunk that prefetch, 8: prefetch distance of the segmented reduce in trips, 9: log2 of the
+ * threads that share a segment); a negative value restores the built-in choice. Results do not depend on the geometry beyond the order of additions. */
 void plast_b200_tune(int key, long value);
 /* Test hook: runs the host-side iteration planner (drop size-1 dims, order by the strides of
  * argument `sort_arg`, merge dims every argument walks as one run) on caller-supplied metadata.

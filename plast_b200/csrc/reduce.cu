@@ -105,6 +105,7 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
       g->seg_len = seg_cap;
       g->nsplit0 = ceil_div(g->len0_items, g->seg_len);
       g->log_tx = 8;
+      if (tuned(kTuneSegLogTx) >= 5 && tuned(kTuneSegLogTx) <= 8) g->log_tx = (int)tuned(kTuneSegLogTx);
     }
     g->nseg = g->nsplit0 * g->n_red;
     const u64 ty_n = (u64)kRedThreads >> g->log_tx;

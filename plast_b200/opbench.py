@@ -24,7 +24,22 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
     fewer so that the device memory a multi-pass capture has to save stays small)."""
     gen = torch.Generator(device=dev)
     flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    flush_sink = torch.zeros(1, device=dev)
     rows = []
+
+    def read_sweep():
+        """Fills L2 with CLEAN lines of another buffer (a write sweep would leave dirty lines whose
+        write-back is then billed to the kernel under test)."""
+        flush_sink.copy_(flush_buf.view(torch.int32).sum().float().reshape(1))
+
+    # what an event pair around nothing reads after such a sweep (subtract it from cold_ms by eye)
+    pair = []
+    for _ in range(5):
+        read_sweep()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); e1.record(); torch.cuda.synchronize()
+        pair.append(e0.elapsed_time(e1))
+    empty_pair_ms = float(np.median(pair))
 
     def wrap(t, shape=None, strides=None, dtype=pb.FLOAT32):
         shape = list(t.shape) if shape is None else shape
@@ -71,10 +86,27 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
             return
         ms = float(np.median(times))
         gbs = nbytes / (ms * 1e-3) / 1e9
+        cold = None
+        if not flush and working_set < (1 << 30) and reps > 0:
+            # Working sets between L2 and 1 GiB: part of the tensor survives in the 126 MB L2 from one
+            # back-to-back launch to the next. cold_ms: ONE launch per event pair after a read sweep
+            # of a 512 MiB buffer (includes the event pair's own ~2.6 us; the timer ticks in ~2 us).
+            ct = []
+            for _ in range(max(reps, 9)):
+                read_sweep()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); fn(); e1.record()
+                torch.cuda.synchronize()
+                ct.append(e0.elapsed_time(e1))
+            cold = float(np.median(ct))
         row = {"config": cfg, "op": name, "kernel": kernel, "ms": round(ms, 5),
                "bytes": int(nbytes), "GBps": round(gbs, 1), "elements_per_s": elems / (ms * 1e-3),
                "frac_of_measured": round(gbs / peak_gbs, 4), "frac_of_nominal": round(gbs / NOMINAL, 4),
                "l2_flushed": flush, "launches_per_timed_region": inner}
+        if cold is not None:
+            row["cold_ms"] = round(cold, 5)
+            row["cold_GBps"] = round(nbytes / (cold * 1e-3) / 1e9, 1)
+            row["empty_event_pair_ms"] = round(empty_pair_ms, 5)
         if flush and reps > 0:
             # Launch-bound sizes: the same call 50 times back to back in the stream (data stays in L2) ...
             bt = []

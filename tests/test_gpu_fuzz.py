@@ -115,3 +115,57 @@ def test_reductions_random_layouts(cuda, oracle, seed):
         n = A.size if dim == FULL_REDUCE else shape[dim]
         scale = (a64.sum() if dim == FULL_REDUCE else a64.sum(axis=dim)) / (n if op == "mean" else 1)
         assert_sum_close(res[0], res[1], np.asarray(scale).reshape(-1), what=what)
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_binary_two_independently_permuted_views(cuda, oracle, seed):
+    """Both operands are permuted views with DIFFERENT permutations, so they can be contiguous along
+    two different dims, neither of them the output's: the gather-then-tile route, the single-tile
+    route and the generic strided kernel all get hit, whatever the extents."""
+    rs = np.random.RandomState(9000 + seed)
+    nd = int(rs.randint(2, 5))
+    shape = tuple(int(rs.choice([3, 8, 12, 17, 32, 40, 64])) for _ in range(nd))
+    A = rs.uniform(-2, 2, shape).astype(np.float32)
+    B = (rs.uniform(0.5, 2, shape) * rs.choice([-1, 1], size=shape)).astype(np.float32)
+    pa, pb_ = list(rs.permutation(nd)), list(rs.permutation(nd))
+    op = BITWISE[seed % 4]
+    outs = []
+    for be in (cuda, oracle):
+        out = be.empty(shape)
+        be.forward(op, [permuted_view(be, A, pa), permuted_view(be, B, pb_)], out)
+        outs.append(out.numpy())
+    assert_bit_equal(outs[0], outs[1], f"{op} {shape} perms {pa} {pb_}")
+
+
+@pytest.mark.parametrize("rows", [7, 64, 200, 1024, 3000])
+@pytest.mark.parametrize("cols", [8, 100, 1024, 4100])
+def test_column_reductions_of_small_and_medium_matrices(cuda, oracle, rows, cols):
+    """Column reductions across the sizes where the geometry changes: narrow strips without a split
+    (inputs that fit L2, short reduced dim), one-warp strips with and without a split over CTAs,
+    vector and scalar widths, and the three-input gradient prologue on the same shapes."""
+    A = np.random.RandomState(rows * 7 + cols).uniform(-1, 1, (rows, cols)).astype(np.float32)
+    for op in ("sum", "max"):
+        res = []
+        for be in (cuda, oracle):
+            out = be.empty((cols,))
+            be.forward(op, [be.tensor(A)], out, dim=0)
+            res.append(out.numpy())
+        if op == "max":
+            assert_bit_equal(res[0], res[1], f"max {rows}x{cols}")
+        else:
+            assert_sum_close(res[0], res[1], np.abs(A.astype(np.float64)).sum(axis=0), what=f"sum {rows}x{cols}")
+    # grad of a broadcast row through the fused add + leaky_relu backward (three inputs per element)
+    b = np.random.RandomState(1).uniform(-1, 1, (1, cols)).astype(np.float32)
+    G = np.random.RandomState(2).randn(rows, cols).astype(np.float32)
+    ta, tb = oracle.tensor(A), oracle.tensor(b, requires_grad=True)
+    ab = oracle.empty(A.shape, requires_grad=True); oracle.forward("add", [ta, tb], ab)
+    c = oracle.empty(A.shape, requires_grad=True); oracle.forward("leaky_relu", [ab], c, fval=0.1)
+    c.grad.copy_from(G)
+    oracle.backward("leaky_relu", [ab], c, fval=0.1); oracle.backward("add", [ta, tb], ab)
+    da, db = cuda.tensor(A), cuda.tensor(b, requires_grad=True)
+    dc = cuda.empty(A.shape, requires_grad=True)
+    cuda.forward("add_leaky_relu", [da, db], dc, fval=0.1)
+    dc.grad.copy_from(G)
+    cuda.backward("add_leaky_relu", [da, db], dc, fval=0.1)
+    scale = np.abs(G.astype(np.float64) * np.where(c.numpy() > 0, 1.0, 0.1)).sum(axis=0, keepdims=True)
+    assert_sum_close(db.grad.numpy(), tb.grad.numpy(), scale, what=f"grad of the broadcast row {rows}x{cols}")
