@@ -303,6 +303,9 @@ static void reduce_forward(const char *name, const Tensor **inputs, Tensor *outp
     memcpy(&bits, &start, 4);
     if (std::is_same<Op, ArgMaxOp>::value) bits = 0;
     fill32(output->data, bits, n_out);
+    // an empty shard inside the cross-GPU bracket still takes part in the exchange (with the
+    // start value just written as its contribution)
+    if (!mean && peer_bracket_open()) exchange_for_empty_shard<Op>((float *)output->data, (float *)output->data, n_out, false);
     end_call();
     return;
   }

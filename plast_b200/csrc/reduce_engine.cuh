@@ -25,6 +25,7 @@
 #include "peer_link.cuh"
 
 #include <float.h>
+#include <string.h>
 
 namespace pb {
 
@@ -711,10 +712,43 @@ template <class Op, class Pro, int NIN> const RedOccupancy &reduce_occupancy() {
   return occ;
 }
 
+// Bracket mode with nothing to reduce on THIS rank (an empty shard): the ranks that hold data make
+// one call of the exchange sequence for this reduction, so this rank makes it too and contributes
+// the identity; its output then receives what the others reduced. `values` holds n identities.
+template <class Op> void exchange_for_empty_shard(float *dst, float *values, u64 n, bool accumulate) {
+  if constexpr (Op::kPeerOp >= 0 && !Op::kIndexed) {
+    if (n > kParkedFloats) {
+      set_error(PLAST_B200_ERR_UNSUPPORTED, "a reduction inside plast_b200_peer_reduce_begin/_end has at most %llu outputs",
+                (unsigned long long)kParkedFloats);
+      return;
+    }
+    launch_peer_exchange(peer_bracket_take(), values, (unsigned)n, Op::kPeerOp);
+    if (dst != values) launch_add_parked(dst, values, (unsigned)n, accumulate);
+  }
+}
+
 template <class Op, class Pro, int NIN>
 void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *const *ins,
                    const Pro &pro, const Op &, bool accumulate, float post_div) {
-  if (plan.numel == 0) return;
+  if (plan.numel == 0) {
+    if constexpr (Op::kPeerOp >= 0 && !Op::kIndexed) {
+      if (peer_bracket_open()) {
+        u64 n_out = 1;
+        for (int d = 0; d < plan.ndim; ++d)
+          if (!plan.reduced[d]) n_out *= plan.size[d];
+        Workspace wsp;
+        if (n_out == 0 || plan.max_offset[0] != n_out - 1 || !get_workspace(&wsp)) return;
+        float ident = 0.0f;
+        if (Op::kPeerOp == PLAST_B200_PEER_MAX) ident = -FLT_MAX;
+        if (Op::kPeerOp == PLAST_B200_PEER_MIN) ident = FLT_MAX;
+        unsigned int bits;
+        memcpy(&bits, &ident, 4);
+        fill32(wsp.parked, bits, n_out < kParkedFloats ? n_out : kParkedFloats);
+        exchange_for_empty_shard<Op>((float *)out, wsp.parked, n_out, accumulate);
+      }
+    }
+    return;
+  }
   RedGeometry g;
   const void *ptrs[NIN];
   for (int a = 0; a < NIN; ++a) ptrs[a] = ins[a];
@@ -802,7 +836,11 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   // the 126 MB L2 from launch to launch, and prefetched lines survive better than streamed ones),
   // 49 -> 51 us (one timer tick) on cold data, neutral from 512 MiB up; prefetching through the
   // whole chunk costs 10 % at 1 GiB, prefetching further ahead gains nothing.
-  p.prefetch_batches = tuned(kTuneColsPrefetch) >= 0 ? (unsigned)tuned(kTuneColsPrefetch) : 1u;
+  // Only long sweeps prefetch: with a handful of batches per row-worker (small inputs, narrow
+  // strips) the extra instructions cost more than they bring (config 1's grad_b: 5.3 -> 10 us).
+  const u64 batches_per_worker = g.per_chunk / (((u64)kRedThreads >> g.log_tx) * 4);
+  p.prefetch_batches = tuned(kTuneColsPrefetch) >= 0 ? (unsigned)tuned(kTuneColsPrefetch)
+                                                     : (g.kind == kRedCols && g.log_tx >= 5 && batches_per_worker >= 16 ? 1u : 0u);
   p.prefetch_until = tuned(kTuneColsPrefetchUntil) >= 0 ? (unsigned)tuned(kTuneColsPrefetchUntil) : 16u;
   p.seg_prefetch = tuned(kTuneSegPrefetch) >= 0 ? (unsigned)tuned(kTuneSegPrefetch) : (unsigned)kPrefetchAhead;
   // a pending cross-GPU exchange rides on the kernel whose last CTA holds THE final value

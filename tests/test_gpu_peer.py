@@ -273,6 +273,12 @@ def test_reductions_inside_the_bracket_are_exchanged_fused_or_parked(cuda):
             assert lib.plast_b200_peer_reduce_end(g) == 1 and n == 2     # rows stage + column stage with the exchange inside
         res.append(tbias.grad.numpy())
     assert np.array_equal(res[0], res[1])
+    # an empty shard still makes its call of the sequence (contributing the start value)
+    empty = cuda.tensor(np.zeros((0, 64), np.float32))
+    got_e = cuda.empty((64,)); got_e.copy_from(np.full(64, 5.0, np.float32))
+    lib.plast_b200_peer_reduce_begin(g)
+    cuda.forward("sum", [empty], got_e, dim=0)
+    assert lib.plast_b200_peer_reduce_end(g) == 1 and np.all(got_e.numpy() == 0.0)
     # what the bracket cannot serve is refused, nothing is launched
     lib.plast_b200_peer_reduce_begin(g)
     n = launches(lambda: pb.forward("mean", [ta], cuda.empty((2048,)), dim=0, check=False))
