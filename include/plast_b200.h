@@ -370,7 +370,13 @@ int plast_b200_chain_backward_try_compile(const PlastChainStep *steps, int n_ste
  * further, 3: resident CTAs per SM the segmented reduce plans for, 5: order of the column reduce's
  * CTAs, 6 / 7: L2 prefetch distance of the column sweep in load batches and the number of batches
  * per chunk that prefetch, 8: prefetch distance of the segmented reduce in trips, 9: log2 of the
- * threads that share a segment); a negative value restores the built-in choice. Results do not depend on the geometry beyond the order of additions. */
+ * threads that share a segment, 10: CTAs per thread-block cluster when the chunks of a column
+ * reduce combine through distributed shared memory instead of a ticket in global memory, 0 or 1 =
+ * never, 11: 1 = the 3-D tile kernel for inputs turned along two different dims uses 32 x 16 x 16
+ * tiles instead of 8 x 32 x 32, 12 / 13 / 14: how many neighbouring tiles along the output's dim 0
+ * and the two turned dims are adjacent in that kernel's launch order); a negative value restores
+ * the built-in choice. Results do not depend on the geometry
+ * beyond the order of additions. */
 void plast_b200_tune(int key, long value);
 /* Test hook: runs the host-side iteration planner (drop size-1 dims, order by the strides of
  * argument `sort_arg`, merge dims every argument walks as one run) on caller-supplied metadata.

@@ -68,7 +68,7 @@ cudaError_t scratch_alloc_async(void **p, size_t bytes);
 // Geometry knobs a test or a tuning run may override (plast_b200_tune); negative = built-in choice.
 enum TuneKey {
   kTuneColsLogTx = 0, kTuneColsCtasPerSm = 1, kTuneColsMinBatches = 2, kTuneSegCtasPerSm = 3,
-  kTuneColsTileMajor = 5, kTuneColsPrefetch = 6, kTuneColsPrefetchUntil = 7, kTuneSegPrefetch = 8, kTuneSegLogTx = 9, kTuneKeys = 12
+  kTuneColsTileMajor = 5, kTuneColsPrefetch = 6, kTuneColsPrefetchUntil = 7, kTuneSegPrefetch = 8, kTuneSegLogTx = 9, kTuneColsCluster = 10, kTuneTile3Shape = 11, kTuneTile3Group0 = 12, kTuneTile3GroupA = 13, kTuneTile3GroupB = 14, kTuneTile3Threads = 15, kTuneKeys = 16
 };
 long tuned(int key);
 
@@ -82,20 +82,38 @@ long tuned(int key);
 // PLAST_B200_PDL=0 in the environment turns the attribute off (plain stream order).
 bool pdl_enabled();
 
+// `cluster` > 1 launches thread-block clusters of that many consecutive CTAs along x (the grid must
+// be a multiple of it).
 template <class... KArgs, class... Args>
-inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
-                            Args &&...args) {
+inline cudaError_t launch_kc(unsigned cluster, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t s, Args &&...args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+template <class... KArgs, class... Args>
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                            Args &&...args) {
+  return launch_kc(1u, kernel, grid, block, smem, s, static_cast<Args &&>(args)...);
 }
 
 // Frees the staging buffers, streams and events of the host-buffer chain (host_pipeline.cu).

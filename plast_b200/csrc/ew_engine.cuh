@@ -344,6 +344,230 @@ bool launch_ew_tiled(const IterPlan &plan, float *out, const float *const *ins, 
   return true;
 }
 
+// ---- inputs contiguous along two DIFFERENT dims, neither of them the output's -------------------------
+// x.transpose(0, 2) + y.transpose(1, 2) on 3-D tensors: one 2-D tile can only turn one of the two
+// dims. A 3-D tile of 32 (output's dim 0) x 16 (dA) x 16 (dB) elements turns both: an input that is
+// contiguous along dA (or dB) is read as float4 along that dim, 64 bytes per tile row, parked in
+// shared memory and read back along dim 0; the output (and any input laid out like it) moves as
+// float4 along dim 0. Every byte crosses DRAM once.
+// Tile shape: D0 along the output's dim 0, DX along dA and dB. 8 x 32 x 32 reads whole 128-byte lines
+// of the turned inputs and writes 32-byte pieces of output lines (the L2 merges those before they
+// reach DRAM); 32 x 16 x 16 reads 64-byte pieces and writes whole lines.
+template <int D0, int DX, int NT> struct Tile3 {
+  static constexpr int kLanes = DX / 4;                    // float4 lanes along an input's own dim
+  static constexpr int kStageH = NT / (kLanes * D0);      // staging: tile rows of the other dim per trip
+  static constexpr int kStageTrips = DX / kStageH;
+  static constexpr int kQ0 = D0 / 4;                       // float4 along dim 0 in the output pass
+  static constexpr int kOutH = NT / (kQ0 * DX);
+  static constexpr int kOutTrips = DX / kOutH;
+  // element (jA, jB, i0) lives at jB * kPlane + jA * kRow + i0; both strides are chosen so that the
+  // four scalar stores of a staged float4 land in distinct banks across a warp
+  static constexpr int kRow = D0 + 1;
+  static constexpr int kWant = (32 / kLanes) / 4;          // kPlane = kWant (mod 8)
+  static constexpr int kPlane = DX * kRow + ((kWant - (DX * kRow) % 8) % 8 + 8) % 8;
+  static constexpr int kFloats = DX * kPlane;              // per staged input
+  static_assert(kStageTrips * NT * 4 == D0 * DX * DX && kOutTrips * NT * 4 == D0 * DX * DX, "whole tile per pass");
+};
+
+template <int NIN> struct Tiled3Params {
+  const float *in[NIN];
+  float *out;
+  u64 n0, nA, nB;
+  u64 s0[NIN + 1], sA[NIN + 1], sB[NIN + 1]; // element strides of out (index 0) and the inputs
+  int cls[NIN];           // 0: read directly along dim 0 (unit stride or broadcast), 1: unit stride along dA, 2: along dB
+  int slot[NIN];          // shared-memory slot of a staged input
+  int n_outer;
+  u64 outer_size[MAX_NDIM];
+  u64 outer_stride[NIN + 1][MAX_NDIM];
+  // Launch order: CTAs come in groups of g0 x gA x gB neighbouring tiles (dim 0 fastest), the groups
+  // again dim 0 fastest, so that the CTAs resident at one time complete whole lines of the output
+  // (g0 tiles along dim 0) and whole rows of the turned inputs (gA, gB tiles along their own dims).
+  unsigned tiles0, tilesA, tilesB, g0, gA, gB, groups0, groupsA;
+};
+
+template <class F, int NIN, int D0, int DX, int NT>
+__global__ void __launch_bounds__(NT, 2) ew_tiled3_kernel(F f, Tiled3Params<NIN> p) {
+  using T = Tile3<D0, DX, NT>;
+  extern __shared__ float tile3_smem[]; // [staged inputs][jB][jA][i0], padded
+  pdl_wait();
+  pdl_launch_dependents();
+  const unsigned gsz = p.g0 * p.gA * p.gB;
+  const unsigned local = blockIdx.x % gsz, grp = blockIdx.x / gsz;
+  const unsigned t0 = (grp % p.groups0) * p.g0 + local % p.g0;
+  const unsigned tA = ((grp / p.groups0) % p.groupsA) * p.gA + (local / p.g0) % p.gA;
+  const unsigned tB = (grp / (p.groups0 * p.groupsA)) * p.gB + local / (p.g0 * p.gA);
+  if (t0 >= p.tiles0 || tA >= p.tilesA || tB >= p.tilesB) return; // padding of a ragged group
+  u64 off[NIN + 1];
+#pragma unroll
+  for (int a = 0; a <= NIN; ++a) off[a] = 0;
+  u64 rest = blockIdx.y;
+  for (int d = 0; d < p.n_outer; ++d) {
+    const u64 q = rest / p.outer_size[d], r = rest - q * p.outer_size[d];
+#pragma unroll
+    for (int a = 0; a <= NIN; ++a) off[a] += r * p.outer_stride[a][d];
+    rest = q;
+  }
+  const u64 c0 = (u64)t0 * D0, cA = (u64)tA * DX, cB = (u64)tB * DX; // tile origin
+  // staging pass: thread = (sq: float4 lane along the input's own dim, si: along dim 0, sh), a few
+  // trips over the remaining dim; every load is issued before the first store to shared memory
+  const unsigned sq = threadIdx.x % T::kLanes, si = (threadIdx.x / T::kLanes) % D0, sh = threadIdx.x / (T::kLanes * D0);
+  float4 v[NIN][T::kStageTrips];
+#pragma unroll
+  for (int a = 0; a < NIN; ++a) {
+    if (p.cls[a] == 0) continue;
+    const bool alongA = p.cls[a] == 1;
+    const u64 own = (alongA ? cA : cB) + sq * 4, own_n = alongA ? p.nA : p.nB;
+    const u64 oth0 = alongA ? cB : cA, oth_n = alongA ? p.nB : p.nA, oth_s = alongA ? p.sB[a + 1] : p.sA[a + 1];
+    const float *base = p.in[a] + off[a + 1] + (c0 + si) * p.s0[a + 1] + own;
+#pragma unroll
+    for (int j = 0; j < T::kStageTrips; ++j) {
+      const u64 oth = oth0 + sh + T::kStageH * j;
+      if (c0 + si < p.n0 && own < own_n && oth < oth_n)
+        v[a][j] = __ldcs(reinterpret_cast<const float4 *>(base + oth * oth_s));
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < NIN; ++a) {
+    if (p.cls[a] == 0) continue;
+    const bool alongA = p.cls[a] == 1;
+    float *tl = tile3_smem + (size_t)p.slot[a] * T::kFloats + si;
+#pragma unroll
+    for (int j = 0; j < T::kStageTrips; ++j) {
+      const unsigned oth = sh + T::kStageH * j;
+      const unsigned at = alongA ? oth * T::kPlane + (sq * 4) * T::kRow : (sq * 4) * T::kPlane + oth * T::kRow;
+      const unsigned step = alongA ? T::kRow : T::kPlane;
+      tl[at] = v[a][j].x; tl[at + step] = v[a][j].y; tl[at + 2 * step] = v[a][j].z; tl[at + 3 * step] = v[a][j].w;
+    }
+  }
+  __syncthreads();
+  // output pass: thread = (q4: float4 along dim 0, jA, oh), a few trips over jB
+  const unsigned q4 = threadIdx.x % T::kQ0, jA = (threadIdx.x / T::kQ0) % DX, oh = threadIdx.x / (T::kQ0 * DX);
+  const u64 i0 = c0 + q4 * 4;
+  if (i0 >= p.n0 || cA + jA >= p.nA) return;
+#pragma unroll
+  for (int j = 0; j < T::kOutTrips; ++j) {
+    const unsigned jB = oh + T::kOutH * j;
+    if (cB + jB >= p.nB) continue;
+    float x[4][NIN];
+#pragma unroll
+    for (int a = 0; a < NIN; ++a) {
+      if (p.cls[a] == 0) {
+        const float *q = p.in[a] + off[a + 1] + i0 * p.s0[a + 1] + (cA + jA) * p.sA[a + 1] + (cB + jB) * p.sB[a + 1];
+        if (p.s0[a + 1] == 1) {
+          const float4 d = __ldcs(reinterpret_cast<const float4 *>(q));
+          x[0][a] = d.x; x[1][a] = d.y; x[2][a] = d.z; x[3][a] = d.w;
+        } else { // broadcast along dim 0
+          const float sc = __ldg(q);
+          x[0][a] = x[1][a] = x[2][a] = x[3][a] = sc;
+        }
+      } else {
+        const float *tl = tile3_smem + (size_t)p.slot[a] * T::kFloats + jB * T::kPlane + jA * T::kRow + q4 * 4;
+        x[0][a] = tl[0]; x[1][a] = tl[1]; x[2][a] = tl[2]; x[3][a] = tl[3];
+      }
+    }
+    __stcs(reinterpret_cast<float4 *>(p.out + off[0] + i0 + (cA + jA) * p.sA[0] + (cB + jB) * p.sB[0]),
+           make_float4(f(x[0]), f(x[1]), f(x[2]), f(x[3])));
+  }
+}
+
+// Runs the plan through the 3-D tile kernel when exactly two different unit-stride dims other than
+// dim 0 occur among the inputs and everything can move as float4; false = not applicable.
+template <class F, int NIN>
+bool launch_ew_tiled3(const IterPlan &plan, float *out, const float *const *ins, const F &f) {
+  if (plan.ndim < 3 || plan.stride[0][0] != 1 || plan.size[0] % 4 != 0 || ((uintptr_t)out) % 16 != 0) return false;
+  Tiled3Params<NIN> p;
+  int dA = -1, dB = -1, staged = 0;
+  for (int a = 0; a < NIN; ++a) {
+    p.cls[a] = 0;
+    p.slot[a] = 0;
+    if (plan.stride[a + 1][0] <= 1) continue;
+    int mine = -1;
+    for (int d = 1; d < plan.ndim; ++d)
+      if (plan.stride[a + 1][d] == 1 && plan.size[d] > 1) mine = d;
+    if (mine < 0) return false;
+    if (dA < 0 || mine == dA) {
+      dA = mine;
+      p.cls[a] = 1;
+    } else if (dB < 0 || mine == dB) {
+      dB = mine;
+      p.cls[a] = 2;
+    } else {
+      return false;
+    }
+    p.slot[a] = staged++;
+  }
+  if (dA < 0 || dB < 0) return false; // one turned dim: the 2-D tile kernel's case
+  if (plan.size[dA] % 4 != 0 || plan.size[dB] % 4 != 0 || plan.size[dA] < 8 || plan.size[dB] < 8) return false;
+  p.out = out;
+  p.n0 = plan.size[0];
+  p.nA = plan.size[dA];
+  p.nB = plan.size[dB];
+  p.n_outer = 0;
+  u64 outer = 1;
+  for (int d = 1; d < plan.ndim; ++d) {
+    if (d == dA || d == dB) continue;
+    p.outer_size[p.n_outer] = plan.size[d];
+    for (int a = 0; a <= NIN; ++a) p.outer_stride[a][p.n_outer] = plan.stride[a][d];
+    outer *= plan.size[d];
+    ++p.n_outer;
+  }
+  for (int d = p.n_outer; d < MAX_NDIM; ++d) {
+    p.outer_size[d] = 1;
+    for (int a = 0; a <= NIN; ++a) p.outer_stride[a][d] = 0;
+  }
+  if (outer > 65535) return false;
+  for (int a = 0; a <= NIN; ++a) {
+    p.s0[a] = plan.stride[a][0];
+    p.sA[a] = plan.stride[a][dA];
+    p.sB[a] = plan.stride[a][dB];
+    // float4 along the argument's own unit-stride dim: every other stride keeps 16-byte alignment
+    const int cls = a == 0 ? 0 : p.cls[a - 1];
+    if (cls == 0 && p.s0[a] == 0) continue; // broadcast along dim 0: scalar loads
+    if (a > 0 && ((uintptr_t)ins[a - 1]) % 16 != 0) return false;
+    if (cls != 0 && p.s0[a] % 4 != 0) return false;
+    if (cls != 1 && p.sA[a] % 4 != 0) return false;
+    if (cls != 2 && p.sB[a] % 4 != 0) return false;
+    for (int d = 0; d < p.n_outer; ++d)
+      if (p.outer_stride[a][d] % 4 != 0) return false;
+  }
+  for (int a = 0; a < NIN; ++a) p.in[a] = ins[a];
+  const bool wide_reads = tuned(kTuneTile3Shape) != 1 && p.nA >= 32 && p.nB >= 32;
+  const u64 d0 = wide_reads ? 8 : 32, dx = wide_reads ? 32 : 16;
+  const u64 tiles0 = (p.n0 + d0 - 1) / d0, tilesA = (p.nA + dx - 1) / dx, tilesB = (p.nB + dx - 1) / dx;
+  if (tiles0 > 0xfffffful || tilesA > 0xfffffful || tilesB > 0xfffffful) return false;
+  auto group = [](long forced, u64 dflt, u64 tiles) {
+    u64 g = forced > 0 ? (u64)forced : dflt;
+    return (unsigned)(g < tiles ? g : tiles);
+  };
+  // a 128-byte output line = 32 / d0 tiles along dim 0; four tiles of 32 floats along dA or dB = 512 B
+  p.g0 = group(tuned(kTuneTile3Group0), 32 / d0, tiles0);
+  p.gA = group(tuned(kTuneTile3GroupA), 4, tilesA);
+  p.gB = group(tuned(kTuneTile3GroupB), 4, tilesB);
+  p.tiles0 = (unsigned)tiles0;
+  p.tilesA = (unsigned)tilesA;
+  p.tilesB = (unsigned)tilesB;
+  p.groups0 = (unsigned)((tiles0 + p.g0 - 1) / p.g0);
+  p.groupsA = (unsigned)((tilesA + p.gA - 1) / p.gA);
+  const u64 groupsB = (tilesB + p.gB - 1) / p.gB;
+  const u64 tiles = (u64)p.groups0 * p.groupsA * groupsB * p.g0 * p.gA * p.gB;
+  if (tiles > 0x7fffffffull) return false;
+  const dim3 grid((unsigned)tiles, (unsigned)outer);
+  // 512 threads with four float4 per thread and input (<= 64 registers, two CTAs per SM) measured
+  // faster than 256 threads with eight (122 registers, two CTAs of half the size).
+  auto go = [&](auto kernel, size_t floats_per_input, unsigned threads) {
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(NIN * floats_per_input * sizeof(float)));
+    launch_k(kernel, grid, dim3(threads), (size_t)staged * floats_per_input * sizeof(float), stream(), f, p);
+  };
+  const bool big_cta = tuned(kTuneTile3Threads) != 256;
+  if (wide_reads && big_cta) go(ew_tiled3_kernel<F, NIN, 8, 32, 512>, Tile3<8, 32, 512>::kFloats, 512);
+  else if (wide_reads) go(ew_tiled3_kernel<F, NIN, 8, 32, 256>, Tile3<8, 32, 256>::kFloats, 256);
+  else if (big_cta) go(ew_tiled3_kernel<F, NIN, 32, 16, 512>, Tile3<32, 16, 512>::kFloats, 512);
+  else go(ew_tiled3_kernel<F, NIN, 32, 16, 256>, Tile3<32, 16, 256>::kFloats, 256);
+  count_launch();
+  note_kernel("ew_tiled_transpose_two_dims");
+  return true;
+}
+
 // Inputs that are contiguous along two DIFFERENT dims other than the output's (x.transpose(0, 2) +
 // y.transpose(1, 2) on 3-D tensors): one tile transpose can only turn one of those dims. The inputs
 // that do not share the first such dim are gathered, each by one pass of the tile kernel, into
@@ -436,6 +660,7 @@ void launch_ew(const IterPlan &plan, float *out, const float *const *ins, const 
     }
   }
   if (plan.numel != 0 && launch_ew_tiled<F, NIN>(plan, out, ins, f)) return;
+  if (plan.numel != 0 && launch_ew_tiled3<F, NIN>(plan, out, ins, f)) return;
   if (plan.numel != 0) {
     IterPlan plan2;
     const float *ins2[NIN];

@@ -24,6 +24,7 @@
 #include "iter.h"
 #include "peer_link.cuh"
 
+#include <cooperative_groups.h>
 #include <float.h>
 #include <string.h>
 
@@ -168,6 +169,8 @@ template <int NIN> struct RedParams {
   unsigned int *counters;
   void *partials;
   const PeerLink *peer; // not NULL: the thread that holds the single final value exchanges it across GPUs
+  unsigned cluster;     // cols: > 1 = the `splits` CTAs of a tile are one thread-block cluster and combine
+                        // through distributed shared memory (no partials in global memory, no ticket)
   bool strip_major;     // cols: consecutive CTAs take neighbouring strips of the same chunk of rows
   unsigned prefetch_batches; // cols: load batches ahead of which a row-worker asks L2 for its rows (0 = off)
   unsigned prefetch_until;   // cols: only the first so many batches of a chunk prefetch (0 = all of them)
@@ -468,7 +471,8 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
 #pragma unroll
   for (int k = 0; k < VEC; ++k) acc[k] = Op::identity();
 
-  const u64 r_begin = (u64)chunk * p.per_chunk;
+  u64 r_begin = (u64)chunk * p.per_chunk;
+  if (r_begin > p.n_red) r_begin = p.n_red; // a cluster keeps its size even when the last chunks are empty
   u64 r_end = r_begin + p.per_chunk;
   if (r_end > p.n_red) r_end = p.n_red;
   constexpr int kRedUnroll = 4;
@@ -634,6 +638,34 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
     }
     return;
   }
+  if (p.cluster > 1) {
+    // The chunks of this tile are the CTAs of one cluster (rank = chunk): each leaves its strip in
+    // its own shared memory, rank 0 reads the others over the SM-to-SM network in rank order and
+    // finishes. Nobody touches global memory or an atomic in between.
+    cooperative_groups::cluster_group cl = cooperative_groups::this_cluster();
+    __syncthreads(); // worker 0 has read its strip out of the tree
+    if (ty == 0) {
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) strip_vals[(k << p.log_tx) + lane] = r[k];
+    }
+    cl.sync();
+    if (chunk == 0) {
+      if (ty == 0 && live) {
+        for (unsigned c = 1; c < p.splits; ++c) {
+          const T *theirs = cl.map_shared_rank(strip_vals, c);
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) r[k] = Op::combine(r[k], theirs[(k << p.log_tx) + lane]);
+        }
+      }
+      across_gpus_strip(r);
+      if (ty == 0 && live) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) Op::store(out + toff + (u64)k * p.tstride0, r[k], p.accumulate, p.post_div);
+      }
+    }
+    cl.sync(); // the other ranks' shared memory stays alive until rank 0 has read it
+    return;
+  }
   T *partials = (T *)p.partials + tile * p.splits * ((u64)VEC << p.log_tx);
   if (ty == 0) {
 #pragma unroll
@@ -677,6 +709,7 @@ struct RedGeometry {
   int log_tx;
   u64 len0_items, seg_len, nsplit0, nseg, per_chunk, n_kept, n_red, grid;
   unsigned splits;
+  unsigned cluster; // cols: the splits of a tile form a cluster of this many CTAs (0 or 1: no cluster)
   int kept_dims[MAX_NDIM], n_kept_dims; // plan dim indices in each sub-space
   int red_dims[MAX_NDIM], n_red_dims;
 };
@@ -829,7 +862,8 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   p.counters = nullptr;
   p.partials = nullptr;
   p.peer = nullptr;
-  p.strip_major = tuned(kTuneColsTileMajor) > 0; // measured: the order of the CTAs makes no difference
+  p.cluster = g.cluster;
+  p.strip_major = g.cluster <= 1 && tuned(kTuneColsTileMajor) > 0; // measured: the order of the CTAs makes no difference
   // Column sweep: every row-worker asks L2 for the rows of its NEXT load batch (one bulk prefetch
   // per 512-byte row piece) during the first 16 batches of its chunk. Measured on B200: 46.5 -> 40.5
   // us for the column sum of 8192 x 8192 issued back to back (part of a 268 MB tensor survives in
@@ -879,7 +913,7 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
     }
   }
   Workspace ws = {};
-  if (g.splits > 1) {
+  if (g.splits > 1 && g.cluster <= 1) {
     if (!get_workspace(&ws)) return;
     p.counters = ws.counters;
     p.partials = ws.partials;
@@ -888,9 +922,9 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   dim3 grid((unsigned)g.grid), block(kRedThreads);
 #define PB_RED_LAUNCH(KERNEL)                                                                      \
   do {                                                                                             \
-    if (g.vec == 4) launch_k(KERNEL<Op, Pro, NIN, 4>, grid, block, 0, s, p, pro);                  \
-    else if (g.vec == 2) launch_k(KERNEL<Op, Pro, NIN, 2>, grid, block, 0, s, p, pro);             \
-    else launch_k(KERNEL<Op, Pro, NIN, 1>, grid, block, 0, s, p, pro);                             \
+    if (g.vec == 4) launch_kc(g.cluster, KERNEL<Op, Pro, NIN, 4>, grid, block, 0, s, p, pro);      \
+    else if (g.vec == 2) launch_kc(g.cluster, KERNEL<Op, Pro, NIN, 2>, grid, block, 0, s, p, pro); \
+    else launch_kc(g.cluster, KERNEL<Op, Pro, NIN, 1>, grid, block, 0, s, p, pro);                 \
   } while (0)
   // float4 plans whose inputs are "the first m vary along the run, the rest are constant"
   // (m = 1 or 2 < NIN) get the kernel that knows this at compile time (fewer registers).

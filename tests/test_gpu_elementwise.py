@@ -109,9 +109,10 @@ def test_inputs_contiguous_along_two_different_dims(cuda, oracle):
     """out[i, j, k] = a.transpose(0, 2)[i, j, k] op b.transpose(1, 2)[i, j, k]: a is contiguous along
     i, b along j, the output along k. Any stride combination is one code path in the reference
     (include/kernels/kernel_macros.h:213-220); here the input that does not share the first
-    transposed dim is gathered through the tile kernel first."""
+    3-D tiles turn both dims in one pass when every extent is a multiple of 4; otherwise the input
+    that does not share the first transposed dim is gathered through the 2-D tile kernel first."""
     import plast_b200 as pb
-    for shape in [(24, 40, 56), (9, 33, 130), (64, 64, 64)]:
+    for shape in [(24, 40, 56), (9, 33, 130), (64, 64, 64), (16, 16, 32), (8, 8, 8), (20, 36, 100), (132, 12, 260)]:
         I, J, K = shape
         a, b = rand_normal(7, (K, J, I)), rand_normal(8, (I, K, J))
         small = rand_uniform(9, (1, J, 1), 0.5, 2.0)
@@ -121,7 +122,8 @@ def test_inputs_contiguous_along_two_different_dims(cuda, oracle):
                 out = be.empty(shape)
                 be.forward(op, [be.tensor(a).transpose(0, 2), be.tensor(b).transpose(1, 2)], out)
                 outs.append(out.numpy())
-            assert pb.last_kernel() == "ew_gather_then_tiled_transpose", shape
+            one_pass = all(s % 4 == 0 for s in shape)
+            assert pb.last_kernel() == ("ew_tiled_transpose_two_dims" if one_pass else "ew_gather_then_tiled_transpose"), shape
             assert_bit_equal(outs[0], outs[1], f"{op} {shape}: two transposed inputs")
         # three operands through a fused entry point: x transposed one way, scale the other, bias broadcast
         outs = []
@@ -135,6 +137,15 @@ def test_inputs_contiguous_along_two_different_dims(cuda, oracle):
                 be.forward("mul", [ta, tb], m); be.forward("add", [m, ts], u); be.forward("leaky_relu", [u], out, fval=0.1)
             outs.append(out.numpy())
         assert_bit_equal(outs[0], outs[1], f"fused epilogue {shape}: two transposed inputs")
+    # 4-D: a batch dim outside the three that the tile covers
+    a, b = rand_normal(10, (3, 24, 16, 40)), rand_normal(11, (3, 40, 24, 16))
+    outs = []
+    for be in (cuda, oracle):
+        out = be.empty((3, 40, 16, 24))
+        be.forward("sub", [be.tensor(a).transpose(1, 3), be.tensor(b).transpose(2, 3)], out)
+        outs.append(out.numpy())
+    assert pb.last_kernel() == "ew_tiled_transpose_two_dims"
+    assert_bit_equal(outs[0], outs[1], "two transposed inputs with a batch dim")
 
 
 def test_relu_negative_zero_and_config1_forward(cuda, oracle):

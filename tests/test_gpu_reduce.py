@@ -203,6 +203,32 @@ def test_broadcast_gradient_reduce(cuda, oracle, op, sa, sb):
     assert_sum_close(res["cuda"][1], res["oracle"][1], fold(terms_b, sb) + np.abs(DB), what=f"{op} db")
 
 
+@pytest.mark.parametrize("cluster,log_tx", [(2, 1), (4, 3), (8, 2), (8, 5), (3, 4)])
+def test_column_reduce_combined_inside_a_cluster(cuda, oracle, cluster, log_tx):
+    # The chunks of a strip as one thread-block cluster that combines through distributed shared
+    # memory (forced through the tuning hook; by default only small inputs take this route). Shapes:
+    # ragged chunks, fewer rows than CTAs in the cluster can use, an outer kept dim, a ragged strip.
+    import plast_b200 as pb
+    pb.lib.plast_b200_tune(0, log_tx)
+    pb.lib.plast_b200_tune(10, cluster)
+    try:
+        for shape, dim in [((1024, 1024), 0), ((1001, 36), 0), ((9, 260), 0), ((5, 77, 128), 1), ((64, 8), 0)]:
+            A = rand_uniform(3, shape)
+            for op in ("sum", "mean", "max", "argmax"):
+                got, want = reduce_both(cuda, oracle, op, A, dim, False)
+                what = f"{op}{shape} dim={dim} cluster={cluster} log_tx={log_tx}"
+                if op == "max":
+                    assert_bit_equal(got, want, what)
+                elif op == "argmax":
+                    assert np.array_equal(got, want), what
+                else:
+                    scale = abs_sum(A, dim) / (shape[dim] if op == "mean" else 1)
+                    assert_sum_close(got.reshape(-1), want.reshape(-1), np.asarray(scale).reshape(-1), what=what)
+    finally:
+        pb.lib.plast_b200_tune(0, -1)
+        pb.lib.plast_b200_tune(10, -1)
+
+
 def test_config1_backward_grad_b(cuda, oracle):
     # grad_b = sum_rows(G * (A + b > 0)): leaky_relu(0) backward followed by add backward
     A, b, G = rand_uniform(0, (1024, 1024)), rand_uniform(1, (1, 1024)), rand_normal(2, (1024, 1024))
