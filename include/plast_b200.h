@@ -373,9 +373,7 @@ int plast_b200_chain_backward_try_compile(const PlastChainStep *steps, int n_ste
  * threads that share a segment, 10: CTAs per thread-block cluster when the chunks of a column
  * reduce combine through distributed shared memory instead of a ticket in global memory, 0 or 1 =
  * never, 11: 1 = the 3-D tile kernel for inputs turned along two different dims uses 32 x 16 x 16
- * tiles instead of 8 x 32 x 32, 12 / 13 / 14: how many neighbouring tiles along the output's dim 0
- * and the two turned dims are adjacent in that kernel's launch order); a negative value restores
- * the built-in choice. Results do not depend on the geometry
+ * tiles instead of 8 x 32 x 32); a negative value restores the built-in choice. Results do not depend on the geometry
  * beyond the order of additions. */
 void plast_b200_tune(int key, long value);
 /* Test hook: runs the host-side iteration planner (drop size-1 dims, order by the strides of

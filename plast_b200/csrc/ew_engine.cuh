@@ -14,6 +14,7 @@
 #include "iter.h"
 
 #include "ew_kernel_device.cuh"
+#include <type_traits>
 
 namespace pb {
 
@@ -379,10 +380,10 @@ template <int NIN> struct Tiled3Params {
   int n_outer;
   u64 outer_size[MAX_NDIM];
   u64 outer_stride[NIN + 1][MAX_NDIM];
-  // Launch order: CTAs come in groups of g0 x gA x gB neighbouring tiles (dim 0 fastest), the groups
-  // again dim 0 fastest, so that the CTAs resident at one time complete whole lines of the output
-  // (g0 tiles along dim 0) and whole rows of the turned inputs (gA, gB tiles along their own dims).
-  unsigned tiles0, tilesA, tilesB, g0, gA, gB, groups0, groupsA;
+  // blockIdx.x = tile0 + tiles0 * (tileA + tilesA * tileB). Dealing the tiles out in groups of
+  // neighbours along the three dims instead (so that resident CTAs complete whole output lines and
+  // whole rows of the turned inputs together) measured no different on B200.
+  unsigned tiles0, tilesA;
 };
 
 template <class F, int NIN, int D0, int DX, int NT>
@@ -391,12 +392,8 @@ __global__ void __launch_bounds__(NT, 2) ew_tiled3_kernel(F f, Tiled3Params<NIN>
   extern __shared__ float tile3_smem[]; // [staged inputs][jB][jA][i0], padded
   pdl_wait();
   pdl_launch_dependents();
-  const unsigned gsz = p.g0 * p.gA * p.gB;
-  const unsigned local = blockIdx.x % gsz, grp = blockIdx.x / gsz;
-  const unsigned t0 = (grp % p.groups0) * p.g0 + local % p.g0;
-  const unsigned tA = ((grp / p.groups0) % p.groupsA) * p.gA + (local / p.g0) % p.gA;
-  const unsigned tB = (grp / (p.groups0 * p.groupsA)) * p.gB + local / (p.g0 * p.gA);
-  if (t0 >= p.tiles0 || tA >= p.tilesA || tB >= p.tilesB) return; // padding of a ragged group
+  const unsigned t0 = blockIdx.x % p.tiles0, tAB = blockIdx.x / p.tiles0;
+  const unsigned tA = tAB % p.tilesA, tB = tAB / p.tilesA;
   u64 off[NIN + 1];
 #pragma unroll
   for (int a = 0; a <= NIN; ++a) off[a] = 0;
@@ -408,66 +405,171 @@ __global__ void __launch_bounds__(NT, 2) ew_tiled3_kernel(F f, Tiled3Params<NIN>
     rest = q;
   }
   const u64 c0 = (u64)t0 * D0, cA = (u64)tA * DX, cB = (u64)tB * DX; // tile origin
-  // staging pass: thread = (sq: float4 lane along the input's own dim, si: along dim 0, sh), a few
-  // trips over the remaining dim; every load is issued before the first store to shared memory
-  const unsigned sq = threadIdx.x % T::kLanes, si = (threadIdx.x / T::kLanes) % D0, sh = threadIdx.x / (T::kLanes * D0);
-  float4 v[NIN][T::kStageTrips];
-#pragma unroll
-  for (int a = 0; a < NIN; ++a) {
-    if (p.cls[a] == 0) continue;
-    const bool alongA = p.cls[a] == 1;
-    const u64 own = (alongA ? cA : cB) + sq * 4, own_n = alongA ? p.nA : p.nB;
-    const u64 oth0 = alongA ? cB : cA, oth_n = alongA ? p.nB : p.nA, oth_s = alongA ? p.sB[a + 1] : p.sA[a + 1];
-    const float *base = p.in[a] + off[a + 1] + (c0 + si) * p.s0[a + 1] + own;
-#pragma unroll
-    for (int j = 0; j < T::kStageTrips; ++j) {
-      const u64 oth = oth0 + sh + T::kStageH * j;
-      if (c0 + si < p.n0 && own < own_n && oth < oth_n)
-        v[a][j] = __ldcs(reinterpret_cast<const float4 *>(base + oth * oth_s));
-    }
-  }
-#pragma unroll
-  for (int a = 0; a < NIN; ++a) {
-    if (p.cls[a] == 0) continue;
-    const bool alongA = p.cls[a] == 1;
-    float *tl = tile3_smem + (size_t)p.slot[a] * T::kFloats + si;
-#pragma unroll
-    for (int j = 0; j < T::kStageTrips; ++j) {
-      const unsigned oth = sh + T::kStageH * j;
-      const unsigned at = alongA ? oth * T::kPlane + (sq * 4) * T::kRow : (sq * 4) * T::kPlane + oth * T::kRow;
-      const unsigned step = alongA ? T::kRow : T::kPlane;
-      tl[at] = v[a][j].x; tl[at + step] = v[a][j].y; tl[at + 2 * step] = v[a][j].z; tl[at + 3 * step] = v[a][j].w;
-    }
-  }
-  __syncthreads();
-  // output pass: thread = (q4: float4 along dim 0, jA, oh), a few trips over jB
-  const unsigned q4 = threadIdx.x % T::kQ0, jA = (threadIdx.x / T::kQ0) % DX, oh = threadIdx.x / (T::kQ0 * DX);
-  const u64 i0 = c0 + q4 * 4;
-  if (i0 >= p.n0 || cA + jA >= p.nA) return;
-#pragma unroll
-  for (int j = 0; j < T::kOutTrips; ++j) {
-    const unsigned jB = oh + T::kOutH * j;
-    if (cB + jB >= p.nB) continue;
-    float x[4][NIN];
-#pragma unroll
+  // A tile that lies wholly inside the tensor (all of them, for extents that are multiples of the tile)
+  // runs without per-access bounds checks.
+  auto run = [&](auto full_tile) {
+    constexpr bool FULL = decltype(full_tile)::value;
+    // staging pass: thread = (sq: float4 lane along the input's own dim, si: along dim 0, sh), a few
+    // trips over the remaining dim; every load is issued before the first store to shared memory
+    const unsigned sq = threadIdx.x % T::kLanes, si = (threadIdx.x / T::kLanes) % D0, sh = threadIdx.x / (T::kLanes * D0);
+    float4 v[NIN][T::kStageTrips];
+  #pragma unroll
     for (int a = 0; a < NIN; ++a) {
-      if (p.cls[a] == 0) {
-        const float *q = p.in[a] + off[a + 1] + i0 * p.s0[a + 1] + (cA + jA) * p.sA[a + 1] + (cB + jB) * p.sB[a + 1];
-        if (p.s0[a + 1] == 1) {
-          const float4 d = __ldcs(reinterpret_cast<const float4 *>(q));
-          x[0][a] = d.x; x[1][a] = d.y; x[2][a] = d.z; x[3][a] = d.w;
-        } else { // broadcast along dim 0
-          const float sc = __ldg(q);
-          x[0][a] = x[1][a] = x[2][a] = x[3][a] = sc;
-        }
-      } else {
-        const float *tl = tile3_smem + (size_t)p.slot[a] * T::kFloats + jB * T::kPlane + jA * T::kRow + q4 * 4;
-        x[0][a] = tl[0]; x[1][a] = tl[1]; x[2][a] = tl[2]; x[3][a] = tl[3];
+      if (p.cls[a] == 0) continue;
+      const bool alongA = p.cls[a] == 1;
+      const u64 own = (alongA ? cA : cB) + sq * 4, own_n = alongA ? p.nA : p.nB;
+      const u64 oth0 = alongA ? cB : cA, oth_n = alongA ? p.nB : p.nA, oth_s = alongA ? p.sB[a + 1] : p.sA[a + 1];
+      const float *base = p.in[a] + off[a + 1] + (c0 + si) * p.s0[a + 1] + own;
+  #pragma unroll
+      for (int j = 0; j < T::kStageTrips; ++j) {
+        const u64 oth = oth0 + sh + T::kStageH * j;
+        if (FULL || (c0 + si < p.n0 && own < own_n && oth < oth_n))
+          v[a][j] = __ldcs(reinterpret_cast<const float4 *>(base + oth * oth_s));
       }
     }
-    __stcs(reinterpret_cast<float4 *>(p.out + off[0] + i0 + (cA + jA) * p.sA[0] + (cB + jB) * p.sB[0]),
-           make_float4(f(x[0]), f(x[1]), f(x[2]), f(x[3])));
+  #pragma unroll
+    for (int a = 0; a < NIN; ++a) {
+      if (p.cls[a] == 0) continue;
+      const bool alongA = p.cls[a] == 1;
+      float *tl = tile3_smem + (size_t)p.slot[a] * T::kFloats + si;
+  #pragma unroll
+      for (int j = 0; j < T::kStageTrips; ++j) {
+        const unsigned oth = sh + T::kStageH * j;
+        const unsigned at = alongA ? oth * T::kPlane + (sq * 4) * T::kRow : (sq * 4) * T::kPlane + oth * T::kRow;
+        const unsigned step = alongA ? T::kRow : T::kPlane;
+        tl[at] = v[a][j].x; tl[at + step] = v[a][j].y; tl[at + 2 * step] = v[a][j].z; tl[at + 3 * step] = v[a][j].w;
+      }
+    }
+    __syncthreads();
+    // output pass: thread = (q4: float4 along dim 0, jA, oh), a few trips over jB
+    const unsigned q4 = threadIdx.x % T::kQ0, jA = (threadIdx.x / T::kQ0) % DX, oh = threadIdx.x / (T::kQ0 * DX);
+    const u64 i0 = c0 + q4 * 4;
+    if (!FULL && (i0 >= p.n0 || cA + jA >= p.nA)) return;
+  #pragma unroll
+    for (int j = 0; j < T::kOutTrips; ++j) {
+      const unsigned jB = oh + T::kOutH * j;
+      if (!FULL && cB + jB >= p.nB) continue;
+      float x[4][NIN];
+  #pragma unroll
+      for (int a = 0; a < NIN; ++a) {
+        if (p.cls[a] == 0) {
+          const float *q = p.in[a] + off[a + 1] + i0 * p.s0[a + 1] + (cA + jA) * p.sA[a + 1] + (cB + jB) * p.sB[a + 1];
+          if (p.s0[a + 1] == 1) {
+            const float4 d = __ldcs(reinterpret_cast<const float4 *>(q));
+            x[0][a] = d.x; x[1][a] = d.y; x[2][a] = d.z; x[3][a] = d.w;
+          } else { // broadcast along dim 0
+            const float sc = __ldg(q);
+            x[0][a] = x[1][a] = x[2][a] = x[3][a] = sc;
+          }
+        } else {
+          const float *tl = tile3_smem + (size_t)p.slot[a] * T::kFloats + jB * T::kPlane + jA * T::kRow + q4 * 4;
+          x[0][a] = tl[0]; x[1][a] = tl[1]; x[2][a] = tl[2]; x[3][a] = tl[3];
+        }
+      }
+      __stcs(reinterpret_cast<float4 *>(p.out + off[0] + i0 + (cA + jA) * p.sA[0] + (cB + jB) * p.sB[0]),
+             make_float4(f(x[0]), f(x[1]), f(x[2]), f(x[3])));
+    }
+  };
+  if (c0 + D0 <= p.n0 && cA + DX <= p.nA && cB + DX <= p.nB) run(std::true_type{});
+  else run(std::false_type{});
+}
+
+// The same turn with 8 x 32 x 32 tiles staged by cp.async: every thread sends four 16-byte pieces per
+// turned input straight from global to shared memory (no registers in between, no scalar scatter),
+// rows kept as they lie in memory; the turn happens when the output pass reads shared memory along
+// dim 0. Row stride 36 floats and plane stride 292 keep every piece 16-byte aligned and make the
+// reads of BOTH kinds of input conflict-free when a warp covers 2 float4 (dim 0) x 4 (dA) x 4 (dB):
+// bank = 16 * q4 + jA + 4 * jB for an input that runs along dA, 16 * q4 + jB + 4 * jA along dB.
+struct Tile3Async {
+  static constexpr int kD0 = 8, kDX = 32, kThreads = 512;
+  static constexpr int kRow = kDX + 4;            // floats between rows (dim 0) of one plane
+  static constexpr int kPlane = kD0 * kRow + 4;   // floats between planes (the input's other dim)
+  static constexpr int kFloats = kDX * kPlane;    // per staged input
+};
+
+__device__ __forceinline__ void cp_async_16(float *smem_dst, const float *src) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() {
+  asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
+}
+
+template <class F, int NIN>
+__global__ void __launch_bounds__(Tile3Async::kThreads, 3) ew_tiled3_async_kernel(F f, Tiled3Params<NIN> p) {
+  using T = Tile3Async;
+  extern __shared__ __align__(16) float tile3a_smem[]; // [staged inputs][other dim][dim 0][own dim], padded
+  pdl_wait();
+  pdl_launch_dependents();
+  const unsigned t0 = blockIdx.x % p.tiles0, tAB = blockIdx.x / p.tiles0;
+  const unsigned tA = tAB % p.tilesA, tB = tAB / p.tilesA;
+  u64 off[NIN + 1];
+#pragma unroll
+  for (int a = 0; a <= NIN; ++a) off[a] = 0;
+  u64 rest = blockIdx.y;
+  for (int d = 0; d < p.n_outer; ++d) {
+    const u64 q = rest / p.outer_size[d], r = rest - q * p.outer_size[d];
+#pragma unroll
+    for (int a = 0; a <= NIN; ++a) off[a] += r * p.outer_stride[a][d];
+    rest = q;
   }
+  const u64 c0 = (u64)t0 * T::kD0, cA = (u64)tA * T::kDX, cB = (u64)tB * T::kDX; // tile origin
+  auto run = [&](auto full_tile) {
+    constexpr bool FULL = decltype(full_tile)::value;
+    // staging: thread = (sq: 16-byte piece along the input's own dim, si: row along dim 0, sh), four
+    // trips over the input's other dim
+    const unsigned sq = threadIdx.x & 7, si = (threadIdx.x >> 3) & 7, sh = threadIdx.x >> 6;
+#pragma unroll
+    for (int a = 0; a < NIN; ++a) {
+      if (p.cls[a] == 0) continue;
+      const bool alongA = p.cls[a] == 1;
+      const u64 own = (alongA ? cA : cB) + sq * 4, own_n = alongA ? p.nA : p.nB;
+      const u64 oth0 = (alongA ? cB : cA) + sh, oth_n = alongA ? p.nB : p.nA, oth_s = alongA ? p.sB[a + 1] : p.sA[a + 1];
+      const float *src = p.in[a] + off[a + 1] + (c0 + si) * p.s0[a + 1] + own + oth0 * oth_s;
+      float *dst = tile3a_smem + (size_t)p.slot[a] * T::kFloats + sh * T::kPlane + si * T::kRow + sq * 4;
+      const bool mine = FULL || (c0 + si < p.n0 && own < own_n);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (mine && (FULL || oth0 + 8 * j < oth_n)) cp_async_16(dst + j * 8 * T::kPlane, src);
+        src += 8 * oth_s;
+      }
+    }
+    cp_async_wait_all();
+    __syncthreads();
+    // output pass: a warp covers 2 float4 along dim 0 x 4 along dA x 4 along dB; 16 warps, four trips
+    const unsigned q4 = threadIdx.x & 1, jAl = (threadIdx.x >> 1) & 3, jBl = (threadIdx.x >> 3) & 3, w = threadIdx.x >> 5;
+    const u64 i0 = c0 + q4 * 4;
+    if (!FULL && i0 >= p.n0) return;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const unsigned pair = w + 16 * j;
+      const unsigned jA = (pair & 7) * 4 + jAl, jB = (pair >> 3) * 4 + jBl;
+      if (!FULL && (cA + jA >= p.nA || cB + jB >= p.nB)) continue;
+      float x[4][NIN];
+#pragma unroll
+      for (int a = 0; a < NIN; ++a) {
+        if (p.cls[a] == 0) {
+          const float *q = p.in[a] + off[a + 1] + i0 * p.s0[a + 1] + (cA + jA) * p.sA[a + 1] + (cB + jB) * p.sB[a + 1];
+          if (p.s0[a + 1] == 1) {
+            const float4 d = __ldcs(reinterpret_cast<const float4 *>(q));
+            x[0][a] = d.x; x[1][a] = d.y; x[2][a] = d.z; x[3][a] = d.w;
+          } else { // broadcast along dim 0
+            const float sc = __ldg(q);
+            x[0][a] = x[1][a] = x[2][a] = x[3][a] = sc;
+          }
+        } else {
+          const bool alongA = p.cls[a] == 1;
+          const float *tl = tile3a_smem + (size_t)p.slot[a] * T::kFloats + (alongA ? jB : jA) * T::kPlane +
+                            (q4 * 4) * T::kRow + (alongA ? jA : jB);
+          x[0][a] = tl[0]; x[1][a] = tl[T::kRow]; x[2][a] = tl[2 * T::kRow]; x[3][a] = tl[3 * T::kRow];
+        }
+      }
+      __stcs(reinterpret_cast<float4 *>(p.out + off[0] + i0 + (cA + jA) * p.sA[0] + (cB + jB) * p.sB[0]),
+             make_float4(f(x[0]), f(x[1]), f(x[2]), f(x[3])));
+    }
+  };
+  if (c0 + T::kD0 <= p.n0 && cA + T::kDX <= p.nA && cB + T::kDX <= p.nB) run(std::true_type{});
+  else run(std::false_type{});
 }
 
 // Runs the plan through the 3-D tile kernel when exactly two different unit-stride dims other than
@@ -535,34 +637,19 @@ bool launch_ew_tiled3(const IterPlan &plan, float *out, const float *const *ins,
   const u64 d0 = wide_reads ? 8 : 32, dx = wide_reads ? 32 : 16;
   const u64 tiles0 = (p.n0 + d0 - 1) / d0, tilesA = (p.nA + dx - 1) / dx, tilesB = (p.nB + dx - 1) / dx;
   if (tiles0 > 0xfffffful || tilesA > 0xfffffful || tilesB > 0xfffffful) return false;
-  auto group = [](long forced, u64 dflt, u64 tiles) {
-    u64 g = forced > 0 ? (u64)forced : dflt;
-    return (unsigned)(g < tiles ? g : tiles);
-  };
-  // a 128-byte output line = 32 / d0 tiles along dim 0; four tiles of 32 floats along dA or dB = 512 B
-  p.g0 = group(tuned(kTuneTile3Group0), 32 / d0, tiles0);
-  p.gA = group(tuned(kTuneTile3GroupA), 4, tilesA);
-  p.gB = group(tuned(kTuneTile3GroupB), 4, tilesB);
   p.tiles0 = (unsigned)tiles0;
   p.tilesA = (unsigned)tilesA;
-  p.tilesB = (unsigned)tilesB;
-  p.groups0 = (unsigned)((tiles0 + p.g0 - 1) / p.g0);
-  p.groupsA = (unsigned)((tilesA + p.gA - 1) / p.gA);
-  const u64 groupsB = (tilesB + p.gB - 1) / p.gB;
-  const u64 tiles = (u64)p.groups0 * p.groupsA * groupsB * p.g0 * p.gA * p.gB;
+  const u64 tiles = tiles0 * tilesA * tilesB;
   if (tiles > 0x7fffffffull) return false;
   const dim3 grid((unsigned)tiles, (unsigned)outer);
-  // 512 threads with four float4 per thread and input (<= 64 registers, two CTAs per SM) measured
+  // 512 threads with four float4 per thread and input (64 registers, two CTAs per SM) measured 3 %
   // faster than 256 threads with eight (122 registers, two CTAs of half the size).
-  auto go = [&](auto kernel, size_t floats_per_input, unsigned threads) {
+  auto go = [&](auto kernel, size_t floats_per_input) {
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(NIN * floats_per_input * sizeof(float)));
-    launch_k(kernel, grid, dim3(threads), (size_t)staged * floats_per_input * sizeof(float), stream(), f, p);
+    launch_k(kernel, grid, dim3(512), (size_t)staged * floats_per_input * sizeof(float), stream(), f, p);
   };
-  const bool big_cta = tuned(kTuneTile3Threads) != 256;
-  if (wide_reads && big_cta) go(ew_tiled3_kernel<F, NIN, 8, 32, 512>, Tile3<8, 32, 512>::kFloats, 512);
-  else if (wide_reads) go(ew_tiled3_kernel<F, NIN, 8, 32, 256>, Tile3<8, 32, 256>::kFloats, 256);
-  else if (big_cta) go(ew_tiled3_kernel<F, NIN, 32, 16, 512>, Tile3<32, 16, 512>::kFloats, 512);
-  else go(ew_tiled3_kernel<F, NIN, 32, 16, 256>, Tile3<32, 16, 256>::kFloats, 256);
+  if (wide_reads) go(ew_tiled3_async_kernel<F, NIN>, Tile3Async::kFloats);
+  else go(ew_tiled3_kernel<F, NIN, 32, 16, 512>, Tile3<32, 16, 512>::kFloats);
   count_launch();
   note_kernel("ew_tiled_transpose_two_dims");
   return true;
