@@ -318,6 +318,12 @@ def cpu_per_op_baselines(rows):
             fns[(6, f"{kindname}_step_24_params")] = (lambda fn=fn, opt=opt, keep=keep: fn(C.byref(opt), arr, len(params)),
                                                       frac6, smp6)
 
+    # tall column sums: 8192 rows of each shape
+    for rows7, cols7 in ((65536, 256), (262144, 128), (32768, 512), (16384, 2048), (8192, 1024)):
+        X7, o7 = be.tensor(Nrm(20, (8192, cols7))), be.empty((cols7,))
+        fns[(7, f"sum_axis0_{rows7}x{cols7}")] = (lambda X7=X7, o7=o7: be.forward("sum", [X7], o7, dim=0), 8192.0 / rows7,
+                                                  f"8192 of {rows7} rows")
+
     for row in rows:
         key = (row.get("config"), row.get("op"))
         if key not in fns or "bytes" not in row:
@@ -693,7 +699,8 @@ def main():
     ap.add_argument("--per-op-only", action="store_true",
                     help="only the per-op table (1 GPU); with --op-reps 0 every op is launched 3 times and "
                          "not timed, which is the command the profiler captures use")
-    ap.add_argument("--configs", default="1,2,3,4,5,6", help="configs of the per-op table (6 = optimiser steps)")
+    ap.add_argument("--configs", default="1,2,3,4,5,6,7",
+                    help="configs of the per-op table (6 = optimiser steps, 7 = column sums of tall matrices)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -131,10 +131,12 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
     g->kind = kRedCols;
     // A CTA sweeps a strip of tx_n lanes (x VEC outputs) with 256 / tx_n row-workers; the reduced
     // dim is cut into `splits` chunks so that ONE resident wave of equally loaded CTAs covers the
-    // tensor (CTAs beyond the wave would run as a second, mostly empty one). Strips one warp wide
-    // (512 B per row with float4, eight row-workers) measured fastest by a wide margin on B200:
-    // 46 us for the column sum of 8192 x 8192 against 49 / 62 / 113 us with 64 / 128 / 256 lanes,
-    // whichever way the wave was filled; wider strips are only for plast_b200_tune.
+    // tensor (CTAs beyond the wave would run as a second, mostly empty one). Strip width: the widest
+    // of 8 / 16 / 32 lanes that still leaves 64 strips, i.e. FEW chunks per strip. Measured on B200
+    // (graph replay, float4 lanes): 8192 x 8192 46 us with 8 lanes, 40 with 32, 49 / 62 / 113 with
+    // 64 / 128 / 256; but with few columns 32 lanes leave a handful of strips cut into hundreds of
+    // chunks each, and narrower strips win by far: 65536 x 256 46.6 -> 13.6 us, 262144 x 128
+    // 95 -> 30, 32768 x 512 29.7 -> 13.5, 8192 x 1024 18.0 -> 8.2, 4096 x 4096 13.8 -> 10.2 (16 lanes).
     u64 ctas_per_sm = (u64)occ.ctas_per_sm[kRedCols][vi] < 4 ? (u64)occ.ctas_per_sm[kRedCols][vi] : 4;
     if (tuned(kTuneColsCtasPerSm) > 0) ctas_per_sm = (u64)tuned(kTuneColsCtasPerSm);
     const u64 wave = sms * ctas_per_sm;
@@ -142,17 +144,22 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
     u64 min_batches = 2; // (one batch per row-worker, i.e. twice the CTAs, measured slower even at 4 MiB)
     if (tuned(kTuneColsMinBatches) > 0) min_batches = (u64)tuned(kTuneColsMinBatches);
     double best_fill = -1.0;
-    int forced_ltx = 5;
+    int forced_ltx = 3;
+    for (int ltx = 5; ltx > 3; --ltx)
+      if (g->n_kept * ceil_div(g->len0_items, (u64)1 << ltx) >= 64) {
+        forced_ltx = ltx;
+        break;
+      }
     u64 cluster = 0;      // forced cluster size (tuning hook)
     bool auto_cluster = true;
+    u64 in_bytes = 0;
+    for (int a = 0; a < nin; ++a) in_bytes += (plan.max_offset[a + 1] + 1) * sizeof(float);
     {
       // Inputs that fit L2 with a short reduced dim (the bias gradient of a 1024 x 1024 layer) are
       // bound by the latencies of a split reduction: partial store, fence, ticket, second pass.
       // Narrow strips (2+ lanes of float4, the other threads of the CTA as row-workers) give the
       // same number of CTAs without a split: every CTA reduces its columns over ALL rows in at most
       // four load batches per thread and stores the result itself.
-      u64 in_bytes = 0;
-      for (int a = 0; a < nin; ++a) in_bytes += (plan.max_offset[a + 1] + 1) * sizeof(float);
       if (in_bytes <= ((u64)32 << 20) && g->n_red_dims <= 1) {
         for (int ltx = 1; ltx < 5; ++ltx) {
           const u64 tx_n = (u64)1 << ltx, ty_n = (u64)kRedThreads >> ltx;
@@ -187,7 +194,11 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
       // against the ticket with the same strips: 8192 x 8192 38.4 against 40.5 us (eight chunks
       // instead of nine), 1024 x 8192 7.6 against 12.8 us. A tile that needs more than ~8 chunks to
       // fill the GPU keeps the ticket (4096 x 4096: 18 chunks, 14.3 us; as a cluster of 8, 16.5 us).
-      if (auto_cluster && splits >= 2 && splits <= 10) cluster = splits < 8 ? splits : 8;
+      // Up to 64 MiB eight chunks per strip also beat a wave-filling ticket split when that still
+      // gives ~1.5 CTAs per SM (8192 x 1024: 32 strips x 8 = 256 CTAs 8.2 us, x 18 with a ticket 10.0).
+      if (auto_cluster && splits >= 2 &&
+          (splits <= 10 || (tiles * 16 >= 3 * sms && in_bytes <= ((u64)64 << 20))))
+        cluster = splits < 8 ? splits : 8;
       if (cluster > 1 && g->n_red >= cluster) {
         // exactly `cluster` chunks (trailing ones may be empty)
         splits = cluster;

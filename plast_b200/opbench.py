@@ -18,7 +18,7 @@ import numpy as np
 NOMINAL = 8000.0
 
 
-def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2, 3, 4, 5, 6),
+def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2, 3, 4, 5, 6, 7),
                  chain_elems: int = 1 << 28):
     """chain_elems: length of configuration 2's vectors (2^28 in the benchmark; profiler captures use
     fewer so that the device memory a multi-pass capture has to save stays small)."""
@@ -365,5 +365,16 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
         timeit(6, "adamw_step_24_params", lambda: pb.lib.adamw_step_cuda(C.byref(adamw), arr, len(params)), 7 * n * F, n, 4 * n * F)
         O.release_state(adamw)
         del ps, gs
+    if 7 in configs:
+        # Column sums of TALL matrices (not one of the reference's benchmark configurations): the
+        # shape of a bias gradient, sum over (batch x positions) rows for a few hundred or thousand
+        # features. Few columns leave few strips for the column kernel; see its strip-width rule.
+        for rows_, cols_ in ((65536, 256), (262144, 128), (32768, 512), (16384, 2048), (8192, 1024)):
+            X = randn((rows_, cols_), 20)
+            o = torch.empty(cols_, device=dev)
+            tX, to = wrap(X), wrap(o)
+            n = rows_ * cols_
+            timeit(7, f"sum_axis0_{rows_}x{cols_}", lambda: pb.forward("sum", [tX], to, dim=0, check=False), n * F, n, n * F)
+            del X, o
     torch.cuda.synchronize()
     return rows
