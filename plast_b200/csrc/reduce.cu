@@ -71,6 +71,7 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
   const u64 target_ctas = sms * (u64)occ.ctas_per_sm[dim0_reduced ? kRedSeg : kRedCols][vi];
   g->splits = 1;
   g->cluster = 0;
+  g->outers_per_cta = 1;
   g->seg_len = g->nsplit0 = g->nseg = g->per_chunk = 0;
   g->log_tx = 5;
 
@@ -87,7 +88,7 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
       g->log_tx = log_tx;
       const u64 rows_per_cta = (u64)kRedThreads >> log_tx;
       u64 blocks = ceil_div(g->n_kept, rows_per_cta);
-      const u64 cap = sms * 64; // grid-stride beyond this
+      const u64 cap = sms * 64; // grid-stride beyond this (a CTA per group of rows measured 15 % slower for short rows)
       g->grid = blocks < cap ? blocks : cap;
       return true;
     }
@@ -150,6 +151,15 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
         forced_ltx = ltx;
         break;
       }
+    // A SHORT reduced dim (a [4096, 16, 1024] sum over the middle axis) cannot feed many row-workers:
+    // widen the strip instead until every worker has at least 16 indices (four load batches) or the
+    // strip covers the whole kept run; with 16 indices that is one thread per output vector and no
+    // tree at all (268 MB: 186 us with eight workers of two rows each).
+    // A kept run shorter than that strip ([65536, 16, 64] over the middle axis) shares the CTA with
+    // the runs of the next outer indices: lanes = (outer index, item).
+    while (forced_ltx < 8 && ((u64)kRedThreads >> forced_ltx) * 16 > g->n_red &&
+           ((u64)1 << forced_ltx) < g->len0_items * g->n_kept)
+      ++forced_ltx;
     u64 cluster = 0;      // forced cluster size (tuning hook)
     bool auto_cluster = true;
     u64 in_bytes = 0;
@@ -178,9 +188,16 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
     }
     for (int ltx = forced_ltx; ltx <= forced_ltx; ++ltx) {
       const u64 tx_n = (u64)1 << ltx, ty_n = (u64)kRedThreads >> ltx;
-      const u64 strips = ceil_div(g->len0_items, tx_n);
-      const u64 tiles = g->n_kept * strips;
+      u64 outers = 1;
+      if (g->n_kept > 1 && tx_n >= 2 * g->len0_items && g->len0_items <= 0xffffu) {
+        outers = tx_n / g->len0_items;
+        if (outers > g->n_kept) outers = g->n_kept;
+      }
+      g->outers_per_cta = (unsigned)outers;
+      const u64 strips = outers > 1 ? 1 : ceil_div(g->len0_items, tx_n);
+      const u64 tiles = outers > 1 ? ceil_div(g->n_kept, outers) : g->n_kept * strips;
       u64 splits = wave / tiles > 0 ? wave / tiles : 1;
+      if (outers > 1) splits = 1;
       const u64 min_per = ty_n * 4 * min_batches;
       const u64 max_splits = g->n_red / min_per > 0 ? g->n_red / min_per : 1;
       if (splits > max_splits) splits = max_splits;
@@ -199,7 +216,7 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
       if (auto_cluster && splits >= 2 &&
           (splits <= 10 || (tiles * 16 >= 3 * sms && in_bytes <= ((u64)64 << 20))))
         cluster = splits < 8 ? splits : 8;
-      if (cluster > 1 && g->n_red >= cluster) {
+      if (cluster > 1 && g->n_red >= cluster && outers <= 1) {
         // exactly `cluster` chunks (trailing ones may be empty)
         splits = cluster;
         per_chunk = ceil_div(g->n_red, splits);

@@ -171,6 +171,8 @@ template <int NIN> struct RedParams {
   const PeerLink *peer; // not NULL: the thread that holds the single final value exchanges it across GPUs
   unsigned cluster;     // cols: > 1 = the `splits` CTAs of a tile are one thread-block cluster and combine
                         // through distributed shared memory (no partials in global memory, no ticket)
+  unsigned outers_per_cta; // cols: > 1 = the kept run along dim 0 is shorter than the strip and the lanes of
+                        // a CTA cover this many consecutive outer kept indices (no split: splits == 1)
   bool strip_major;     // cols: consecutive CTAs take neighbouring strips of the same chunk of rows
   unsigned prefetch_batches; // cols: load batches ahead of which a row-worker asks L2 for its rows (0 = off)
   unsigned prefetch_until;   // cols: only the first so many batches of a chunk prefetch (0 = all of them)
@@ -454,10 +456,22 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
   const unsigned n_tiles = gridDim.x / p.splits;
   const u64 tile = p.strip_major ? blockIdx.x % n_tiles : blockIdx.x / p.splits;
   const unsigned chunk = p.strip_major ? blockIdx.x / n_tiles : blockIdx.x % p.splits;
-  const u64 outer = tile / strips;
-  const u64 strip = tile - outer * strips;
-  const u64 item = (strip << p.log_tx) + lane;
-  const bool live = item < p.len0;
+  u64 outer, strip, item;
+  bool live;
+  if (p.outers_per_cta > 1) {
+    // short kept runs: lanes = (outer kept index, item of its run)
+    const unsigned sub = lane / (unsigned)p.len0;
+    outer = tile * p.outers_per_cta + sub;
+    strip = 0;
+    item = lane - sub * (unsigned)p.len0;
+    live = sub < p.outers_per_cta && outer < p.n_kept;
+    if (!live) outer = 0;
+  } else {
+    outer = tile / strips;
+    strip = tile - outer * strips;
+    item = (strip << p.log_tx) + lane;
+    live = item < p.len0;
+  }
 
   u64 toff = 0, base[NIN];
 #pragma unroll
@@ -710,6 +724,7 @@ struct RedGeometry {
   u64 len0_items, seg_len, nsplit0, nseg, per_chunk, n_kept, n_red, grid;
   unsigned splits;
   unsigned cluster; // cols: the splits of a tile form a cluster of this many CTAs (0 or 1: no cluster)
+  unsigned outers_per_cta; // cols: outer kept indices covered by the lanes of one CTA (short kept runs)
   int kept_dims[MAX_NDIM], n_kept_dims; // plan dim indices in each sub-space
   int red_dims[MAX_NDIM], n_red_dims;
 };
@@ -863,6 +878,7 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   p.partials = nullptr;
   p.peer = nullptr;
   p.cluster = g.cluster;
+  p.outers_per_cta = g.kind == kRedCols ? g.outers_per_cta : 1;
   p.strip_major = g.cluster <= 1 && tuned(kTuneColsTileMajor) > 0; // measured: the order of the CTAs makes no difference
   // Column sweep: every row-worker asks L2 for the rows of its NEXT load batch (one bulk prefetch
   // per 512-byte row piece) during the first 16 batches of its chunk. Measured on B200: 46.5 -> 40.5
@@ -874,7 +890,8 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
   // strips) the extra instructions cost more than they bring (config 1's grad_b: 5.3 -> 10 us).
   const u64 batches_per_worker = g.per_chunk / (((u64)kRedThreads >> g.log_tx) * 4);
   p.prefetch_batches = tuned(kTuneColsPrefetch) >= 0 ? (unsigned)tuned(kTuneColsPrefetch)
-                                                     : (g.kind == kRedCols && g.log_tx >= 5 && batches_per_worker >= 16 ? 1u : 0u);
+                                                     : (g.kind == kRedCols && g.log_tx >= 5 && batches_per_worker >= 16 &&
+                                                                g.outers_per_cta <= 1 ? 1u : 0u);
   p.prefetch_until = tuned(kTuneColsPrefetchUntil) >= 0 ? (unsigned)tuned(kTuneColsPrefetchUntil) : 16u;
   p.seg_prefetch = tuned(kTuneSegPrefetch) >= 0 ? (unsigned)tuned(kTuneSegPrefetch) : (unsigned)kPrefetchAhead;
   // a pending cross-GPU exchange rides on the kernel whose last CTA holds THE final value

@@ -54,11 +54,11 @@ struct SmRows {
   u64 x_axis_stride, y_axis_stride, z_axis_stride; // element strides along the axis
 };
 
-// Reduction over the TX threads of a row-worker (TX = 1 << log_tx, 32 <= TX <= 256).
+// Reduction over the TX threads of a row-worker (TX = 1 << log_tx, 1 <= TX <= 256).
 // Every thread of the CTA must call it (it synchronises when TX > 32).
 template <class Op>
 __device__ __forceinline__ float row_reduce(float v, int log_tx, float *smem /* [8] */) {
-  v = warp_reduce<Op>(v, 32);
+  v = warp_reduce<Op>(v, log_tx < 5 ? 1 << log_tx : 32);
   if (log_tx > 5) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wpr = 1 << (log_tx - 5); // warps per row-worker
@@ -74,7 +74,10 @@ __device__ __forceinline__ float row_reduce(float v, int log_tx, float *smem /* 
 
 // ---- forward, fast path ---------------------------------------------------------------------------
 // CE: `labels` int32 per row, per-CTA partial loss sums go through the ticket scheme.
-template <int MODE, int VPT>
+// VEC = 4: rows are read and written as float4 (cols % 4 == 0, 16-byte aligned rows). VEC = 1: any
+// row length up to 2048 as scalars (10 classes, odd sizes). Rows shorter than 32 vectors take a
+// power-of-two slice of a warp each, so that a warp reads several whole rows per instruction.
+template <int MODE, int VPT, int VEC>
 __global__ void __launch_bounds__(kSmThreads, 4)
 softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const int *__restrict__ labels,
                     SmRows g, int log_tx, float *row_loss) {
@@ -84,26 +87,36 @@ softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const in
   const int tx_n = 1 << log_tx;
   const int tx = threadIdx.x & (tx_n - 1), ty = threadIdx.x >> log_tx;
   const int rows_per_cta = kSmThreads >> log_tx;
-  const u64 nvec = g.cols >> 2;
+  const u64 nvec = g.cols / VEC;
   // Every thread of the CTA reaches both row_reduce calls (they synchronise when TX > 32).
   { // one group of rows per CTA (the grid covers every row)
     const u64 row = (u64)blockIdx.x * rows_per_cta + ty;
     const bool live = row < g.rows;
     u64 yoff = 0, ioff[2] = {0, 0};
     if (live) g.outer.offsets(row, &yoff, ioff);
-    const float4 *xr = reinterpret_cast<const float4 *>(x + ioff[0]);
+    const float *xr = x + ioff[0];
 
-    float4 v[VPT];
+    float v[VPT][VEC];
     float m = -FLT_MAX; // src/kernels/cpu/reduce_ops.c:273
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const u64 j = (u64)tx + (u64)i * tx_n;
-      if (live && j < nvec) v[i] = __ldcs(xr + j);
+      if (live && j < nvec) {
+        if (VEC == 4) {
+          const float4 t = __ldcs(reinterpret_cast<const float4 *>(xr) + j);
+          v[i][0] = t.x; v[i][1] = t.y; v[i][VEC > 2 ? 2 : 0] = t.z; v[i][VEC > 3 ? 3 : 0] = t.w;
+        } else {
+          v[i][0] = __ldcs(xr + j);
+        }
+      }
     }
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const u64 j = (u64)tx + (u64)i * tx_n;
-      if (live && j < nvec) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+      if (live && j < nvec) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) m = fmaxf(m, v[i][k]);
+      }
     }
     m = row_reduce<MaxOp>(m, log_tx, red_smem);
     float s = 0.0f;
@@ -112,13 +125,14 @@ softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const in
       const u64 j = (u64)tx + (u64)i * tx_n;
       if (live && j < nvec) {
         // sub, then exp: two separately rounded ops
-        v[i].x = v[i].x - m; v[i].y = v[i].y - m; v[i].z = v[i].z - m; v[i].w = v[i].w - m;
-        if (MODE == kSoftmax) {
-          v[i].x = exp_softmax(v[i].x); v[i].y = exp_softmax(v[i].y); v[i].z = exp_softmax(v[i].z); v[i].w = exp_softmax(v[i].w);
-          s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-        } else {
-          s += (exp_softmax(v[i].x) + exp_softmax(v[i].y)) + (exp_softmax(v[i].z) + exp_softmax(v[i].w));
+        float e[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+          v[i][k] = v[i][k] - m;
+          e[k] = exp_softmax(v[i][k]);
+          if (MODE == kSoftmax) v[i][k] = e[k];
         }
+        s += VEC == 4 ? (e[0] + e[1]) + (e[VEC > 2 ? 2 : 0] + e[VEC > 3 ? 3 : 0]) : e[0];
       }
     }
     s = row_reduce<SumOp>(s, log_tx, red_smem);
@@ -129,13 +143,15 @@ softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const in
       if (live) {
         const int label = labels[row];
         if (label >= 0 && (u64)label < g.cols) {
-          const u64 jv = (u64)label >> 2;
+          const u64 jv = (u64)label / VEC;
           if ((int)(jv & (u64)(tx_n - 1)) == tx) {
-            const int slot = (int)(jv >> log_tx), comp = label & 3;
+            const int slot = (int)(jv >> log_tx), comp = label % VEC;
             float sh = 0.0f;
 #pragma unroll
             for (int i = 0; i < VPT; ++i)
-              if (i == slot) sh = comp == 0 ? v[i].x : (comp == 1 ? v[i].y : (comp == 2 ? v[i].z : v[i].w));
+#pragma unroll
+              for (int k = 0; k < VEC; ++k)
+                if (i == slot && k == comp) sh = v[i][k];
             row_loss[row] = -(sh - logf(s));
           }
         } else if (tx == 0) {
@@ -145,7 +161,7 @@ softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const in
       return;
     }
 
-    float4 *yr = reinterpret_cast<float4 *>(y + yoff);
+    float *yr = y + yoff;
     const float lse = (MODE == kLogSoftmax) ? logf(s) : 0.0f;
     // One correctly rounded reciprocal per row, then a multiply per element: within 1 ulp of the
     // recipe's exp_x / sum_exp (the exponentials themselves are ~3 ulp), and a tenth of the
@@ -155,15 +171,67 @@ softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const in
     for (int i = 0; i < VPT; ++i) {
       const u64 j = (u64)tx + (u64)i * tx_n;
       if (live && j < nvec) {
-        float4 r;
-        if (MODE == kSoftmax) {
-          r.x = v[i].x * inv_s; r.y = v[i].y * inv_s; r.z = v[i].z * inv_s; r.w = v[i].w * inv_s;
-        } else {
-          r.x = v[i].x - lse; r.y = v[i].y - lse; r.z = v[i].z - lse; r.w = v[i].w - lse;
-        }
-        __stcs(yr + j, r);
+        float r[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) r[k] = (MODE == kSoftmax) ? v[i][k] * inv_s : v[i][k] - lse;
+        if (VEC == 4) __stcs(reinterpret_cast<float4 *>(yr) + j, make_float4(r[0], r[1], r[VEC > 2 ? 2 : 0], r[VEC > 3 ? 3 : 0]));
+        else __stcs(yr + j, r[0]);
       }
     }
+  }
+}
+
+// ---- forward, tiny rows (<= 32 classes: a 10-way classifier head) ---------------------------------------
+// Dense rows this short leave most lanes of any per-row thread group idle. Here a CTA moves 256
+// whole rows between global and shared memory with fully coalesced accesses (row stride in shared
+// memory made odd: conflict-free for the next step), and every THREAD owns one row there: max, the
+// exponentials and their sum, the results written back in place, no shuffles.
+constexpr int kTinyCols = 32;
+template <int MODE>
+__global__ void __launch_bounds__(kSmThreads)
+softmax_tiny_rows_kernel(const float *__restrict__ x, float *__restrict__ y, const int *__restrict__ labels,
+                         u64 rows, unsigned cols, unsigned div_magic, float *row_loss) {
+  __shared__ float tile[kSmThreads * (kTinyCols + 1)];
+  pdl_wait();
+  pdl_launch_dependents();
+  const unsigned stride = cols | 1u;
+  const u64 row0 = (u64)blockIdx.x * kSmThreads;
+  const unsigned n_rows = (unsigned)(rows - row0 < (u64)kSmThreads ? rows - row0 : (u64)kSmThreads);
+  const unsigned n = n_rows * cols;
+  const float *xs = x + row0 * cols;
+  for (unsigned i = threadIdx.x; i < n; i += kSmThreads) {
+    const unsigned r = (unsigned)(((u64)i * div_magic) >> 21); // i / cols for i < 2^16, cols <= 32
+    tile[r * stride + (i - r * cols)] = __ldcs(xs + i);
+  }
+  __syncthreads();
+  if (threadIdx.x < n_rows) {
+    float *mine = tile + threadIdx.x * stride;
+    float m = -FLT_MAX; // src/kernels/cpu/reduce_ops.c:273
+    for (unsigned c = 0; c < cols; ++c) m = fmaxf(m, mine[c]);
+    float sum = 0.0f;
+    for (unsigned c = 0; c < cols; ++c) {
+      const float sh = mine[c] - m; // sub, then exp: two separately rounded ops
+      const float e = exp_softmax(sh);
+      sum += e;
+      mine[c] = (MODE == kSoftmax) ? e : sh;
+    }
+    if (MODE == kCrossEntropy) {
+      const int label = labels[row0 + threadIdx.x];
+      row_loss[row0 + threadIdx.x] = (label >= 0 && (unsigned)label < cols) ? -(mine[label] - logf(sum)) : 0.0f;
+    } else if (MODE == kSoftmax) {
+      const float inv_s = 1.0f / sum; // as in the fast kernel: one reciprocal per row
+      for (unsigned c = 0; c < cols; ++c) mine[c] *= inv_s;
+    } else {
+      const float lse = logf(sum);
+      for (unsigned c = 0; c < cols; ++c) mine[c] -= lse;
+    }
+  }
+  if (MODE == kCrossEntropy) return;
+  __syncthreads();
+  float *ys = y + row0 * cols;
+  for (unsigned i = threadIdx.x; i < n; i += kSmThreads) {
+    const unsigned r = (unsigned)(((u64)i * div_magic) >> 21);
+    __stcs(ys + i, tile[r * stride + (i - r * cols)]);
   }
 }
 
@@ -202,15 +270,54 @@ softmax_generic_kernel(const float *x, float *y, const int *labels, SmRows g, fl
     u64 yoff = 0, ioff[2] = {0, 0};
     g.outer.offsets(row, &yoff, ioff);
     const float *xr = x + ioff[0];
+    float *yr = y + yoff;
+    // Rows that are contiguous along the axis (any length, any alignment: a 50257-wide vocabulary)
+    // are walked as a scalar head up to the first 16-byte boundary, a float4 body and a scalar tail;
+    // the output row must share the input row's alignment phase to be written as float4 too.
+    const bool unit = g.x_axis_stride == 1 && (MODE == kCrossEntropy || g.y_axis_stride == 1);
+    const bool vec = unit && (MODE == kCrossEntropy || (((uintptr_t)xr ^ (uintptr_t)yr) & 15) == 0);
+    u64 head = 0, nvec = 0;
+    if (vec) {
+      head = ((16 - ((uintptr_t)xr & 15)) & 15) / sizeof(float);
+      if (head > g.cols) head = g.cols;
+      nvec = (g.cols - head) >> 2;
+    }
+    const u64 tail_begin = head + (nvec << 2); // [0, head) and [tail_begin, cols) are scalar
     MaxSum acc{-FLT_MAX, 0.0f};
-    for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
-      const float xv = xr[j * g.x_axis_stride];
+    auto take = [&](float xv) {
       if (xv > acc.m) {
         acc.s = acc.s * exp_softmax(acc.m - xv) + 1.0f;
         acc.m = xv;
       } else {
         acc.s += exp_softmax(xv - acc.m);
       }
+    };
+    if (vec) {
+      const float4 *xb = reinterpret_cast<const float4 *>(xr + head);
+      // batches of four float4 per thread: all loads first, one re-basing per batch
+      for (u64 j0 = threadIdx.x; j0 < nvec; j0 += 4 * kSmThreads) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (j0 + (u64)u * kSmThreads < nvec) v[u] = __ldg(xb + j0 + (u64)u * kSmThreads);
+        float bm = -FLT_MAX;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (j0 + (u64)u * kSmThreads < nvec) bm = fmaxf(bm, fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w)));
+        if (bm > acc.m) {
+          acc.s *= exp_softmax(acc.m - bm);
+          acc.m = bm;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (j0 + (u64)u * kSmThreads < nvec)
+            acc.s += (exp_softmax(v[u].x - acc.m) + exp_softmax(v[u].y - acc.m)) +
+                     (exp_softmax(v[u].z - acc.m) + exp_softmax(v[u].w - acc.m));
+      }
+      const u64 loose = head + (g.cols - tail_begin);
+      if (threadIdx.x < loose) take(xr[threadIdx.x < head ? threadIdx.x : tail_begin + (threadIdx.x - head)]);
+    } else {
+      for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) take(xr[j * g.x_axis_stride]);
     }
     acc = ms_block_reduce(acc);
     if (MODE == kCrossEntropy) {
@@ -225,11 +332,33 @@ softmax_generic_kernel(const float *x, float *y, const int *labels, SmRows g, fl
       }
       continue;
     }
-    float *yr = y + yoff;
     const float lse = (MODE == kLogSoftmax) ? logf(acc.s) : 0.0f;
-    for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
-      const float sh = xr[j * g.x_axis_stride] - acc.m;
-      yr[j * g.y_axis_stride] = (MODE == kSoftmax) ? exp_softmax(sh) / acc.s : sh - lse;
+    auto finish = [&](float xv) {
+      const float sh = xv - acc.m;
+      return (MODE == kSoftmax) ? exp_softmax(sh) / acc.s : sh - lse;
+    };
+    if (vec) {
+      // the row was just read by this CTA: the second pass finds it in L2
+      const float4 *xb = reinterpret_cast<const float4 *>(xr + head);
+      float4 *yb = reinterpret_cast<float4 *>(yr + head);
+      for (u64 j0 = threadIdx.x; j0 < nvec; j0 += 4 * kSmThreads) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (j0 + (u64)u * kSmThreads < nvec) v[u] = __ldcs(xb + j0 + (u64)u * kSmThreads);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (j0 + (u64)u * kSmThreads < nvec)
+            __stcs(yb + j0 + (u64)u * kSmThreads, make_float4(finish(v[u].x), finish(v[u].y), finish(v[u].z), finish(v[u].w)));
+      }
+      const u64 loose = head + (g.cols - tail_begin);
+      if (threadIdx.x < loose) {
+        const u64 j = threadIdx.x < head ? threadIdx.x : tail_begin + (threadIdx.x - head);
+        yr[j] = finish(xr[j]);
+      }
+    } else {
+      for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads)
+        yr[j * g.y_axis_stride] = finish(xr[j * g.x_axis_stride]);
     }
   }
 }
@@ -476,6 +605,11 @@ static bool fast_ok(const SmRows &g, const void *x, const void *y, bool writes_r
   }
   return true;
 }
+// The same kernel with scalar accesses: any row length up to 2048 along a unit-stride axis.
+static bool fast_scalar_ok(const SmRows &g, bool writes_rows) {
+  if (g.cols == 0 || g.cols > (u64)kSmThreads * kSmMaxVpt) return false;
+  return g.x_axis_stride == 1 && (!writes_rows || g.y_axis_stride == 1);
+}
 
 template <int MODE>
 static void softmax_family_forward(const char *name, const Tensor **inputs, Tensor *output,
@@ -507,7 +641,17 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
   if (!make_rows(name, x, MODE == kCrossEntropy ? nullptr : output, nullptr, axis, &g)) return;
   if (g.rows == 0 || g.cols == 0) return;
   cudaStream_t s = stream();
-  const bool fast = fast_ok(g, x->data, output->data, MODE != kCrossEntropy);
+  // rows of at most 32 elements lying densely one after another, in x and in the output
+  bool tiny = g.cols <= (u64)kTinyCols && g.x_axis_stride == 1 && (MODE == kCrossEntropy || g.y_axis_stride == 1);
+  {
+    u64 run = g.cols;
+    for (int d = 0; tiny && d < g.outer.n; ++d) {
+      if (g.outer.istride[0][d] != run || (MODE != kCrossEntropy && g.outer.tstride[d] != run)) tiny = false;
+      run *= g.outer.size[d];
+    }
+  }
+  const bool fast_vec = fast_ok(g, x->data, output->data, MODE != kCrossEntropy);
+  const bool fast = fast_vec || fast_scalar_ok(g, MODE != kCrossEntropy);
   // the streaming cross-entropy kernel takes rows of any length (float4 layout permitting)
   SmRows any_len = g;
   any_len.cols = g.cols > 4 ? 4 : g.cols;
@@ -515,8 +659,12 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
                                 fast_ok(any_len, x->data, output->data, false);
   u64 grid;
   int log_tx = 5, vpt = 1;
-  if (fast) {
-    const u64 nvec = g.cols >> 2;
+  if (tiny) {
+    grid = (g.rows + kSmThreads - 1) / kSmThreads;
+  } else if (fast) {
+    const u64 nvec = fast_vec ? g.cols >> 2 : g.cols;
+    log_tx = 0;
+    while (log_tx < 5 && ((u64)1 << log_tx) < nvec) ++log_tx; // short rows: a slice of a warp each
     while (((u64)kSmMaxVpt << log_tx) < nvec) ++log_tx; // smallest TX with <= 8 vectors per thread
     vpt = (int)((nvec + ((u64)1 << log_tx) - 1) >> log_tx);
     const u64 rows_per_cta = (u64)kSmThreads >> log_tx;
@@ -568,15 +716,24 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
     note_kernel("cross_entropy_rows");
     end_call();
     return;
+  } else if (tiny) {
+    launch_k(softmax_tiny_rows_kernel<MODE>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g.rows,
+             (unsigned)g.cols, (unsigned)(((u64)1 << 21) / g.cols + 1), row_loss);
   } else if (fast) {
     int v = 1;
     while (v < vpt) v <<= 1;
+#define PB_SM_LAUNCH(VPT)                                                                                      \
+  do {                                                                                                        \
+    if (fast_vec) launch_k(softmax_fast_kernel<MODE, VPT, 4>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); \
+    else launch_k(softmax_fast_kernel<MODE, VPT, 1>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); \
+  } while (0)
     switch (v) {
-    case 1: launch_k(softmax_fast_kernel<MODE, 1>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); break;
-    case 2: launch_k(softmax_fast_kernel<MODE, 2>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); break;
-    case 4: launch_k(softmax_fast_kernel<MODE, 4>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); break;
-    default: launch_k(softmax_fast_kernel<MODE, 8>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); break;
+    case 1: PB_SM_LAUNCH(1); break;
+    case 2: PB_SM_LAUNCH(2); break;
+    case 4: PB_SM_LAUNCH(4); break;
+    default: PB_SM_LAUNCH(8); break;
     }
+#undef PB_SM_LAUNCH
   } else {
     launch_k(softmax_generic_kernel<MODE>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, row_loss);
   }
@@ -596,6 +753,7 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
   }
   if (!failed())
     note_kernel((MODE == kCrossEntropy && fast_ok_any_cols) ? "cross_entropy_rows" :
+                tiny ? (MODE == kSoftmax ? "softmax_tiny_rows" : (MODE == kLogSoftmax ? "log_softmax_tiny_rows" : "cross_entropy_tiny_rows")) :
                 fast ? (MODE == kSoftmax ? "softmax_fast" : (MODE == kLogSoftmax ? "log_softmax_fast" : "cross_entropy_fast"))
                      : (MODE == kSoftmax ? "softmax_online" : (MODE == kLogSoftmax ? "log_softmax_online" : "cross_entropy_online")));
   end_call();

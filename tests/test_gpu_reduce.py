@@ -14,7 +14,8 @@ from harness import (FULL_REDUCE, INT32, assert_bit_equal, assert_sum_close, ass
 pytestmark = pytest.mark.gpu
 
 REDUCE_SHAPES = [(4,), (2, 3), (3, 2, 4), (7, 33), (33, 7), (5, 1, 9), (128, 1024), (1000, 3),
-                 (3, 1000), (17, 5, 64), (6, 8, 5, 5), (2, 3, 4, 5, 6), (70000,), (3, 100000)]
+                 (3, 1000), (17, 5, 64), (6, 8, 5, 5), (2, 3, 4, 5, 6), (70000,), (3, 100000),
+                 (64, 16, 1024), (1000, 16, 64), (5, 3, 4096), (40, 64, 260)]
 
 
 def reduce_both(cuda, oracle, op, A, dim, keepdim, view=None):
@@ -254,7 +255,9 @@ def test_config1_backward_grad_b(cuda, oracle):
     assert_sum_close(tb.grad.numpy(), res["oracle"], scale, what="fused grad_b")
 
 
-@pytest.mark.parametrize("shape", [(64, 4096), (33, 1000), (8, 10), (5, 16384), (3, 7, 128), (2, 9000)])
+@pytest.mark.parametrize("shape", [(64, 4096), (33, 1000), (8, 10), (5, 16384), (3, 7, 128), (2, 9000),
+                                   (1000, 10), (257, 7), (64, 64), (100, 33), (50, 2047), (3, 2049), (700, 1),
+                                   (129, 16), (31, 260), (6, 50, 10), (2, 3, 5, 32), (513, 31), (3, 70000), (2, 50257)])
 def test_softmax_log_softmax(cuda, recipes, shape):
     X = rand_normal(0, shape, std=2.0)
     for op, fn in (("softmax", recipes.softmax), ("log_softmax", recipes.log_softmax)):
@@ -275,7 +278,7 @@ def test_softmax_over_strided_axis(cuda, recipes):
     np.testing.assert_allclose(out.numpy(), recipes.softmax(X.T.copy()).T, rtol=1e-5)
 
 
-@pytest.mark.parametrize("rows,cols", [(256, 4096), (100, 10), (37, 1000)])
+@pytest.mark.parametrize("rows,cols", [(256, 4096), (100, 10), (37, 1000), (5000, 10), (300, 33), (64, 2047)])
 def test_cross_entropy(cuda, recipes, rows, cols):
     X = rand_normal(0, (rows, cols), std=2.0)
     labels = np.random.RandomState(1).randint(0, cols, size=rows).astype(np.int32)
