@@ -17,6 +17,7 @@
 #include "iter.h"
 #include "reduce_engine.cuh"
 
+#include <cooperative_groups.h>
 #include <float.h>
 
 namespace pb {
@@ -181,17 +182,103 @@ softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const in
   }
 }
 
-// ---- forward, tiny rows (<= 32 classes: a 10-way classifier head) ---------------------------------------
+// ---- forward, rows of 8193 ... 65536 elements: one thread-block cluster per row -------------------------
+// The CTAs of a cluster (2, 4 or 8 x 256 threads) take consecutive slices of ONE row, each slice in
+// registers as above, so the row is read once and written once. Every CTA reduces its slice to a
+// pair (m_i, s_i = sum exp(x - m_i)), stores the pair into slot `rank` of EVERY CTA of the cluster
+// (distributed shared memory), and after ONE cluster barrier reads all pairs from its own shared
+// memory: m = max m_i, s = sum s_i * exp(m_i - m); its elements leave as exp(x - m_i) * (exp(m_i - m) / s)
+// or (x - m_i) + ((m_i - m) - log s). Nobody reads a neighbour's memory after the barrier, so CTAs
+// leave without a second one; the barrier that makes sure every CTA of the cluster is running
+// before its memory is written is split (arrive at entry, wait right before the stores).
+constexpr int kSmMaxCluster = 8;
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
+template <int MODE>
+__global__ void __launch_bounds__(kSmThreads, 4)
+softmax_cluster_kernel(const float *__restrict__ x, float *__restrict__ y, SmRows g, unsigned cluster_n) {
+  constexpr int VPT = kSmMaxVpt;
+  __shared__ float red_smem[kSmThreads / 32];
+  __shared__ float2 pairs[kSmMaxCluster]; // (m_i, s_i) of every CTA of the cluster, written by their owners
+  cluster_arrive();
+  pdl_wait();
+  pdl_launch_dependents();
+  const unsigned rank = blockIdx.x % cluster_n; // cluster dims (cluster_n, 1, 1): rank in the cluster
+  const u64 row = blockIdx.x / cluster_n;
+  const u64 all_vec = g.cols >> 2;
+  const u64 slice = (all_vec + cluster_n - 1) / cluster_n;
+  const u64 first = (u64)rank * slice;
+  const u64 nvec = first >= all_vec ? 0 : (all_vec - first < slice ? all_vec - first : slice);
+  u64 yoff = 0, ioff[2] = {0, 0};
+  g.outer.offsets(row, &yoff, ioff);
+  const float4 *xr = reinterpret_cast<const float4 *>(x + ioff[0]) + first;
+  float4 v[VPT];
+  float m = -FLT_MAX;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const u64 j = (u64)threadIdx.x + (u64)i * kSmThreads;
+    if (j < nvec) v[i] = __ldcs(xr + j);
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const u64 j = (u64)threadIdx.x + (u64)i * kSmThreads;
+    if (j < nvec) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+  }
+  m = row_reduce<MaxOp>(m, 8, red_smem);
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const u64 j = (u64)threadIdx.x + (u64)i * kSmThreads;
+    if (j < nvec) {
+      v[i].x = v[i].x - m; v[i].y = v[i].y - m; v[i].z = v[i].z - m; v[i].w = v[i].w - m;
+      const float e0 = exp_softmax(v[i].x), e1 = exp_softmax(v[i].y), e2 = exp_softmax(v[i].z), e3 = exp_softmax(v[i].w);
+      s += (e0 + e1) + (e2 + e3);
+      if (MODE == kSoftmax) v[i] = make_float4(e0, e1, e2, e3);
+    }
+  }
+  s = row_reduce<SumOp>(s, 8, red_smem);
+  cluster_wait(); // every CTA of the cluster has started: its shared memory may be written
+  if (threadIdx.x < cluster_n) {
+    cooperative_groups::cluster_group cl = cooperative_groups::this_cluster();
+    float2 *theirs = cl.map_shared_rank(pairs, threadIdx.x);
+    theirs[rank] = make_float2(m, s);
+  }
+  cluster_arrive();
+  cluster_wait();
+  float gm = -FLT_MAX;
+  for (unsigned c = 0; c < cluster_n; ++c) gm = fmaxf(gm, pairs[c].x);
+  float gs = 0.0f;
+  for (unsigned c = 0; c < cluster_n; ++c) gs += pairs[c].y * exp_softmax(pairs[c].x - gm);
+  float4 *yr = reinterpret_cast<float4 *>(y + yoff) + first;
+  // softmax: one factor per CTA; log-softmax: one offset per CTA
+  const float k = (MODE == kSoftmax) ? exp_softmax(m - gm) * (1.0f / gs) : (m - gm) - logf(gs);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const u64 j = (u64)threadIdx.x + (u64)i * kSmThreads;
+    if (j < nvec) {
+      float4 r;
+      if (MODE == kSoftmax) {
+        r.x = v[i].x * k; r.y = v[i].y * k; r.z = v[i].z * k; r.w = v[i].w * k;
+      } else {
+        r.x = v[i].x + k; r.y = v[i].y + k; r.z = v[i].z + k; r.w = v[i].w + k;
+      }
+      __stcs(yr + j, r);
+    }
+  }
+}
+
+// ---- forward, tiny rows (<= 64 classes: a 10-way classifier head) ---------------------------------------
 // Dense rows this short leave most lanes of any per-row thread group idle. Here a CTA moves 256
 // whole rows between global and shared memory with fully coalesced accesses (row stride in shared
 // memory made odd: conflict-free for the next step), and every THREAD owns one row there: max, the
 // exponentials and their sum, the results written back in place, no shuffles.
-constexpr int kTinyCols = 32;
+constexpr int kTinyCols = 64;
 template <int MODE>
 __global__ void __launch_bounds__(kSmThreads)
 softmax_tiny_rows_kernel(const float *__restrict__ x, float *__restrict__ y, const int *__restrict__ labels,
                          u64 rows, unsigned cols, unsigned div_magic, float *row_loss) {
-  __shared__ float tile[kSmThreads * (kTinyCols + 1)];
+  extern __shared__ float tile[]; // kSmThreads rows of (cols | 1) floats
   pdl_wait();
   pdl_launch_dependents();
   const unsigned stride = cols | 1u;
@@ -200,7 +287,7 @@ softmax_tiny_rows_kernel(const float *__restrict__ x, float *__restrict__ y, con
   const unsigned n = n_rows * cols;
   const float *xs = x + row0 * cols;
   for (unsigned i = threadIdx.x; i < n; i += kSmThreads) {
-    const unsigned r = (unsigned)(((u64)i * div_magic) >> 21); // i / cols for i < 2^16, cols <= 32
+    const unsigned r = (unsigned)(((u64)i * div_magic) >> 21); // i / cols for i < 2^15, cols <= 64
     tile[r * stride + (i - r * cols)] = __ldcs(xs + i);
   }
   __syncthreads();
@@ -595,8 +682,8 @@ static bool make_rows(const char *name, const Tensor *x, const Tensor *t, const 
   return true;
 }
 
-static bool fast_ok(const SmRows &g, const void *x, const void *y, bool writes_rows) {
-  if (g.cols == 0 || (g.cols & 3) || g.cols > (u64)kSmThreads * 4 * kSmMaxVpt) return false;
+static bool fast_ok(const SmRows &g, const void *x, const void *y, bool writes_rows, unsigned max_cluster = 1) {
+  if (g.cols == 0 || (g.cols & 3) || g.cols > (u64)kSmThreads * 4 * kSmMaxVpt * max_cluster) return false;
   if (g.x_axis_stride != 1 || ((uintptr_t)x & 15)) return false;
   if (writes_rows && (g.y_axis_stride != 1 || ((uintptr_t)y & 15))) return false;
   for (int d = 0; d < g.outer.n; ++d) {
@@ -641,8 +728,14 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
   if (!make_rows(name, x, MODE == kCrossEntropy ? nullptr : output, nullptr, axis, &g)) return;
   if (g.rows == 0 || g.cols == 0) return;
   cudaStream_t s = stream();
-  // rows of at most 32 elements lying densely one after another, in x and in the output
-  bool tiny = g.cols <= (u64)kTinyCols && g.x_axis_stride == 1 && (MODE == kCrossEntropy || g.y_axis_stride == 1);
+  // softmax / log-softmax rows of up to 8 x 8192 elements: a cluster of up to eight CTAs per row
+  const bool fast_vec = fast_ok(g, x->data, output->data, MODE != kCrossEntropy, MODE == kCrossEntropy ? 1 : 8);
+  unsigned cluster_n = 1;
+  if (fast_vec)
+    while ((u64)kSmThreads * 4 * kSmMaxVpt * cluster_n < g.cols) cluster_n *= 2;
+  // rows of at most 64 elements lying densely one after another, in x and in the output
+  // (from 33 elements on only where the float4 kernel does not apply: it is faster at 64)
+  bool tiny = g.cols <= (u64)(fast_vec ? 32 : kTinyCols) && g.x_axis_stride == 1 && (MODE == kCrossEntropy || g.y_axis_stride == 1);
   {
     u64 run = g.cols;
     for (int d = 0; tiny && d < g.outer.n; ++d) {
@@ -650,7 +743,6 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
       run *= g.outer.size[d];
     }
   }
-  const bool fast_vec = fast_ok(g, x->data, output->data, MODE != kCrossEntropy);
   const bool fast = fast_vec || fast_scalar_ok(g, MODE != kCrossEntropy);
   // the streaming cross-entropy kernel takes rows of any length (float4 layout permitting)
   SmRows any_len = g;
@@ -662,13 +754,15 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
   if (tiny) {
     grid = (g.rows + kSmThreads - 1) / kSmThreads;
   } else if (fast) {
-    const u64 nvec = fast_vec ? g.cols >> 2 : g.cols;
+    const u64 nvec = fast_vec ? ((g.cols >> 2) + cluster_n - 1) / cluster_n : g.cols;
     log_tx = 0;
     while (log_tx < 5 && ((u64)1 << log_tx) < nvec) ++log_tx; // short rows: a slice of a warp each
     while (((u64)kSmMaxVpt << log_tx) < nvec) ++log_tx; // smallest TX with <= 8 vectors per thread
+    if (cluster_n > 1) log_tx = 8; // the whole CTA on its slice of the row
     vpt = (int)((nvec + ((u64)1 << log_tx) - 1) >> log_tx);
     const u64 rows_per_cta = (u64)kSmThreads >> log_tx;
     grid = (g.rows + rows_per_cta - 1) / rows_per_cta; // one trip per CTA: many small CTAs balance best
+    if (cluster_n > 1) grid = g.rows * cluster_n;
   } else {
     grid = g.rows;
     const u64 cap = (u64)sm_count() * 16;
@@ -717,8 +811,18 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
     end_call();
     return;
   } else if (tiny) {
-    launch_k(softmax_tiny_rows_kernel<MODE>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g.rows,
-             (unsigned)g.cols, (unsigned)(((u64)1 << 21) / g.cols + 1), row_loss);
+    static bool ready = false;
+    if (!ready) {
+      cudaFuncSetAttribute(softmax_tiny_rows_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)(kSmThreads * (kTinyCols + 1) * sizeof(float)));
+      ready = true;
+    }
+    launch_k(softmax_tiny_rows_kernel<MODE>, dim3((unsigned)grid), dim3(kSmThreads),
+             (size_t)kSmThreads * (g.cols | 1) * sizeof(float), s, xd, y, labels, g.rows, (unsigned)g.cols,
+             (unsigned)(((u64)1 << 21) / g.cols + 1), row_loss);
+  } else if (fast && cluster_n > 1) {
+    if constexpr (MODE != kCrossEntropy)
+      launch_kc(cluster_n, softmax_cluster_kernel<MODE>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, g, cluster_n);
   } else if (fast) {
     int v = 1;
     while (v < vpt) v <<= 1;
@@ -754,6 +858,7 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
   if (!failed())
     note_kernel((MODE == kCrossEntropy && fast_ok_any_cols) ? "cross_entropy_rows" :
                 tiny ? (MODE == kSoftmax ? "softmax_tiny_rows" : (MODE == kLogSoftmax ? "log_softmax_tiny_rows" : "cross_entropy_tiny_rows")) :
+                (fast && cluster_n > 1) ? (MODE == kSoftmax ? "softmax_fast_cluster" : "log_softmax_fast_cluster") :
                 fast ? (MODE == kSoftmax ? "softmax_fast" : (MODE == kLogSoftmax ? "log_softmax_fast" : "cross_entropy_fast"))
                      : (MODE == kSoftmax ? "softmax_online" : (MODE == kLogSoftmax ? "log_softmax_online" : "cross_entropy_online")));
   end_call();
