@@ -26,6 +26,7 @@
 
 #include <cooperative_groups.h>
 #include <float.h>
+#include <type_traits>
 #include <string.h>
 
 namespace pb {
@@ -329,6 +330,37 @@ __global__ void __launch_bounds__(kRedThreads) reduce_rows_kernel(RedParams<NIN>
     for (int k = 1; k < VEC; ++k) r = Op::combine(r, acc[k]);
     r = warp_reduce<Op>(r, (int)tx_n);
     if (tx == 0) Op::store((typename Op::Out *)p.out + toff, r, p.accumulate, p.post_div);
+  }
+}
+
+// ---- tiny rows: one THREAD per output ------------------------------------------------------------------
+// Dense rows of at most 64 elements (argmax over ten classes, the sum of a [N, 4] tensor) leave most
+// lanes of a per-row thread group idle. A CTA moves 256 whole rows into shared memory with coalesced
+// loads (odd row stride there: conflict-free afterwards) and every thread walks its own row left to
+// right, which is also the reference's order of accumulation (src/kernels/cpu/reduce_ops.c:24-87).
+constexpr int kTinyRowCols = 64;
+template <class Op>
+__global__ void __launch_bounds__(kRedThreads)
+reduce_tiny_rows_kernel(const float *__restrict__ x, typename Op::Out *out, u64 rows, unsigned cols, unsigned div_magic,
+                        bool accumulate, float post_div) {
+  extern __shared__ float tiny_rows_tile[]; // kRedThreads rows of (cols | 1) floats
+  pdl_wait();
+  pdl_launch_dependents();
+  const unsigned stride = cols | 1u;
+  const u64 row0 = (u64)blockIdx.x * kRedThreads;
+  const unsigned n_rows = (unsigned)(rows - row0 < (u64)kRedThreads ? rows - row0 : (u64)kRedThreads);
+  const unsigned n = n_rows * cols;
+  const float *xs = x + row0 * cols;
+  for (unsigned i = threadIdx.x; i < n; i += kRedThreads) {
+    const unsigned r = (unsigned)(((u64)i * div_magic) >> 21); // i / cols for i < 2^15, cols <= 64
+    tiny_rows_tile[r * stride + (i - r * cols)] = __ldcs(xs + i);
+  }
+  __syncthreads();
+  if (threadIdx.x < n_rows) {
+    const float *mine = tiny_rows_tile + threadIdx.x * stride;
+    typename Op::T acc = Op::identity();
+    for (unsigned c = 0; c < cols; ++c) acc = Op::step(acc, mine[c], c);
+    Op::store(out + row0 + threadIdx.x, acc, accumulate, post_div);
   }
 }
 
@@ -954,7 +986,33 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
     else if (prefix && lead == 2) launch_k(KERNEL<Op, Pro, NIN, 4, (NIN > 2 ? 2 : NIN)>, grid, block, 0, s, p, pro); \
     else PB_RED_LAUNCH(KERNEL);                                                                    \
   } while (0)
-  if (g.kind == kRedRows) {
+  // dense rows of at most 64 elements, one plain input, many of them: a thread per row
+  bool tiny_rows = false;
+  if constexpr (NIN == 1 && std::is_same<Pro, IdentityPro>::value) {
+    tiny_rows = g.kind == kRedRows && g.n_red == 1 && plan.size[0] <= (u64)kTinyRowCols && plan.stride[1][0] == 1 &&
+                g.n_kept >= 4096 && g.n_kept < ((u64)1 << 39);
+    u64 run = 1;
+    for (int d = 0; tiny_rows && d < g.n_kept_dims; ++d) {
+      const int kd = g.kept_dims[d];
+      if (plan.stride[1][kd] != run * plan.size[0] || plan.stride[0][kd] != run) tiny_rows = false;
+      run *= plan.size[kd];
+    }
+  }
+  if (tiny_rows) {
+    if constexpr (NIN == 1 && std::is_same<Pro, IdentityPro>::value) {
+      static bool ready = false;
+      if (!ready) {
+        cudaFuncSetAttribute(reduce_tiny_rows_kernel<Op>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)(kRedThreads * (kTinyRowCols + 1) * sizeof(float)));
+        ready = true;
+      }
+      const unsigned cols = (unsigned)plan.size[0];
+      launch_k(reduce_tiny_rows_kernel<Op>, dim3((unsigned)((g.n_kept + kRedThreads - 1) / kRedThreads)), block,
+               (size_t)kRedThreads * (cols | 1u) * sizeof(float), s, p.in[0], (typename Op::Out *)p.out, g.n_kept, cols,
+               (unsigned)(((u64)1 << 21) / cols + 1), p.accumulate, p.post_div);
+      note_kernel("reduce_tiny_rows");
+    }
+  } else if (g.kind == kRedRows) {
     PB_RED_LAUNCH_NS(reduce_rows_kernel);
     note_kernel(g.vec == 4 ? "reduce_rows_vec4" : (g.vec == 2 ? "reduce_rows_vec2" : "reduce_rows_scalar"));
   } else if (g.kind == kRedSeg) {
