@@ -57,10 +57,13 @@ struct SmRows {
 
 // Reduction over the TX threads of a row-worker (TX = 1 << log_tx, 1 <= TX <= 256).
 // Every thread of the CTA must call it (it synchronises when TX > 32).
-template <class Op>
+// SUB: TX < 32 is possible (rows that take a slice of a warp); kernels that never see it keep the
+// constant-width, fully unrolled shuffle tree (the float4 kernel is issue-bound: a run-time width
+// cost it 2 - 4 % on [65536, 4096]).
+template <class Op, bool SUB = false>
 __device__ __forceinline__ float row_reduce(float v, int log_tx, float *smem /* [8] */) {
-  if (log_tx >= 5) v = warp_reduce<Op>(v, 32); // the common case with a constant width (unrolled)
-  else v = warp_reduce<Op>(v, 1 << log_tx);
+  if (SUB && log_tx < 5) return warp_reduce<Op>(v, 1 << log_tx);
+  v = warp_reduce<Op>(v, 32);
   if (log_tx > 5) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int wpr = 1 << (log_tx - 5); // warps per row-worker
@@ -78,7 +81,7 @@ __device__ __forceinline__ float row_reduce(float v, int log_tx, float *smem /* 
 // CE: `labels` int32 per row, per-CTA partial loss sums go through the ticket scheme.
 // Rows shorter than 32 vectors take a power-of-two slice of a warp each (log_tx < 5), so that a warp
 // reads several whole rows per instruction.
-template <int MODE, int VPT>
+template <int MODE, int VPT, bool SUB = false>
 __global__ void __launch_bounds__(kSmThreads, 4)
 softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const int *__restrict__ labels,
                     SmRows g, int log_tx, float *row_loss) {
@@ -109,7 +112,7 @@ softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const in
       const u64 j = (u64)tx + (u64)i * tx_n;
       if (live && j < nvec) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
     }
-    m = row_reduce<MaxOp>(m, log_tx, red_smem);
+    m = row_reduce<MaxOp, SUB>(m, log_tx, red_smem);
     float s = 0.0f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -125,7 +128,7 @@ softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const in
         }
       }
     }
-    s = row_reduce<SumOp>(s, log_tx, red_smem);
+    s = row_reduce<SumOp, SUB>(s, log_tx, red_smem);
 
     if (MODE == kCrossEntropy) {
       // loss_row = -((x[label] - m) - log(s)); v[] still holds x - m, so the thread that loaded
@@ -215,7 +218,7 @@ softmax_fast_any_kernel(const float *__restrict__ x, float *__restrict__ y, cons
         for (int k = 0; k < VEC; ++k) m = fmaxf(m, v[i][k]);
       }
     }
-    m = row_reduce<MaxOp>(m, log_tx, red_smem);
+    m = row_reduce<MaxOp, true>(m, log_tx, red_smem);
     float s = 0.0f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -232,7 +235,7 @@ softmax_fast_any_kernel(const float *__restrict__ x, float *__restrict__ y, cons
         s += VEC == 4 ? (e[0] + e[1]) + (e[VEC > 2 ? 2 : 0] + e[VEC > 3 ? 3 : 0]) : e[0];
       }
     }
-    s = row_reduce<SumOp>(s, log_tx, red_smem);
+    s = row_reduce<SumOp, true>(s, log_tx, red_smem);
 
     if (MODE == kCrossEntropy) {
       // loss_row = -((x[label] - m) - log(s)); v[] still holds x - m, so the thread that loaded
@@ -924,7 +927,8 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
     while (v < vpt) v <<= 1;
 #define PB_SM_LAUNCH(VPT)                                                                                      \
   do {                                                                                                        \
-    if (fast_vec) launch_k(softmax_fast_kernel<MODE, VPT>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); \
+    if (fast_vec && VPT == 1 && log_tx < 5) launch_k(softmax_fast_kernel<MODE, 1, true>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); \
+    else if (fast_vec) launch_k(softmax_fast_kernel<MODE, VPT>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); \
     else launch_k(softmax_fast_any_kernel<MODE, VPT, 1>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); \
   } while (0)
     switch (v) {
