@@ -80,7 +80,12 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
       set_error(PLAST_B200_ERR_LIMIT, "argmax over more than 2^32 elements");
       return false;
     }
-    int log_tx = log2_ceil(g->len0_items);
+    // Lanes per row: about eight items per lane (eight loads in flight), at least eight lanes (a
+    // 128-byte piece per load instruction and row), at most a warp. A lane per item left rows of
+    // 65 ... 512 elements with one or two loads in flight per lane ([262144, 256]: 3.3 TB/s).
+    int log_tx = log2_ceil(ceil_div(g->len0_items, 8));
+    if (log_tx < 3) log_tx = 3;
+    if (log_tx > log2_ceil(g->len0_items)) log_tx = log2_ceil(g->len0_items);
     if (log_tx > 5) log_tx = 5;
     const u64 warps = g->n_kept * ((u64)1 << log_tx) / 32;
     if (g->n_red == 1 && (warps >= sms * 16 || g->len0_items <= 256)) {

@@ -854,9 +854,13 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
     grid = (g.rows + kSmThreads - 1) / kSmThreads;
   } else if (fast) {
     const u64 nvec = fast_vec ? ((g.cols >> 2) + cluster_n - 1) / cluster_n : g.cols;
+    // Threads per row: the smallest power of two with <= 8 vectors per thread (eight loads in flight),
+    // but at least 128 bytes per load instruction and row (8 float4 lanes, 32 scalar lanes) where the
+    // row is that long: short rows take a slice of a warp each.
     log_tx = 0;
-    while (log_tx < 5 && ((u64)1 << log_tx) < nvec) ++log_tx; // short rows: a slice of a warp each
-    while (((u64)kSmMaxVpt << log_tx) < nvec) ++log_tx; // smallest TX with <= 8 vectors per thread
+    while (((u64)kSmMaxVpt << log_tx) < nvec) ++log_tx;
+    const int min_log_tx = fast_vec ? 3 : 5;
+    while (log_tx < min_log_tx && ((u64)1 << log_tx) < nvec) ++log_tx;
     if (cluster_n > 1) log_tx = 8; // the whole CTA on its slice of the row
     vpt = (int)((nvec + ((u64)1 << log_tx) - 1) >> log_tx);
     const u64 rows_per_cta = (u64)kSmThreads >> log_tx;
@@ -927,7 +931,7 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
     while (v < vpt) v <<= 1;
 #define PB_SM_LAUNCH(VPT)                                                                                      \
   do {                                                                                                        \
-    if (fast_vec && VPT == 1 && log_tx < 5) launch_k(softmax_fast_kernel<MODE, 1, true>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); \
+    if (fast_vec && log_tx < 5) launch_k(softmax_fast_kernel<MODE, VPT, true>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); \
     else if (fast_vec) launch_k(softmax_fast_kernel<MODE, VPT>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); \
     else launch_k(softmax_fast_any_kernel<MODE, VPT, 1>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); \
   } while (0)
