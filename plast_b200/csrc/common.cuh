@@ -67,7 +67,7 @@ cudaError_t scratch_alloc_async(void **p, size_t bytes);
 
 // Geometry knobs a test or a tuning run may override (plast_b200_tune); negative = built-in choice.
 enum TuneKey {
-  kTuneColsLogTx = 0, kTuneColsCtasPerSm = 1, kTuneColsMinBatches = 2, kTuneSegCtasPerSm = 3,
+  kTuneColsLogTx = 0, kTuneColsCtasPerSm = 1, kTuneColsMinBatches = 2, kTuneSegCtasPerSm = 3, kTuneTinyRowCols = 4,
   kTuneColsTileMajor = 5, kTuneColsPrefetch = 6, kTuneColsPrefetchUntil = 7, kTuneSegPrefetch = 8, kTuneSegLogTx = 9, kTuneColsCluster = 10, kTuneTile3Shape = 11, kTuneKeys = 12
 };
 long tuned(int key);

@@ -334,11 +334,11 @@ __global__ void __launch_bounds__(kRedThreads) reduce_rows_kernel(RedParams<NIN>
 }
 
 // ---- tiny rows: one THREAD per output ------------------------------------------------------------------
-// Dense rows of at most 64 elements (argmax over ten classes, the sum of a [N, 4] tensor) leave most
+// Dense rows of at most 48 elements (argmax over ten classes, the sum of a [N, 4] tensor) leave most
 // lanes of a per-row thread group idle. A CTA moves 256 whole rows into shared memory with coalesced
 // loads (odd row stride there: conflict-free afterwards) and every thread walks its own row left to
 // right, which is also the reference's order of accumulation (src/kernels/cpu/reduce_ops.c:24-87).
-constexpr int kTinyRowCols = 64;
+constexpr int kTinyRowCols = 48; // measured against a slice of a warp per row: ahead up to 48 elements, behind at 64
 template <class Op>
 __global__ void __launch_bounds__(kRedThreads)
 reduce_tiny_rows_kernel(const float *__restrict__ x, typename Op::Out *out, u64 rows, unsigned cols, unsigned div_magic,
@@ -986,10 +986,12 @@ void launch_reduce(const IterPlan &plan, typename Op::Out *out, const float *con
     else if (prefix && lead == 2) launch_k(KERNEL<Op, Pro, NIN, 4, (NIN > 2 ? 2 : NIN)>, grid, block, 0, s, p, pro); \
     else PB_RED_LAUNCH(KERNEL);                                                                    \
   } while (0)
-  // dense rows of at most 64 elements, one plain input, many of them: a thread per row
+  // dense rows of at most 48 elements, one plain input, many of them: a thread per row
   bool tiny_rows = false;
   if constexpr (NIN == 1 && std::is_same<Pro, IdentityPro>::value) {
-    tiny_rows = g.kind == kRedRows && g.n_red == 1 && plan.size[0] <= (u64)kTinyRowCols && plan.stride[1][0] == 1 &&
+    const u64 tiny_max = tuned(kTuneTinyRowCols) >= 0 ? (u64)tuned(kTuneTinyRowCols) : (u64)kTinyRowCols;
+    tiny_rows = g.kind == kRedRows && g.n_red == 1 && plan.size[0] <= tiny_max && plan.size[0] <= (u64)kTinyRowCols &&
+                plan.stride[1][0] == 1 &&
                 g.n_kept >= 4096 && g.n_kept < ((u64)1 << 39);
     u64 run = 1;
     for (int d = 0; tiny_rows && d < g.n_kept_dims; ++d) {

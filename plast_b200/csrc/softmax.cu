@@ -174,9 +174,16 @@ softmax_fast_kernel(const float *__restrict__ x, float *__restrict__ y, const in
   }
 }
 
-// The same kernel written over VEC-wide accesses; instantiated with VEC = 1 for row lengths that are
-// not multiples of 4 (up to 2048 elements as scalars). The float4 rows keep the kernel above: this
-// form of it measured 4 % slower on [65536, 4096].
+// The same kernel for rows the float4 kernel above cannot take: a row length that is not a multiple
+// of 4, or rows that do not start on a 16-byte boundary (up to 8192 elements).
+// VEC = 4: every row is covered by the ALIGNED float4 vectors that overlap it; a row that starts
+//   `phase` floats into its first vector has phase + cols elements to cover, the vectors that lie
+//   wholly inside the row move as float4, and the (at most two) vectors that hang over an end of the
+//   row are read and written element by element, so nothing outside the row is touched. The output
+//   row must start at the same phase (same shape and strides, equally aligned bases).
+// VEC = 1: scalar accesses throughout, for outputs whose phase differs.
+// This form measured 4 % slower than the kernel above on [65536, 4096], which therefore keeps the
+// aligned rows.
 template <int MODE, int VPT, int VEC>
 __global__ void __launch_bounds__(kSmThreads, 4)
 softmax_fast_any_kernel(const float *__restrict__ x, float *__restrict__ y, const int *__restrict__ labels,
@@ -187,49 +194,56 @@ softmax_fast_any_kernel(const float *__restrict__ x, float *__restrict__ y, cons
   const int tx_n = 1 << log_tx;
   const int tx = threadIdx.x & (tx_n - 1), ty = threadIdx.x >> log_tx;
   const int rows_per_cta = kSmThreads >> log_tx;
-  const u64 nvec = g.cols / VEC;
   // Every thread of the CTA reaches both row_reduce calls (they synchronise when TX > 32).
   { // one group of rows per CTA (the grid covers every row)
     const u64 row = (u64)blockIdx.x * rows_per_cta + ty;
     const bool live = row < g.rows;
     u64 yoff = 0, ioff[2] = {0, 0};
     if (live) g.outer.offsets(row, &yoff, ioff);
-    const float *xr = x + ioff[0];
+    // element e of the covering vectors is element e - lo of the row; valid for lo <= e < hi
+    const unsigned lo = VEC == 4 ? (unsigned)(((uintptr_t)(x + ioff[0]) >> 2) & 3) : 0;
+    const unsigned hi = lo + (unsigned)g.cols;
+    const unsigned nvec = (hi + VEC - 1) / VEC;
+    const float *xr = x + ioff[0] - lo;
+    auto whole = [&](unsigned j) { return VEC == 1 || (j * VEC >= lo && j * VEC + VEC <= hi); };
+    auto valid = [&](unsigned j, int k) { return j * VEC + k >= lo && j * VEC + k < hi; };
 
     float v[VPT][VEC];
     float m = -FLT_MAX; // src/kernels/cpu/reduce_ops.c:273
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const u64 j = (u64)tx + (u64)i * tx_n;
+      const unsigned j = (unsigned)tx + (unsigned)i * tx_n;
       if (live && j < nvec) {
-        if (VEC == 4) {
+        if (VEC == 4 && whole(j)) {
           const float4 t = __ldcs(reinterpret_cast<const float4 *>(xr) + j);
           v[i][0] = t.x; v[i][1] = t.y; v[i][VEC > 2 ? 2 : 0] = t.z; v[i][VEC > 3 ? 3 : 0] = t.w;
         } else {
-          v[i][0] = __ldcs(xr + j);
+#pragma unroll
+          for (int k = 0; k < VEC; ++k) v[i][k] = valid(j, k) ? __ldcs(xr + j * VEC + k) : -FLT_MAX;
         }
       }
     }
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const u64 j = (u64)tx + (u64)i * tx_n;
+      const unsigned j = (unsigned)tx + (unsigned)i * tx_n;
       if (live && j < nvec) {
 #pragma unroll
-        for (int k = 0; k < VEC; ++k) m = fmaxf(m, v[i][k]);
+        for (int k = 0; k < VEC; ++k) m = fmaxf(m, v[i][k]); // the fill value of an overhang never wins
       }
     }
     m = row_reduce<MaxOp, true>(m, log_tx, red_smem);
     float s = 0.0f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const u64 j = (u64)tx + (u64)i * tx_n;
+      const unsigned j = (unsigned)tx + (unsigned)i * tx_n;
       if (live && j < nvec) {
         // sub, then exp: two separately rounded ops
         float e[VEC];
+        const bool all = whole(j);
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
           v[i][k] = v[i][k] - m;
-          e[k] = exp_softmax(v[i][k]);
+          e[k] = (all || valid(j, k)) ? exp_softmax(v[i][k]) : 0.0f;
           if (MODE == kSoftmax) v[i][k] = e[k];
         }
         s += VEC == 4 ? (e[0] + e[1]) + (e[VEC > 2 ? 2 : 0] + e[VEC > 3 ? 3 : 0]) : e[0];
@@ -243,9 +257,10 @@ softmax_fast_any_kernel(const float *__restrict__ x, float *__restrict__ y, cons
       if (live) {
         const int label = labels[row];
         if (label >= 0 && (u64)label < g.cols) {
-          const u64 jv = (u64)label / VEC;
-          if ((int)(jv & (u64)(tx_n - 1)) == tx) {
-            const int slot = (int)(jv >> log_tx), comp = label % VEC;
+          const unsigned at = (unsigned)label + lo;
+          const unsigned jv = at / VEC;
+          if ((int)(jv & (unsigned)(tx_n - 1)) == tx) {
+            const int slot = (int)(jv >> log_tx), comp = (int)(at % VEC);
             float sh = 0.0f;
 #pragma unroll
             for (int i = 0; i < VPT; ++i)
@@ -261,7 +276,7 @@ softmax_fast_any_kernel(const float *__restrict__ x, float *__restrict__ y, cons
       return;
     }
 
-    float *yr = y + yoff;
+    float *yr = y + yoff - lo;
     const float lse = (MODE == kLogSoftmax) ? logf(s) : 0.0f;
     // One correctly rounded reciprocal per row, then a multiply per element: within 1 ulp of the
     // recipe's exp_x / sum_exp (the exponentials themselves are ~3 ulp), and a tenth of the
@@ -269,13 +284,18 @@ softmax_fast_any_kernel(const float *__restrict__ x, float *__restrict__ y, cons
     const float inv_s = 1.0f / s;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const u64 j = (u64)tx + (u64)i * tx_n;
+      const unsigned j = (unsigned)tx + (unsigned)i * tx_n;
       if (live && j < nvec) {
         float r[VEC];
 #pragma unroll
         for (int k = 0; k < VEC; ++k) r[k] = (MODE == kSoftmax) ? v[i][k] * inv_s : v[i][k] - lse;
-        if (VEC == 4) __stcs(reinterpret_cast<float4 *>(yr) + j, make_float4(r[0], r[1], r[VEC > 2 ? 2 : 0], r[VEC > 3 ? 3 : 0]));
-        else __stcs(yr + j, r[0]);
+        if (VEC == 4 && whole(j)) {
+          __stcs(reinterpret_cast<float4 *>(yr) + j, make_float4(r[0], r[1], r[VEC > 2 ? 2 : 0], r[VEC > 3 ? 3 : 0]));
+        } else {
+#pragma unroll
+          for (int k = 0; k < VEC; ++k)
+            if (valid(j, k)) __stcs(yr + j * VEC + k, r[k]);
+        }
       }
     }
   }
@@ -796,6 +816,16 @@ static bool fast_scalar_ok(const SmRows &g, bool writes_rows) {
   if (g.cols == 0 || g.cols > (u64)kSmThreads * kSmMaxVpt) return false;
   return g.x_axis_stride == 1 && (!writes_rows || g.y_axis_stride == 1);
 }
+// Rows of any length up to 8188 and any alignment, as aligned float4 vectors with ragged ends: the
+// output rows must start at the same phase of a 16-byte vector as the input rows.
+static bool fast_ragged_ok(const SmRows &g, const void *x, const void *y, bool writes_rows) {
+  if (g.cols < 8 || g.cols + 6 > (u64)kSmThreads * 4 * kSmMaxVpt || g.x_axis_stride != 1) return false;
+  if (!writes_rows) return true;
+  if (g.y_axis_stride != 1 || ((((uintptr_t)x ^ (uintptr_t)y) >> 2) & 3) != 0) return false;
+  for (int d = 0; d < g.outer.n; ++d)
+    if ((g.outer.istride[0][d] - g.outer.tstride[d]) & 3) return false;
+  return true;
+}
 
 template <int MODE>
 static void softmax_family_forward(const char *name, const Tensor **inputs, Tensor *output,
@@ -842,7 +872,8 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
       run *= g.outer.size[d];
     }
   }
-  const bool fast = fast_vec || fast_scalar_ok(g, MODE != kCrossEntropy);
+  const bool fast_ragged = !fast_vec && fast_ragged_ok(g, x->data, output->data, MODE != kCrossEntropy);
+  const bool fast = fast_vec || fast_ragged || fast_scalar_ok(g, MODE != kCrossEntropy);
   // the streaming cross-entropy kernel takes rows of any length (float4 layout permitting)
   SmRows any_len = g;
   any_len.cols = g.cols > 4 ? 4 : g.cols;
@@ -853,13 +884,13 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
   if (tiny) {
     grid = (g.rows + kSmThreads - 1) / kSmThreads;
   } else if (fast) {
-    const u64 nvec = fast_vec ? ((g.cols >> 2) + cluster_n - 1) / cluster_n : g.cols;
+    const u64 nvec = fast_vec ? ((g.cols >> 2) + cluster_n - 1) / cluster_n : (fast_ragged ? (g.cols + 6) >> 2 : g.cols);
     // Threads per row: the smallest power of two with <= 8 vectors per thread (eight loads in flight),
     // but at least 128 bytes per load instruction and row (8 float4 lanes, 32 scalar lanes) where the
     // row is that long: short rows take a slice of a warp each.
     log_tx = 0;
     while (((u64)kSmMaxVpt << log_tx) < nvec) ++log_tx;
-    const int min_log_tx = fast_vec ? 3 : 5;
+    const int min_log_tx = (fast_vec || fast_ragged) ? 3 : 5;
     while (log_tx < min_log_tx && ((u64)1 << log_tx) < nvec) ++log_tx;
     if (cluster_n > 1) log_tx = 8; // the whole CTA on its slice of the row
     vpt = (int)((nvec + ((u64)1 << log_tx) - 1) >> log_tx);
@@ -933,6 +964,7 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
   do {                                                                                                        \
     if (fast_vec && log_tx < 5) launch_k(softmax_fast_kernel<MODE, VPT, true>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); \
     else if (fast_vec) launch_k(softmax_fast_kernel<MODE, VPT>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); \
+    else if (fast_ragged) launch_k(softmax_fast_any_kernel<MODE, VPT, 4>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); \
     else launch_k(softmax_fast_any_kernel<MODE, VPT, 1>, dim3((unsigned)grid), dim3(kSmThreads), 0, s, xd, y, labels, g, log_tx, row_loss); \
   } while (0)
     switch (v) {

@@ -257,7 +257,8 @@ def test_config1_backward_grad_b(cuda, oracle):
 
 @pytest.mark.parametrize("shape", [(64, 4096), (33, 1000), (8, 10), (5, 16384), (3, 7, 128), (2, 9000),
                                    (1000, 10), (257, 7), (64, 64), (100, 33), (50, 2047), (3, 2049), (700, 1),
-                                   (129, 16), (31, 260), (6, 50, 10), (2, 3, 5, 32), (513, 31), (3, 70000), (2, 50257), (3, 65536), (2, 40000), (7, 8196), (4, 12288)])
+                                   (129, 16), (31, 260), (6, 50, 10), (2, 3, 5, 32), (513, 31), (3, 70000), (2, 50257), (3, 65536), (2, 40000), (7, 8196), (4, 12288),
+                                   (64, 1001), (10, 8186), (33, 65), (5, 4095), (2, 3, 129), (40, 9)])
 def test_softmax_log_softmax(cuda, recipes, shape):
     X = rand_normal(0, shape, std=2.0)
     for op, fn in (("softmax", recipes.softmax), ("log_softmax", recipes.log_softmax)):
