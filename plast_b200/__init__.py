@@ -278,11 +278,12 @@ class Tensor:
         self.c.requires_grad = True
         return g
 
-    def view(self, shape, strides) -> "Tensor":
+    def view(self, shape, strides, offset: int = 0) -> "Tensor":
         """Metadata-only view sharing this tensor's memory (what plast's shape ops produce,
-        src/kernels/cpu/shape_ops.c:28-80)."""
+        src/kernels/cpu/shape_ops.c:28-80); `offset` elements into it (a slice: the view's data
+        pointer is moved, as plast's Tensor has no offset field)."""
         return Tensor(shape, device=self.device, dtype=self.c.dtype, strides=strides, _base=self,
-                      _storage_elems=self._storage_elems, _ptr=self.c.data)
+                      _storage_elems=self._storage_elems, _ptr=int(self.c.data) + 4 * int(offset))
 
     def transpose(self, a1: int, a2: int) -> "Tensor":
         sh, st = self.shape, self.strides

@@ -169,3 +169,51 @@ def test_column_reductions_of_small_and_medium_matrices(cuda, oracle, rows, cols
     cuda.backward("add_leaky_relu", [da, db], dc, fval=0.1)
     scale = np.abs(G.astype(np.float64) * np.where(c.numpy() > 0, 1.0, 0.1)).sum(axis=0, keepdims=True)
     assert_sum_close(db.grad.numpy(), tb.grad.numpy(), scale, what=f"grad of the broadcast row {rows}x{cols}")
+
+
+def _log_uniform(rs, lo, hi):
+    return int(round(np.exp(rs.uniform(np.log(lo), np.log(hi)))))
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_softmax_family_random_rows(cuda, recipes, seed):
+    """Random row counts and row lengths (1 ... 70000, any remainder mod 4) through softmax,
+    log-softmax and cross-entropy, dense and as column slices of a wider buffer (rows that start at
+    any 4-byte phase, outputs at the same or another phase): every kernel of the family (thread per
+    row, slice of a warp, float4 with ragged ends, scalar, cluster per row, two-pass) is reached."""
+    rs = np.random.RandomState(7000 + seed)
+    cols = _log_uniform(rs, 1, 70000) if seed % 4 else int(rs.choice([1, 2, 3, 5, 8, 31, 33, 64, 65, 127, 1001, 8193]))
+    rows = max(1, min(_log_uniform(rs, 1, 6000), 400000 // cols))
+    X = (2.0 * rs.randn(rows, cols)).astype(np.float32)
+    want_sm, want_ls = recipes.softmax(X), recipes.log_softmax(X)
+    layouts = [("dense", 0, 0, 0)]
+    if cols > 1:
+        layouts.append(("sliced, same phase", int(rs.randint(1, 4)), None, int(rs.randint(0, 5))))
+        layouts.append(("sliced, other phase", int(rs.randint(1, 4)), int(rs.randint(0, 4)), int(rs.randint(0, 5))))
+    for what, lead, out_lead, pad in layouts:
+        # the tensor is columns [lead, lead + cols) of a [rows, lead + cols + pad] buffer
+        width = lead + cols + pad
+        buf = np.zeros((rows, width), np.float32)
+        buf[:, lead:lead + cols] = X
+        tb = cuda.tensor(buf)
+        x = tb.view([rows, cols], [width, 1], offset=lead) if (lead or pad) else tb
+        out_lead = lead if out_lead is None else out_lead
+        owidth = out_lead + cols + pad
+        for op, want in (("softmax", want_sm), ("log_softmax", want_ls)):
+            ob = cuda.tensor(np.full((rows, owidth), 7.0, np.float32))
+            o = ob.view([rows, cols], [owidth, 1], offset=out_lead) if (out_lead or pad) else ob
+            cuda.forward(op, [x], o, dim=1)
+            full = ob.numpy()
+            got = full[:, out_lead:out_lead + cols]
+            tag = f"{op} [{rows}, {cols}] {what} (lead {lead}/{out_lead}, pad {pad})"
+            if op == "softmax":
+                np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-30, err_msg=tag)
+            else:
+                np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5, err_msg=tag)
+            # nothing outside the rows was written
+            assert np.all(full[:, :out_lead] == 7.0) and np.all(full[:, out_lead + cols:] == 7.0), tag
+    labels = rs.randint(0, cols, size=rows).astype(np.int32)
+    out = cuda.empty((1,))
+    cuda.forward("cross_entropy", [cuda.tensor(X), cuda.tensor(labels)], out)
+    want, per_row = recipes.cross_entropy(X, labels)
+    assert_sum_close(out.numpy(), want, np.abs(per_row).sum() / rows, what=f"cross-entropy mean [{rows}, {cols}]")

@@ -15,7 +15,8 @@ pytestmark = pytest.mark.gpu
 
 REDUCE_SHAPES = [(4,), (2, 3), (3, 2, 4), (7, 33), (33, 7), (5, 1, 9), (128, 1024), (1000, 3),
                  (3, 1000), (17, 5, 64), (6, 8, 5, 5), (2, 3, 4, 5, 6), (70000,), (3, 100000),
-                 (64, 16, 1024), (1000, 16, 64), (5, 3, 4096), (40, 64, 260)]
+                 (64, 16, 1024), (1000, 16, 64), (5, 3, 4096), (40, 64, 260),
+                 (5000, 10), (4100, 33), (70, 80, 7), (4096, 48), (100000, 4), (4097, 1), (300, 100), (2000, 256)]
 
 
 def reduce_both(cuda, oracle, op, A, dim, keepdim, view=None):
