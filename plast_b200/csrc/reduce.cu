@@ -83,7 +83,8 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
     // Lanes per row: about eight items per lane (eight loads in flight), at least eight lanes (a
     // 128-byte piece per load instruction and row), at most a warp. A lane per item left rows of
     // 65 ... 512 elements with one or two loads in flight per lane ([262144, 256]: 3.3 TB/s).
-    int log_tx = log2_ceil(ceil_div(g->len0_items, 8));
+    // (scalar items come in batches of sixteen)
+    int log_tx = log2_ceil(ceil_div(g->len0_items, g->vec == 1 ? 16 : 8));
     if (log_tx < 3) log_tx = 3;
     if (log_tx > log2_ceil(g->len0_items)) log_tx = log2_ceil(g->len0_items);
     if (log_tx > 5) log_tx = 5;
@@ -98,7 +99,7 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
       return true;
     }
     g->kind = kRedSeg;
-    const u64 seg_cap = (u64)kRedThreads * (nin == 1 ? 8 : 4);
+    const u64 seg_cap = (u64)kRedThreads * (nin == 1 ? 8 : 4) * (g->vec == 1 ? 2 : 1); // one full load batch
     if (g->len0_items <= seg_cap) {
       // whole runs as segments: a row-worker of ~1/16 of the run's items walks it in several
       // full load batches; the other row-workers of the CTA take the next runs
@@ -150,8 +151,11 @@ bool plan_reduce_geometry(const IterPlan &plan, const void *const *in_ptrs, int 
     u64 min_batches = 2; // (one batch per row-worker, i.e. twice the CTAs, measured slower even at 4 MiB)
     if (tuned(kTuneColsMinBatches) > 0) min_batches = (u64)tuned(kTuneColsMinBatches);
     double best_fill = -1.0;
-    int forced_ltx = 3;
-    for (int ltx = 5; ltx > 3; --ltx)
+    // (lanes of narrower items, when the layout does not allow float4, are scaled up to the same
+    // bytes per row: 32 ... 128 scalar lanes)
+    const int wider = g->vec == 4 ? 0 : (g->vec == 2 ? 1 : 2);
+    int forced_ltx = 3 + wider;
+    for (int ltx = 5 + wider; ltx > 3 + wider; --ltx)
       if (g->n_kept * ceil_div(g->len0_items, (u64)1 << ltx) >= 64) {
         forced_ltx = ltx;
         break;

@@ -262,7 +262,7 @@ __device__ __forceinline__ void accumulate_run(const RedParams<NIN> &p, const Pr
   }
   const unsigned n = (unsigned)(end - begin);
   idx_base += (unsigned)begin * VEC;
-  constexpr int kRedUnroll = RedUnroll<NV>::value;
+  constexpr int kRedUnroll = RedUnroll<NV>::value * (VEC == 1 ? 2 : 1); // scalar items: more of them in flight
   auto load_item = [&](int a, unsigned i, float *v) {
     if (!kStatic && p.istride0[a] == 0) return;
     if (VEC == 4) {
@@ -521,7 +521,7 @@ __global__ void __launch_bounds__(kRedThreads) reduce_cols_kernel(RedParams<NIN>
   if (r_begin > p.n_red) r_begin = p.n_red; // a cluster keeps its size even when the last chunks are empty
   u64 r_end = r_begin + p.per_chunk;
   if (r_end > p.n_red) r_end = p.n_red;
-  constexpr int kRedUnroll = 4;
+  constexpr int kRedUnroll = VEC == 1 ? 8 : 4; // scalar items: twice the rows per batch for bytes in flight
   const unsigned n = (unsigned)(r_end - r_begin); // the host keeps a chunk below 2^31 indices
   if (live && p.red.n <= 1) {
     // One reduced dim (the usual case): walk it with pointer increments, no index decoding.

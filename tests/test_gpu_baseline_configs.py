@@ -19,8 +19,8 @@ and the nine-op chain are compositions: exp within 2 ulp of glibc's moves 1/(1+e
 and z = t + e2 can cancel, so their bounds are the measured worst cases stated at the asserts
 (sigmoid 4 ulp; chain 3 * 2^-23 * (|t| + |e2|)).
 
-Every test records the largest error it saw; the last test prints the table (and leaves it in
-gpurun_out/parity_table.json when that folder can be written).
+Every test records the largest error it saw; the last test prints the table (and leaves it as
+parity_table.json in the run's output folder when that can be written).
 """
 import json
 import os
