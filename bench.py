@@ -237,6 +237,38 @@ def cpu_per_op_baselines(rows):
     fns[(3, "cross_entropy_mean")] = (ce3, frac3, smp3 + ", as log_softmax -> * one-hot -> sum -> neg -> mean "
                                       "(the one-hot matrix is built outside the timed region)")
 
+    # backward of the three, as the reverse of those op sequences over tensors that carry gradients
+    # (src/core/graph.c:57-65 order; the forward pass runs once, outside the timed region)
+    def graph3():
+        xg = be.tensor(X3np, requires_grad=True)
+        m = be.empty((R3, 1), requires_grad=True); be.forward("max", [xg], m, dim=1, keepdim=1)
+        sh = be.empty((R3, C3), requires_grad=True); be.forward("sub", [xg, m], sh)
+        e = be.empty((R3, C3), requires_grad=True); be.forward("exp", [sh], e)
+        s = be.empty((R3, 1), requires_grad=True); be.forward("sum", [e], s, dim=1, keepdim=1)
+        head = lambda: (be.backward("sum", [e], s, dim=1, keepdim=1), be.backward("exp", [sh], e),
+                        be.backward("sub", [xg, m], sh), be.backward("max", [xg], m, dim=1, keepdim=1))
+        return xg, sh, e, s, head
+
+    G3 = Nrm(3, (R3, C3))
+    xg, sh, e, s, head = graph3()
+    ysm = be.empty((R3, C3), requires_grad=True); be.forward("div", [e, s], ysm); ysm.grad.copy_from(G3)
+    fns[(3, "softmax_backward")] = (lambda e=e, s=s, ysm=ysm, head=head: (be.backward("div", [e, s], ysm), head()), frac3,
+                                    smp3 + ", as div / sum / exp / sub / max backward")
+    xg2, sh2, e2, s2, head2 = graph3()
+    ls2 = be.empty((R3, 1), requires_grad=True); be.forward("log", [s2], ls2)
+    yls = be.empty((R3, C3), requires_grad=True); be.forward("sub", [sh2, ls2], yls); yls.grad.copy_from(G3)
+    lsm_bwd = lambda: (be.backward("sub", [sh2, ls2], yls), be.backward("log", [s2], ls2), head2())
+    fns[(3, "log_softmax_backward")] = (lsm_bwd, frac3, smp3 + ", as sub / log / sum / exp / sub / max backward")
+    prod = be.empty((R3, C3), requires_grad=True); be.forward("mul", [yls, OH], prod)
+    rsum = be.empty((R3,), requires_grad=True); be.forward("sum", [prod], rsum, dim=1)
+    ngl = be.empty((R3,), requires_grad=True); be.forward("neg", [rsum], ngl)
+    lss = be.empty((1,), requires_grad=True); be.forward("mean", [ngl], lss, dim=FULL)
+    lss.grad.copy_from(np.ones(1, np.float32))
+    fns[(3, "cross_entropy_backward")] = (lambda: (be.backward("mean", [ngl], lss, dim=FULL), be.backward("neg", [rsum], ngl),
+                                                   be.backward("sum", [prod], rsum, dim=1), be.backward("mul", [yls, OH], prod),
+                                                   lsm_bwd()), frac3,
+                                          smp3 + ", as mean / neg / sum / mul backward, then log_softmax backward")
+
     # config 4: a 4096 x 4096 corner of the 8192 x 8192 tensor
     M4 = 4096
     frac4, smp4 = (M4 * M4) / float(8192 * 8192), "4096 x 4096 of 8192 x 8192"

@@ -1000,6 +1000,103 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
   end_call();
 }
 
+// ---- backward, fast path --------------------------------------------------------------------------------
+// Rows contiguous along the axis in all three tensors, 16-byte aligned, cols % 4 == 0, cols <= 8192:
+// the row of y (or of the logits), of dy and of dx in registers, TX threads per row as in the
+// forward kernel; one read of each, one write of dx (backward ACCUMULATES into dx).
+//   softmax       dx += y * (dy - sum(y * dy))
+//   log_softmax   dx += dy - exp(y) * sum(dy)
+//   cross_entropy dx += (softmax(x) - onehot(label)) * dloss / rows
+// Up to four vectors per thread the dx row is requested together with the others; with eight it is
+// read after the row sum (registers).
+template <int MODE, int VPT>
+__global__ void __launch_bounds__(kSmThreads, 2)
+softmax_backward_fast_kernel(const float *__restrict__ a, const float *__restrict__ dy, float *__restrict__ dx,
+                             const int *__restrict__ labels, SmRows g, int log_tx) {
+  __shared__ float red_smem[kSmThreads / 32];
+  pdl_wait();
+  pdl_launch_dependents();
+  constexpr bool kEarlyDx = VPT <= 4;
+  const int tx_n = 1 << log_tx;
+  const int tx = threadIdx.x & (tx_n - 1), ty = threadIdx.x >> log_tx;
+  const int rows_per_cta = kSmThreads >> log_tx;
+  const u64 nvec = g.cols >> 2;
+  const u64 row = (u64)blockIdx.x * rows_per_cta + ty;
+  const bool live = row < g.rows;
+  u64 doff = 0, ioff[2] = {0, 0};
+  if (live) g.outer.offsets(row, &doff, ioff);
+  const float4 *ar = reinterpret_cast<const float4 *>(a + ioff[0]);
+  const float4 *dyr = reinterpret_cast<const float4 *>(dy + ioff[1]);
+  float4 *dxr = reinterpret_cast<float4 *>(dx + doff);
+  float4 va[VPT], vd[VPT], vx[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const u64 j = (u64)tx + (u64)i * tx_n;
+    if (live && j < nvec) {
+      va[i] = __ldcs(ar + j);
+      if (MODE != kCrossEntropy) vd[i] = __ldcs(dyr + j);
+      if (kEarlyDx) vx[i] = __ldcs(dxr + j);
+    }
+  }
+  float k0 = 0.0f, k1 = 0.0f; // per-row constants of the last pass
+  if (MODE == kCrossEntropy) {
+    float m = -FLT_MAX;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const u64 j = (u64)tx + (u64)i * tx_n;
+      if (live && j < nvec) m = fmaxf(m, fmaxf(fmaxf(va[i].x, va[i].y), fmaxf(va[i].z, va[i].w)));
+    }
+    m = row_reduce<MaxOp, true>(m, log_tx, red_smem);
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const u64 j = (u64)tx + (u64)i * tx_n;
+      if (live && j < nvec) {
+        va[i].x = exp_softmax(va[i].x - m); va[i].y = exp_softmax(va[i].y - m);
+        va[i].z = exp_softmax(va[i].z - m); va[i].w = exp_softmax(va[i].w - m);
+        sum += (va[i].x + va[i].y) + (va[i].z + va[i].w);
+      }
+    }
+    sum = row_reduce<SumOp, true>(sum, log_tx, red_smem);
+    k0 = 1.0f / sum;
+    k1 = dy[0] / (float)g.rows;
+  } else {
+    float part = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const u64 j = (u64)tx + (u64)i * tx_n;
+      if (live && j < nvec) {
+        if (MODE == kSoftmax) part += (vd[i].x * va[i].x + vd[i].y * va[i].y) + (vd[i].z * va[i].z + vd[i].w * va[i].w);
+        else part += (vd[i].x + vd[i].y) + (vd[i].z + vd[i].w);
+      }
+    }
+    k0 = row_reduce<SumOp, true>(part, log_tx, red_smem);
+  }
+  const int label = (MODE == kCrossEntropy && live) ? labels[row] : -1;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const u64 j = (u64)tx + (u64)i * tx_n;
+    if (live && j < nvec) {
+      float4 gr;
+      if (MODE == kSoftmax) {
+        gr.x = va[i].x * (vd[i].x - k0); gr.y = va[i].y * (vd[i].y - k0);
+        gr.z = va[i].z * (vd[i].z - k0); gr.w = va[i].w * (vd[i].w - k0);
+      } else if (MODE == kLogSoftmax) {
+        gr.x = vd[i].x - exp_softmax(va[i].x) * k0; gr.y = vd[i].y - exp_softmax(va[i].y) * k0;
+        gr.z = vd[i].z - exp_softmax(va[i].z) * k0; gr.w = vd[i].w - exp_softmax(va[i].w) * k0;
+      } else {
+        const long e0 = (long)(j << 2);
+        gr.x = (va[i].x * k0 - (label == e0 ? 1.0f : 0.0f)) * k1;
+        gr.y = (va[i].y * k0 - (label == e0 + 1 ? 1.0f : 0.0f)) * k1;
+        gr.z = (va[i].z * k0 - (label == e0 + 2 ? 1.0f : 0.0f)) * k1;
+        gr.w = (va[i].w * k0 - (label == e0 + 3 ? 1.0f : 0.0f)) * k1;
+      }
+      const float4 old = kEarlyDx ? vx[i] : __ldcs(dxr + j);
+      __stcs(dxr + j, make_float4(old.x + gr.x, old.y + gr.y, old.z + gr.z, old.w + gr.w));
+    }
+  }
+}
+
 template <int MODE>
 static void softmax_family_backward(const char *name, Tensor **inputs, const Tensor *output,
                                     KernelParams params) {
@@ -1034,11 +1131,45 @@ static void softmax_family_backward(const char *name, Tensor **inputs, const Ten
     a = (const float *)output->data;
   }
   if (g.rows == 0 || g.cols == 0) return;
+  const float *dyp = (const float *)output->grad->data;
+  float *dxp = (float *)x->grad->data;
+  // every row contiguous and 16-byte aligned in y (or x), dy and dx: the register-resident kernel
+  bool fast = (g.cols & 3) == 0 && g.cols <= (u64)kSmThreads * 4 * kSmMaxVpt && g.x_axis_stride == 1 &&
+              g.y_axis_stride == 1 && (MODE == kCrossEntropy || g.z_axis_stride == 1) &&
+              (((uintptr_t)a | (uintptr_t)dxp | (MODE == kCrossEntropy ? 0 : (uintptr_t)dyp)) & 15) == 0;
+  for (int d = 0; fast && d < g.outer.n; ++d)
+    if ((g.outer.istride[0][d] | g.outer.tstride[d] | (MODE == kCrossEntropy ? 0 : g.outer.istride[1][d])) & 3) fast = false;
+  if (fast) {
+    const u64 nvec = g.cols >> 2;
+    int log_tx = 0;
+    while (((u64)kSmMaxVpt << log_tx) < nvec) ++log_tx;
+    while (log_tx < 3 && ((u64)1 << log_tx) < nvec) ++log_tx;
+    // prefer four vectors per thread (dx requested up front) while that still fits one CTA per row
+    if (log_tx < 8 && ((nvec + ((u64)1 << log_tx) - 1) >> log_tx) > 4) ++log_tx;
+    const int vpt = (int)((nvec + ((u64)1 << log_tx) - 1) >> log_tx);
+    const u64 rows_per_cta = (u64)kSmThreads >> log_tx;
+    const u64 grid = (g.rows + rows_per_cta - 1) / rows_per_cta;
+    if (grid > 0x7fffffffull) {
+      set_error(PLAST_B200_ERR_LIMIT, "%s: too many rows", name);
+      return;
+    }
+    int v = 1;
+    while (v < vpt) v <<= 1;
+    switch (v) {
+    case 1: launch_k(softmax_backward_fast_kernel<MODE, 1>, dim3((unsigned)grid), dim3(kSmThreads), 0, stream(), a, dyp, dxp, labels, g, log_tx); break;
+    case 2: launch_k(softmax_backward_fast_kernel<MODE, 2>, dim3((unsigned)grid), dim3(kSmThreads), 0, stream(), a, dyp, dxp, labels, g, log_tx); break;
+    case 4: launch_k(softmax_backward_fast_kernel<MODE, 4>, dim3((unsigned)grid), dim3(kSmThreads), 0, stream(), a, dyp, dxp, labels, g, log_tx); break;
+    default: launch_k(softmax_backward_fast_kernel<MODE, 8>, dim3((unsigned)grid), dim3(kSmThreads), 0, stream(), a, dyp, dxp, labels, g, log_tx); break;
+    }
+    count_launch();
+    note_kernel("softmax_backward_fast");
+    end_call();
+    return;
+  }
   u64 grid = g.rows;
   const u64 cap = (u64)sm_count() * 16;
   if (grid > cap) grid = cap;
-  launch_k(softmax_backward_kernel<MODE>, dim3((unsigned)grid), dim3(kSmThreads), 0, stream(), a,
-           (const float *)output->grad->data, (float *)x->grad->data, labels, g);
+  launch_k(softmax_backward_kernel<MODE>, dim3((unsigned)grid), dim3(kSmThreads), 0, stream(), a, dyp, dxp, labels, g);
   count_launch();
   note_kernel("softmax_backward");
   end_call();

@@ -289,7 +289,20 @@ def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2,
         timeit(3, "log_softmax", lambda: pb.forward("log_softmax", [tX], tY, dim=1, check=False), 2 * R * Cn * F, R * Cn, ws)
         timeit(3, "cross_entropy_mean", lambda: pb.forward("cross_entropy", [tX, tl], tloss, check=False),
                (R * Cn + R) * F + 4, R * Cn, ws)
-        del X, Y
+        # backward of the three (plast/nn/functional.py:77-97, 312-333 run in reverse): dx accumulates,
+        # so a pass reads y (or the logits), dy and dx and writes dx
+        dY, dX = randn((R, Cn), 3), torch.zeros((R, Cn), device=dev)
+        dl = torch.ones(1, device=dev)
+        tXg = wrap(X); tXg.c.requires_grad = True
+        gX = wrap(dX); tXg.grad = gX; tXg.c.grad = C.pointer(gX.c)
+        tYg = wrap(Y); gY = wrap(dY); tYg.grad = gY; tYg.c.grad = C.pointer(gY.c)
+        tlg = wrap(loss); gl = wrap(dl); tlg.grad = gl; tlg.c.grad = C.pointer(gl.c)
+        pb.forward("softmax", [tX], tY)
+        timeit(3, "softmax_backward", lambda: pb.backward("softmax", [tXg], tYg, dim=1, check=False), 4 * R * Cn * F, R * Cn, 4 * R * Cn * F)
+        pb.forward("log_softmax", [tX], tY)
+        timeit(3, "log_softmax_backward", lambda: pb.backward("log_softmax", [tXg], tYg, dim=1, check=False), 4 * R * Cn * F, R * Cn, 4 * R * Cn * F)
+        timeit(3, "cross_entropy_backward", lambda: pb.backward("cross_entropy", [tXg, tl], tlg, check=False), 3 * R * Cn * F, R * Cn, 3 * R * Cn * F)
+        del X, Y, dY, dX
     if 4 in configs:
         M = 8192
         X = uniform((M, M), 0, -1, 1)
