@@ -717,7 +717,7 @@ cross_entropy_rows_kernel(const float *__restrict__ x, const int *__restrict__ l
 //   log_softmax  dx += dy - exp(y) * sum(dy)
 //   cross_entropy (mean)  dlogits += (softmax(x) - onehot(label)) * dout / rows
 template <int MODE>
-__global__ void __launch_bounds__(kSmThreads)
+__global__ void __launch_bounds__(kSmThreads, 2)
 softmax_backward_kernel(const float *y_or_x, const float *dy, float *dx, const int *labels, SmRows g) {
   pdl_wait();
   pdl_launch_dependents();
@@ -726,32 +726,107 @@ softmax_backward_kernel(const float *y_or_x, const float *dy, float *dx, const i
     g.outer.offsets(row, &doff, ioff);
     const float *a = y_or_x + ioff[0]; // y (softmax / log_softmax) or logits x (cross entropy)
     float *dxr = dx + doff;
+    const float *dyr = dy + ioff[1];
+    // Long rows (a 32000 ... 128256-wide vocabulary) whose three tensors are contiguous along the axis
+    // and 16-byte aligned are walked as float4 in batches of four loads per thread; the second pass
+    // finds the row in L2.
+    const bool vec = (g.cols & 3) == 0 && g.x_axis_stride == 1 && g.y_axis_stride == 1 &&
+                     (MODE == kCrossEntropy || g.z_axis_stride == 1) &&
+                     ((((uintptr_t)a | (uintptr_t)dxr | (MODE == kCrossEntropy ? 0 : (uintptr_t)dyr)) & 15) == 0);
+    const u64 nvec = g.cols >> 2;
     if (MODE == kCrossEntropy) {
       MaxSum acc{-FLT_MAX, 0.0f};
-      for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
-        const float xv = a[j * g.x_axis_stride];
-        if (xv > acc.m) {
-          acc.s = acc.s * exp_softmax(acc.m - xv) + 1.0f;
-          acc.m = xv;
-        } else {
-          acc.s += exp_softmax(xv - acc.m);
+      if (vec) {
+        const float4 *xb = reinterpret_cast<const float4 *>(a);
+        for (u64 j0 = threadIdx.x; j0 < nvec; j0 += 4 * kSmThreads) {
+          float4 v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (j0 + (u64)u * kSmThreads < nvec) v[u] = __ldg(xb + j0 + (u64)u * kSmThreads);
+          float bm = -FLT_MAX;
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (j0 + (u64)u * kSmThreads < nvec) bm = fmaxf(bm, fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w)));
+          if (bm > acc.m) {
+            acc.s *= exp_softmax(acc.m - bm);
+            acc.m = bm;
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (j0 + (u64)u * kSmThreads < nvec)
+              acc.s += (exp_softmax(v[u].x - acc.m) + exp_softmax(v[u].y - acc.m)) +
+                       (exp_softmax(v[u].z - acc.m) + exp_softmax(v[u].w - acc.m));
+        }
+      } else {
+        for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
+          const float xv = a[j * g.x_axis_stride];
+          if (xv > acc.m) {
+            acc.s = acc.s * exp_softmax(acc.m - xv) + 1.0f;
+            acc.m = xv;
+          } else {
+            acc.s += exp_softmax(xv - acc.m);
+          }
         }
       }
       acc = ms_block_reduce(acc);
       const float gscale = dy[0] / (float)g.rows;
       const int label = labels[row];
-      for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
-        const float p = exp_softmax(a[j * g.x_axis_stride] - acc.m) / acc.s;
-        const float t = ((u64)label == j) ? 1.0f : 0.0f;
-        dxr[j * g.y_axis_stride] += (p - t) * gscale;
+      if (vec) {
+        const float4 *xb = reinterpret_cast<const float4 *>(a);
+        float4 *db = reinterpret_cast<float4 *>(dxr);
+        const float inv_s = 1.0f / acc.s;
+        for (u64 j0 = threadIdx.x; j0 < nvec; j0 += 4 * kSmThreads) {
+          float4 v[4], o[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (j0 + (u64)u * kSmThreads < nvec) {
+              v[u] = __ldcs(xb + j0 + (u64)u * kSmThreads);
+              o[u] = __ldcs(db + j0 + (u64)u * kSmThreads);
+            }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const u64 j = j0 + (u64)u * kSmThreads;
+            if (j < nvec) {
+              const long e0 = (long)(j << 2);
+              o[u].x += (exp_softmax(v[u].x - acc.m) * inv_s - (label == e0 ? 1.0f : 0.0f)) * gscale;
+              o[u].y += (exp_softmax(v[u].y - acc.m) * inv_s - (label == e0 + 1 ? 1.0f : 0.0f)) * gscale;
+              o[u].z += (exp_softmax(v[u].z - acc.m) * inv_s - (label == e0 + 2 ? 1.0f : 0.0f)) * gscale;
+              o[u].w += (exp_softmax(v[u].w - acc.m) * inv_s - (label == e0 + 3 ? 1.0f : 0.0f)) * gscale;
+              __stcs(db + j, o[u]);
+            }
+          }
+        }
+      } else {
+        for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
+          const float p = exp_softmax(a[j * g.x_axis_stride] - acc.m) / acc.s;
+          const float t = ((u64)label == j) ? 1.0f : 0.0f;
+          dxr[j * g.y_axis_stride] += (p - t) * gscale;
+        }
       }
       continue;
     }
-    const float *dyr = dy + ioff[1];
     float part = 0.0f;
-    for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
-      const float d = dyr[j * g.z_axis_stride];
-      part += (MODE == kSoftmax) ? d * a[j * g.x_axis_stride] : d;
+    if (vec) {
+      const float4 *yb = reinterpret_cast<const float4 *>(a), *gb = reinterpret_cast<const float4 *>(dyr);
+      for (u64 j0 = threadIdx.x; j0 < nvec; j0 += 4 * kSmThreads) {
+        float4 v[4], d[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (j0 + (u64)u * kSmThreads < nvec) {
+            d[u] = __ldg(gb + j0 + (u64)u * kSmThreads);
+            if (MODE == kSoftmax) v[u] = __ldg(yb + j0 + (u64)u * kSmThreads);
+          }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (j0 + (u64)u * kSmThreads < nvec)
+            part += (MODE == kSoftmax) ? (d[u].x * v[u].x + d[u].y * v[u].y) + (d[u].z * v[u].z + d[u].w * v[u].w)
+                                       : (d[u].x + d[u].y) + (d[u].z + d[u].w);
+      }
+    } else {
+      for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
+        const float d = dyr[j * g.z_axis_stride];
+        part += (MODE == kSoftmax) ? d * a[j * g.x_axis_stride] : d;
+      }
     }
     __syncthreads();
     float tot = block_reduce<SumOp>(part);
@@ -759,11 +834,40 @@ softmax_backward_kernel(const float *y_or_x, const float *dy, float *dx, const i
     if (threadIdx.x == 0) bcast = tot;
     __syncthreads();
     tot = bcast;
-    for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
-      const float d = dyr[j * g.z_axis_stride];
-      const float yv = a[j * g.x_axis_stride];
-      const float gr = (MODE == kSoftmax) ? yv * (d - tot) : d - exp_softmax(yv) * tot;
-      dxr[j * g.y_axis_stride] += gr;
+    if (vec) {
+      const float4 *yb = reinterpret_cast<const float4 *>(a), *gb = reinterpret_cast<const float4 *>(dyr);
+      float4 *db = reinterpret_cast<float4 *>(dxr);
+      for (u64 j0 = threadIdx.x; j0 < nvec; j0 += 4 * kSmThreads) {
+        float4 v[4], d[4], o[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (j0 + (u64)u * kSmThreads < nvec) {
+            v[u] = __ldcs(yb + j0 + (u64)u * kSmThreads);
+            d[u] = __ldcs(gb + j0 + (u64)u * kSmThreads);
+            o[u] = __ldcs(db + j0 + (u64)u * kSmThreads);
+          }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const u64 j = j0 + (u64)u * kSmThreads;
+          if (j < nvec) {
+            if (MODE == kSoftmax) {
+              o[u].x += v[u].x * (d[u].x - tot); o[u].y += v[u].y * (d[u].y - tot);
+              o[u].z += v[u].z * (d[u].z - tot); o[u].w += v[u].w * (d[u].w - tot);
+            } else {
+              o[u].x += d[u].x - exp_softmax(v[u].x) * tot; o[u].y += d[u].y - exp_softmax(v[u].y) * tot;
+              o[u].z += d[u].z - exp_softmax(v[u].z) * tot; o[u].w += d[u].w - exp_softmax(v[u].w) * tot;
+            }
+            __stcs(db + j, o[u]);
+          }
+        }
+      }
+    } else {
+      for (u64 j = threadIdx.x; j < g.cols; j += kSmThreads) {
+        const float d = dyr[j * g.z_axis_stride];
+        const float yv = a[j * g.x_axis_stride];
+        const float gr = (MODE == kSoftmax) ? yv * (d - tot) : d - exp_softmax(yv) * tot;
+        dxr[j * g.y_axis_stride] += gr;
+      }
     }
   }
 }
@@ -1001,14 +1105,13 @@ static void softmax_family_forward(const char *name, const Tensor **inputs, Tens
 }
 
 // ---- backward, fast path --------------------------------------------------------------------------------
-// Rows contiguous along the axis in all three tensors, 16-byte aligned, cols % 4 == 0, cols <= 8192:
+// Rows contiguous along the axis in all three tensors, 16-byte aligned, cols % 4 == 0, cols <= 4096:
 // the row of y (or of the logits), of dy and of dx in registers, TX threads per row as in the
 // forward kernel; one read of each, one write of dx (backward ACCUMULATES into dx).
 //   softmax       dx += y * (dy - sum(y * dy))
 //   log_softmax   dx += dy - exp(y) * sum(dy)
 //   cross_entropy dx += (softmax(x) - onehot(label)) * dloss / rows
-// Up to four vectors per thread the dx row is requested together with the others; with eight it is
-// read after the row sum (registers).
+// The dx row is requested together with the others (at most four vectors of each per thread).
 template <int MODE, int VPT>
 __global__ void __launch_bounds__(kSmThreads, 2)
 softmax_backward_fast_kernel(const float *__restrict__ a, const float *__restrict__ dy, float *__restrict__ dx,
@@ -1134,7 +1237,9 @@ static void softmax_family_backward(const char *name, Tensor **inputs, const Ten
   const float *dyp = (const float *)output->grad->data;
   float *dxp = (float *)x->grad->data;
   // every row contiguous and 16-byte aligned in y (or x), dy and dx: the register-resident kernel
-  bool fast = (g.cols & 3) == 0 && g.cols <= (u64)kSmThreads * 4 * kSmMaxVpt && g.x_axis_stride == 1 &&
+  // (up to four vectors per thread: rows of 4097 ... 8192 elements measured faster in the long-row
+  // kernel, 6.6 against 4.9 TB/s, where eight vectors per thread leave no registers for dx)
+  bool fast = (g.cols & 3) == 0 && g.cols <= (u64)kSmThreads * 4 * 4 && g.x_axis_stride == 1 &&
               g.y_axis_stride == 1 && (MODE == kCrossEntropy || g.z_axis_stride == 1) &&
               (((uintptr_t)a | (uintptr_t)dxp | (MODE == kCrossEntropy ? 0 : (uintptr_t)dyp)) & 15) == 0;
   for (int d = 0; fast && d < g.outer.n; ++d)
@@ -1142,10 +1247,8 @@ static void softmax_family_backward(const char *name, Tensor **inputs, const Ten
   if (fast) {
     const u64 nvec = g.cols >> 2;
     int log_tx = 0;
-    while (((u64)kSmMaxVpt << log_tx) < nvec) ++log_tx;
+    while (((u64)4 << log_tx) < nvec) ++log_tx; // smallest TX with <= 4 vectors per thread
     while (log_tx < 3 && ((u64)1 << log_tx) < nvec) ++log_tx;
-    // prefer four vectors per thread (dx requested up front) while that still fits one CTA per row
-    if (log_tx < 8 && ((nvec + ((u64)1 << log_tx) - 1) >> log_tx) > 4) ++log_tx;
     const int vpt = (int)((nvec + ((u64)1 << log_tx) - 1) >> log_tx);
     const u64 rows_per_cta = (u64)kSmThreads >> log_tx;
     const u64 grid = (g.rows + rows_per_cta - 1) / rows_per_cta;
@@ -1158,8 +1261,7 @@ static void softmax_family_backward(const char *name, Tensor **inputs, const Ten
     switch (v) {
     case 1: launch_k(softmax_backward_fast_kernel<MODE, 1>, dim3((unsigned)grid), dim3(kSmThreads), 0, stream(), a, dyp, dxp, labels, g, log_tx); break;
     case 2: launch_k(softmax_backward_fast_kernel<MODE, 2>, dim3((unsigned)grid), dim3(kSmThreads), 0, stream(), a, dyp, dxp, labels, g, log_tx); break;
-    case 4: launch_k(softmax_backward_fast_kernel<MODE, 4>, dim3((unsigned)grid), dim3(kSmThreads), 0, stream(), a, dyp, dxp, labels, g, log_tx); break;
-    default: launch_k(softmax_backward_fast_kernel<MODE, 8>, dim3((unsigned)grid), dim3(kSmThreads), 0, stream(), a, dyp, dxp, labels, g, log_tx); break;
+    default: launch_k(softmax_backward_fast_kernel<MODE, 4>, dim3((unsigned)grid), dim3(kSmThreads), 0, stream(), a, dyp, dxp, labels, g, log_tx); break;
     }
     count_launch();
     note_kernel("softmax_backward_fast");
