@@ -1123,7 +1123,7 @@ softmax_backward_fast_kernel(const float *__restrict__ a, const float *__restric
   const int tx_n = 1 << log_tx;
   const int tx = threadIdx.x & (tx_n - 1), ty = threadIdx.x >> log_tx;
   const int rows_per_cta = kSmThreads >> log_tx;
-  const u64 nvec = g.cols >> 2;
+  const unsigned nvec = (unsigned)(g.cols >> 2); // at most 1024: 32-bit index math in the loops
   const u64 row = (u64)blockIdx.x * rows_per_cta + ty;
   const bool live = row < g.rows;
   u64 doff = 0, ioff[2] = {0, 0};
@@ -1134,7 +1134,7 @@ softmax_backward_fast_kernel(const float *__restrict__ a, const float *__restric
   float4 va[VPT], vd[VPT], vx[VPT];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const u64 j = (u64)tx + (u64)i * tx_n;
+    const unsigned j = (unsigned)tx + (unsigned)i * (unsigned)tx_n;
     if (live && j < nvec) {
       va[i] = __ldcs(ar + j);
       if (MODE != kCrossEntropy) vd[i] = __ldcs(dyr + j);
@@ -1146,14 +1146,14 @@ softmax_backward_fast_kernel(const float *__restrict__ a, const float *__restric
     float m = -FLT_MAX;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const u64 j = (u64)tx + (u64)i * tx_n;
+      const unsigned j = (unsigned)tx + (unsigned)i * (unsigned)tx_n;
       if (live && j < nvec) m = fmaxf(m, fmaxf(fmaxf(va[i].x, va[i].y), fmaxf(va[i].z, va[i].w)));
     }
     m = row_reduce<MaxOp, true>(m, log_tx, red_smem);
     float sum = 0.0f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const u64 j = (u64)tx + (u64)i * tx_n;
+      const unsigned j = (unsigned)tx + (unsigned)i * (unsigned)tx_n;
       if (live && j < nvec) {
         va[i].x = exp_softmax(va[i].x - m); va[i].y = exp_softmax(va[i].y - m);
         va[i].z = exp_softmax(va[i].z - m); va[i].w = exp_softmax(va[i].w - m);
@@ -1167,7 +1167,7 @@ softmax_backward_fast_kernel(const float *__restrict__ a, const float *__restric
     float part = 0.0f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const u64 j = (u64)tx + (u64)i * tx_n;
+      const unsigned j = (unsigned)tx + (unsigned)i * (unsigned)tx_n;
       if (live && j < nvec) {
         if (MODE == kSoftmax) part += (vd[i].x * va[i].x + vd[i].y * va[i].y) + (vd[i].z * va[i].z + vd[i].w * va[i].w);
         else part += (vd[i].x + vd[i].y) + (vd[i].z + vd[i].w);
@@ -1175,10 +1175,15 @@ softmax_backward_fast_kernel(const float *__restrict__ a, const float *__restric
     }
     k0 = row_reduce<SumOp, true>(part, log_tx, red_smem);
   }
+  // cross-entropy: every element gets softmax * dloss / rows; the one-hot term is subtracted by the
+  // single thread that holds the label's vector (a compare per element would double the instruction
+  // count of this pass)
   const int label = (MODE == kCrossEntropy && live) ? labels[row] : -1;
+  const float kk = k0 * k1;
+  const unsigned label_vec = label >= 0 ? (unsigned)label >> 2 : 0xffffffffu;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const u64 j = (u64)tx + (u64)i * tx_n;
+    const unsigned j = (unsigned)tx + (unsigned)i * (unsigned)tx_n;
     if (live && j < nvec) {
       float4 gr;
       if (MODE == kSoftmax) {
@@ -1188,11 +1193,14 @@ softmax_backward_fast_kernel(const float *__restrict__ a, const float *__restric
         gr.x = vd[i].x - exp_softmax(va[i].x) * k0; gr.y = vd[i].y - exp_softmax(va[i].y) * k0;
         gr.z = vd[i].z - exp_softmax(va[i].z) * k0; gr.w = vd[i].w - exp_softmax(va[i].w) * k0;
       } else {
-        const long e0 = (long)(j << 2);
-        gr.x = (va[i].x * k0 - (label == e0 ? 1.0f : 0.0f)) * k1;
-        gr.y = (va[i].y * k0 - (label == e0 + 1 ? 1.0f : 0.0f)) * k1;
-        gr.z = (va[i].z * k0 - (label == e0 + 2 ? 1.0f : 0.0f)) * k1;
-        gr.w = (va[i].w * k0 - (label == e0 + 3 ? 1.0f : 0.0f)) * k1;
+        gr.x = va[i].x * kk; gr.y = va[i].y * kk; gr.z = va[i].z * kk; gr.w = va[i].w * kk;
+        if (j == label_vec) {
+          const int comp = label & 3;
+          if (comp == 0) gr.x -= k1;
+          else if (comp == 1) gr.y -= k1;
+          else if (comp == 2) gr.z -= k1;
+          else gr.w -= k1;
+        }
       }
       const float4 old = kEarlyDx ? vx[i] : __ldcs(dxr + j);
       __stcs(dxr + j, make_float4(old.x + gr.x, old.y + gr.y, old.z + gr.z, old.w + gr.w));
