@@ -1208,6 +1208,42 @@ softmax_backward_fast_kernel(const float *__restrict__ a, const float *__restric
   }
 }
 
+// ---- backward, tiny rows (<= 32 classes, dense): one THREAD per row -------------------------------------
+// The classifier-head case again (10 classes x a batch): a CTA per row would run two block
+// reductions for ten elements. Here every thread walks its own row three times straight from
+// global memory; the rows of a warp are neighbours, so its loads share cache lines.
+template <int MODE>
+__global__ void __launch_bounds__(kSmThreads)
+softmax_backward_tiny_kernel(const float *__restrict__ a, const float *__restrict__ dy, float *__restrict__ dx,
+                             const int *__restrict__ labels, u64 rows, unsigned cols) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const u64 row = (u64)blockIdx.x * kSmThreads + threadIdx.x;
+  if (row >= rows) return;
+  const float *ar = a + row * cols;
+  float *dxr = dx + row * cols;
+  if (MODE == kCrossEntropy) {
+    float m = -FLT_MAX;
+    for (unsigned c = 0; c < cols; ++c) m = fmaxf(m, ar[c]);
+    float sum = 0.0f;
+    for (unsigned c = 0; c < cols; ++c) sum += exp_softmax(ar[c] - m);
+    const float gscale = dy[0] / (float)rows;
+    const int label = labels[row];
+    for (unsigned c = 0; c < cols; ++c) {
+      const float p = exp_softmax(ar[c] - m) / sum;
+      dxr[c] += (p - ((int)c == label ? 1.0f : 0.0f)) * gscale;
+    }
+    return;
+  }
+  const float *dyr = dy + row * cols;
+  float tot = 0.0f;
+  for (unsigned c = 0; c < cols; ++c) tot += (MODE == kSoftmax) ? dyr[c] * ar[c] : dyr[c];
+  for (unsigned c = 0; c < cols; ++c) {
+    const float d = dyr[c], yv = ar[c];
+    dxr[c] += (MODE == kSoftmax) ? yv * (d - tot) : d - exp_softmax(yv) * tot;
+  }
+}
+
 template <int MODE>
 static void softmax_family_backward(const char *name, Tensor **inputs, const Tensor *output,
                                     KernelParams params) {
@@ -1252,6 +1288,31 @@ static void softmax_family_backward(const char *name, Tensor **inputs, const Ten
               (((uintptr_t)a | (uintptr_t)dxp | (MODE == kCrossEntropy ? 0 : (uintptr_t)dyp)) & 15) == 0;
   for (int d = 0; fast && d < g.outer.n; ++d)
     if ((g.outer.istride[0][d] | g.outer.tstride[d] | (MODE == kCrossEntropy ? 0 : g.outer.istride[1][d])) & 3) fast = false;
+  // dense rows of at most 32 elements that the float4 kernel does not take: a thread per row
+  bool tiny = !fast && g.cols <= 32 && g.rows >= 64 && g.x_axis_stride == 1 && g.y_axis_stride == 1 &&
+              (MODE == kCrossEntropy || g.z_axis_stride == 1);
+  {
+    u64 run = g.cols;
+    for (int d = 0; tiny && d < g.outer.n; ++d) {
+      if (g.outer.istride[0][d] != run || g.outer.tstride[d] != run ||
+          (MODE != kCrossEntropy && g.outer.istride[1][d] != run))
+        tiny = false;
+      run *= g.outer.size[d];
+    }
+  }
+  if (tiny) {
+    const u64 grid = (g.rows + kSmThreads - 1) / kSmThreads;
+    if (grid > 0x7fffffffull) {
+      set_error(PLAST_B200_ERR_LIMIT, "%s: too many rows", name);
+      return;
+    }
+    launch_k(softmax_backward_tiny_kernel<MODE>, dim3((unsigned)grid), dim3(kSmThreads), 0, stream(), a, dyp, dxp, labels,
+             g.rows, (unsigned)g.cols);
+    count_launch();
+    note_kernel("softmax_backward_tiny_rows");
+    end_call();
+    return;
+  }
   if (fast) {
     const u64 nvec = g.cols >> 2;
     int log_tx = 0;

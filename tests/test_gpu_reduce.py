@@ -290,7 +290,8 @@ def test_cross_entropy(cuda, recipes, rows, cols):
     assert_sum_close(out.numpy(), want, np.abs(per_row).sum() / rows, what="ce mean")
 
 
-@pytest.mark.parametrize("rows,cols", [(33, 200), (16, 4096), (5, 1003), (300, 64), (7, 8192), (100, 8), (9, 2048), (3, 8196), (2, 16384), (3, 9000)])
+@pytest.mark.parametrize("rows,cols", [(33, 200), (16, 4096), (5, 1003), (300, 64), (7, 8192), (100, 8), (9, 2048), (3, 8196), (2, 16384), (3, 9000),
+                                       (5000, 10), (300, 7), (64, 31), (70, 33), (1000, 1)])
 def test_softmax_family_backward(cuda, oracle, rows, cols):
     """Against the reference's OWN backward: the op sequence of plast/nn/functional.py run node by
     node through the CPU kernels, forward and then backward in reverse (harness.cpu_recipe_graph).
