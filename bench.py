@@ -727,7 +727,7 @@ def main():
     ap.add_argument("--regions", type=int, default=5, help="how often the K-step timed region is repeated (median reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-per-op", action="store_true", help="skip the per-op table (configs 1-5 and the optimiser steps)")
-    ap.add_argument("--op-reps", type=int, default=20)
+    ap.add_argument("--op-reps", type=int, default=10)
     ap.add_argument("--per-op-only", action="store_true",
                     help="only the per-op table (1 GPU); with --op-reps 0 every op is launched 3 times and "
                          "not timed, which is the command the profiler captures use")

@@ -18,7 +18,7 @@ import numpy as np
 NOMINAL = 8000.0
 
 
-def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 20, configs=(1, 2, 3, 4, 5, 6, 7),
+def per_op_table(torch, pb, dev, peak_gbs: float, reps: int = 10, configs=(1, 2, 3, 4, 5, 6, 7),
                  chain_elems: int = 1 << 28):
     """chain_elems: length of configuration 2's vectors (2^28 in the benchmark; profiler captures use
     fewer so that the device memory a multi-pass capture has to save stays small)."""
