@@ -367,14 +367,15 @@ int plast_b200_chain_backward_try_compile(const PlastChainStep *steps, int n_ste
 /* Tuning hook: overrides one launch-geometry choice of the reductions for the whole process
  * (key 0: log2 of the lanes across a strip of the column reduce, 1: resident CTAs per SM the
  * column reduce plans for, 2: load batches per row-worker below which a column reduce is not split
- * further, 3: resident CTAs per SM the segmented reduce plans for, 5: order of the column reduce's
+ * further, 3: resident CTAs per SM the segmented reduce plans for, 4: longest dense row that the
+ * thread-per-row reduction takes (0 = never; at most 48), 5: order of the column reduce's
  * CTAs, 6 / 7: L2 prefetch distance of the column sweep in load batches and the number of batches
  * per chunk that prefetch, 8: prefetch distance of the segmented reduce in trips, 9: log2 of the
  * threads that share a segment, 10: CTAs per thread-block cluster when the chunks of a column
  * reduce combine through distributed shared memory instead of a ticket in global memory, 0 or 1 =
  * never, 11: 1 = the 3-D tile kernel for inputs turned along two different dims uses 32 x 16 x 16
- * tiles instead of 8 x 32 x 32); a negative value restores the built-in choice. Results do not depend on the geometry
- * beyond the order of additions. */
+ * tiles instead of 8 x 32 x 32); a negative value restores the built-in choice. Results do not
+ * depend on the geometry beyond the order of additions. */
 void plast_b200_tune(int key, long value);
 /* Test hook: runs the host-side iteration planner (drop size-1 dims, order by the strides of
  * argument `sort_arg`, merge dims every argument walks as one run) on caller-supplied metadata.
