@@ -119,6 +119,99 @@ static void binary_backward_one(const char *name, const Tensor *a, const Tensor 
                              Term{});
 }
 
+// ---- both gradients of a binary op in one pass --------------------------------------------------------
+// When both operands want a gradient and nothing broadcasts (five dense tensors of one shape), the
+// two accumulations share their reads: dout (and a, b for mul / div) cross HBM once instead of
+// once per operand. Same terms, same `old + term` rounding as the one-operand passes.
+struct BothAdd {
+  static constexpr bool kNeedsAB = false;
+  __device__ __forceinline__ static float ta(float g, float, float) { return g; }
+  __device__ __forceinline__ static float tb(float g, float, float) { return g; }
+};
+struct BothSub {
+  static constexpr bool kNeedsAB = false;
+  __device__ __forceinline__ static float ta(float g, float, float) { return g; }
+  __device__ __forceinline__ static float tb(float g, float, float) { return -g; }
+};
+struct BothMul {
+  static constexpr bool kNeedsAB = true;
+  __device__ __forceinline__ static float ta(float g, float, float b) { return g * b; }
+  __device__ __forceinline__ static float tb(float g, float a, float) { return g * a; }
+};
+struct BothDiv {
+  static constexpr bool kNeedsAB = true;
+  __device__ __forceinline__ static float ta(float g, float, float b) { return g / b; }
+  __device__ __forceinline__ static float tb(float g, float a, float b) { return -g * a / (b * b); }
+};
+
+template <class T>
+__global__ void __launch_bounds__(256)
+binary_backward_both_kernel(const float4 *__restrict__ g, const float4 *__restrict__ a, const float4 *__restrict__ b,
+                            float4 *__restrict__ da, float4 *__restrict__ db, u64 nvec) {
+  pdl_wait();
+  pdl_launch_dependents();
+  constexpr int kItems = 2; // float4 per thread and tensor: up to ten loads in flight
+  const u64 first = (u64)blockIdx.x * (256 * kItems) + threadIdx.x;
+  float4 vg[kItems], va[kItems], vb[kItems], oa[kItems], ob[kItems];
+#pragma unroll
+  for (int i = 0; i < kItems; ++i) {
+    const u64 j = first + (u64)i * 256;
+    if (j < nvec) {
+      vg[i] = __ldcs(g + j);
+      if (T::kNeedsAB) {
+        va[i] = __ldcs(a + j);
+        vb[i] = __ldcs(b + j);
+      }
+      oa[i] = __ldcs(da + j);
+      ob[i] = __ldcs(db + j);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kItems; ++i) {
+    const u64 j = first + (u64)i * 256;
+    if (j < nvec) {
+      const float4 x = T::kNeedsAB ? va[i] : vg[i], y = T::kNeedsAB ? vb[i] : vg[i];
+      oa[i].x += T::ta(vg[i].x, x.x, y.x); oa[i].y += T::ta(vg[i].y, x.y, y.y);
+      oa[i].z += T::ta(vg[i].z, x.z, y.z); oa[i].w += T::ta(vg[i].w, x.w, y.w);
+      ob[i].x += T::tb(vg[i].x, x.x, y.x); ob[i].y += T::tb(vg[i].y, x.y, y.y);
+      ob[i].z += T::tb(vg[i].z, x.z, y.z); ob[i].w += T::tb(vg[i].w, x.w, y.w);
+      __stcs(da + j, oa[i]);
+      __stcs(db + j, ob[i]);
+    }
+  }
+}
+
+// Takes the fused pass when it applies; false = the caller runs the two one-operand passes.
+template <class T>
+static bool binary_backward_both(const Tensor *a, const Tensor *b, const Tensor *dout) {
+  if (!a->requires_grad || !b->requires_grad || !a->grad || !b->grad || !a->grad->data || !b->grad->data) return false;
+  const Tensor *five[5] = {a, b, dout, a->grad, b->grad};
+  const u64 n = numel(dout);
+  if (n == 0 || (n & 3)) return false;
+  for (const Tensor *t : five) {
+    if (t->ndim != dout->ndim || ((uintptr_t)t->data & 15)) return false;
+    u64 expect = 1; // dense row-major, dim 0 included
+    for (u64 d = dout->ndim; d-- > 0;) {
+      if (t->shape[d] != dout->shape[d]) return false;
+      if (t->shape[d] > 1 && t->strides[d] != expect) return false;
+      expect *= t->shape[d];
+    }
+  }
+  // gradient buffers that alias each other (x * x) or an input must go through the ordered passes
+  const void *p[5] = {a->data, b->data, dout->data, a->grad->data, b->grad->data};
+  for (int i = 0; i < 5; ++i)
+    for (int j = i + 1; j < 5; ++j)
+      if (p[i] == p[j] && (i >= 3 || j >= 3)) return false;
+  const u64 nvec = n >> 2, per_cta = 256 * 2;
+  const u64 grid = (nvec + per_cta - 1) / per_cta;
+  if (grid > 0x7fffffffull) return false;
+  launch_k(binary_backward_both_kernel<T>, dim3((unsigned)grid), dim3(256), 0, stream(), (const float4 *)dout->data,
+           (const float4 *)a->data, (const float4 *)b->data, (float4 *)a->grad->data, (float4 *)b->grad->data, nvec);
+  count_launch();
+  note_kernel("binary_backward_both");
+  return true;
+}
+
 static bool binary_backward_begin(const char *name, Tensor **inputs, const Tensor *output) {
   begin_call();
   if (!inputs || !check_tensor(inputs[0], name) || !check_tensor(inputs[1], name) ||
@@ -151,24 +244,40 @@ PB_BINARY_FWD(div, DivF)
 // src/kernels/cpu/binary_ops.c:18-60 gradient terms
 void add_cuda_backward(Tensor **in, const Tensor *out, KernelParams) {
   if (!binary_backward_begin("add", in, out)) return;
+  if (binary_backward_both<BothAdd>(in[0], in[1], out->grad)) {
+    end_call();
+    return;
+  }
   binary_backward_one<GradPass, 1>("add", in[0], in[1], out->grad, 0, 0, 0);
   if (!failed()) binary_backward_one<GradPass, 1>("add", in[0], in[1], out->grad, 1, 0, 0);
   end_call();
 }
 void sub_cuda_backward(Tensor **in, const Tensor *out, KernelParams) {
   if (!binary_backward_begin("sub", in, out)) return;
+  if (binary_backward_both<BothSub>(in[0], in[1], out->grad)) {
+    end_call();
+    return;
+  }
   binary_backward_one<GradPass, 1>("sub", in[0], in[1], out->grad, 0, 0, 0);
   if (!failed()) binary_backward_one<GradNeg, 1>("sub", in[0], in[1], out->grad, 1, 0, 0);
   end_call();
 }
 void mul_cuda_backward(Tensor **in, const Tensor *out, KernelParams) {
   if (!binary_backward_begin("mul", in, out)) return;
+  if (binary_backward_both<BothMul>(in[0], in[1], out->grad)) {
+    end_call();
+    return;
+  }
   binary_backward_one<GradMul, 2>("mul", in[0], in[1], out->grad, 0, /*p=b*/ 1, 0);
   if (!failed()) binary_backward_one<GradMul, 2>("mul", in[0], in[1], out->grad, 1, /*p=a*/ 0, 0);
   end_call();
 }
 void div_cuda_backward(Tensor **in, const Tensor *out, KernelParams) {
   if (!binary_backward_begin("div", in, out)) return;
+  if (binary_backward_both<BothDiv>(in[0], in[1], out->grad)) {
+    end_call();
+    return;
+  }
   binary_backward_one<GradDiv, 2>("div", in[0], in[1], out->grad, 0, /*p=b*/ 1, 0);
   if (!failed()) binary_backward_one<GradDivB, 3>("div", in[0], in[1], out->grad, 1, /*p=a*/ 0, /*q=b*/ 1);
   end_call();

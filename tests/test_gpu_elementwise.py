@@ -240,9 +240,10 @@ def test_unary_backward(cuda, oracle, op):
         np.testing.assert_allclose(res["cuda"], res["oracle"], rtol=2e-6, atol=1e-6)
 
 
+@pytest.mark.parametrize("shape", [(77, 130), (64, 256), (3, 5, 1024), (4,)])
 @pytest.mark.parametrize("op", BINARY)
-def test_binary_backward_same_shape(cuda, oracle, op):
-    shape = (77, 130)
+def test_binary_backward_same_shape(cuda, oracle, op, shape):
+    import plast_b200 as pb
     A, B = rand_normal(0, shape), rand_uniform(1, shape, 0.5, 2.0)
     G, DA, DB = rand_normal(2, shape), rand_normal(3, shape), rand_normal(4, shape)
     res = {}
@@ -255,6 +256,26 @@ def test_binary_backward_same_shape(cuda, oracle, op):
         res[be.name] = (ta.grad.numpy(), tb.grad.numpy())
     assert_bit_equal(res["cuda"][0], res["oracle"][0], f"{op} da")
     assert_bit_equal(res["cuda"][1], res["oracle"][1], f"{op} db")
+    # five dense tensors of one shape with a multiple of four elements: both gradients in one pass
+    if int(np.prod(shape)) % 4 == 0:
+        assert pb.last_kernel() == "binary_backward_both"
+
+
+@pytest.mark.parametrize("op", BINARY)
+def test_binary_backward_of_a_tensor_with_itself(cuda, oracle, op):
+    """x op x: both operands share one gradient buffer, which receives the two terms one after the other
+    (include/kernels/kernel_macros.h:301-325); the one-pass kernel must not be taken."""
+    shape = (32, 64)
+    A, G, DA = rand_uniform(0, shape, 0.5, 2.0), rand_normal(2, shape), rand_normal(3, shape)
+    res = {}
+    for be in (cuda, oracle):
+        ta = be.tensor(A, requires_grad=True)
+        ta.grad.copy_from(DA)
+        out = be.empty(shape, requires_grad=True)
+        out.grad.copy_from(G)
+        be.backward(op, [ta, ta], out)
+        res[be.name] = ta.grad.numpy()
+    assert_bit_equal(res["cuda"], res["oracle"], f"{op}(x, x) dx")
 
 
 def test_backward_skips_inputs_without_grad(cuda):
