@@ -90,29 +90,38 @@ __device__ __forceinline__ void peer_exchange_strip(const PeerLink &link, float 
     for (int k = 0; k < VEC; ++k)
       store_packet(dst + k, ((unsigned long long)seq << 32) | (unsigned long long)__float_as_uint(v[k]));
   }
+  // The VEC packets of one rank are requested together, rank after rank: a thread's chain of
+  // dependent round trips is `world` long, as in the stand-alone exchange kernel, not world x VEC
+  // (polled one packet at a time the fused column sum took 19 us at eight GPUs against 17 us for
+  // reduce + exchange as two kernels).
   const unsigned long long *mine = link.packets[link.rank] + parity_base + elem;
+  const unsigned spin_limit = peer_spin_limit(link);
+  float acc[VEC];
+  bool complete = true;
+  for (int p = 0; p < link.world && complete; ++p) {
+    const unsigned long long *slot = mine + (size_t)p * PLAST_B200_PEER_MAX_FLOATS;
+    unsigned long long got[VEC];
 #pragma unroll
-  for (int k = 0; k < VEC; ++k) {
-    const unsigned spin_limit = peer_spin_limit(link);
-    float acc = 0.0f;
-    bool complete = true;
-    for (int p = 0; p < link.world && complete; ++p) {
-      const unsigned long long *slot = mine + (size_t)p * PLAST_B200_PEER_MAX_FLOATS + k;
-      unsigned long long got = load_packet(slot);
+    for (int k = 0; k < VEC; ++k) got[k] = load_packet(slot + k);
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
       unsigned spins = 0;
-      while ((unsigned)(got >> 32) != seq) {
+      while (complete && (unsigned)(got[k] >> 32) != seq) {
         if (++spins > spin_limit) {
           atomicCAS(&link.words[0], 0u, 1u + (unsigned)p);
           complete = false;
           break;
         }
         __nanosleep(64);
-        got = load_packet(slot);
+        got[k] = load_packet(slot + k);
       }
-      const float x = __uint_as_float((unsigned)got);
-      acc = p == 0 ? x : peer_combine(op, acc, x);
+      const float x = __uint_as_float((unsigned)got[k]);
+      acc[k] = p == 0 ? x : peer_combine(op, acc[k], x);
     }
-    if (complete) v[k] = acc; // a give-up leaves the local value and raises the status word
+  }
+  if (complete) { // a give-up leaves the local values and raises the status word
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) v[k] = acc[k];
   }
 }
 // One thread per strip, after every thread of the strip has returned from peer_exchange_strip
